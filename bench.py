@@ -1,0 +1,460 @@
+#!/usr/bin/env python
+"""Benchmark of the logits -> per-token log-prob path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--skip-extra]
+
+One JSON line on stdout (rank 0).  Headline workload: selective log-softmax over bf16 logits
+[20480 x 151936] (4 prompts x group 8 x 640 tokens), one step = one pass of the kernel over
+that matrix.  With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank
+scores its own 20480 rows: the path has no exchange step, so scaling is weak and there is
+no collective.  The "extra" object carries the other workloads: fp32 selective, fused LM
+head + log-prob (tensor cores), the vocab-parallel head over the N ranks (one all-reduce),
+and GRPO dual scoring.
+
+``--impl reference`` times the CPU restatement of the reference's MLX arithmetic
+(oracle/oracle.py; MLX itself is not installable here and its Metal kernel is Apple-only)
+on the host cores, on a bounded row sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+ROWS = 20480
+VOCAB = 151936
+METRIC = "selective_logprob_rows_per_s"
+UNIT = "rows/s"
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the headline kernel, taken from
+# the ncu capture summarised in profiles/ (None until a capture exists).
+NCU_TRAFFIC_BYTES = None
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+                "source": "fallback"}
+
+
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+# ---------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while a region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.002):
+        self.index, self.period, self.samples, self.reasons = index, period_s, [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nvml = None
+
+    def _reasons(self):
+        n = self.nvml
+        try:
+            bits = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+        except Exception:
+            try:
+                bits = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+            except Exception:
+                return
+        names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+                 0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown"}
+        for bit, name in names.items():
+            if bits & bit:
+                self.reasons.add(name)
+
+    def _sample(self):
+        try:
+            self.samples.append(int(self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM)))
+            self._reasons()
+        except Exception:
+            pass
+
+    def _loop(self):
+        while not self._stop.is_set():
+            self._sample()
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nvml is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+            if not self.samples:
+                self._sample()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def physical_gpu_index(local_index: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_index])
+        except Exception:
+            return local_index
+    return local_index
+
+
+# ---------------------------------------------------------------------------- timing
+def timed_steps(fn, steps, warmup, barrier, sampler=None):
+    """W untimed steps, then K steps between barrier+synchronize, one CUDA-event pair per
+    step on the launching stream.  Returns (total ms, per-launch ms list)."""
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    barrier()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+          for _ in range(steps)]
+    t_begin = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    ctx = sampler if sampler is not None else _Null()
+    with ctx:
+        t_begin.record()
+        for a, b in ev:
+            a.record()
+            fn()
+            b.record()
+        t_end.record()
+        torch.cuda.synchronize()
+    barrier()
+    total = t_begin.elapsed_time(t_end)
+    return total, [a.elapsed_time(b) for a, b in ev]
+
+
+class _Null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+def max_over_ranks(x: float, dist_on: bool, device) -> float:
+    if not dist_on:
+        return x
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+# ---------------------------------------------------------------------------- CPU legs
+def cpu_selective(rows_sample: int, threads: int, seed: int = 1002, repeats: int = 1):
+    """Times the CPU oracle on ``rows_sample`` rows of the headline workload; rows/s."""
+    import torch
+    from oracle import oracle
+    from tome_b200 import synthetic
+    torch.set_num_threads(threads)
+    x, ids = synthetic.cfg2_rollout_bf16(rows=rows_sample, device="cpu", seed=seed)
+    oracle.selective_logprob(x[:64], ids[:64], 1.0)
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        oracle.selective_logprob(x, ids, 1.0)
+        best = min(best, time.perf_counter() - t0)
+    return rows_sample / best, best
+
+
+def run_reference(args, rank: int):
+    """CPU implementation of the path on the host cores; same metric, config and unit."""
+    if rank != 0:
+        return
+    import torch
+    from oracle import oracle
+    from tome_b200 import synthetic
+    threads = host_cores()
+    torch.set_num_threads(threads)
+    sample = 1024
+    x, ids = synthetic.cfg2_rollout_bf16(rows=sample, device="cpu")
+    for _ in range(max(1, args.warmup)):
+        oracle.selective_logprob(x, ids, 1.0)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.selective_logprob(x, ids, 1.0)
+    dt = time.perf_counter() - t0
+    value = sample * args.steps / dt
+    desc = f"{sample} rows x {VOCAB} bf16 per step (of {ROWS}), same distribution"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "cfg2: selective log-softmax, bf16 logits [20480 x 151936]",
+                   "rows": ROWS, "vocab": VOCAB, "sample": desc},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "CPU restatement of mlx-impl/node.py:400-404 (MLX is not installable offline; "
+                "the Metal kernel is Apple-only)",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------- GPU legs
+def run_ours(args):
+    import torch
+    import tome_b200
+    from tome_b200 import synthetic
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU fallback")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist_on = world > 1
+    if dist_on:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+        barrier = lambda: dist.barrier(device_ids=[local])  # noqa: E731
+    else:
+        barrier = lambda: None  # noqa: E731
+    peaks = measured_peaks()
+    steps, warmup = args.steps, max(args.warmup, 0)
+
+    # ---------------- headline: cfg2 selective log-softmax, bf16 [20480 x 151936] per GPU
+    logits, targets = synthetic.cfg2_rollout_bf16(ROWS, VOCAB, device, seed=1002 + rank)
+    out_box = {}
+
+    def step():
+        out_box["lp"] = tome_b200.local_compute_logprobs(logits, targets, 1.0)
+
+    sampler = ClockSampler(physical_gpu_index(local)) if rank == 0 else None
+    total_ms, per_launch = timed_steps(step, steps, warmup, barrier, sampler)
+    total_ms = max_over_ranks(total_ms, dist_on, device)
+    tome_b200.check_device_status(device)
+    ms_per_step = total_ms / steps
+    value = world * ROWS * steps / (total_ms * 1e-3)
+    launch_ms = sum(per_launch) / len(per_launch)
+    algo_bytes = ROWS * VOCAB * 2 + ROWS * 8
+    achieved = algo_bytes / (launch_ms * 1e-3) / 1e9
+    # independent check that the timed kernel did the work: torch reduction on a row sample
+    sample = torch.arange(0, ROWS, 320, device=device)
+    ref = torch.log_softmax(logits[sample].float(), dim=-1).gather(
+        1, targets[sample].long()[:, None]).squeeze(1)
+    check_err = float((out_box["lp"][sample] - ref).abs().max())
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "cfg2: selective log-softmax, bf16 logits [20480 x 151936] per GPU "
+                               "(4 prompts x group 8 x 640 tokens), fp32 accumulate",
+                   "rows_per_gpu": ROWS, "vocab": VOCAB, "temperature": 1.0,
+                   "l2": "inputs (6.2 GB per step) are larger than L2; no flush needed",
+                   "parallelism": "row-sharded replicas, no collective"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                     "traffic": NCU_TRAFFIC_BYTES, "peak_source": peaks["source"],
+                     "algorithmic_bytes_per_launch": algo_bytes,
+                     "launch_ms": launch_ms, "frac_of_nominal_8TBps": achieved / 8000.0},
+        "gpu_launches": steps,
+        "check": {"max_abs_vs_torch_log_softmax": check_err, "rows_checked": int(sample.numel())},
+    }
+    if sampler is not None:
+        line["clocks"] = sampler.summary()
+
+    # ---------------- end to end through the public host-buffer call (rank-local)
+    e2e_steps = max(2, min(steps, 3))
+    host_logits = torch.empty((ROWS, VOCAB), dtype=torch.bfloat16).pin_memory()
+    host_logits.copy_(logits)
+    host_ids = targets.cpu().pin_memory()
+    staging = {"key": (tuple(logits.shape), logits.dtype), "logits": logits,
+               "ids": torch.empty_like(targets),
+               "out": torch.empty((ROWS,), dtype=torch.float32).pin_memory()}
+    tome_b200.local_compute_logprobs_host(host_logits, host_ids, 1.0, device, staging)
+    barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        tome_b200.local_compute_logprobs_host(host_logits, host_ids, 1.0, device, staging)
+    torch.cuda.synchronize()
+    e2e_s = max_over_ranks(time.perf_counter() - t0, dist_on, device)
+    line["e2e"] = {"value": world * ROWS * e2e_steps / e2e_s, "unit": UNIT,
+                   "h2d_bytes_per_step": ROWS * VOCAB * 2 + ROWS * 4,
+                   "d2h_bytes_per_step": ROWS * 4, "steps": e2e_steps,
+                   "ms_per_step": 1e3 * e2e_s / e2e_steps,
+                   "call": "tome_b200.local_compute_logprobs_host (pinned host logits -> host fp32)"}
+    del host_logits, staging, logits, targets
+    torch.cuda.empty_cache()
+
+    extra = {}
+    if not args.skip_extra:
+        extra = run_extra(args, device, rank, world, dist_on, barrier, peaks)
+    line["extra"] = extra
+
+    # ---------------- CPU baseline beside the GPU number (rank 0, N = 1 only)
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        threads = host_cores()
+        probe_rps, _ = cpu_selective(256, threads)
+        n = int(min(8192, max(512, probe_rps * 12.0)))  # about 12 s of CPU work
+        rps, secs = cpu_selective(n, threads)
+        line["cpu_baseline"] = {
+            "value": rps, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{n} rows x {VOCAB} bf16 of the same distribution, {secs:.1f} s, "
+                      "oracle/oracle.py (torch CPU restatement of mlx-impl/node.py:400-404)"}
+    elif rank == 0:
+        line["cpu_baseline"] = None
+
+    if dist_on:
+        import torch.distributed as dist
+        dist.barrier(device_ids=[local])
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+def run_extra(args, device, rank, world, dist_on, barrier, peaks):
+    """The other workloads: reported under "extra", each timed like the headline."""
+    import torch
+    import tome_b200
+    from tome_b200 import synthetic
+    extra = {}
+    steps = max(3, min(args.steps, 20))
+    warm = max(3, min(args.warmup, 5))
+
+    def timed(fn, k=steps, w=warm):
+        total, per = timed_steps(fn, k, w, barrier)
+        return max_over_ranks(total, dist_on, device) / k, sum(per) / len(per)
+
+    # cfg1: fp32 selective [1024 x 151936]; L2 (126 MB) is flushed by a 256 MB write per step
+    x, ids = synthetic.cfg1_selective_fp32(1024, VOCAB, device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    evs = []
+
+    def cfg1_step():
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        tome_b200.local_compute_logprobs(x, ids, 1.0)
+        b.record()
+        evs.append((a, b))
+
+    for _ in range(warm + steps):
+        cfg1_step()
+    torch.cuda.synchronize()
+    ms = sum(a.elapsed_time(b) for a, b in evs[warm:]) / steps
+    nbytes = 1024 * VOCAB * 4 + 1024 * 8
+    extra["cfg1_selective_fp32"] = {"rows": 1024, "ms": ms, "rows_per_s": 1024 / (ms * 1e-3),
+                                    "GBps": nbytes / ms / 1e6,
+                                    "frac_of_measured_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+                                    "l2": "flushed by a 256 MB write before each launch"}
+    del x, ids, flush
+
+    # cfg5: dual scoring + k3 KL, bf16 [32 x 768 x 151936] x 2, ragged lengths, temperature 0.7
+    pol, ref, tg, lengths, temp = synthetic.cfg5_dual(32, 768, VOCAB, device)
+    active = int(lengths.sum().item())
+    ms, launch = timed(lambda: tome_b200.grpo_dual_logprob_kl(pol, ref, tg, lengths, temp))
+    nbytes = 2 * active * VOCAB * 2
+    extra["cfg5_dual_kl"] = {"active_rows": active, "dense_rows": 32 * 768, "ms": ms,
+                             "active_rows_per_s": active / (ms * 1e-3),
+                             "GBps": nbytes / launch / 1e6,
+                             "frac_of_measured_hbm": nbytes / launch / 1e6 / peaks["hbm_gbs"]}
+    del pol, ref, tg, lengths
+    torch.cuda.empty_cache()
+
+    # cfg3: fused LM head + log-prob, Qwen3-0.6B head shape
+    hidden, weight, ids = synthetic.cfg3_lm_head(16384, 1024, VOCAB, device)
+    ws = torch.empty(tome_b200.lm_head_workspace_bytes(16384, 1024, VOCAB), dtype=torch.uint8,
+                     device=device)
+    ms, launch = timed(lambda: tome_b200.lm_head_logprob(hidden, weight, ids, 1.0, workspace=ws))
+    flops = 2.0 * 16384 * VOCAB * 1024
+    extra["cfg3_lm_head"] = {"rows": 16384, "hidden": 1024, "ms": ms,
+                             "rows_per_s": 16384 / (ms * 1e-3), "TFLOPs": flops / ms / 1e9,
+                             "frac_of_measured_bf16": flops / ms / 1e9 / peaks["bf16_tflops"],
+                             "frac_of_nominal_2250": flops / ms / 1e9 / 2250.0,
+                             "launches_per_step": 2}
+    del hidden, weight, ids, ws
+    torch.cuda.empty_cache()
+
+    # cfg4: vocab-parallel head over the N ranks, strong scaling (total work fixed)
+    hidden, weight, ids = synthetic.cfg4_vocab_parallel(32768, 4096, VOCAB, device)
+    b, e = synthetic.shard_bounds(VOCAB, rank, world)
+    shard = weight[b:e].contiguous()
+    del weight
+    torch.cuda.empty_cache()
+    ws = torch.empty(tome_b200.lm_head_workspace_bytes(32768, 4096, e - b), dtype=torch.uint8,
+                     device=device)
+    packed = torch.zeros((2 * world + 1, 32768), dtype=torch.float32, device=device)
+    k4 = max(3, min(args.steps, 5))
+    ms, launch = timed(lambda: tome_b200.lm_head_logprob_vocab_parallel(
+        hidden, shard, b, ids, 1.0, workspace=ws, packed=packed), k=k4, w=3)
+    flops = 2.0 * 32768 * VOCAB * 4096
+    extra["cfg4_vocab_parallel"] = {"rows": 32768, "hidden": 4096, "shards": world,
+                                    "vocab_per_gpu": e - b, "ms": ms, "scaling": "strong",
+                                    "TFLOPs_total": flops / ms / 1e9,
+                                    "TFLOPs_per_gpu": flops / ms / 1e9 / world,
+                                    "frac_of_measured_bf16_sustained":
+                                        flops / ms / 1e9 / world / peaks["bf16_tflops_sustained"],
+                                    "collective": "one all_reduce of [2N+1, rows] fp32"}
+    tome_b200.check_device_status(device)
+    return extra
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--skip-extra", action="store_true", help="headline workload only")
+    ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args, int(os.environ.get("RANK", "0")))
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus != world and world == 1 and args.gpus > 1:
+        # launched without torchrun: re-launch one rank per GPU on this node
+        import subprocess
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+               f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1", "--master-port",
+               os.environ.get("MASTER_PORT", "29531"), os.path.abspath(__file__)] + sys.argv[1:]
+        raise SystemExit(subprocess.call(cmd))
+    run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,171 @@
+/*
+ * tome_b200 -- C ABI of the B200 (sm_100a) log-probability library.
+ *
+ * The library replaces one path of feitreim/Tome: LM-head logits -> per-token
+ * log-probabilities of the sampled tokens (GRPO rollout / reference-logprob path).
+ * The reference implements that path as MLX expressions and one Metal kernel
+ * that MLX JIT-compiles; it has no FFI of its own, so every entry point below
+ * cites the reference Python code whose arithmetic it replaces.
+ *
+ * Conventions
+ *   - every pointer named "device" points to CUDA device memory owned by the caller;
+ *     the library allocates nothing and keeps no device state between calls;
+ *   - calls are asynchronous on `stream` (a cudaStream_t passed as void*; NULL is the
+ *     legacy default stream); no call synchronises the host with the device;
+ *   - the return value is a tome_status: 0 = success, negative = an argument was
+ *     rejected on the host before anything was launched, positive = a CUDA runtime
+ *     error.  Conditions that only the device can see (a target index outside
+ *     [0, vocab), a bounded wait that ran out) are OR-ed as TOME_DEV_* bits into the
+ *     optional caller-owned `dev_status` word (device memory, int32, zero it before
+ *     the first call; nullable); kernels never trap;
+ *   - dtype codes: TOME_F32 = 0, TOME_BF16 = 1;
+ *   - all index arithmetic is 64-bit.
+ */
+#ifndef TOME_B200_H_
+#define TOME_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TOME_B200_VERSION 100
+
+enum tome_dtype { TOME_F32 = 0, TOME_BF16 = 1 };
+
+enum tome_status {
+  TOME_OK = 0,
+  TOME_ERR_NULL_POINTER = -1,
+  TOME_ERR_MISALIGNED = -2,
+  TOME_ERR_BAD_DTYPE = -3,
+  TOME_ERR_BAD_SHAPE = -4,
+  TOME_ERR_BAD_STRIDE = -5,
+  TOME_ERR_WORKSPACE_TOO_SMALL = -6,
+  TOME_ERR_BAD_TEMPERATURE = -7,
+  TOME_ERR_UNSUPPORTED = -8,
+  TOME_ERR_TOO_LARGE = -9,
+  TOME_ERR_CUDA = 1
+};
+
+/* bits OR-ed into *dev_status by kernels */
+#define TOME_DEV_TARGET_OUT_OF_RANGE 1
+#define TOME_DEV_TIMEOUT 2
+
+/* Library version (TOME_B200_VERSION of the build). */
+int32_t tome_version(void);
+
+/* Static, human-readable name of a status code. */
+const char* tome_status_string(int32_t status);
+
+/* Detail text of the last non-zero status returned on the calling thread. */
+const char* tome_last_error_string(void);
+
+/*
+ * Selective log-softmax: out_logprob[i] = x[i, targets[i]]/T - logsumexp_j(x[i, j]/T), fp32.
+ * Replaces local_compute_logprobs (mlx-impl/node.py:400-404) and the
+ * "fused_log_softmax(...) then lp[b, token]" pattern of the policy call sites
+ * (mlx-impl/node.py:558-571, 590-605, 331-340, 356-373).
+ *
+ *   logits        device, [rows, vocab], row r starts at element r*row_stride (row_stride >= vocab)
+ *   dtype         TOME_F32 or TOME_BF16
+ *   targets       device int32 [rows], each in [0, vocab); a target outside the range
+ *                 gives NaN in that row and sets TOME_DEV_TARGET_OUT_OF_RANGE
+ *   temperature   > 0 and finite (the "temperature or 1.0" convention of node.py is the caller's)
+ *   out_logprob   device fp32 [rows]
+ *   out_lse       device fp32 [rows] or NULL: logsumexp_j(x/T)
+ *   out_target_raw device fp32 [rows] or NULL: the gathered logit x[i, targets[i]],
+ *                 converted to fp32 without scaling (bit-exact copy of the input element)
+ * One pass over the logits; accumulation in fp32.
+ */
+int32_t tome_selective_logprob(const void* logits, int32_t dtype, int64_t rows, int64_t vocab,
+                               int64_t row_stride, const int32_t* targets, float temperature,
+                               float* out_logprob, float* out_lse, float* out_target_raw,
+                               int32_t* dev_status, void* stream);
+
+/*
+ * Full-matrix log-softmax with the order of operations of the reference's Metal kernel
+ * (mlx-impl/model.py:16-66, wrapper fused_log_softmax model.py:77-89):
+ *   out[i, j] = T(float(x[i, j]) * (1/temperature)) - T(max + log(sum exp(...))), in dtype T.
+ *   out       device, same dtype as logits, [rows, vocab] with row stride out_row_stride
+ *   out_lse   device fp32 [rows] or NULL
+ */
+int32_t tome_log_softmax_full(const void* logits, int32_t dtype, int64_t rows, int64_t vocab,
+                              int64_t row_stride, float temperature, void* out,
+                              int64_t out_row_stride, float* out_lse, int32_t* dev_status,
+                              void* stream);
+
+/*
+ * GRPO dual scoring: per-token log-probs of the policy and of the reference model on a
+ * ragged window of each sequence, and the masked k3 KL estimate
+ *   kl = exp(r - p) - (r - p) - 1,  r = reference logprob, p = policy logprob.
+ * The window is the completion slice of _process_ref_logprobs_batched
+ * (mlx-impl/node.py:446-451): positions [starts[i], starts[i] + lengths[i]) of sequence i.
+ * The KL formula has no counterpart in the reference (the external trainer forms it).
+ *
+ *   policy_logits, ref_logits  device, [n_seq * seq_len, vocab], row stride row_stride, same dtype
+ *   targets   device int32 [n_seq * seq_len]
+ *   lengths   device int32 [n_seq]; clamped to [0, seq_len - start]
+ *   starts    device int32 [n_seq] or NULL (all zero)
+ *   out_*     device fp32 [n_seq * seq_len]; positions outside the window are written as 0
+ * Rows outside the windows are never read.  n_seq <= 4096.
+ */
+int32_t tome_dual_logprob_kl(const void* policy_logits, const void* ref_logits, int32_t dtype,
+                             int64_t n_seq, int64_t seq_len, int64_t vocab, int64_t row_stride,
+                             const int32_t* targets, const int32_t* lengths,
+                             const int32_t* starts, float temperature, float* out_lp_policy,
+                             float* out_lp_ref, float* out_kl, int32_t* dev_status,
+                             void* stream);
+
+/*
+ * Fused LM head + selective log-prob: logits = hidden @ weight^T are formed tile by tile
+ * on the tensor cores and reduced on the fly; no logits buffer exists.
+ * Replaces "x @ embed_tokens.weight.T" (mlx-impl/model.py:538) followed by
+ * local_compute_logprobs (mlx-impl/node.py:400-404).
+ *
+ *   hidden       device bf16 [rows, hidden_dim], contiguous, 16-byte aligned, hidden_dim % 8 == 0
+ *   weight       device bf16 [vocab_local, hidden_dim], contiguous (a row shard of the head)
+ *   vocab_offset global vocabulary index of weight row 0 (0 when unsharded)
+ *   targets      device int32 [rows], GLOBAL vocabulary indices
+ *   workspace    device scratch of at least tome_lmhead_workspace_bytes(...) bytes, 16-byte aligned
+ *
+ * tome_lmhead_partials writes the shard's triple per row (all device fp32 [rows]):
+ *   out_m = max_j(x_j)/T, out_s = sum_j exp(x_j/T - out_m), out_t = x_target/T if the
+ *   shard owns the target, else 0.
+ * tome_lmhead_logprob (unsharded: vocab_offset 0, vocab_local = vocab) writes
+ *   out_logprob = x_target/T - lse and out_lse (nullable).
+ */
+size_t tome_lmhead_workspace_bytes(int64_t rows, int64_t hidden_dim, int64_t vocab_local);
+
+int32_t tome_lmhead_partials(const void* hidden, const void* weight, int64_t rows,
+                             int64_t hidden_dim, int64_t vocab_local, int64_t vocab_offset,
+                             const int32_t* targets, float temperature, float* out_m,
+                             float* out_s, float* out_t, void* workspace, size_t workspace_bytes,
+                             int32_t* dev_status, void* stream);
+
+int32_t tome_lmhead_logprob(const void* hidden, const void* weight, int64_t rows,
+                            int64_t hidden_dim, int64_t vocab, const int32_t* targets,
+                            float temperature, float* out_logprob, float* out_lse,
+                            void* workspace, size_t workspace_bytes, int32_t* dev_status,
+                            void* stream);
+
+/*
+ * Combine per-shard triples into log-probs (the step after the vocab-parallel exchange;
+ * no counterpart in the reference, which has no sharded head):
+ *   M = max_p m[p], S = sum_p s[p] * exp(m[p] - M), lse = M + log S,
+ *   out_logprob = sum_q t[q] - lse.
+ *   m, s   device fp32, part p of row i at m[p * ms_part_stride + i], n_parts parts
+ *   t      device fp32, part q of row i at t[q * t_part_stride + i], n_t_parts parts
+ *          (1 when the exchange already summed the target column)
+ *   out_lse nullable
+ */
+int32_t tome_combine_triples(const float* m, const float* s, int64_t ms_part_stride,
+                             int32_t n_parts, const float* t, int64_t t_part_stride,
+                             int32_t n_t_parts, int64_t rows, float* out_logprob,
+                             float* out_lse, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TOME_B200_H_ */

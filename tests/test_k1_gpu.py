@@ -1,0 +1,289 @@
+"""GPU parity tests of the streaming log-softmax kernels (selective / full / dual) against
+the CPU oracle, through the C ABI.  Tolerances: max-abs 1e-4 for fp32 logits, 2e-3 for bf16
+logits; the gathered target logit must be bit-exact."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import TOL, from_bits, load_golden, max_abs
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(rows, vocab, dtype, seed, scale=3.0):
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.randn((rows, vocab), generator=g) * scale).to(dtype)
+    ids = torch.randint(0, vocab, (rows,), generator=g, dtype=torch.int32)
+    return x, ids
+
+
+def _check_selective(x, ids, temp, dev, tol=None):
+    import tome_b200
+    lp, lse, raw = tome_b200.selective_log_softmax(x.to(dev), ids.to(dev), temp, return_lse=True,
+                                                   return_target_logit=True, check=True)
+    o_lp, o_lse, o_raw = oracle.selective_logprob(x, ids, temp)
+    tol = TOL[x.dtype] if tol is None else tol
+    assert lp.dtype == torch.float32 and lp.shape == ids.shape
+    assert max_abs(lp, o_lp) <= tol, (max_abs(lp, o_lp), tol)
+    assert max_abs(lse, o_lse) <= tol
+    assert torch.equal(raw.cpu(), o_raw), "gathered target logit must be bit-exact"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("vocab", [1, 7, 8, 9, 4095, 4096, 4097, 16392, 32768 + 16, 151936])
+def test_selective_vocab_edges(cuda_device, dtype, vocab):
+    x, ids = _case(5, vocab, dtype, 100 + vocab % 97)
+    _check_selective(x, ids, 1.0, cuda_device)
+    _check_selective(x, ids, 0.7, cuda_device)
+
+
+@pytest.mark.parametrize("rows", [1, 2, 147, 148, 149, 300])
+def test_selective_row_counts(cuda_device, rows):
+    x, ids = _case(rows, 4096 + 8, torch.bfloat16, rows)
+    _check_selective(x, ids, 0.7, cuda_device)
+
+
+def test_selective_targets_at_the_ends(cuda_device):
+    x, ids = _case(4, 151936, torch.bfloat16, 5)
+    ids[:] = torch.tensor([0, 151935, 151936 - 384, 4096], dtype=torch.int32)
+    _check_selective(x, ids, 1.0, cuda_device)
+
+
+def test_selective_masked_columns_and_constant_rows(cuda_device):
+    x, ids = _case(4, 10000, torch.float32, 6)
+    x[0, :9000] = float("-inf")
+    ids[0] = 9500
+    x[1, :] = 3.0
+    x[2, :] = -1e30
+    x[2, 17] = 0.0
+    ids[2] = 17
+    _check_selective(x, ids, 1.0, cuda_device)
+    lp = __import__("tome_b200").selective_log_softmax(x.to(cuda_device), ids.to(cuda_device), 1.0)
+    assert abs(float(lp[2])) < 1e-6
+    # a masked target scores -inf, as in the oracle
+    ids[0] = 3
+    lp = __import__("tome_b200").selective_log_softmax(x.to(cuda_device), ids.to(cuda_device), 1.0)
+    assert float(lp[0]) == float("-inf")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_selective_unaligned_views_take_the_plain_kernel(cuda_device, dtype):
+    import tome_b200
+    x, ids = _case(6, 1003, dtype, 8)
+    xd = x.to(cuda_device)
+    # odd base offset and a row pitch that is not a multiple of 16 bytes
+    view = xd[:, 1:1000]
+    ids = ids.clamp(max=998)
+    lp = tome_b200.local_compute_logprobs(view, ids.to(cuda_device), 0.7)
+    o_lp, _, _ = oracle.selective_logprob(x[:, 1:1000], ids, 0.7)
+    assert max_abs(lp, o_lp) <= TOL[dtype]
+
+
+def test_selective_strided_rows_and_leading_dims(cuda_device):
+    import tome_b200
+    x, ids = _case(12, 2048, torch.bfloat16, 9)
+    xd = x.to(cuda_device)
+    wide = torch.zeros((12, 4096), dtype=torch.bfloat16, device=cuda_device)
+    wide[:, :2048] = xd
+    lp = tome_b200.local_compute_logprobs(wide[:, :2048], ids.to(cuda_device), 1.0)
+    o_lp, _, _ = oracle.selective_logprob(x, ids, 1.0)
+    assert max_abs(lp, o_lp) <= 2e-3
+    lp3 = tome_b200.local_compute_logprobs(xd.view(3, 4, 2048), ids.view(3, 4).to(cuda_device), 1.0)
+    assert lp3.shape == (3, 4) and max_abs(lp3.reshape(-1), o_lp) <= 2e-3
+
+
+def test_temperature_zero_means_one(cuda_device):
+    import tome_b200
+    x, ids = _case(3, 500, torch.float32, 10)
+    a = tome_b200.local_compute_logprobs(x.to(cuda_device), ids.to(cuda_device), 0.0)
+    b = tome_b200.local_compute_logprobs(x.to(cuda_device), ids.to(cuda_device), 1.0)
+    assert torch.equal(a, b)
+
+
+def test_empty_input(cuda_device):
+    import tome_b200
+    x = torch.zeros((0, 128), dtype=torch.bfloat16, device=cuda_device)
+    ids = torch.zeros((0,), dtype=torch.int32, device=cuda_device)
+    assert tome_b200.local_compute_logprobs(x, ids, 1.0).shape == (0,)
+    assert tome_b200.fused_log_softmax(x, 1.0).shape == (0, 128)
+
+
+def test_out_of_range_target_sets_status_and_nan(cuda_device):
+    import tome_b200
+    x, ids = _case(4, 100, torch.float32, 11)
+    ids[2] = 100
+    lp = tome_b200.local_compute_logprobs(x.to(cuda_device), ids.to(cuda_device), 1.0)
+    assert torch.isnan(lp[2]) and not torch.isnan(lp[[0, 1, 3]]).any()
+    with pytest.raises(tome_b200.TomeRuntimeError):
+        tome_b200.check_device_status(cuda_device)
+    tome_b200.check_device_status(cuda_device)  # cleared by the failed check
+
+
+def test_outputs_stay_inside_their_buffers(cuda_device):
+    from tome_b200 import _lib
+    rows, vocab, pad = 37, 5000, 64
+    x, ids = _case(rows, vocab, torch.bfloat16, 12)
+    xd, idd = x.to(cuda_device), ids.to(cuda_device)
+    bufs = [torch.full((rows + 2 * pad,), 1234.5, dtype=torch.float32, device=cuda_device) for _ in range(3)]
+    ptrs = [b.data_ptr() + pad * 4 for b in bufs]
+    st = _lib.lib.tome_selective_logprob(xd.data_ptr(), 1, rows, vocab, vocab, idd.data_ptr(), 1.0,
+                                         ptrs[0], ptrs[1], ptrs[2], None,
+                                         torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    torch.cuda.synchronize()
+    for b in bufs:
+        assert float((b[:pad] - 1234.5).abs().max()) == 0 and float((b[-pad:] - 1234.5).abs().max()) == 0
+    o_lp, _, _ = oracle.selective_logprob(x, ids, 1.0)
+    assert max_abs(bufs[0][pad:pad + rows], o_lp) <= 2e-3
+
+
+def test_cfg1_shape_fp32(cuda_device):
+    from tome_b200 import synthetic
+    x, ids = synthetic.cfg1_selective_fp32(rows=256)
+    _check_selective(x, ids, 1.0, cuda_device)
+    _check_selective(x, ids, 0.7, cuda_device)
+
+
+def test_cfg2_shape_bf16_planted(cuda_device):
+    from tome_b200 import synthetic
+    x, ids = synthetic.cfg2_rollout_bf16(rows=512)
+    _check_selective(x, ids, 1.0, cuda_device)
+
+
+def test_cfg2_full_size_properties(cuda_device):
+    """20480 x 151936 bf16 (6.2 GB), generated on the device: every row's lse against an
+    independent torch reduction on the GPU, a 256-row sample against the oracle, and
+    invariance under a row permutation."""
+    import tome_b200
+    from tome_b200 import synthetic
+    x, ids = synthetic.cfg2_rollout_bf16(device=cuda_device)
+    lp, lse, raw = tome_b200.selective_log_softmax(x, ids, 1.0, return_lse=True,
+                                                   return_target_logit=True, check=True)
+    for b in range(0, x.shape[0], 2048):
+        ref = torch.logsumexp(x[b:b + 2048].float(), dim=-1)
+        assert max_abs(lse[b:b + 2048], ref) <= 2e-3
+    assert torch.equal(raw, x.gather(1, ids.long()[:, None]).squeeze(1).float())
+    sample = torch.arange(0, x.shape[0], 80, device=cuda_device)
+    o_lp, _, _ = oracle.selective_logprob(x[sample].cpu(), ids[sample].cpu(), 1.0)
+    assert max_abs(lp[sample], o_lp) <= 2e-3
+    lp_rev = tome_b200.local_compute_logprobs(x[sample.flip(0)], ids[sample.flip(0)], 1.0)
+    assert torch.equal(lp_rev.flip(0), tome_b200.local_compute_logprobs(x[sample], ids[sample], 1.0))
+
+
+# ------------------------------------------------------------------ full matrix (compat)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 151936), (3, 4097), (5, 8), (2, 3), (149, 1024), (2, 4, 520)])
+def test_full_log_softmax_matches_metal_order(cuda_device, dtype, shape):
+    import tome_b200
+    g = torch.Generator().manual_seed(sum(shape))
+    x = torch.randn(shape, generator=g).to(dtype)
+    for temp in (1.0, 0.7):
+        out = tome_b200.fused_log_softmax(x.to(cuda_device), temp)
+        assert out.dtype == dtype and out.shape == x.shape
+        ref = oracle.log_softmax_metal_order(x, temp)
+        if dtype == torch.float32:
+            assert max_abs(out, ref) <= 1e-4
+        else:
+            # outputs are bf16 values near -12: one bf16 ulp there is 0.0625; lse rounding may
+            # differ by one ulp between two fp32 summation orders
+            assert max_abs(out.float(), ref.float()) <= 0.0625 + 1e-6
+            exact = (out.cpu() == ref).float().mean()
+            assert float(exact) > 0.99 or max_abs(out.float(), ref.float()) <= 0.0625 + 1e-6
+
+
+def test_full_log_softmax_reference_unit_test_shape(cuda_device):
+    # mlx-impl/tests/test_logprob_comparison.py:84-102 with its 5e-3 tolerance
+    import tome_b200
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn((1, 151936), generator=g).to(torch.bfloat16)
+    out = tome_b200.fused_log_softmax(x.to(cuda_device), temperature=1.0)
+    lse = oracle.logsumexp_f32(x.float()).to(torch.bfloat16)
+    expected = (x.float() - lse.float()[:, None]).to(torch.bfloat16)
+    assert max_abs(out.float(), expected.float()) < 5e-3 or float((out.cpu() == expected).float().mean()) > 0.99
+    full32 = tome_b200.fused_log_softmax(x.float().to(cuda_device), 1.0)
+    assert max_abs(torch.logsumexp(full32.double(), -1), torch.zeros(1)) < 1e-4
+
+
+def test_fused_log_softmax_with_targets_is_selective(cuda_device):
+    import tome_b200
+    x, ids = _case(9, 3000, torch.float32, 13)
+    full = tome_b200.fused_log_softmax(x.to(cuda_device), 0.7)
+    sel = tome_b200.fused_log_softmax(x.to(cuda_device), 0.7, targets=ids.to(cuda_device))
+    assert max_abs(full.gather(1, ids.long().to(cuda_device)[:, None]).squeeze(1), sel) <= 1e-4
+
+
+# ------------------------------------------------------------------ dual scoring + KL
+def _check_dual(pol, ref, ids, lengths, temp, dev, starts=None, tol=2e-3):
+    import tome_b200
+    p, r, kl = tome_b200.grpo_dual_logprob_kl(pol.to(dev), ref.to(dev), ids.to(dev), lengths.to(dev),
+                                              temp, starts=None if starts is None else starts.to(dev),
+                                              check=True)
+    o_p, o_r, o_kl = oracle.dual_logprob_kl(pol, ref, ids, lengths, temp, starts)
+    assert max_abs(p, o_p) <= tol and max_abs(r, o_r) <= tol
+    assert max_abs(kl, o_kl) <= 2 * tol
+    return p, r, kl
+
+
+def test_dual_ragged(cuda_device):
+    from tome_b200 import synthetic
+    pol, ref, ids, lengths, temp = synthetic.cfg5_dual(6, 24, 8200, "cpu", 21, min_len=0)
+    lengths[0], lengths[1] = 0, 24
+    p, r, kl = _check_dual(pol, ref, ids, lengths, temp, cuda_device)
+    assert float(p[0].abs().max()) == 0 and float(kl[0].abs().max()) == 0
+
+
+def test_dual_windows_with_starts_and_poisoned_padding(cuda_device):
+    from tome_b200 import synthetic
+    pol, ref, ids, lengths, temp = synthetic.cfg5_dual(5, 16, 2048, "cpu", 22, min_len=0)
+    starts = torch.tensor([0, 3, 15, 16, 7], dtype=torch.int32)
+    lengths = torch.tensor([4, 13, 5, 2, 0], dtype=torch.int32)  # two get clamped
+    pol_p, ref_p = pol.clone(), ref.clone()
+    for i in range(5):
+        st = int(starts[i]); ln = max(0, min(int(lengths[i]), 16 - st))
+        mask = torch.ones(16, dtype=torch.bool); mask[st:st + ln] = False
+        pol_p[i, mask] = float("nan"); ref_p[i, mask] = float("nan")
+    p, r, kl = _check_dual(pol_p, ref_p, ids, lengths, temp, cuda_device, starts=starts)
+    assert not torch.isnan(p).any() and not torch.isnan(kl).any()
+
+
+def test_dual_fp32_and_cfg5_shape(cuda_device):
+    from tome_b200 import synthetic
+    pol, ref, ids, lengths, temp = synthetic.cfg5_dual(2, 96, 151936, "cpu", 1005)
+    _check_dual(pol, ref, ids, lengths, temp, cuda_device)
+    _check_dual(pol[:, :8, :5000].float().contiguous(), ref[:, :8, :5000].float().contiguous(),
+                ids[:, :8] % 5000, torch.tensor([8, 3], dtype=torch.int32), 1.0, cuda_device, tol=1e-4)
+
+
+# ------------------------------------------------------------------ committed fixtures
+@pytest.mark.parametrize("name,dtype", [("selective_bf16.npz", torch.bfloat16),
+                                        ("selective_fp32.npz", torch.float32)])
+def test_golden_selective_and_full(cuda_device, name, dtype):
+    import tome_b200
+    gld = load_golden(name)
+    x = from_bits(gld["logits"], dtype).to(cuda_device)
+    ids = torch.from_numpy(gld["ids"]).to(cuda_device)
+    temp = float(gld["temp"])
+    lp, lse, raw = tome_b200.selective_log_softmax(x, ids, temp, return_lse=True,
+                                                   return_target_logit=True)
+    assert max_abs(lp, torch.from_numpy(gld["logprob"])) <= TOL[dtype]
+    assert max_abs(lse, torch.from_numpy(gld["lse"])) <= TOL[dtype]
+    assert torch.equal(raw.cpu(), torch.from_numpy(gld["raw"]))
+    full = tome_b200.fused_log_softmax(x, temp)
+    want = from_bits(gld["full"], dtype)
+    assert max_abs(full.float(), want.float()) <= (1e-4 if dtype == torch.float32 else 0.0625 + 1e-6)
+
+
+def test_golden_dual(cuda_device):
+    import tome_b200
+    gld = load_golden("dual_bf16.npz")
+    p, r, kl = tome_b200.grpo_dual_logprob_kl(
+        from_bits(gld["policy"], torch.bfloat16).to(cuda_device),
+        from_bits(gld["ref"], torch.bfloat16).to(cuda_device),
+        torch.from_numpy(gld["ids"]).to(cuda_device), torch.from_numpy(gld["lengths"]).to(cuda_device),
+        float(gld["temp"]))
+    assert max_abs(p, torch.from_numpy(gld["lp_policy"])) <= 2e-3
+    assert max_abs(r, torch.from_numpy(gld["lp_ref"])) <= 2e-3
+    assert max_abs(kl, torch.from_numpy(gld["kl"])) <= 4e-3

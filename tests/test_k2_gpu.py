@@ -1,0 +1,124 @@
+"""GPU parity tests of the fused LM-head + log-prob kernel (tcgen05 / TMEM) against the CPU
+oracle, through the C ABI.  Tolerance: max-abs 2e-3 on log-probs (bf16 operands, fp32
+accumulation; the oracle multiplies the same bf16 values in fp32)."""
+import pytest
+import torch
+
+from helpers import from_bits, load_golden, max_abs
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3
+
+
+def _run(rows, k, vocab, temp, dev, seed=0, w_scale=0.05):
+    import tome_b200
+    from tome_b200 import synthetic
+    hidden, weight, ids = synthetic.cfg3_lm_head(rows, k, vocab, "cpu", 3000 + seed, w_scale)
+    lp, lse = tome_b200.lm_head_logprob(hidden.to(dev), weight.to(dev), ids.to(dev), temp, check=True)
+    o_lp, o_lse = oracle.lm_head_logprob(hidden, weight, ids, temp)
+    assert lp.shape == (rows,) and lp.dtype == torch.float32
+    assert max_abs(lse, o_lse) <= TOL, ("lse", max_abs(lse, o_lse))
+    assert max_abs(lp, o_lp) <= TOL, ("logprob", max_abs(lp, o_lp))
+
+
+def test_one_tile(cuda_device):
+    _run(128, 64, 256, 1.0, cuda_device)
+
+
+@pytest.mark.parametrize("rows", [1, 40, 127, 129, 300])
+def test_row_tails(cuda_device, rows):
+    _run(rows, 128, 512, 1.0, cuda_device, seed=rows)
+
+
+@pytest.mark.parametrize("vocab", [8, 255, 257, 700, 4096 + 48, 18992])
+def test_vocab_tails(cuda_device, vocab):
+    _run(130, 192, vocab, 0.7, cuda_device, seed=vocab)
+
+
+@pytest.mark.parametrize("k", [8, 72, 200, 1024, 4096])
+def test_hidden_sizes(cuda_device, k):
+    _run(140, k, 1000, 1.0, cuda_device, seed=k, w_scale=0.02)
+
+
+def test_many_bands_and_row_tile_groups(cuda_device):
+    # K = 4096 makes bands short (8 column tiles) and row-tile groups small
+    _run(128 * 41, 4096, 256 * 20, 0.9, cuda_device, seed=5, w_scale=0.015)
+
+
+def test_cfg3_shape_row_slice(cuda_device):
+    # Qwen3-0.6B head shape with a 512-row slice of the 16384 rows
+    _run(512, 1024, 151936, 1.0, cuda_device, seed=7, w_scale=0.02)
+
+
+def test_leading_dims_and_golden(cuda_device):
+    import tome_b200
+    gld = load_golden("lm_head.npz")
+    hidden = from_bits(gld["hidden"], torch.bfloat16).to(cuda_device)
+    weight = from_bits(gld["weight"], torch.bfloat16).to(cuda_device)
+    ids = torch.from_numpy(gld["ids"]).to(cuda_device)
+    lp, lse = tome_b200.lm_head_logprob(hidden.view(4, 10, -1), weight, ids.view(4, 10), float(gld["temp"]))
+    assert lp.shape == (4, 10)
+    assert max_abs(lp.reshape(-1), torch.from_numpy(gld["logprob"])) <= TOL
+    assert max_abs(lse.reshape(-1), torch.from_numpy(gld["lse"])) <= TOL
+
+
+def test_shards_combine_to_the_unsharded_result(cuda_device):
+    import tome_b200
+    from tome_b200 import synthetic
+    hidden, weight, ids = synthetic.cfg4_vocab_parallel(200, 256, 3000, "cpu", 1004)
+    hd, wd, idd = hidden.to(cuda_device), weight.to(cuda_device), ids.to(cuda_device)
+    full_lp, full_lse = tome_b200.lm_head_logprob(hd, wd, idd, 0.8)
+    o_lp, o_lse = oracle.lm_head_logprob(hidden, weight, ids, 0.8)
+    assert max_abs(full_lp, o_lp) <= TOL
+    for world in (2, 4, 8):
+        ms, ss, ts = [], [], []
+        for r in range(world):
+            b, e = synthetic.shard_bounds(3000, r, world)
+            m, s, t = tome_b200.lm_head_partials(hd, wd[b:e].contiguous(), b, idd, 0.8)
+            om, os_, ot = oracle.shard_triple(hidden, weight[b:e], b, ids, 0.8)
+            assert max_abs(m, om) <= TOL and max_abs(t, ot) <= TOL
+            assert max_abs(s / os_, torch.ones_like(os_)) <= TOL
+            ms.append(m), ss.append(s), ts.append(t)
+        lp, lse = tome_b200.combine_triples(torch.stack(ms), torch.stack(ss), torch.stack(ts))
+        assert max_abs(lp, o_lp) <= TOL and max_abs(lse, o_lse) <= TOL
+        # the packed form of the all-reduce exchange: pre-summed target column
+        lp2, _ = tome_b200.combine_triples(torch.stack(ms), torch.stack(ss),
+                                           torch.stack(ts).sum(0, keepdim=True))
+        assert max_abs(lp2, o_lp) <= TOL
+
+
+def test_vocab_parallel_single_process_equals_unsharded(cuda_device):
+    import tome_b200
+    from tome_b200 import synthetic
+    hidden, weight, ids = synthetic.cfg3_lm_head(100, 64, 900, "cpu", 31)
+    hd, wd, idd = hidden.to(cuda_device), weight.to(cuda_device), ids.to(cuda_device)
+    a, _ = tome_b200.lm_head_logprob_vocab_parallel(hd, wd, 0, idd, 1.0)
+    b, _ = tome_b200.lm_head_logprob(hd, wd, idd, 1.0)
+    assert max_abs(a, b) <= 1e-5
+
+
+def test_out_of_range_target_is_reported(cuda_device):
+    import tome_b200
+    from tome_b200 import synthetic
+    hidden, weight, ids = synthetic.cfg3_lm_head(64, 64, 500, "cpu", 32)
+    ids[3] = 500
+    tome_b200.lm_head_logprob(hidden.to(cuda_device), weight.to(cuda_device), ids.to(cuda_device), 1.0)
+    with pytest.raises(tome_b200.TomeRuntimeError):
+        tome_b200.check_device_status(cuda_device)
+
+
+def test_caller_workspace_and_size_check(cuda_device):
+    import tome_b200
+    from tome_b200 import synthetic
+    hidden, weight, ids = synthetic.cfg3_lm_head(64, 64, 500, "cpu", 33)
+    need = tome_b200.lm_head_workspace_bytes(64, 64, 500)
+    ws = torch.empty(need, dtype=torch.uint8, device=cuda_device)
+    lp, _ = tome_b200.lm_head_logprob(hidden.to(cuda_device), weight.to(cuda_device),
+                                      ids.to(cuda_device), 1.0, workspace=ws)
+    o_lp, _ = oracle.lm_head_logprob(hidden, weight, ids, 1.0)
+    assert max_abs(lp, o_lp) <= TOL
+    with pytest.raises(ValueError):
+        tome_b200.lm_head_logprob(hidden.to(cuda_device), weight.to(cuda_device), ids.to(cuda_device),
+                                  1.0, workspace=ws[: need - 16])

@@ -1,0 +1,81 @@
+// Version, status text and per-device property cache of the C ABI.
+#include <mutex>
+
+#include "host_common.h"
+
+namespace tome {
+
+static thread_local char g_last_error[512] = "";
+
+int32_t fail(int32_t status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+int32_t check_cuda(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return TOME_OK;
+  return fail(TOME_ERR_CUDA, "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+}
+
+int32_t current_device_info(DeviceInfo* out) {
+  constexpr int MAX_DEV = 64;
+  static std::mutex mu;
+  static DeviceInfo cache[MAX_DEV];
+  static bool valid[MAX_DEV] = {false};
+  int dev = 0;
+  int32_t st = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+  if (st != TOME_OK) return st;
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev >= 0 && dev < MAX_DEV && valid[dev]) {
+    *out = cache[dev];
+    return TOME_OK;
+  }
+  DeviceInfo info;
+  info.device = dev;
+  st = check_cuda(cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, dev),
+                  "cudaDeviceGetAttribute(sm count)");
+  if (st != TOME_OK) return st;
+  st = check_cuda(
+      cudaDeviceGetAttribute(&info.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev),
+      "cudaDeviceGetAttribute(smem optin)");
+  if (st != TOME_OK) return st;
+  st = check_cuda(cudaDeviceGetAttribute(&info.cc_major, cudaDevAttrComputeCapabilityMajor, dev),
+                  "cudaDeviceGetAttribute(cc major)");
+  if (st != TOME_OK) return st;
+  if (dev >= 0 && dev < MAX_DEV) {
+    cache[dev] = info;
+    valid[dev] = true;
+  }
+  *out = info;
+  return TOME_OK;
+}
+
+}  // namespace tome
+
+extern "C" {
+
+int32_t tome_version(void) { return TOME_B200_VERSION; }
+
+const char* tome_status_string(int32_t status) {
+  switch (status) {
+    case TOME_OK: return "TOME_OK";
+    case TOME_ERR_NULL_POINTER: return "TOME_ERR_NULL_POINTER";
+    case TOME_ERR_MISALIGNED: return "TOME_ERR_MISALIGNED";
+    case TOME_ERR_BAD_DTYPE: return "TOME_ERR_BAD_DTYPE";
+    case TOME_ERR_BAD_SHAPE: return "TOME_ERR_BAD_SHAPE";
+    case TOME_ERR_BAD_STRIDE: return "TOME_ERR_BAD_STRIDE";
+    case TOME_ERR_WORKSPACE_TOO_SMALL: return "TOME_ERR_WORKSPACE_TOO_SMALL";
+    case TOME_ERR_BAD_TEMPERATURE: return "TOME_ERR_BAD_TEMPERATURE";
+    case TOME_ERR_UNSUPPORTED: return "TOME_ERR_UNSUPPORTED";
+    case TOME_ERR_TOO_LARGE: return "TOME_ERR_TOO_LARGE";
+    case TOME_ERR_CUDA: return "TOME_ERR_CUDA";
+    default: return "TOME_STATUS_UNKNOWN";
+  }
+}
+
+const char* tome_last_error_string(void) { return tome::g_last_error; }
+
+}  // extern "C"

@@ -1,0 +1,704 @@
+// K1: streaming log-softmax kernels over materialised logits (HBM-bound).
+//
+// One persistent CTA per SM.  A producer thread streams each logits row through a ring of
+// shared-memory stages with 1-D bulk (TMA) copies that complete on mbarriers; eight consumer
+// warps read the stages with 128-bit shared loads and keep a per-thread online (max, sum-exp)
+// pair in fp32, so every logit is read from HBM exactly once.  The ring runs across row
+// boundaries, so the loads of the next row are in flight while a row is being reduced.
+//
+// Three modes share the pipeline:
+//   SELECTIVE  logprob of one target per row             (mlx-impl/node.py:400-404)
+//   DUAL       policy + reference rows of a ragged window, plus the k3 KL estimate
+//              (window = completion slice, mlx-impl/node.py:446-451)
+//   FULL       full-matrix log-softmax in the input dtype, with the order of operations of
+//              the reference's Metal kernel (mlx-impl/model.py:16-66); the row is streamed
+//              twice (the second pass is served mostly by L2)
+//
+// Inputs that do not meet the bulk-copy alignment rules (base or row pitch not a multiple
+// of 16 bytes) take a plain-load kernel with the same arithmetic.
+#include <cuda_bf16.h>
+#include <float.h>
+#include <math.h>
+
+#include <algorithm>
+
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace tome {
+
+enum K1Mode { K1_SELECTIVE = 0, K1_DUAL = 1, K1_FULL = 2 };
+
+constexpr int K1_CONSUMER_WARPS = 8;
+constexpr int K1_CONSUMERS = K1_CONSUMER_WARPS * 32;
+constexpr int K1_THREADS = K1_CONSUMERS + 32;
+constexpr int K1_STAGES = 6;
+constexpr int K1_CHUNK_BYTES = 32768;
+constexpr int K1_MAX_SEQ = 4096;
+
+struct K1Params {
+  const void* src[2];      // DUAL: policy, reference
+  int64_t n_rows;          // SELECTIVE/FULL: rows; DUAL: n_seq * seq_len (dense row count)
+  int64_t vocab;
+  int64_t stride;          // elements between rows
+  const int32_t* targets;  // SELECTIVE, DUAL
+  float c;                 // log2(e) / temperature
+  float temp;
+  float inv_temp;
+  float* out0;             // SELECTIVE: logprob   DUAL: policy logprob   FULL: lse (nullable)
+  float* out1;             // SELECTIVE: lse (nullable)   DUAL: reference logprob
+  float* out2;             // SELECTIVE: raw target logit (nullable)   DUAL: k3 KL
+  void* out_full;          // FULL
+  int64_t out_stride;      // FULL
+  const int32_t* lengths;  // DUAL
+  const int32_t* starts;   // DUAL, nullable
+  int32_t n_seq;           // DUAL
+  int32_t seq_len;         // DUAL
+  int32_t* status;         // nullable
+};
+
+// ------------------------------------------------------------------ online (max, sum-exp)
+struct Online {
+  float m;   // running maximum of the raw logits
+  float mc;  // m * c
+  float s;   // sum of 2^(x*c - mc)
+};
+
+__device__ __forceinline__ void online_init(Online& st) {
+  st.m = -FLT_MAX;
+  st.mc = -FLT_MAX;
+  st.s = 0.0f;
+}
+
+__device__ __forceinline__ void online_raise(Online& st, float vmax, float c) {
+  if (vmax > st.m) {
+    st.s *= ex2f((st.m - vmax) * c);
+    st.m = vmax;
+    st.mc = vmax * c;
+  }
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+__device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t w) {
+  return *reinterpret_cast<__nv_bfloat162*>(&w);
+}
+
+// 8 bf16 logits
+__device__ __forceinline__ void online_update(Online& st, uint4 v, float c, __nv_bfloat16) {
+  const __nv_bfloat162 mx = __hmax2(__hmax2(as_bf162(v.x), as_bf162(v.y)),
+                                    __hmax2(as_bf162(v.z), as_bf162(v.w)));
+  online_raise(st, fmaxf(__low2float(mx), __high2float(mx)), c);
+  const float nmc = -st.mc;
+  const float e0 = ex2f(fmaf(bf16_lo(v.x), c, nmc));
+  const float e1 = ex2f(fmaf(bf16_hi(v.x), c, nmc));
+  const float e2 = ex2f(fmaf(bf16_lo(v.y), c, nmc));
+  const float e3 = ex2f(fmaf(bf16_hi(v.y), c, nmc));
+  const float e4 = ex2f(fmaf(bf16_lo(v.z), c, nmc));
+  const float e5 = ex2f(fmaf(bf16_hi(v.z), c, nmc));
+  const float e6 = ex2f(fmaf(bf16_lo(v.w), c, nmc));
+  const float e7 = ex2f(fmaf(bf16_hi(v.w), c, nmc));
+  st.s += ((e0 + e1) + (e2 + e3)) + ((e4 + e5) + (e6 + e7));
+}
+
+// 4 fp32 logits
+__device__ __forceinline__ void online_update(Online& st, uint4 v, float c, float) {
+  const float x0 = __uint_as_float(v.x), x1 = __uint_as_float(v.y);
+  const float x2 = __uint_as_float(v.z), x3 = __uint_as_float(v.w);
+  online_raise(st, fmaxf(fmaxf(x0, x1), fmaxf(x2, x3)), c);
+  const float nmc = -st.mc;
+  const float e0 = ex2f(fmaf(x0, c, nmc));
+  const float e1 = ex2f(fmaf(x1, c, nmc));
+  const float e2 = ex2f(fmaf(x2, c, nmc));
+  const float e3 = ex2f(fmaf(x3, c, nmc));
+  st.s += (e0 + e1) + (e2 + e3);
+}
+
+__device__ __forceinline__ void online_update_scalar(Online& st, float x, float c) {
+  online_raise(st, x, c);
+  st.s += ex2f(fmaf(x, c, -st.mc));
+}
+
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+// Merge the 32 per-thread states of a warp; every lane gets the result.
+__device__ __forceinline__ void online_warp_reduce(Online& st, float c) {
+  float m = st.m;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  float s = st.s * ex2f((st.m - m) * c);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  st.m = m;
+  st.mc = m * c;
+  st.s = s;
+}
+
+// ------------------------------------------------------------------ FULL mode output
+// out = T(float(x) * inv_temp) - T(lse), subtraction in T (mlx-impl/model.py:57-60)
+__device__ __forceinline__ uint32_t full_out_bf16x2(uint32_t w, float inv_temp,
+                                                    __nv_bfloat16 lse_t) {
+  const __nv_bfloat16 a = __float2bfloat16_rn(bf16_lo(w) * inv_temp);
+  const __nv_bfloat16 b = __float2bfloat16_rn(bf16_hi(w) * inv_temp);
+  const __nv_bfloat16 ra = __hsub(a, lse_t);
+  const __nv_bfloat16 rb = __hsub(b, lse_t);
+  return static_cast<uint32_t>(__bfloat16_as_ushort(ra)) |
+         (static_cast<uint32_t>(__bfloat16_as_ushort(rb)) << 16);
+}
+
+__device__ __forceinline__ uint4 full_out_vec(uint4 v, float inv_temp, float lse, __nv_bfloat16) {
+  const __nv_bfloat16 lse_t = __float2bfloat16_rn(lse);
+  uint4 o;
+  o.x = full_out_bf16x2(v.x, inv_temp, lse_t);
+  o.y = full_out_bf16x2(v.y, inv_temp, lse_t);
+  o.z = full_out_bf16x2(v.z, inv_temp, lse_t);
+  o.w = full_out_bf16x2(v.w, inv_temp, lse_t);
+  return o;
+}
+
+__device__ __forceinline__ uint4 full_out_vec(uint4 v, float inv_temp, float lse, float) {
+  uint4 o;
+  o.x = __float_as_uint(__fsub_rn(__fmul_rn(__uint_as_float(v.x), inv_temp), lse));
+  o.y = __float_as_uint(__fsub_rn(__fmul_rn(__uint_as_float(v.y), inv_temp), lse));
+  o.z = __float_as_uint(__fsub_rn(__fmul_rn(__uint_as_float(v.z), inv_temp), lse));
+  o.w = __float_as_uint(__fsub_rn(__fmul_rn(__uint_as_float(v.w), inv_temp), lse));
+  return o;
+}
+
+__device__ __forceinline__ float full_out_scalar(float x, float inv_temp, float lse) {
+  return __fsub_rn(__fmul_rn(x, inv_temp), lse);
+}
+
+__device__ __forceinline__ __nv_bfloat16 full_out_scalar(__nv_bfloat16 x, float inv_temp,
+                                                         float lse) {
+  return __hsub(__float2bfloat16_rn(__bfloat162float(x) * inv_temp), __float2bfloat16_rn(lse));
+}
+
+// ------------------------------------------------------------------ row results
+// lse of x/T from the raw maximum m and s = sum 2^((x - m) * c).
+template <int MODE>
+__device__ __forceinline__ float finish_lse(float m, float s, const K1Params& p) {
+  // SELECTIVE/DUAL follow node.py:401 (true division); FULL follows the Metal kernel
+  // (multiplication by the reciprocal, model.py:27).
+  const float ms = (MODE == K1_FULL) ? __fmul_rn(m, p.inv_temp) : __fdiv_rn(m, p.temp);
+  return ms + logf(s);
+}
+
+__device__ __forceinline__ void raise_status(int32_t* status, int32_t bit) {
+  if (status != nullptr) atomicOr(status, bit);
+}
+
+// DUAL: window of sequence i, clamped to the sequence.
+__device__ __forceinline__ void dual_window(const K1Params& p, int i, int& start, int& len) {
+  start = (p.starts != nullptr) ? p.starts[i] : 0;
+  start = max(0, min(start, p.seq_len));
+  len = max(0, min(p.lengths[i], p.seq_len - start));
+}
+
+// DUAL: dense row of the a-th active position; cum[] = exclusive prefix sums of the lengths.
+__device__ __forceinline__ int64_t dual_row_of_item(const K1Params& p, const int32_t* cum,
+                                                    int64_t a) {
+  int lo = 0, hi = p.n_seq;  // find i with cum[i] <= a < cum[i+1]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (cum[mid] <= a) lo = mid; else hi = mid;
+  }
+  int start = (p.starts != nullptr) ? p.starts[lo] : 0;
+  start = max(0, min(start, p.seq_len));
+  return static_cast<int64_t>(lo) * p.seq_len + start + (a - cum[lo]);
+}
+
+// Block-wide exclusive prefix sum of the window lengths into cum[0..n_seq]; returns the total.
+__device__ int64_t dual_build_prefix(const K1Params& p, int32_t* cum, int32_t* scratch) {
+  const int n = p.n_seq;
+  const int nt = blockDim.x;
+  const int per = (n + nt - 1) / nt;
+  const int b = min(n, static_cast<int>(threadIdx.x) * per);
+  const int e = min(n, b + per);
+  int32_t local = 0;
+  for (int i = b; i < e; ++i) {
+    int st, ln;
+    dual_window(p, i, st, ln);
+    local += ln;
+  }
+  scratch[threadIdx.x] = local;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int32_t run = 0;
+    for (int t = 0; t < nt; ++t) {
+      const int32_t v = scratch[t];
+      scratch[t] = run;
+      run += v;
+    }
+    cum[n] = run;
+  }
+  __syncthreads();
+  int32_t run = scratch[threadIdx.x];
+  for (int i = b; i < e; ++i) {
+    int st, ln;
+    dual_window(p, i, st, ln);
+    cum[i] = run;
+    run += ln;
+  }
+  __syncthreads();
+  return cum[n];
+}
+
+// DUAL: zero the outputs of every position outside its sequence's window.
+__device__ void dual_zero_masked(const K1Params& p) {
+  const int64_t total = p.n_rows;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int i = static_cast<int>(idx / p.seq_len);
+    const int pos = static_cast<int>(idx - static_cast<int64_t>(i) * p.seq_len);
+    int st, ln;
+    dual_window(p, i, st, ln);
+    if (pos < st || pos >= st + ln) {
+      p.out0[idx] = 0.0f;
+      p.out1[idx] = 0.0f;
+      p.out2[idx] = 0.0f;
+    }
+  }
+}
+
+// Writes the per-row results once the row's (m, s) and raw target logit are known.
+// Called by one thread.  `carry` holds the policy logprob between the two DUAL sub-rows.
+template <int MODE>
+__device__ __forceinline__ void emit_row(const K1Params& p, int64_t row, int sub, float m, float s,
+                                         float x_t, bool target_ok, float& carry) {
+  const float lse = finish_lse<MODE>(m, s, p);
+  if (MODE == K1_FULL) {
+    if (p.out0 != nullptr) p.out0[row] = lse;
+    return;
+  }
+  float lp = __fdiv_rn(x_t, p.temp) - lse;
+  if (!target_ok) lp = __int_as_float(0x7fc00000);
+  if (MODE == K1_SELECTIVE) {
+    p.out0[row] = lp;
+    if (p.out1 != nullptr) p.out1[row] = lse;
+    if (p.out2 != nullptr) p.out2[row] = target_ok ? x_t : __int_as_float(0x7fc00000);
+  } else {
+    if (sub == 0) {
+      carry = lp;
+      p.out0[row] = lp;
+    } else {
+      const float d = lp - carry;  // r - p
+      p.out1[row] = lp;
+      p.out2[row] = expf(d) - d - 1.0f;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ bulk-copy pipeline kernel
+struct K1Smem {
+  static constexpr int DATA = K1_STAGES * K1_CHUNK_BYTES;
+  static constexpr int BAR_OFF = DATA;                                   // 2 * STAGES mbarriers
+  static constexpr int PART_OFF = BAR_OFF + 2 * K1_STAGES * 8;           // [2][WARPS] float2
+  static constexpr int CUM_OFF = PART_OFF + 2 * K1_CONSUMER_WARPS * 8;   // DUAL: prefix sums
+  static constexpr int SCRATCH_OFF = CUM_OFF + (K1_MAX_SEQ + 1) * 4 + 12;
+  static constexpr int TOTAL_DUAL = SCRATCH_OFF + K1_THREADS * 4;
+  static constexpr int TOTAL_PLAIN = CUM_OFF;
+};
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(K1_THREADS, 1) k1_stream_kernel(const K1Params p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  constexpr int NSUB = (MODE == K1_SELECTIVE) ? 1 : 2;
+  constexpr int ES = sizeof(T);
+  constexpr int PER_VEC = 16 / ES;
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t full_bar = smem_base + K1Smem::BAR_OFF;
+  const uint32_t empty_bar = full_bar + K1_STAGES * 8;
+  float2* part = reinterpret_cast<float2*>(smem + K1Smem::PART_OFF);
+  int32_t* cum = reinterpret_cast<int32_t*>(smem + K1Smem::CUM_OFF);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < K1_STAGES; ++i) {
+      mbar_init(full_bar + i * 8, 1);
+      mbar_init(empty_bar + i * 8, K1_CONSUMER_WARPS);
+    }
+    fence_mbar_init();
+  }
+  int64_t n_items = p.n_rows;
+  if (MODE == K1_DUAL) {
+    n_items = dual_build_prefix(p, cum, reinterpret_cast<int32_t*>(smem + K1Smem::SCRATCH_OFF));
+    dual_zero_masked(p);
+  }
+  __syncthreads();
+
+  const int64_t row_bytes = p.vocab * ES;
+  const int64_t bulk_bytes = row_bytes & ~static_cast<int64_t>(15);
+  const int64_t n_chunks = (bulk_bytes + K1_CHUNK_BYTES - 1) / K1_CHUNK_BYTES;
+  const int64_t tail_begin = bulk_bytes / ES;  // first element not covered by bulk copies
+
+  if (warp == K1_CONSUMER_WARPS) {
+    // ---------------- producer: one thread issues every bulk copy of this CTA
+    if (lane == 0) {
+      const uint64_t policy = policy_evict_first();
+      uint32_t it = 0;
+      bool ok = true;
+      for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const int64_t row = (MODE == K1_DUAL) ? dual_row_of_item(p, cum, item) : item;
+        for (int sub = 0; sub < NSUB && ok; ++sub) {
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(
+                                   p.src[(MODE == K1_DUAL) ? sub : 0]) + row * p.stride * ES;
+          for (int64_t k = 0; k < n_chunks; ++k, ++it) {
+            const uint32_t stage = it % K1_STAGES;
+            const uint32_t phase = (it / K1_STAGES) & 1u;
+            if (!mbar_wait(empty_bar + stage * 8, phase ^ 1u)) {
+              raise_status(p.status, TOME_DEV_TIMEOUT);
+              ok = false;
+              break;
+            }
+            const int64_t off = k * K1_CHUNK_BYTES;
+            const uint32_t bytes =
+                static_cast<uint32_t>(min(static_cast<int64_t>(K1_CHUNK_BYTES), bulk_bytes - off));
+            mbar_arrive_expect_tx(full_bar + stage * 8, bytes);
+            // FULL re-reads the row in its second pass: keep it in L2 after the first.
+            if (MODE == K1_FULL && sub == 0)
+              bulk_g2s(smem_base + stage * K1_CHUNK_BYTES, src + off, bytes, full_bar + stage * 8);
+            else
+              bulk_g2s_hint(smem_base + stage * K1_CHUNK_BYTES, src + off, bytes,
+                            full_bar + stage * 8, policy);
+          }
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers
+  const int ctid = threadIdx.x;  // 0 .. K1_CONSUMERS-1
+  uint32_t it = 0;
+  uint32_t red_it = 0;
+  float carry = 0.0f;
+  for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int64_t row = (MODE == K1_DUAL) ? dual_row_of_item(p, cum, item) : item;
+    float lse_row = 0.0f;
+    for (int sub = 0; sub < NSUB; ++sub) {
+      const T* src = reinterpret_cast<const T*>(p.src[(MODE == K1_DUAL) ? sub : 0]) +
+                     row * p.stride;
+      const bool reduce_pass = (MODE != K1_FULL) || (sub == 0);
+
+      // the one thread that finishes the row fetches the target logit early
+      float x_t = 0.0f;
+      bool target_ok = true;
+      if (MODE != K1_FULL && ctid == 0) {
+        const int32_t t = p.targets[row];
+        target_ok = (t >= 0) && (static_cast<int64_t>(t) < p.vocab);
+        if (target_ok) x_t = to_float(src[t]);
+        else raise_status(p.status, TOME_DEV_TARGET_OUT_OF_RANGE);
+      }
+
+      Online st;
+      online_init(st);
+      T* dst = nullptr;
+      if (MODE == K1_FULL) dst = reinterpret_cast<T*>(p.out_full) + row * p.out_stride;
+
+      for (int64_t k = 0; k < n_chunks; ++k, ++it) {
+        const uint32_t stage = it % K1_STAGES;
+        const uint32_t phase = (it / K1_STAGES) & 1u;
+        if (!mbar_wait(full_bar + stage * 8, phase)) {
+          raise_status(p.status, TOME_DEV_TIMEOUT);
+          return;
+        }
+        const int64_t off = k * K1_CHUNK_BYTES;
+        const uint32_t bytes =
+            static_cast<uint32_t>(min(static_cast<int64_t>(K1_CHUNK_BYTES), bulk_bytes - off));
+        const uint32_t nvec = bytes >> 4;
+        const uint32_t sbase = smem_base + stage * K1_CHUNK_BYTES;
+        uint32_t v = ctid;
+        if (reduce_pass) {
+          for (; v + 3 * K1_CONSUMERS < nvec; v += 4 * K1_CONSUMERS) {
+            const uint4 a = lds128(sbase + v * 16);
+            const uint4 b = lds128(sbase + (v + K1_CONSUMERS) * 16);
+            const uint4 cc = lds128(sbase + (v + 2 * K1_CONSUMERS) * 16);
+            const uint4 d = lds128(sbase + (v + 3 * K1_CONSUMERS) * 16);
+            online_update(st, a, p.c, T());
+            online_update(st, b, p.c, T());
+            online_update(st, cc, p.c, T());
+            online_update(st, d, p.c, T());
+          }
+          for (; v < nvec; v += K1_CONSUMERS) online_update(st, lds128(sbase + v * 16), p.c, T());
+        } else {
+          uint8_t* drow = reinterpret_cast<uint8_t*>(dst) + off;
+          for (; v < nvec; v += K1_CONSUMERS) {
+            const uint4 a = lds128(sbase + v * 16);
+            stg128(drow + static_cast<size_t>(v) * 16, full_out_vec(a, p.inv_temp, lse_row, T()));
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar + stage * 8);
+      }
+
+      // elements past the last 16-byte boundary of the row (at most PER_VEC - 1)
+      if (ctid == 0) {
+        for (int64_t j = tail_begin; j < p.vocab; ++j) {
+          if (reduce_pass) online_update_scalar(st, to_float(src[j]), p.c);
+          else dst[j] = full_out_scalar(src[j], p.inv_temp, lse_row);
+        }
+      }
+
+      if (reduce_pass) {
+        online_warp_reduce(st, p.c);
+        float2* slot = part + (red_it & 1u) * K1_CONSUMER_WARPS;
+        if (lane == 0) slot[warp] = make_float2(st.m, st.s);
+        named_bar_sync(1, K1_CONSUMERS);
+        if (warp == 0 || MODE == K1_FULL) {
+          float2 ms = (lane < K1_CONSUMER_WARPS) ? slot[lane] : make_float2(-FLT_MAX, 0.0f);
+          float m = ms.x;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+          float s = ms.y * ex2f((ms.x - m) * p.c);
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+          if (MODE == K1_FULL) lse_row = finish_lse<MODE>(m, s, p);
+          if (ctid == 0) emit_row<MODE>(p, row, sub, m, s, x_t, target_ok, carry);
+        }
+        ++red_it;
+      }
+    }
+  }
+  (void)PER_VEC;
+}
+
+// ------------------------------------------------------------------ plain-load kernel
+// Same arithmetic with ordinary loads; any alignment, any pitch.  One CTA per row at a time.
+constexpr int K1_PLAIN_THREADS = 256;
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(K1_PLAIN_THREADS) k1_plain_kernel(const K1Params p) {
+  __shared__ float2 part[K1_PLAIN_THREADS / 32];
+  __shared__ float2 result;
+  __shared__ int32_t cum[(MODE == K1_DUAL) ? (K1_MAX_SEQ + 1) : 1];
+  __shared__ int32_t scratch[(MODE == K1_DUAL) ? K1_PLAIN_THREADS : 1];
+  constexpr int NSUB = (MODE == K1_DUAL) ? 2 : 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  int64_t n_items = p.n_rows;
+  if (MODE == K1_DUAL) {
+    n_items = dual_build_prefix(p, cum, scratch);
+    dual_zero_masked(p);
+    __syncthreads();
+  }
+  float carry = 0.0f;
+  for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int64_t row = (MODE == K1_DUAL) ? dual_row_of_item(p, cum, item) : item;
+    for (int sub = 0; sub < NSUB; ++sub) {
+      const T* src = reinterpret_cast<const T*>(p.src[(MODE == K1_DUAL) ? sub : 0]) +
+                     row * p.stride;
+      Online st;
+      online_init(st);
+      for (int64_t j = threadIdx.x; j < p.vocab; j += K1_PLAIN_THREADS)
+        online_update_scalar(st, to_float(src[j]), p.c);
+      online_warp_reduce(st, p.c);
+      if (lane == 0) part[warp] = make_float2(st.m, st.s);
+      __syncthreads();
+      if (warp == 0) {
+        float2 ms = (lane < K1_PLAIN_THREADS / 32) ? part[lane] : make_float2(-FLT_MAX, 0.0f);
+        float m = ms.x;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float s = ms.y * ex2f((ms.x - m) * p.c);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) {
+          float x_t = 0.0f;
+          bool target_ok = true;
+          if (MODE != K1_FULL) {
+            const int32_t t = p.targets[row];
+            target_ok = (t >= 0) && (static_cast<int64_t>(t) < p.vocab);
+            if (target_ok) x_t = to_float(src[t]);
+            else raise_status(p.status, TOME_DEV_TARGET_OUT_OF_RANGE);
+          }
+          emit_row<MODE>(p, row, sub, m, s, x_t, target_ok, carry);
+          result = make_float2(m, s);
+        }
+      }
+      __syncthreads();
+      if (MODE == K1_FULL) {
+        const float lse = finish_lse<MODE>(result.x, result.y, p);
+        T* dst = reinterpret_cast<T*>(p.out_full) + row * p.out_stride;
+        for (int64_t j = threadIdx.x; j < p.vocab; j += K1_PLAIN_THREADS)
+          dst[j] = full_out_scalar(src[j], p.inv_temp, lse);
+        __syncthreads();
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ host side
+template <typename T, int MODE>
+static int32_t k1_launch_typed(const K1Params& p, bool bulk_ok, int64_t max_items,
+                               cudaStream_t stream) {
+  DeviceInfo info;
+  int32_t st = current_device_info(&info);
+  if (st != TOME_OK) return st;
+  if (bulk_ok) {
+    const int smem = (MODE == K1_DUAL) ? K1Smem::TOTAL_DUAL : K1Smem::TOTAL_PLAIN;
+    if (smem > info.max_smem_optin)
+      return fail(TOME_ERR_UNSUPPORTED, "device offers %d bytes of shared memory, need %d",
+                  info.max_smem_optin, smem);
+    st = check_cuda(cudaFuncSetAttribute(k1_stream_kernel<T, MODE>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+                    "cudaFuncSetAttribute");
+    if (st != TOME_OK) return st;
+    const int grid = static_cast<int>(
+        std::max<int64_t>(1, std::min<int64_t>(info.sm_count, max_items)));
+    k1_stream_kernel<T, MODE><<<grid, K1_THREADS, smem, stream>>>(p);
+  } else {
+    const int grid = static_cast<int>(std::max<int64_t>(
+        1, std::min<int64_t>(static_cast<int64_t>(info.sm_count) * 8, max_items)));
+    k1_plain_kernel<T, MODE><<<grid, K1_PLAIN_THREADS, 0, stream>>>(p);
+  }
+  return check_cuda(cudaGetLastError(), "k1 launch");
+}
+
+template <int MODE>
+static int32_t k1_launch(const K1Params& p, int32_t dtype, bool bulk_ok, int64_t max_items,
+                         cudaStream_t stream) {
+  if (dtype == TOME_F32) return k1_launch_typed<float, MODE>(p, bulk_ok, max_items, stream);
+  return k1_launch_typed<__nv_bfloat16, MODE>(p, bulk_ok, max_items, stream);
+}
+
+static int32_t k1_check_common(const void* logits, int32_t dtype, int64_t rows, int64_t vocab,
+                               int64_t row_stride, float temperature) {
+  if (dtype != TOME_F32 && dtype != TOME_BF16)
+    return fail(TOME_ERR_BAD_DTYPE, "dtype %d is neither TOME_F32 nor TOME_BF16", dtype);
+  if (rows < 0 || vocab <= 0)
+    return fail(TOME_ERR_BAD_SHAPE, "rows=%lld vocab=%lld", (long long)rows, (long long)vocab);
+  if (vocab > 0x7fffffffLL)
+    return fail(TOME_ERR_BAD_SHAPE, "vocab=%lld does not fit int32 targets", (long long)vocab);
+  if (row_stride < vocab)
+    return fail(TOME_ERR_BAD_STRIDE, "row_stride=%lld < vocab=%lld", (long long)row_stride,
+                (long long)vocab);
+  if (!temperature_ok(temperature))
+    return fail(TOME_ERR_BAD_TEMPERATURE, "temperature=%g must be > 0 and finite", temperature);
+  if (rows > 0 && logits == nullptr) return fail(TOME_ERR_NULL_POINTER, "logits is NULL");
+  const size_t es = (dtype == TOME_F32) ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(logits) % es) != 0)
+    return fail(TOME_ERR_MISALIGNED, "logits is not aligned to its element size");
+  return TOME_OK;
+}
+
+static bool bulk_eligible(const void* base, int64_t stride, int32_t dtype) {
+  const int64_t es = (dtype == TOME_F32) ? 4 : 2;
+  return aligned16(base) && ((stride * es) % 16 == 0);
+}
+
+}  // namespace tome
+
+using namespace tome;
+
+extern "C" int32_t tome_selective_logprob(const void* logits, int32_t dtype, int64_t rows,
+                                          int64_t vocab, int64_t row_stride,
+                                          const int32_t* targets, float temperature,
+                                          float* out_logprob, float* out_lse,
+                                          float* out_target_raw, int32_t* dev_status,
+                                          void* stream) {
+  int32_t st = k1_check_common(logits, dtype, rows, vocab, row_stride, temperature);
+  if (st != TOME_OK) return st;
+  if (rows == 0) return TOME_OK;
+  if (targets == nullptr || out_logprob == nullptr)
+    return fail(TOME_ERR_NULL_POINTER, "targets or out_logprob is NULL");
+  K1Params p = {};
+  p.src[0] = logits;
+  p.n_rows = rows;
+  p.vocab = vocab;
+  p.stride = row_stride;
+  p.targets = targets;
+  p.c = LOG2E / temperature;
+  p.temp = temperature;
+  p.inv_temp = 1.0f / temperature;
+  p.out0 = out_logprob;
+  p.out1 = out_lse;
+  p.out2 = out_target_raw;
+  p.status = dev_status;
+  return k1_launch<K1_SELECTIVE>(p, dtype, bulk_eligible(logits, row_stride, dtype), rows,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int32_t tome_log_softmax_full(const void* logits, int32_t dtype, int64_t rows,
+                                         int64_t vocab, int64_t row_stride, float temperature,
+                                         void* out, int64_t out_row_stride, float* out_lse,
+                                         int32_t* dev_status, void* stream) {
+  int32_t st = k1_check_common(logits, dtype, rows, vocab, row_stride, temperature);
+  if (st != TOME_OK) return st;
+  if (out_row_stride < vocab)
+    return fail(TOME_ERR_BAD_STRIDE, "out_row_stride=%lld < vocab=%lld",
+                (long long)out_row_stride, (long long)vocab);
+  if (rows == 0) return TOME_OK;
+  if (out == nullptr) return fail(TOME_ERR_NULL_POINTER, "out is NULL");
+  const size_t es = (dtype == TOME_F32) ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(out) % es) != 0)
+    return fail(TOME_ERR_MISALIGNED, "out is not aligned to its element size");
+  K1Params p = {};
+  p.src[0] = logits;
+  p.n_rows = rows;
+  p.vocab = vocab;
+  p.stride = row_stride;
+  p.c = LOG2E / temperature;
+  p.temp = temperature;
+  p.inv_temp = 1.0f / temperature;
+  p.out0 = out_lse;
+  p.out_full = out;
+  p.out_stride = out_row_stride;
+  p.status = dev_status;
+  const bool bulk = bulk_eligible(logits, row_stride, dtype) &&
+                    bulk_eligible(out, out_row_stride, dtype);
+  return k1_launch<K1_FULL>(p, dtype, bulk, rows, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int32_t tome_dual_logprob_kl(const void* policy_logits, const void* ref_logits,
+                                        int32_t dtype, int64_t n_seq, int64_t seq_len,
+                                        int64_t vocab, int64_t row_stride,
+                                        const int32_t* targets, const int32_t* lengths,
+                                        const int32_t* starts, float temperature,
+                                        float* out_lp_policy, float* out_lp_ref, float* out_kl,
+                                        int32_t* dev_status, void* stream) {
+  if (n_seq < 0 || seq_len < 0)
+    return fail(TOME_ERR_BAD_SHAPE, "n_seq=%lld seq_len=%lld", (long long)n_seq,
+                (long long)seq_len);
+  if (n_seq > K1_MAX_SEQ)
+    return fail(TOME_ERR_TOO_LARGE, "n_seq=%lld exceeds the limit of %d sequences per call",
+                (long long)n_seq, K1_MAX_SEQ);
+  if (seq_len > 0x7fffffffLL / (n_seq > 0 ? n_seq : 1))
+    return fail(TOME_ERR_TOO_LARGE, "n_seq * seq_len does not fit int32");
+  const int64_t rows = n_seq * seq_len;
+  int32_t st = k1_check_common(policy_logits, dtype, rows, vocab, row_stride, temperature);
+  if (st != TOME_OK) return st;
+  if (rows == 0) return TOME_OK;
+  if (ref_logits == nullptr || targets == nullptr || lengths == nullptr ||
+      out_lp_policy == nullptr || out_lp_ref == nullptr || out_kl == nullptr)
+    return fail(TOME_ERR_NULL_POINTER, "a required pointer is NULL");
+  const size_t es = (dtype == TOME_F32) ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(ref_logits) % es) != 0)
+    return fail(TOME_ERR_MISALIGNED, "ref_logits is not aligned to its element size");
+  K1Params p = {};
+  p.src[0] = policy_logits;
+  p.src[1] = ref_logits;
+  p.n_rows = rows;
+  p.vocab = vocab;
+  p.stride = row_stride;
+  p.targets = targets;
+  p.c = LOG2E / temperature;
+  p.temp = temperature;
+  p.inv_temp = 1.0f / temperature;
+  p.out0 = out_lp_policy;
+  p.out1 = out_lp_ref;
+  p.out2 = out_kl;
+  p.lengths = lengths;
+  p.starts = starts;
+  p.n_seq = static_cast<int32_t>(n_seq);
+  p.seq_len = static_cast<int32_t>(seq_len);
+  p.status = dev_status;
+  const bool bulk = bulk_eligible(policy_logits, row_stride, dtype) &&
+                    bulk_eligible(ref_logits, row_stride, dtype);
+  return k1_launch<K1_DUAL>(p, dtype, bulk, rows, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,531 @@
+// K2: fused LM head + selective log-prob on the 5th-generation tensor cores (tensor-bound).
+//
+// logits = hidden[rows, K] @ weight[V, K]^T are produced 128 x 256 tiles at a time by
+// tcgen05.mma (bf16 in, fp32 accumulate in TMEM) and consumed straight out of TMEM by the
+// epilogue warps, which keep a running (max, sum-exp, target-logit) per row in registers.
+// No logits are ever written to memory.  Replaces "x @ embed_tokens.weight.T"
+// (mlx-impl/model.py:538) followed by local_compute_logprobs (mlx-impl/node.py:400-404).
+//
+// Structure of one persistent CTA (192 threads, one per SM):
+//   warp 0      producer: 2-D tiled TMA loads of the hidden tile (128 x 64) and the weight
+//               tile (256 x 64) into a ring of 128B-swizzled shared-memory stages
+//   warp 1      one thread issues tcgen05.mma into one of two 256-column TMEM accumulators
+//   warps 2-5   epilogue: thread i owns row i of the tile (tcgen05.ld 32x32b), reduces the
+//               256 columns into its running triple while the next tile is being multiplied
+//
+// Work decomposition.  The vocabulary is cut into bands of NB column tiles.  A work item is
+// (row tile, band): the CTA sweeps the band's column tiles with the running triple in
+// registers and writes one partial triple per row to the workspace; a merge kernel folds
+// the bands.  Items are ordered so that the CTAs running at the same time share a small set
+// of hidden tiles (GM row tiles, sized to stay in L2) and stream the same few weight bands,
+// so the weight matrix is read from HBM about once per GM row tiles.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <float.h>
+
+#include <algorithm>
+#include <mutex>
+
+#include "combine.h"
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace tome {
+
+constexpr int K2_BM = 128;
+constexpr int K2_BN = 256;
+constexpr int K2_BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int K2_STAGES = 4;
+constexpr int K2_A_BYTES = K2_BM * K2_BK * 2;
+constexpr int K2_B_BYTES = K2_BN * K2_BK * 2;
+constexpr int K2_STAGE_BYTES = K2_A_BYTES + K2_B_BYTES;
+constexpr int K2_THREADS = 192;
+constexpr int K2_EPI_WARPS = 4;
+constexpr int K2_TMEM_COLS = 512;
+constexpr int K2_SMEM_BYTES = K2_STAGES * K2_STAGE_BYTES + 1024 /*alignment slack*/ + 256;
+
+struct K2Params {
+  int64_t rows;
+  int64_t k_dim;
+  int64_t vocab_local;
+  int64_t vocab_offset;
+  int64_t vocab_check;     // > 0: targets must lie in [0, vocab_check)
+  const int32_t* targets;
+  float c;                 // log2(e) / temperature
+  float temp;
+  float* part_m;           // [n_bands][rows]
+  float* part_s;
+  float* part_t;
+  int32_t m_tiles, n_tiles, k_blocks;
+  int32_t nb;              // column tiles per band
+  int32_t n_bands;
+  int32_t gm;              // row tiles per group
+  int64_t n_items;
+  int32_t* status;
+};
+
+struct K2Item {
+  int32_t mt;     // row tile
+  int32_t band;
+  int32_t n_begin, n_end;  // column tiles
+};
+
+// Item order: row-tile groups outermost, then bands, then the row tiles of the group.
+__device__ __forceinline__ K2Item k2_decode(const K2Params& p, int64_t i) {
+  const int32_t full_groups = p.m_tiles / p.gm;
+  const int64_t per_group = static_cast<int64_t>(p.n_bands) * p.gm;
+  int32_t g, gm_here;
+  int64_t r;
+  if (i < full_groups * per_group) {
+    g = static_cast<int32_t>(i / per_group);
+    r = i - g * per_group;
+    gm_here = p.gm;
+  } else {
+    g = full_groups;
+    r = i - full_groups * per_group;
+    gm_here = p.m_tiles - full_groups * p.gm;
+  }
+  K2Item it;
+  it.band = static_cast<int32_t>(r / gm_here);
+  it.mt = g * p.gm + static_cast<int32_t>(r - static_cast<int64_t>(it.band) * gm_here);
+  it.n_begin = it.band * p.nb;
+  it.n_end = min(p.n_tiles, it.n_begin + p.nb);
+  return it;
+}
+
+// K-major, 128B-swizzled operand tile whose rows are 128 bytes: 8-row groups are 1024 bytes
+// apart (stride byte offset), the leading byte offset is unused (1), descriptor version 1.
+__device__ __forceinline__ uint64_t k2_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// kind::f16 instruction descriptor: fp32 accumulator, bf16 A and B, both K-major.
+__host__ __device__ constexpr uint32_t k2_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void k2_raise(int32_t* status, int32_t bit) {
+  if (status != nullptr) atomicOr(status, bit);
+}
+
+__global__ void __launch_bounds__(K2_THREADS, 1)
+k2_lmhead_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                 const __grid_constant__ CUtensorMap tmap_b, const K2Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles want 1024-byte alignment
+  uint8_t* smem = smem_raw + (base - raw);
+  const uint32_t bars = base + K2_STAGES * K2_STAGE_BYTES;
+  const uint32_t full_bar = bars;
+  const uint32_t empty_bar = bars + K2_STAGES * 8;
+  const uint32_t tfull_bar = bars + 2 * K2_STAGES * 8;
+  const uint32_t tempty_bar = tfull_bar + 16;
+  const uint32_t tmem_slot = tempty_bar + 16;
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(smem + K2_STAGES * K2_STAGE_BYTES + 2 * K2_STAGES * 8 + 32);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < K2_STAGES; ++i) {
+      mbar_init(full_bar + i * 8, 1);
+      mbar_init(empty_bar + i * 8, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tfull_bar + i * 8, 1);
+      mbar_init(tempty_bar + i * 8, K2_EPI_WARPS);
+    }
+    fence_mbar_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, K2_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int64_t i = blockIdx.x; i < p.n_items && ok; i += gridDim.x) {
+        const K2Item item = k2_decode(p, i);
+        for (int32_t n = item.n_begin; n < item.n_end && ok; ++n) {
+          for (int32_t kb = 0; kb < p.k_blocks; ++kb, ++it) {
+            const uint32_t stage = it % K2_STAGES;
+            const uint32_t phase = (it / K2_STAGES) & 1u;
+            if (!mbar_wait(empty_bar + stage * 8, phase ^ 1u)) {
+              k2_raise(p.status, TOME_DEV_TIMEOUT);
+              ok = false;
+              break;
+            }
+            const uint32_t sa = base + stage * K2_STAGE_BYTES;
+            mbar_arrive_expect_tx(full_bar + stage * 8, K2_STAGE_BYTES);
+            tma_load_2d(sa, &tmap_a, kb * K2_BK, item.mt * K2_BM, full_bar + stage * 8);
+            tma_load_2d(sa + K2_A_BYTES, &tmap_b, kb * K2_BK, n * K2_BN, full_bar + stage * 8);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = k2_idesc(K2_BM, K2_BN);
+      uint32_t it = 0, tc = 0;
+      bool ok = true;
+      for (int64_t i = blockIdx.x; i < p.n_items && ok; i += gridDim.x) {
+        const K2Item item = k2_decode(p, i);
+        for (int32_t n = item.n_begin; n < item.n_end && ok; ++n, ++tc) {
+          const uint32_t acc = tc & 1u;
+          const uint32_t aphase = (tc >> 1) & 1u;
+          if (!mbar_wait(tempty_bar + acc * 8, aphase ^ 1u)) {
+            k2_raise(p.status, TOME_DEV_TIMEOUT);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t d_tmem = tmem_base + acc * K2_BN;
+          for (int32_t kb = 0; kb < p.k_blocks; ++kb, ++it) {
+            const uint32_t stage = it % K2_STAGES;
+            const uint32_t phase = (it / K2_STAGES) & 1u;
+            if (!mbar_wait(full_bar + stage * 8, phase)) {
+              k2_raise(p.status, TOME_DEV_TIMEOUT);
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            const uint32_t sa = base + stage * K2_STAGE_BYTES;
+            const uint64_t da = k2_smem_desc(sa);
+            const uint64_t db = k2_smem_desc(sa + K2_A_BYTES);
+#pragma unroll
+            for (int k = 0; k < K2_BK / 16; ++k) {
+              // 16 bf16 = 32 bytes further along K inside the swizzle row: +2 in 16-byte units
+              umma_bf16_ss(d_tmem, da + static_cast<uint64_t>(k * 2),
+                           db + static_cast<uint64_t>(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(empty_bar + stage * 8);  // frees the stage once these MMAs have read it
+          }
+          if (ok) umma_commit(tfull_bar + acc * 8);  // accumulator complete
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+    uint32_t tc = 0;
+    bool ok = true;
+    const float c = p.c;
+    for (int64_t i = blockIdx.x; i < p.n_items && ok; i += gridDim.x) {
+      const K2Item item = k2_decode(p, i);
+      const int64_t row = static_cast<int64_t>(item.mt) * K2_BM + q * 32 + lane;
+      const bool row_ok = row < p.rows;
+      int64_t tloc = -1;  // target column local to this shard, -1 if not owned
+      if (row_ok) {
+        const int64_t t = p.targets[row];
+        if (p.vocab_check > 0 && (t < 0 || t >= p.vocab_check) && item.band == 0)
+          k2_raise(p.status, TOME_DEV_TARGET_OUT_OF_RANGE);
+        const int64_t l = t - p.vocab_offset;
+        if (l >= 0 && l < p.vocab_local) tloc = l;
+      }
+      float m = -FLT_MAX, mc = -FLT_MAX, s = 0.0f, xt = 0.0f;
+      for (int32_t n = item.n_begin; n < item.n_end && ok; ++n, ++tc) {
+        const uint32_t acc = tc & 1u;
+        const uint32_t aphase = (tc >> 1) & 1u;
+        if (!mbar_wait(tfull_bar + acc * 8, aphase)) {
+          k2_raise(p.status, TOME_DEV_TIMEOUT);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const int64_t col0 = static_cast<int64_t>(n) * K2_BN;
+        const int32_t n_valid =
+            static_cast<int32_t>(min(static_cast<int64_t>(K2_BN), p.vocab_local - col0));
+        const int32_t n_chunks = (n_valid + 31) >> 5;
+        const uint32_t taddr = tmem_base + lane_base + acc * K2_BN;
+        const int64_t trel = tloc - col0;  // target column relative to this tile
+
+        uint32_t buf[2][32];
+        tmem_ld32(taddr, buf[0]);
+#pragma unroll
+        for (int ch = 0; ch < K2_BN / 32; ++ch) {
+          if (ch < n_chunks) {
+            tmem_ld_wait_dep(buf[ch & 1]);
+            if (ch + 1 < n_chunks) tmem_ld32(taddr + (ch + 1) * 32, buf[(ch + 1) & 1]);
+            uint32_t(&v)[32] = buf[ch & 1];
+            const int32_t valid = n_valid - ch * 32;
+            if (valid < 32) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j >= valid) v[j] = 0xff800000u;  // -inf: columns past the vocabulary
+            }
+            // target pick (rare: only when some row of the warp has its target in this chunk)
+            const int64_t tj = trel - ch * 32;
+            const bool mine = (tj >= 0) && (tj < 32);
+            if (__any_sync(0xffffffffu, mine)) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (mine && tj == j) xt = __uint_as_float(v[j]);
+            }
+            float cmax = fmax3(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]));
+#pragma unroll
+            for (int j = 3; j + 1 < 32; j += 2)
+              cmax = fmax3(cmax, __uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+            cmax = fmaxf(cmax, __uint_as_float(v[31]));
+            if (cmax > m) {
+              s *= ex2f((m - cmax) * c);
+              m = cmax;
+              mc = cmax * c;
+            }
+            const float nmc = -mc;
+            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              a0 += ex2f(fmaf(__uint_as_float(v[j]), c, nmc));
+              a1 += ex2f(fmaf(__uint_as_float(v[j + 1]), c, nmc));
+              a2 += ex2f(fmaf(__uint_as_float(v[j + 2]), c, nmc));
+              a3 += ex2f(fmaf(__uint_as_float(v[j + 3]), c, nmc));
+            }
+            s += (a0 + a1) + (a2 + a3);
+          }
+        }
+        // accumulator drained: hand it back to the MMA warp
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar + acc * 8);
+      }
+      if (row_ok && ok) {
+        const int64_t o = static_cast<int64_t>(item.band) * p.rows + row;
+        p.part_m[o] = __fdiv_rn(m, p.temp);
+        p.part_s[o] = s;
+        p.part_t[o] = (tloc >= 0) ? __fdiv_rn(xt, p.temp) : 0.0f;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, K2_TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, looked up through the runtime so that the library has no
+// link-time dependency on libcuda (it must load on machines without a driver).
+static int32_t get_encoder(EncodeTiledFn* out) {
+  static std::mutex mu;
+  static EncodeTiledFn fn = nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    int32_t st = check_cuda(
+        cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres),
+        "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+    if (st != TOME_OK) return st;
+    if (sym == nullptr || qres != cudaDriverEntryPointSuccess)
+      return fail(TOME_ERR_CUDA, "cuTensorMapEncodeTiled is not available in this driver");
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  *out = fn;
+  return TOME_OK;
+}
+
+// Row-major bf16 matrix [n_rows, k] with k contiguous; box = 64 columns x box_rows rows.
+static int32_t make_tmap(CUtensorMap* map, const void* ptr, int64_t n_rows, int64_t k,
+                         int box_rows) {
+  EncodeTiledFn enc;
+  int32_t st = get_encoder(&enc);
+  if (st != TOME_OK) return st;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(n_rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(K2_BK), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims,
+                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(TOME_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return TOME_OK;
+}
+
+struct K2Plan {
+  int32_t m_tiles, n_tiles, k_blocks, nb, n_bands, gm;
+  int64_t n_items;
+};
+
+static K2Plan k2_plan(int64_t rows, int64_t k, int64_t vocab_local) {
+  K2Plan pl;
+  pl.m_tiles = static_cast<int32_t>((rows + K2_BM - 1) / K2_BM);
+  pl.n_tiles = static_cast<int32_t>((vocab_local + K2_BN - 1) / K2_BN);
+  pl.k_blocks = static_cast<int32_t>((k + K2_BK - 1) / K2_BK);
+  // band: about 16 MB of weight rows, between 2 and 32 column tiles
+  const int64_t tile_bytes = static_cast<int64_t>(K2_BN) * k * 2;
+  int64_t nb = (16ll << 20) / std::max<int64_t>(tile_bytes, 1);
+  nb = std::max<int64_t>(2, std::min<int64_t>(32, nb));
+  pl.nb = static_cast<int32_t>(std::min<int64_t>(nb, pl.n_tiles));
+  pl.n_bands = (pl.n_tiles + pl.nb - 1) / pl.nb;
+  // row-tile group: hidden tiles of a group stay in L2 (about 40 MB)
+  const int64_t a_bytes = static_cast<int64_t>(K2_BM) * k * 2;
+  int64_t gm = (40ll << 20) / std::max<int64_t>(a_bytes, 1);
+  gm = std::max<int64_t>(1, gm);
+  if (gm < pl.m_tiles) {
+    if (gm >= 148) gm = 148;
+    else if (gm >= 74) gm = 74;
+    else if (gm >= 37) gm = 37;
+  } else {
+    gm = pl.m_tiles;
+  }
+  pl.gm = static_cast<int32_t>(gm);
+  pl.n_items = static_cast<int64_t>(pl.m_tiles) * pl.n_bands;
+  return pl;
+}
+
+static int32_t k2_check(const void* hidden, const void* weight, int64_t rows, int64_t k,
+                        int64_t vocab_local, int64_t vocab_offset, const int32_t* targets,
+                        float temperature, const void* workspace, size_t ws_bytes) {
+  if (rows < 0 || k <= 0 || vocab_local <= 0 || vocab_offset < 0)
+    return fail(TOME_ERR_BAD_SHAPE, "rows=%lld hidden_dim=%lld vocab_local=%lld vocab_offset=%lld",
+                (long long)rows, (long long)k, (long long)vocab_local, (long long)vocab_offset);
+  if (k % 8 != 0)
+    return fail(TOME_ERR_UNSUPPORTED, "hidden_dim=%lld must be a multiple of 8 (16-byte rows)",
+                (long long)k);
+  if (rows > 0x7fffffffLL || vocab_local > 0x7fffffffLL || k > 0x7fffffffLL)
+    return fail(TOME_ERR_TOO_LARGE, "a dimension exceeds int32");
+  if (!temperature_ok(temperature))
+    return fail(TOME_ERR_BAD_TEMPERATURE, "temperature=%g must be > 0 and finite", temperature);
+  if (rows == 0) return TOME_OK;
+  if (hidden == nullptr || weight == nullptr || targets == nullptr || workspace == nullptr)
+    return fail(TOME_ERR_NULL_POINTER, "a required pointer is NULL");
+  if (!aligned16(hidden) || !aligned16(weight) || !aligned16(workspace))
+    return fail(TOME_ERR_MISALIGNED, "hidden, weight and workspace must be 16-byte aligned");
+  const size_t need = tome_lmhead_workspace_bytes(rows, k, vocab_local);
+  if (ws_bytes < need)
+    return fail(TOME_ERR_WORKSPACE_TOO_SMALL, "workspace has %zu bytes, need %zu", ws_bytes, need);
+  return TOME_OK;
+}
+
+// Launches the GEMM+reduce kernel; partial triples land in the workspace.
+static int32_t k2_launch(const void* hidden, const void* weight, int64_t rows, int64_t k,
+                         int64_t vocab_local, int64_t vocab_offset, int64_t vocab_check,
+                         const int32_t* targets, float temperature, void* workspace,
+                         int32_t* dev_status, cudaStream_t stream, K2Plan* plan_out) {
+  DeviceInfo info;
+  int32_t st = current_device_info(&info);
+  if (st != TOME_OK) return st;
+  if (info.cc_major != 10)
+    return fail(TOME_ERR_UNSUPPORTED, "the fused LM head needs an sm_100 device (found sm_%d*)",
+                info.cc_major * 10);
+  const K2Plan pl = k2_plan(rows, k, vocab_local);
+  *plan_out = pl;
+  CUtensorMap ta, tb;
+  st = make_tmap(&ta, hidden, rows, k, K2_BM);
+  if (st != TOME_OK) return st;
+  st = make_tmap(&tb, weight, vocab_local, k, K2_BN);
+  if (st != TOME_OK) return st;
+  K2Params p = {};
+  p.rows = rows;
+  p.k_dim = k;
+  p.vocab_local = vocab_local;
+  p.vocab_offset = vocab_offset;
+  p.vocab_check = vocab_check;
+  p.targets = targets;
+  p.c = LOG2E / temperature;
+  p.temp = temperature;
+  float* ws = static_cast<float*>(workspace);
+  const int64_t plane = static_cast<int64_t>(pl.n_bands) * rows;
+  p.part_m = ws;
+  p.part_s = ws + plane;
+  p.part_t = ws + 2 * plane;
+  p.m_tiles = pl.m_tiles;
+  p.n_tiles = pl.n_tiles;
+  p.k_blocks = pl.k_blocks;
+  p.nb = pl.nb;
+  p.n_bands = pl.n_bands;
+  p.gm = pl.gm;
+  p.n_items = pl.n_items;
+  p.status = dev_status;
+  st = check_cuda(cudaFuncSetAttribute(k2_lmhead_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, K2_SMEM_BYTES),
+                  "cudaFuncSetAttribute(k2)");
+  if (st != TOME_OK) return st;
+  const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(info.sm_count, pl.n_items)));
+  k2_lmhead_kernel<<<grid, K2_THREADS, K2_SMEM_BYTES, stream>>>(ta, tb, p);
+  return check_cuda(cudaGetLastError(), "k2 launch");
+}
+
+}  // namespace tome
+
+using namespace tome;
+
+extern "C" size_t tome_lmhead_workspace_bytes(int64_t rows, int64_t hidden_dim,
+                                              int64_t vocab_local) {
+  if (rows <= 0 || hidden_dim <= 0 || vocab_local <= 0) return 0;
+  const K2Plan pl = k2_plan(rows, hidden_dim, vocab_local);
+  return static_cast<size_t>(3) * pl.n_bands * rows * sizeof(float);
+}
+
+extern "C" int32_t tome_lmhead_partials(const void* hidden, const void* weight, int64_t rows,
+                                        int64_t hidden_dim, int64_t vocab_local,
+                                        int64_t vocab_offset, const int32_t* targets,
+                                        float temperature, float* out_m, float* out_s,
+                                        float* out_t, void* workspace, size_t workspace_bytes,
+                                        int32_t* dev_status, void* stream) {
+  int32_t st = k2_check(hidden, weight, rows, hidden_dim, vocab_local, vocab_offset, targets,
+                        temperature, workspace, workspace_bytes);
+  if (st != TOME_OK || rows == 0) return st;
+  if (out_m == nullptr || out_s == nullptr || out_t == nullptr)
+    return fail(TOME_ERR_NULL_POINTER, "an output pointer is NULL");
+  K2Plan pl;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  st = k2_launch(hidden, weight, rows, hidden_dim, vocab_local, vocab_offset, 0, targets,
+                 temperature, workspace, dev_status, s, &pl);
+  if (st != TOME_OK) return st;
+  const float* ws = static_cast<const float*>(workspace);
+  const int64_t plane = static_cast<int64_t>(pl.n_bands) * rows;
+  return launch_combine(false, ws, ws + plane, rows, pl.n_bands, ws + 2 * plane, rows, pl.n_bands,
+                        rows, out_m, out_s, out_t, s);
+}
+
+extern "C" int32_t tome_lmhead_logprob(const void* hidden, const void* weight, int64_t rows,
+                                       int64_t hidden_dim, int64_t vocab, const int32_t* targets,
+                                       float temperature, float* out_logprob, float* out_lse,
+                                       void* workspace, size_t workspace_bytes,
+                                       int32_t* dev_status, void* stream) {
+  int32_t st = k2_check(hidden, weight, rows, hidden_dim, vocab, 0, targets, temperature,
+                        workspace, workspace_bytes);
+  if (st != TOME_OK || rows == 0) return st;
+  if (out_logprob == nullptr) return fail(TOME_ERR_NULL_POINTER, "out_logprob is NULL");
+  K2Plan pl;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  st = k2_launch(hidden, weight, rows, hidden_dim, vocab, 0, vocab, targets, temperature,
+                 workspace, dev_status, s, &pl);
+  if (st != TOME_OK) return st;
+  const float* ws = static_cast<const float*>(workspace);
+  const int64_t plane = static_cast<int64_t>(pl.n_bands) * rows;
+  return launch_combine(true, ws, ws + plane, rows, pl.n_bands, ws + 2 * plane, rows, pl.n_bands,
+                        rows, out_logprob, out_lse, nullptr, s);
+}

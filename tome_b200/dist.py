@@ -1,0 +1,71 @@
+"""Vocab-parallel LM head: each rank owns a row shard of the weight matrix.
+
+One process per GPU.  Rank r holds weight rows ``[vocab_offset, vocab_offset + V_local)``;
+hidden states and targets are replicated.  Every rank reduces its shard to a per-row triple
+``(m, s, t)`` with the fused kernel, the triples are exchanged with ONE ``all_reduce`` over
+a zero-padded packed buffer (NCCL over NVLink on GPUs), and a merge kernel forms the
+log-probs on every rank.  The reference has no sharded head (it serves one model per
+process, mlx-impl/node.py:966-970); parity is defined against the unsharded result.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import ops
+
+
+def pack_triples(m: torch.Tensor, s: torch.Tensor, t: torch.Tensor, rank: int, world: int,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Packed exchange buffer ``[2*world + 1, rows]`` of one rank.
+
+    Row ``rank`` holds ``m``, row ``world + rank`` holds ``s``, the last row holds ``t``; all
+    other rows are zero, so that a SUM all-reduce leaves every rank with every shard's
+    ``(m, s)`` pair and with the target logit (only the owning shard contributes a non-zero).
+    """
+    rows = m.shape[0]
+    if out is None:
+        out = torch.zeros((2 * world + 1, rows), dtype=torch.float32, device=m.device)
+    else:
+        out.zero_()
+    out[rank].copy_(m)
+    out[world + rank].copy_(s)
+    out[2 * world].copy_(t)
+    return out
+
+
+def exchange_triples(packed: torch.Tensor, group=None):
+    """The single collective of the path: SUM all-reduce of the packed buffer, in place.
+
+    Returns views ``(m_all [world, rows], s_all [world, rows], t_sum [1, rows])``.
+    """
+    world = (packed.shape[0] - 1) // 2
+    if world > 1:
+        dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
+    return packed[:world], packed[world:2 * world], packed[2 * world:]
+
+
+def lm_head_logprob_vocab_parallel(hidden: torch.Tensor, weight_shard: torch.Tensor,
+                                   vocab_offset: int, ids: torch.Tensor, temp: float = 1.0,
+                                   group=None, *, workspace: Optional[torch.Tensor] = None,
+                                   packed: Optional[torch.Tensor] = None):
+    """``(logprob, lse)`` of ``ids`` under the full-vocabulary softmax, head sharded by rows.
+
+    ``weight_shard`` is this rank's ``[V_local, K]`` slice starting at global row
+    ``vocab_offset``; ``ids`` are global indices.  All ranks of ``group`` must call this with
+    the same ``hidden``/``ids``.  ``packed`` may be a reusable ``[2*world+1, rows]`` fp32 buffer.
+    """
+    if dist.is_available() and dist.is_initialized():
+        world = dist.get_world_size(group)
+        rank = dist.get_rank(group)
+    else:
+        world, rank = 1, 0
+    m, s, t = ops.lm_head_partials(hidden, weight_shard, vocab_offset, ids, temp,
+                                   workspace=workspace)
+    buf = pack_triples(m, s, t, rank, world, out=packed)
+    m_all, s_all, t_sum = exchange_triples(buf, group)
+    lp, lse = ops.combine_triples(m_all.contiguous(), s_all.contiguous(), t_sum.contiguous())
+    lead = hidden.shape[:-1]
+    return lp.reshape(lead), lse.reshape(lead)

@@ -1,0 +1,344 @@
+"""Host-side mirror of the reference's log-prob interface, over the C ABI.
+
+Every function takes torch CUDA tensors, passes raw device pointers to ``libtome_b200.so``
+and launches on torch's current stream.  torch is used for memory and streams only; the
+arithmetic happens in the library's kernels and nowhere else (CPU tensors are rejected).
+
+Reference call sites mirrored here
+  * ``fused_log_softmax(logits, temperature=1.0)``      mlx-impl/model.py:77-89
+  * ``local_compute_logprobs(logits, ids, temp)``        mlx-impl/node.py:400-404
+  * ``x @ embed_tokens.weight.T`` then the above         mlx-impl/model.py:538
+  * ``temperature or 1.0`` (greedy decoding scores at temperature 1)
+                                                         mlx-impl/node.py:331,356,451,558,590
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import TOME_BF16, TOME_F32, TomeRuntimeError, check, lib
+
+_DTYPES = {torch.float32: TOME_F32, torch.bfloat16: TOME_BF16}
+_status_words: dict = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    word = _status_words.get(key)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[key] = word
+    return word
+
+
+def check_device_status(device=None) -> None:
+    """Read (and clear) the device status word; raise if a kernel reported a problem.
+
+    Kernels never trap.  A target index outside the vocabulary or a bounded wait that ran
+    out is recorded in a device word instead, which this call inspects.  It synchronises
+    with the device, so the hot calls do not do it on their own unless ``check=True``.
+    """
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = _status_word(device)
+    bits = int(word.item())
+    if bits == 0:
+        return
+    word.zero_()
+    problems = []
+    if bits & _lib.DEV_TARGET_OUT_OF_RANGE:
+        problems.append("a target index lies outside [0, vocab)")
+    if bits & _lib.DEV_TIMEOUT:
+        problems.append("a bounded device-side wait ran out (TOME_DEV_TIMEOUT)")
+    raise TomeRuntimeError("; ".join(problems) or f"device status {bits}")
+
+
+def _require_cuda(name: str, t: torch.Tensor) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor, got {type(t).__name__}")
+    if not t.is_cuda:
+        raise TomeRuntimeError(
+            f"{name} lives on {t.device}: tome_b200 runs on CUDA devices only (no CPU fallback)")
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"logits must be float32 or bfloat16, got {t.dtype}") from None
+
+
+def _rows_view(logits: torch.Tensor) -> Tuple[torch.Tensor, int]:
+    """[..., V] -> 2-D [rows, V] whose last dim is contiguous; returns (view, row stride)."""
+    if logits.dim() == 0:
+        raise ValueError("logits needs at least one dimension")
+    V = logits.shape[-1]
+    if logits.dim() == 2 and logits.stride(1) == 1 and logits.stride(0) >= V:
+        return logits, logits.stride(0)
+    flat = logits.reshape(-1, V)
+    if flat.numel() and (flat.stride(1) != 1 or flat.stride(0) < V):
+        flat = flat.contiguous()
+    return flat, (flat.stride(0) if flat.shape[0] > 1 else max(V, 1))
+
+
+def _ids32(ids: torch.Tensor, n: int, device: torch.device) -> torch.Tensor:
+    if not isinstance(ids, torch.Tensor):
+        ids = torch.as_tensor(ids)
+    if ids.is_floating_point():
+        raise TypeError("token ids must be an integer tensor")
+    ids = ids.reshape(-1)
+    if ids.numel() != n:
+        raise ValueError(f"expected {n} token ids, got {ids.numel()}")
+    if ids.device != device:
+        ids = ids.to(device, non_blocking=True)
+    if ids.dtype != torch.int32:
+        ids = ids.to(torch.int32)
+    return ids.contiguous()
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def selective_log_softmax(logits: torch.Tensor, ids: torch.Tensor, temp: float = 1.0, *,
+                          return_lse: bool = False, return_target_logit: bool = False,
+                          check: bool = False):
+    """Log-probability of ``ids[i]`` under ``softmax(logits[i] / temp)``, fp32, one pass.
+
+    Same arithmetic as ``local_compute_logprobs`` (mlx-impl/node.py:400-404): logits are
+    up-cast to fp32, divided by ``temp``, reduced with a max-shifted logsumexp, and the target
+    column is gathered.  ``logits`` is ``[..., V]`` in bf16 or fp32, ``ids`` has the leading
+    shape.  ``temp`` of 0 or None means 1.0, as at the reference call sites.
+    """
+    _require_cuda("logits", logits)
+    temp = float(temp or 1.0)
+    flat, stride = _rows_view(logits)
+    rows, V = flat.shape
+    device = flat.device
+    ids32 = _ids32(ids, rows, device)
+    out = torch.empty(rows, dtype=torch.float32, device=device)
+    lse = torch.empty(rows, dtype=torch.float32, device=device) if return_lse else None
+    raw = torch.empty(rows, dtype=torch.float32, device=device) if return_target_logit else None
+    with torch.cuda.device(device):
+        status = lib.tome_selective_logprob(
+            flat.data_ptr(), _dtype_code(flat), rows, V, stride, ids32.data_ptr(), temp,
+            out.data_ptr(), _ptr(lse), _ptr(raw), _status_word(device).data_ptr(), _stream(device))
+    _lib.check(status)
+    if check:
+        check_device_status(device)
+    lead = logits.shape[:-1]
+    result = [out.reshape(lead)]
+    if return_lse:
+        result.append(lse.reshape(lead))
+    if return_target_logit:
+        result.append(raw.reshape(lead))
+    return result[0] if len(result) == 1 else tuple(result)
+
+
+def local_compute_logprobs(logits: torch.Tensor, ids: torch.Tensor, temp: float) -> torch.Tensor:
+    """Drop-in for the closure of the same name in mlx-impl/node.py:400-404."""
+    return selective_log_softmax(logits, ids, temp)
+
+
+def local_compute_logprobs_host(logits_host: torch.Tensor, ids_host: torch.Tensor, temp: float,
+                                device=None, staging: Optional[dict] = None) -> torch.Tensor:
+    """Host-buffer form of :func:`local_compute_logprobs`: host logits in, host fp32 out.
+
+    Copies the (ideally pinned) host logits and ids to the device, runs the kernel and
+    copies the log-probs back; this is the call an integration makes when the logits live
+    in host memory.  ``staging`` may hold reusable device/pinned buffers between calls.
+    """
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    staging = {} if staging is None else staging
+    key = (tuple(logits_host.shape), logits_host.dtype)
+    if staging.get("key") != key:
+        staging["key"] = key
+        staging["logits"] = torch.empty(logits_host.shape, dtype=logits_host.dtype, device=device)
+        staging["ids"] = torch.empty(ids_host.shape, dtype=torch.int32, device=device)
+        staging["out"] = torch.empty(ids_host.shape, dtype=torch.float32).pin_memory()
+    staging["logits"].copy_(logits_host, non_blocking=True)
+    staging["ids"].copy_(ids_host.to(torch.int32), non_blocking=True)
+    lp = selective_log_softmax(staging["logits"], staging["ids"], temp)
+    staging["out"].copy_(lp, non_blocking=True)
+    torch.cuda.current_stream(device).synchronize()
+    return staging["out"]
+
+
+def fused_log_softmax(logits: torch.Tensor, temperature: float = 1.0, *,
+                      targets: Optional[torch.Tensor] = None, check: bool = False) -> torch.Tensor:
+    """Drop-in for ``fused_log_softmax`` of mlx-impl/model.py:77-89.
+
+    Without ``targets`` it returns the full ``[..., V]`` log-softmax in the dtype of
+    ``logits`` with the Metal kernel's order of operations (scale by ``1/temperature``, round
+    to the dtype, subtract the rounded logsumexp).  With ``targets`` it returns only the fp32
+    log-probs of those columns, which turns the call sites' ``lp[b, token]`` pattern
+    (mlx-impl/node.py:590-605) into one call that never writes the matrix.
+    """
+    if targets is not None:
+        return selective_log_softmax(logits, targets, temperature, check=check)
+    _require_cuda("logits", logits)
+    temperature = float(temperature or 1.0)
+    flat, stride = _rows_view(logits)
+    rows, V = flat.shape
+    device = flat.device
+    out = torch.empty((rows, V), dtype=flat.dtype, device=device)
+    with torch.cuda.device(device):
+        status = lib.tome_log_softmax_full(
+            flat.data_ptr(), _dtype_code(flat), rows, V, stride, temperature, out.data_ptr(), V,
+            None, _status_word(device).data_ptr(), _stream(device))
+    _lib.check(status)
+    if check:
+        check_device_status(device)
+    return out.reshape(logits.shape)
+
+
+def grpo_dual_logprob_kl(policy_logits: torch.Tensor, ref_logits: torch.Tensor,
+                         ids: torch.Tensor, lengths: torch.Tensor, temp: float = 1.0, *,
+                         starts: Optional[torch.Tensor] = None, check: bool = False):
+    """Policy and reference log-probs of a ragged window per sequence, plus the k3 KL.
+
+    ``policy_logits`` and ``ref_logits`` are ``[n_seq, seq_len, V]``; ``ids`` is
+    ``[n_seq, seq_len]``; ``lengths`` (and optional ``starts``) give the scored window
+    ``[start, start + length)`` of each sequence, the completion slice of
+    mlx-impl/node.py:446-451.  Returns ``(lp_policy, lp_ref, kl)``, fp32 ``[n_seq, seq_len]``,
+    zero outside the windows, with ``kl = exp(r - p) - (r - p) - 1``.  Rows outside the
+    windows are never read.
+    """
+    _require_cuda("policy_logits", policy_logits)
+    _require_cuda("ref_logits", ref_logits)
+    if policy_logits.shape != ref_logits.shape or policy_logits.dtype != ref_logits.dtype:
+        raise ValueError("policy_logits and ref_logits must agree in shape and dtype")
+    if policy_logits.dim() != 3:
+        raise ValueError("expected logits of shape [n_seq, seq_len, V]")
+    temp = float(temp or 1.0)
+    n_seq, seq_len, V = policy_logits.shape
+    device = policy_logits.device
+    pol = policy_logits if policy_logits.is_contiguous() else policy_logits.contiguous()
+    ref = ref_logits if ref_logits.is_contiguous() else ref_logits.contiguous()
+    ids32 = _ids32(ids, n_seq * seq_len, device)
+    len32 = _ids32(lengths, n_seq, device)
+    st32 = None if starts is None else _ids32(starts, n_seq, device)
+    outs = [torch.empty((n_seq, seq_len), dtype=torch.float32, device=device) for _ in range(3)]
+    with torch.cuda.device(device):
+        status = lib.tome_dual_logprob_kl(
+            pol.data_ptr(), ref.data_ptr(), _dtype_code(pol), n_seq, seq_len, V, V,
+            ids32.data_ptr(), len32.data_ptr(), _ptr(st32), temp, outs[0].data_ptr(),
+            outs[1].data_ptr(), outs[2].data_ptr(), _status_word(device).data_ptr(),
+            _stream(device))
+    _lib.check(status)
+    if check:
+        check_device_status(device)
+    return tuple(outs)
+
+
+def lm_head_workspace_bytes(rows: int, hidden_dim: int, vocab_local: int) -> int:
+    """Scratch bytes the fused LM-head kernels need for these sizes."""
+    return int(lib.tome_lmhead_workspace_bytes(rows, hidden_dim, vocab_local))
+
+
+def _lm_head_inputs(hidden: torch.Tensor, weight: torch.Tensor):
+    _require_cuda("hidden", hidden)
+    _require_cuda("weight", weight)
+    if hidden.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise TypeError("hidden and weight must be bfloat16")
+    if weight.dim() != 2 or hidden.shape[-1] != weight.shape[1]:
+        raise ValueError(f"hidden [..., K] and weight [V, K] disagree: {tuple(hidden.shape)} "
+                         f"vs {tuple(weight.shape)}")
+    h2 = hidden.reshape(-1, hidden.shape[-1])
+    if not h2.is_contiguous():
+        h2 = h2.contiguous()
+    w2 = weight if weight.is_contiguous() else weight.contiguous()
+    return h2, w2
+
+
+def _workspace(nbytes: int, device: torch.device, workspace: Optional[torch.Tensor]) -> torch.Tensor:
+    if workspace is not None:
+        if workspace.device != device or workspace.numel() * workspace.element_size() < nbytes:
+            raise ValueError(f"workspace must be a CUDA tensor of at least {nbytes} bytes on {device}")
+        return workspace
+    return torch.empty(max(nbytes, 16), dtype=torch.uint8, device=device)
+
+
+def lm_head_partials(hidden: torch.Tensor, weight_shard: torch.Tensor, vocab_offset: int,
+                     ids: torch.Tensor, temp: float = 1.0, *,
+                     workspace: Optional[torch.Tensor] = None):
+    """Per-row triple ``(m, s, t)`` of one vocabulary shard of the LM head (fp32 ``[rows]`` each).
+
+    ``m = max_j(x_j)/temp``, ``s = sum_j exp(x_j/temp - m)``, ``t = x_target/temp`` if the
+    shard owns the target else 0, for ``x = hidden @ weight_shard.T``; no logits are stored.
+    ``ids`` are global vocabulary indices; ``vocab_offset`` is the global index of shard row 0.
+    """
+    h2, w2 = _lm_head_inputs(hidden, weight_shard)
+    temp = float(temp or 1.0)
+    rows, K = h2.shape
+    V_local = w2.shape[0]
+    device = h2.device
+    ids32 = _ids32(ids, rows, device)
+    nbytes = lm_head_workspace_bytes(rows, K, V_local)
+    ws = _workspace(nbytes, device, workspace)
+    m, s, t = (torch.empty(rows, dtype=torch.float32, device=device) for _ in range(3))
+    with torch.cuda.device(device):
+        status = lib.tome_lmhead_partials(
+            h2.data_ptr(), w2.data_ptr(), rows, K, V_local, int(vocab_offset), ids32.data_ptr(),
+            temp, m.data_ptr(), s.data_ptr(), t.data_ptr(), ws.data_ptr(),
+            ws.numel() * ws.element_size(), _status_word(device).data_ptr(), _stream(device))
+    _lib.check(status)
+    return m, s, t
+
+
+def lm_head_logprob(hidden: torch.Tensor, weight: torch.Tensor, ids: torch.Tensor,
+                    temp: float = 1.0, *, workspace: Optional[torch.Tensor] = None,
+                    check: bool = False):
+    """``(logprob, lse)`` of ``ids`` under ``softmax((hidden @ weight.T) / temp)``, fused.
+
+    Replaces the LM head matmul (mlx-impl/model.py:538) followed by
+    ``local_compute_logprobs`` (mlx-impl/node.py:400-404); the ``[rows, V]`` logits never
+    exist in memory.  ``hidden`` is ``[..., K]`` bf16, ``weight`` ``[V, K]`` bf16 (the tied
+    embedding), outputs are fp32 with the leading shape of ``hidden``.
+    """
+    h2, w2 = _lm_head_inputs(hidden, weight)
+    temp = float(temp or 1.0)
+    rows, K = h2.shape
+    V = w2.shape[0]
+    device = h2.device
+    ids32 = _ids32(ids, rows, device)
+    nbytes = lm_head_workspace_bytes(rows, K, V)
+    ws = _workspace(nbytes, device, workspace)
+    lp = torch.empty(rows, dtype=torch.float32, device=device)
+    lse = torch.empty(rows, dtype=torch.float32, device=device)
+    with torch.cuda.device(device):
+        status = lib.tome_lmhead_logprob(
+            h2.data_ptr(), w2.data_ptr(), rows, K, V, ids32.data_ptr(), temp, lp.data_ptr(),
+            lse.data_ptr(), ws.data_ptr(), ws.numel() * ws.element_size(),
+            _status_word(device).data_ptr(), _stream(device))
+    _lib.check(status)
+    if check:
+        check_device_status(device)
+    lead = hidden.shape[:-1]
+    return lp.reshape(lead), lse.reshape(lead)
+
+
+def combine_triples(m: torch.Tensor, s: torch.Tensor, t: torch.Tensor):
+    """Merge per-part triples: ``m``, ``s`` are ``[parts, rows]``; ``t`` is ``[t_parts, rows]``
+    (``t_parts`` = 1 when already summed).  Returns ``(logprob, lse)``, fp32 ``[rows]``."""
+    for name, x in (("m", m), ("s", s), ("t", t)):
+        _require_cuda(name, x)
+        if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous fp32 [parts, rows] tensor")
+    if m.shape != s.shape or t.shape[1] != m.shape[1]:
+        raise ValueError("m, s and t disagree in shape")
+    parts, rows = m.shape
+    device = m.device
+    lp = torch.empty(rows, dtype=torch.float32, device=device)
+    lse = torch.empty(rows, dtype=torch.float32, device=device)
+    with torch.cuda.device(device):
+        status = lib.tome_combine_triples(m.data_ptr(), s.data_ptr(), rows, parts, t.data_ptr(),
+                                          rows, t.shape[0], rows, lp.data_ptr(), lse.data_ptr(),
+                                          _stream(device))
+    _lib.check(status)
+    return lp, lse
