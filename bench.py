@@ -433,6 +433,32 @@ def run_extra(args, device, rank, world, dist_on, barrier, peaks):
     return extra
 
 
+def run_only(args):
+    """One kernel in a loop on one GPU, at a chosen row count: the command ncu captures."""
+    import torch
+    import tome_b200
+    from tome_b200 import synthetic
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    if args.only == "selective":
+        rows = args.rows or ROWS
+        x, ids = synthetic.cfg2_rollout_bf16(rows, VOCAB, device)
+        fn = lambda: tome_b200.local_compute_logprobs(x, ids, 1.0)  # noqa: E731
+        work, unit = rows * VOCAB * 2 + rows * 8, "GB/s"
+    else:
+        rows = args.rows or 16384
+        hidden, weight, ids = synthetic.cfg3_lm_head(rows, 1024, VOCAB, device)
+        ws = torch.empty(tome_b200.lm_head_workspace_bytes(rows, 1024, VOCAB), dtype=torch.uint8,
+                         device=device)
+        fn = lambda: tome_b200.lm_head_logprob(hidden, weight, ids, 1.0, workspace=ws)  # noqa: E731
+        work, unit = 2.0 * rows * VOCAB * 1024, "TFLOP/s"
+    total, per = timed_steps(fn, args.steps, args.warmup, lambda: None)
+    tome_b200.check_device_status(device)
+    ms = sum(per) / len(per)
+    rate = work / ms / (1e6 if unit == "GB/s" else 1e9)
+    print(json.dumps({"only": args.only, "rows": rows, "ms": ms, "rate": rate, "unit": unit}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -441,9 +467,15 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--skip-extra", action="store_true", help="headline workload only")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg")
+    ap.add_argument("--only", choices=["selective", "lmhead"], default=None,
+                    help="profiling aid: run just one kernel's loop (no e2e, extras or CPU leg)")
+    ap.add_argument("--rows", type=int, default=None, help="row count for --only (small cases)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args, int(os.environ.get("RANK", "0")))
+        return
+    if args.only is not None:
+        run_only(args)
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus != world and world == 1 and args.gpus > 1:

@@ -29,7 +29,7 @@ namespace tome {
 
 enum K1Mode { K1_SELECTIVE = 0, K1_DUAL = 1, K1_FULL = 2 };
 
-constexpr int K1_CONSUMER_WARPS = 8;
+constexpr int K1_CONSUMER_WARPS = 16;
 constexpr int K1_CONSUMERS = K1_CONSUMER_WARPS * 32;
 constexpr int K1_THREADS = K1_CONSUMERS + 32;
 constexpr int K1_STAGES = 6;
@@ -59,14 +59,12 @@ struct K1Params {
 
 // ------------------------------------------------------------------ online (max, sum-exp)
 struct Online {
-  float m;   // running maximum of the raw logits
-  float mc;  // m * c
-  float s;   // sum of 2^(x*c - mc)
+  float m;  // running maximum of the raw logits
+  float s;  // sum of 2^((x - m) * c)
 };
 
 __device__ __forceinline__ void online_init(Online& st) {
   st.m = -FLT_MAX;
-  st.mc = -FLT_MAX;
   st.s = 0.0f;
 }
 
@@ -74,7 +72,6 @@ __device__ __forceinline__ void online_raise(Online& st, float vmax, float c) {
   if (vmax > st.m) {
     st.s *= ex2f((st.m - vmax) * c);
     st.m = vmax;
-    st.mc = vmax * c;
   }
 }
 
@@ -90,15 +87,17 @@ __device__ __forceinline__ void online_update(Online& st, uint4 v, float c, __nv
   const __nv_bfloat162 mx = __hmax2(__hmax2(as_bf162(v.x), as_bf162(v.y)),
                                     __hmax2(as_bf162(v.z), as_bf162(v.w)));
   online_raise(st, fmaxf(__low2float(mx), __high2float(mx)), c);
-  const float nmc = -st.mc;
-  const float e0 = ex2f(fmaf(bf16_lo(v.x), c, nmc));
-  const float e1 = ex2f(fmaf(bf16_hi(v.x), c, nmc));
-  const float e2 = ex2f(fmaf(bf16_lo(v.y), c, nmc));
-  const float e3 = ex2f(fmaf(bf16_hi(v.y), c, nmc));
-  const float e4 = ex2f(fmaf(bf16_lo(v.z), c, nmc));
-  const float e5 = ex2f(fmaf(bf16_hi(v.z), c, nmc));
-  const float e6 = ex2f(fmaf(bf16_lo(v.w), c, nmc));
-  const float e7 = ex2f(fmaf(bf16_hi(v.w), c, nmc));
+  // (x - m) is formed first: exact for equal values, so huge-magnitude rows (masks such as
+  // -1e30) cannot cancel catastrophically the way x*c - m*c would.
+  const float m = st.m;
+  const float e0 = ex2f((bf16_lo(v.x) - m) * c);
+  const float e1 = ex2f((bf16_hi(v.x) - m) * c);
+  const float e2 = ex2f((bf16_lo(v.y) - m) * c);
+  const float e3 = ex2f((bf16_hi(v.y) - m) * c);
+  const float e4 = ex2f((bf16_lo(v.z) - m) * c);
+  const float e5 = ex2f((bf16_hi(v.z) - m) * c);
+  const float e6 = ex2f((bf16_lo(v.w) - m) * c);
+  const float e7 = ex2f((bf16_hi(v.w) - m) * c);
   st.s += ((e0 + e1) + (e2 + e3)) + ((e4 + e5) + (e6 + e7));
 }
 
@@ -107,17 +106,17 @@ __device__ __forceinline__ void online_update(Online& st, uint4 v, float c, floa
   const float x0 = __uint_as_float(v.x), x1 = __uint_as_float(v.y);
   const float x2 = __uint_as_float(v.z), x3 = __uint_as_float(v.w);
   online_raise(st, fmaxf(fmaxf(x0, x1), fmaxf(x2, x3)), c);
-  const float nmc = -st.mc;
-  const float e0 = ex2f(fmaf(x0, c, nmc));
-  const float e1 = ex2f(fmaf(x1, c, nmc));
-  const float e2 = ex2f(fmaf(x2, c, nmc));
-  const float e3 = ex2f(fmaf(x3, c, nmc));
+  const float m = st.m;
+  const float e0 = ex2f((x0 - m) * c);
+  const float e1 = ex2f((x1 - m) * c);
+  const float e2 = ex2f((x2 - m) * c);
+  const float e3 = ex2f((x3 - m) * c);
   st.s += (e0 + e1) + (e2 + e3);
 }
 
 __device__ __forceinline__ void online_update_scalar(Online& st, float x, float c) {
   online_raise(st, x, c);
-  st.s += ex2f(fmaf(x, c, -st.mc));
+  st.s += ex2f((x - st.m) * c);
 }
 
 __device__ __forceinline__ float to_float(float x) { return x; }
@@ -132,7 +131,6 @@ __device__ __forceinline__ void online_warp_reduce(Online& st, float c) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
   st.m = m;
-  st.mc = m * c;
   st.s = s;
 }
 

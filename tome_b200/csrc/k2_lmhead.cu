@@ -288,9 +288,12 @@ k2_lmhead_kernel(const __grid_constant__ CUtensorMap tmap_a,
               cmax = fmax3(cmax, __uint_as_float(v[j]), __uint_as_float(v[j + 1]));
             cmax = fmaxf(cmax, __uint_as_float(v[31]));
             if (cmax > m) {
-              s *= ex2f((m - cmax) * c);
+              // s always equals sum 2^(x*c - mc) for the CURRENT rounded mc, so the rescale
+              // uses the difference of the two rounded products
+              const float mc_new = cmax * c;
+              s *= ex2f(mc - mc_new);
               m = cmax;
-              mc = cmax * c;
+              mc = mc_new;
             }
             const float nmc = -mc;
             float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
@@ -311,8 +314,10 @@ k2_lmhead_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       if (row_ok && ok) {
         const int64_t o = static_cast<int64_t>(item.band) * p.rows + row;
+        // exponents were formed as x*c - fl(m*c); fold the rounding residual of m*c back in
+        const float delta = fmaf(m, c, -mc);
         p.part_m[o] = __fdiv_rn(m, p.temp);
-        p.part_s[o] = s;
+        p.part_s[o] = s * ex2f(-delta);
         p.part_t[o] = (tloc >= 0) ? __fdiv_rn(xt, p.temp) : 0.0f;
       }
     }
