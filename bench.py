@@ -247,6 +247,8 @@ def run_ours(args):
     if dist_on:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout
         dist.init_process_group("nccl", device_id=device)
         barrier = lambda: dist.barrier(device_ids=[local])  # noqa: E731
     else:

@@ -3,26 +3,29 @@
 The functions keep the call signatures of the reference's hot path
 (``fused_log_softmax`` in mlx-impl/model.py:77-89 and ``local_compute_logprobs`` in
 mlx-impl/node.py:400-404), with torch CUDA tensors in place of ``mx.array``.
-"""
-from .ops import (  # noqa: F401
-    check_device_status,
-    combine_triples,
-    fused_log_softmax,
-    grpo_dual_logprob_kl,
-    lm_head_logprob,
-    lm_head_partials,
-    lm_head_workspace_bytes,
-    local_compute_logprobs,
-    local_compute_logprobs_host,
-    selective_log_softmax,
-)
-from .dist import lm_head_logprob_vocab_parallel, pack_triples  # noqa: F401
-from ._lib import TomeArgumentError, TomeRuntimeError  # noqa: F401
 
-__all__ = [
-    "fused_log_softmax", "local_compute_logprobs", "selective_log_softmax",
-    "local_compute_logprobs_host", "lm_head_logprob", "lm_head_partials",
-    "lm_head_workspace_bytes", "combine_triples", "grpo_dual_logprob_kl",
-    "lm_head_logprob_vocab_parallel", "pack_triples", "check_device_status",
-    "TomeArgumentError", "TomeRuntimeError",
-]
+The CUDA library is loaded on first use of any of these names, so that
+``python -m tome_b200.build`` can (re)build it even when the existing ``.so`` is stale.
+"""
+import importlib
+
+_OPS = ["check_device_status", "combine_triples", "fused_log_softmax", "grpo_dual_logprob_kl",
+        "lm_head_logprob", "lm_head_logprob_static", "lm_head_partials",
+        "lm_head_workspace_bytes", "local_compute_logprobs", "local_compute_logprobs_host",
+        "selective_log_softmax"]
+_DIST = ["lm_head_logprob_vocab_parallel", "pack_triples", "exchange_triples"]
+_LIB = ["TomeArgumentError", "TomeRuntimeError"]
+
+__all__ = _OPS + _DIST + _LIB
+
+
+def __getattr__(name):
+    if name in _OPS:
+        return getattr(importlib.import_module(".ops", __name__), name)
+    if name in _DIST:
+        return getattr(importlib.import_module(".dist", __name__), name)
+    if name in _LIB:
+        return getattr(importlib.import_module("._lib", __name__), name)
+    if name in ("ops", "dist", "_lib", "synthetic", "build"):
+        return importlib.import_module("." + name, __name__)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
