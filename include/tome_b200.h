@@ -9,7 +9,8 @@
  *
  * Conventions
  *   - every pointer named "device" points to CUDA device memory owned by the caller;
- *     the library allocates nothing and keeps no device state between calls;
+ *     the library allocates nothing and keeps no device state between calls (the one
+ *     exception is the fixed scratch array of tome_lmhead_logprob_static, described there);
  *   - calls are asynchronous on `stream` (a cudaStream_t passed as void*; NULL is the
  *     legacy default stream); no call synchronises the host with the device;
  *   - the return value is a tome_status: 0 = success, negative = an argument was
@@ -149,6 +150,36 @@ int32_t tome_lmhead_logprob(const void* hidden, const void* weight, int64_t rows
                             float temperature, float* out_logprob, float* out_lse,
                             void* workspace, size_t workspace_bytes, int32_t* dev_status,
                             void* stream);
+
+/*
+ * tome_lmhead_logprob without a workspace argument and without any allocation.
+ * (No counterpart in the reference: MLX owns all memory there.)
+ *
+ * Some hosts cannot hand this library a scratch buffer: a serving process whose device
+ * memory is entirely reserved by another framework's pool (so a cudaMalloc of its own would
+ * fail or fragment the pool), a latency-critical loop that must not hit the implicit device
+ * synchronisation of cudaMalloc/cudaFree, or a foreign-language binding that has no device
+ * allocator at all.  For them the partial-triple scratch lives in a fixed array inside the
+ * library's device image, tome_lmhead_static_scratch_bytes() = 8 MiB per GPU that loads
+ * the library, held until the process exits.  Inputs and outputs are still the caller's.
+ *
+ *   - Sizes whose scratch need (tome_lmhead_workspace_bytes) exceeds the array are rejected
+ *     with TOME_ERR_TOO_LARGE; Qwen3-0.6B head shape fits up to 16384 rows per call.
+ *   - The first call on each device looks the array's device address up (with that device
+ *     current) and remembers it; make that first call before any stream capture begins.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.
+ *     Nothing in it has to start at zero (each call overwrites every slot it later reads), but
+ *     two calls that overlap in time on the same GPU (different streams, or different host
+ *     threads) race on it: serialise them on one stream.
+ *   - Calls no cudaMalloc, cudaFree or other allocating routine.
+ * Arguments and results are those of tome_lmhead_logprob.
+ */
+size_t tome_lmhead_static_scratch_bytes(void);
+
+int32_t tome_lmhead_logprob_static(const void* hidden, const void* weight, int64_t rows,
+                                   int64_t hidden_dim, int64_t vocab, const int32_t* targets,
+                                   float temperature, float* out_logprob, float* out_lse,
+                                   int32_t* dev_status, void* stream);
 
 /*
  * Combine per-shard triples into log-probs (the step after the vocab-parallel exchange;

@@ -37,6 +37,10 @@ SIGNATURES = {
     "tome_lmhead_logprob": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p,
                                       c_float, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p,
                                       c_void_p]),
+    "tome_lmhead_static_scratch_bytes": (c_size_t, []),
+    "tome_lmhead_logprob_static": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                             c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+                                             c_void_p]),
     "tome_combine_triples": (c_int32, [c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_int64,
                                        c_int32, c_int64, c_void_p, c_void_p, c_void_p]),
 }

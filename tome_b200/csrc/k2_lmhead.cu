@@ -534,3 +534,61 @@ extern "C" int32_t tome_lmhead_logprob(const void* hidden, const void* weight, i
   return launch_combine(true, ws, ws + plane, rows, pl.n_bands, ws + 2 * plane, rows, pl.n_bands,
                         rows, out_logprob, out_lse, nullptr, s);
 }
+
+// ------------------------------------------------------------------ no-allocation variant
+// Scratch for tome_lmhead_logprob_static: one fixed array in the library's device image.
+// Every GPU that loads the library holds these 8 MiB until the process exits.
+constexpr size_t K2_STATIC_SCRATCH_BYTES = static_cast<size_t>(8) << 20;
+static __device__ __align__(256) unsigned char k2_static_scratch[K2_STATIC_SCRATCH_BYTES];
+
+// Device address of the static scratch on the CURRENT device.  In host code the array's name
+// is only a handle, not a device pointer, so the address is asked for once per device (with
+// that device current) through cudaGetSymbolAddress and remembered.
+static int32_t k2_static_scratch_address(void** out) {
+  constexpr int MAX_DEV = 64;
+  static std::mutex mu;
+  static void* cached[MAX_DEV] = {nullptr};
+  int dev = 0;
+  int32_t st = tome::check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+  if (st != TOME_OK) return st;
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev >= 0 && dev < MAX_DEV && cached[dev] != nullptr) {
+    *out = cached[dev];
+    return TOME_OK;
+  }
+  void* ptr = nullptr;
+  st = tome::check_cuda(cudaGetSymbolAddress(&ptr, k2_static_scratch),
+                        "cudaGetSymbolAddress(k2_static_scratch)");
+  if (st != TOME_OK) return st;
+  if (ptr == nullptr) return tome::fail(TOME_ERR_CUDA, "static scratch has no device address");
+  if (dev >= 0 && dev < MAX_DEV) cached[dev] = ptr;
+  *out = ptr;
+  return TOME_OK;
+}
+
+extern "C" size_t tome_lmhead_static_scratch_bytes(void) { return K2_STATIC_SCRATCH_BYTES; }
+
+extern "C" int32_t tome_lmhead_logprob_static(const void* hidden, const void* weight,
+                                              int64_t rows, int64_t hidden_dim, int64_t vocab,
+                                              const int32_t* targets, float temperature,
+                                              float* out_logprob, float* out_lse,
+                                              int32_t* dev_status, void* stream) {
+  if (rows > 0 && hidden_dim > 0 && vocab > 0) {
+    const size_t need = tome_lmhead_workspace_bytes(rows, hidden_dim, vocab);
+    if (need > K2_STATIC_SCRATCH_BYTES)
+      return fail(TOME_ERR_TOO_LARGE,
+                  "this problem needs %zu bytes of scratch but the built-in scratch holds %zu; "
+                  "use tome_lmhead_logprob with a caller-provided workspace, or fewer rows per call",
+                  need, K2_STATIC_SCRATCH_BYTES);
+  }
+  void* scratch = nullptr;
+  if (rows > 0) {
+    const int32_t st = k2_static_scratch_address(&scratch);
+    if (st != TOME_OK) return st;
+  } else {
+    scratch = reinterpret_cast<void*>(static_cast<uintptr_t>(256));  // never used when rows == 0
+  }
+  return tome_lmhead_logprob(hidden, weight, rows, hidden_dim, vocab, targets, temperature,
+                             out_logprob, out_lse, scratch, K2_STATIC_SCRATCH_BYTES, dev_status,
+                             stream);
+}

@@ -323,6 +323,35 @@ def lm_head_logprob(hidden: torch.Tensor, weight: torch.Tensor, ids: torch.Tenso
     return lp.reshape(lead), lse.reshape(lead)
 
 
+def lm_head_logprob_static(hidden: torch.Tensor, weight: torch.Tensor, ids: torch.Tensor,
+                           temp: float, out_logprob: torch.Tensor,
+                           out_lse: Optional[torch.Tensor] = None) -> None:
+    """:func:`lm_head_logprob` for hosts that cannot allocate device memory around the call.
+
+    Nothing is allocated here or in the library: ``hidden`` ``[rows, K]`` and ``weight``
+    ``[V, K]`` must already be contiguous bf16, ``ids`` contiguous int32 ``[rows]``, and the
+    fp32 outputs ``[rows]`` are written in place.  The kernel's scratch is a fixed 8 MiB
+    array inside the library (see ``tome_lmhead_logprob_static`` in the header), so sizes
+    that need more raise ``TomeArgumentError``; calls on one GPU must not overlap in time.
+    The first call on a device resolves the array's address: make it before stream capture.
+    """
+    for name, t, dt in (("hidden", hidden, torch.bfloat16), ("weight", weight, torch.bfloat16),
+                        ("ids", ids, torch.int32), ("out_logprob", out_logprob, torch.float32)):
+        _require_cuda(name, t)
+        if t.dtype != dt or not t.is_contiguous():
+            raise TypeError(f"{name} must be a contiguous {dt} tensor")
+    if out_lse is not None and (out_lse.dtype != torch.float32 or not out_lse.is_contiguous()):
+        raise TypeError("out_lse must be a contiguous float32 tensor")
+    rows, K = hidden.shape
+    device = hidden.device
+    with torch.cuda.device(device):
+        status = lib.tome_lmhead_logprob_static(
+            hidden.data_ptr(), weight.data_ptr(), rows, K, weight.shape[0], ids.data_ptr(),
+            float(temp or 1.0), out_logprob.data_ptr(), _ptr(out_lse),
+            _status_word(device).data_ptr(), _stream(device))
+    _lib.check(status)
+
+
 def combine_triples(m: torch.Tensor, s: torch.Tensor, t: torch.Tensor):
     """Merge per-part triples: ``m``, ``s`` are ``[parts, rows]``; ``t`` is ``[t_parts, rows]``
     (``t_parts`` = 1 when already summed).  Returns ``(logprob, lse)``, fp32 ``[rows]``."""
