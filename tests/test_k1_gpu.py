@@ -70,6 +70,48 @@ def test_selective_masked_columns_and_constant_rows(cuda_device):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_selective_mask_values_and_extreme_magnitudes(cuda_device, dtype):
+    """Finite mask fills (-1e30, finfo.min, -1e9) over long runs of a row, rows that lie
+    entirely below the streaming floor, and huge positive logits: all must match the oracle."""
+    x, ids = _case(8, 40000, dtype, 14)
+    lowest = torch.finfo(dtype).min
+    x[0, :30000] = -1e30
+    x[1, 5000:] = lowest
+    x[2, ::2] = -1e9
+    x[3, :] = -2.0e6                      # whole row below the floor, constant
+    x[4, :] = -3.0e6
+    x[4, 777] = -2.9e6                    # below the floor with one clear winner
+    x[5, :] = x[5, :] * 1e18              # huge magnitudes of both signs
+    x[6, :] = 1e20
+    x[7, :39000] = lowest
+    x[7, 39000:] = -1e30
+    ids[:] = torch.tensor([35000, 100, 1, 5, 777, 9, 11, 39500], dtype=torch.int32)
+    _check_selective(x, ids, 1.0, cuda_device)
+    _check_selective(x[:5], ids[:5], 0.7, cuda_device)
+
+
+@pytest.mark.parametrize("poly", ["1", "2"])
+def test_selective_polynomial_exp_variants(cuda_device, poly):
+    """The FMA-pipe exp2 variants (TOME_K1_POLY, read once per process) in a child process."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import sys, torch; sys.path.insert(0, %r); sys.path.insert(0, %r)\n"
+        "import tome_b200; from oracle import oracle; from tome_b200 import synthetic\n"
+        "x, ids = synthetic.cfg2_rollout_bf16(rows=300)\n"
+        "lp = tome_b200.local_compute_logprobs(x.cuda(), ids.cuda(), 0.7)\n"
+        "ref, _, _ = oracle.selective_logprob(x, ids, 0.7)\n"
+        "err = float((lp.cpu() - ref).abs().max()); print(err); assert err <= 2e-3\n"
+    ) % (os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+         os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, TOME_K1_POLY=poly)
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True,
+                         timeout=600)
+    assert out.returncode == 0, out.stdout + out.stderr
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_selective_unaligned_views_take_the_plain_kernel(cuda_device, dtype):
     import tome_b200
     x, ids = _case(6, 1003, dtype, 8)

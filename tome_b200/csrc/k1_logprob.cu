@@ -20,7 +20,10 @@
 #include <float.h>
 #include <math.h>
 
+#include <stdlib.h>
+
 #include <algorithm>
+#include <type_traits>
 
 #include "host_common.h"
 #include "ptx.cuh"
@@ -35,6 +38,7 @@ constexpr int K1_THREADS = K1_CONSUMERS + 32;
 constexpr int K1_STAGES = 6;
 constexpr int K1_CHUNK_BYTES = 32768;
 constexpr int K1_MAX_SEQ = 4096;
+constexpr int K1_POLY_DEFAULT = 0;
 
 struct K1Params {
   const void* src[2];      // DUAL: policy, reference
@@ -82,36 +86,105 @@ __device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t w) {
   return *reinterpret_cast<__nv_bfloat162*>(&w);
 }
 
+// ------------------------------------------------------------------ streaming inner loop
+// Inside the streaming loop a thread keeps
+//   m   running maximum of its raw logits, never below K1_M_FLOOR
+//   mc  fl(m * c)
+//   a,b packed partial sums of 2^(x*c - mc), two fp32 lanes each
+// so that one packed FFMA (fma.rn.f32x2) forms two exponents.  The exponent x*c - fl(m*c)
+// differs from (x - m)*c by delta = m*c - fl(m*c), the same for every term of the thread;
+// fast_finish() folds 2^-delta back in exactly.  The floor keeps |mc| small enough for that
+// to work when a thread has so far seen nothing but mask values (-1e30, -FLT_MAX, -inf).
+// Rows whose result is not a positive finite sum (every logit below the floor, or logits
+// beyond ~1e7 in magnitude) are redone by exact_row() with the (x - m) form.
+constexpr float K1_M_FLOOR = -1048576.0f;
+
+struct Fast {
+  float m, mc;
+  float2 a, b;
+};
+
+__device__ __forceinline__ void fast_init(Fast& f, float c) {
+  f.m = K1_M_FLOOR;
+  f.mc = K1_M_FLOOR * c;
+  f.a = make_float2(0.0f, 0.0f);
+  f.b = make_float2(0.0f, 0.0f);
+}
+
+__device__ __forceinline__ void fast_raise(Fast& f, float vmax, float c) {
+  if (vmax > f.m) {
+    const float mc_new = vmax * c;
+    const float r = ex2f(f.mc - mc_new);
+    const float2 r2 = make_float2(r, r);
+    f.a = __fmul2_rn(f.a, r2);
+    f.b = __fmul2_rn(f.b, r2);
+    f.m = vmax;
+    f.mc = mc_new;
+  }
+}
+
+__device__ __forceinline__ Online fast_finish(const Fast& f, float c) {
+  Online st;
+  st.m = f.m;
+  const float delta = fmaf(f.m, c, -f.mc);  // exact residual of the product
+  st.s = ((f.a.x + f.a.y) + (f.b.x + f.b.y)) * ex2f(-delta);
+  return st;
+}
+
+// 2^x for x <= 0 on the FMA pipe (Cody-Waite split + cubic, relative error 7.5e-5), used
+// for a few logits per vector to take load off the exp unit.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -126.0f);
+  const float t = x + 12582912.0f;           // 1.5 * 2^23: low mantissa bits = round(x)
+  const float fr = x - (t - 12582912.0f);    // in [-0.5, 0.5]
+  float p = fmaf(fr, 0.0551716648f, 0.2426111251f);
+  p = fmaf(p, fr, 0.6932609677f);
+  p = fmaf(p, fr, 0.9999280572f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
+template <int POLY>
+__device__ __forceinline__ float2 ex2_pair(float2 t, int slot) {
+  // slot 0 is the first pair of the vector; POLY of its lanes go to the polynomial
+  float2 e;
+  e.x = (POLY >= 1 && slot == 0) ? ex2_poly(t.x) : ex2f(t.x);
+  e.y = (POLY >= 2 && slot == 0) ? ex2_poly(t.y) : ex2f(t.y);
+  return e;
+}
+
 // 8 bf16 logits
-__device__ __forceinline__ void online_update(Online& st, uint4 v, float c, __nv_bfloat16) {
+template <int POLY>
+__device__ __forceinline__ void fast_update(Fast& f, uint4 v, float c, __nv_bfloat16) {
   const __nv_bfloat162 mx = __hmax2(__hmax2(as_bf162(v.x), as_bf162(v.y)),
                                     __hmax2(as_bf162(v.z), as_bf162(v.w)));
-  online_raise(st, fmaxf(__low2float(mx), __high2float(mx)), c);
-  // (x - m) is formed first: exact for equal values, so huge-magnitude rows (masks such as
-  // -1e30) cannot cancel catastrophically the way x*c - m*c would.
-  const float m = st.m;
-  const float e0 = ex2f((bf16_lo(v.x) - m) * c);
-  const float e1 = ex2f((bf16_hi(v.x) - m) * c);
-  const float e2 = ex2f((bf16_lo(v.y) - m) * c);
-  const float e3 = ex2f((bf16_hi(v.y) - m) * c);
-  const float e4 = ex2f((bf16_lo(v.z) - m) * c);
-  const float e5 = ex2f((bf16_hi(v.z) - m) * c);
-  const float e6 = ex2f((bf16_lo(v.w) - m) * c);
-  const float e7 = ex2f((bf16_hi(v.w) - m) * c);
-  st.s += ((e0 + e1) + (e2 + e3)) + ((e4 + e5) + (e6 + e7));
+  const uint32_t mw = *reinterpret_cast<const uint32_t*>(&mx);
+  fast_raise(f, fmaxf(bf16_lo(mw), bf16_hi(mw)), c);
+  const float2 c2 = make_float2(c, c);
+  const float2 n2 = make_float2(-f.mc, -f.mc);
+  const float2 t0 = __ffma2_rn(make_float2(bf16_lo(v.x), bf16_hi(v.x)), c2, n2);
+  const float2 t1 = __ffma2_rn(make_float2(bf16_lo(v.y), bf16_hi(v.y)), c2, n2);
+  const float2 t2 = __ffma2_rn(make_float2(bf16_lo(v.z), bf16_hi(v.z)), c2, n2);
+  const float2 t3 = __ffma2_rn(make_float2(bf16_lo(v.w), bf16_hi(v.w)), c2, n2);
+  const float2 e0 = ex2_pair<POLY>(t0, 0);
+  const float2 e1 = ex2_pair<POLY>(t1, 1);
+  const float2 e2 = ex2_pair<POLY>(t2, 1);
+  const float2 e3 = ex2_pair<POLY>(t3, 1);
+  f.a = __fadd2_rn(f.a, __fadd2_rn(e0, e1));
+  f.b = __fadd2_rn(f.b, __fadd2_rn(e2, e3));
 }
 
 // 4 fp32 logits
-__device__ __forceinline__ void online_update(Online& st, uint4 v, float c, float) {
+template <int POLY>
+__device__ __forceinline__ void fast_update(Fast& f, uint4 v, float c, float) {
   const float x0 = __uint_as_float(v.x), x1 = __uint_as_float(v.y);
   const float x2 = __uint_as_float(v.z), x3 = __uint_as_float(v.w);
-  online_raise(st, fmaxf(fmaxf(x0, x1), fmaxf(x2, x3)), c);
-  const float m = st.m;
-  const float e0 = ex2f((x0 - m) * c);
-  const float e1 = ex2f((x1 - m) * c);
-  const float e2 = ex2f((x2 - m) * c);
-  const float e3 = ex2f((x3 - m) * c);
-  st.s += (e0 + e1) + (e2 + e3);
+  fast_raise(f, fmaxf(fmaxf(x0, x1), fmaxf(x2, x3)), c);
+  const float2 c2 = make_float2(c, c);
+  const float2 n2 = make_float2(-f.mc, -f.mc);
+  const float2 t0 = __ffma2_rn(make_float2(x0, x1), c2, n2);
+  const float2 t1 = __ffma2_rn(make_float2(x2, x3), c2, n2);
+  f.a = __fadd2_rn(f.a, make_float2(ex2f(t0.x), ex2f(t0.y)));
+  f.b = __fadd2_rn(f.b, make_float2(ex2f(t1.x), ex2f(t1.y)));
 }
 
 __device__ __forceinline__ void online_update_scalar(Online& st, float x, float c) {
@@ -300,7 +373,24 @@ struct K1Smem {
   static constexpr int TOTAL_PLAIN = CUM_OFF;
 };
 
-template <typename T, int MODE>
+// Exact two-pass (max, sum 2^((x - max) * c)) of one row with plain loads, by one full warp.
+// Only used for rows the streaming arithmetic cannot represent (see K1_M_FLOOR).
+template <typename T>
+__device__ __noinline__ void exact_row(const T* src, int64_t vocab, float c, int lane, float& m,
+                                       float& s) {
+  float mx = __int_as_float(0xff800000);  // -inf
+  for (int64_t j = lane; j < vocab; j += 32) mx = fmaxf(mx, to_float(src[j]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.0f;
+  for (int64_t j = lane; j < vocab; j += 32) sum += ex2f((to_float(src[j]) - mx) * c);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  m = mx;
+  s = sum;
+}
+
+template <typename T, int MODE, int POLY>
 __global__ void __launch_bounds__(K1_THREADS, 1) k1_stream_kernel(const K1Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   constexpr int NSUB = (MODE == K1_SELECTIVE) ? 1 : 2;
@@ -394,8 +484,8 @@ __global__ void __launch_bounds__(K1_THREADS, 1) k1_stream_kernel(const K1Params
         else raise_status(p.status, TOME_DEV_TARGET_OUT_OF_RANGE);
       }
 
-      Online st;
-      online_init(st);
+      Fast fs;
+      fast_init(fs, p.c);
       T* dst = nullptr;
       if (MODE == K1_FULL) dst = reinterpret_cast<T*>(p.out_full) + row * p.out_stride;
 
@@ -418,12 +508,13 @@ __global__ void __launch_bounds__(K1_THREADS, 1) k1_stream_kernel(const K1Params
             const uint4 b = lds128(sbase + (v + K1_CONSUMERS) * 16);
             const uint4 cc = lds128(sbase + (v + 2 * K1_CONSUMERS) * 16);
             const uint4 d = lds128(sbase + (v + 3 * K1_CONSUMERS) * 16);
-            online_update(st, a, p.c, T());
-            online_update(st, b, p.c, T());
-            online_update(st, cc, p.c, T());
-            online_update(st, d, p.c, T());
+            fast_update<POLY>(fs, a, p.c, T());
+            fast_update<POLY>(fs, b, p.c, T());
+            fast_update<POLY>(fs, cc, p.c, T());
+            fast_update<POLY>(fs, d, p.c, T());
           }
-          for (; v < nvec; v += K1_CONSUMERS) online_update(st, lds128(sbase + v * 16), p.c, T());
+          for (; v < nvec; v += K1_CONSUMERS)
+            fast_update<POLY>(fs, lds128(sbase + v * 16), p.c, T());
         } else {
           uint8_t* drow = reinterpret_cast<uint8_t*>(dst) + off;
           for (; v < nvec; v += K1_CONSUMERS) {
@@ -435,6 +526,7 @@ __global__ void __launch_bounds__(K1_THREADS, 1) k1_stream_kernel(const K1Params
         if (lane == 0) mbar_arrive(empty_bar + stage * 8);
       }
 
+      Online st = fast_finish(fs, p.c);
       // elements past the last 16-byte boundary of the row (at most PER_VEC - 1)
       if (ctid == 0) {
         for (int64_t j = tail_begin; j < p.vocab; ++j) {
@@ -456,6 +548,8 @@ __global__ void __launch_bounds__(K1_THREADS, 1) k1_stream_kernel(const K1Params
           float s = ms.y * ex2f((ms.x - m) * p.c);
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+          // the true maximum contributes 2^0, so a healthy row has s >= ~1
+          if (!(s >= 0.5f && s <= FLT_MAX)) exact_row(src, p.vocab, p.c, lane, m, s);
           if (MODE == K1_FULL) lse_row = finish_lse<MODE>(m, s, p);
           if (ctid == 0) emit_row<MODE>(p, row, sub, m, s, x_t, target_ok, carry);
         }
@@ -532,6 +626,27 @@ __global__ void __launch_bounds__(K1_PLAIN_THREADS) k1_plain_kernel(const K1Para
 }
 
 // ------------------------------------------------------------------ host side
+// Tuning knob TOME_K1_POLY = 0 | 1 | 2: how many of the 8 logits of a bf16 vector take the
+// polynomial exp2 (FMA pipe) instead of ex2.approx (exp unit).  Read once per process.
+static int k1_poly_setting() {
+  static const int value = [] {
+    const char* e = getenv("TOME_K1_POLY");
+    const int v = (e != nullptr) ? atoi(e) : K1_POLY_DEFAULT;
+    return v < 0 ? 0 : (v > 2 ? 2 : v);
+  }();
+  return value;
+}
+
+template <typename T, int MODE>
+static void (*pick_stream_kernel())(K1Params) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value && MODE != K1_FULL) {
+    const int poly = k1_poly_setting();
+    if (poly == 1) return k1_stream_kernel<T, MODE, 1>;
+    if (poly == 2) return k1_stream_kernel<T, MODE, 2>;
+  }
+  return k1_stream_kernel<T, MODE, 0>;
+}
+
 template <typename T, int MODE>
 static int32_t k1_launch_typed(const K1Params& p, bool bulk_ok, int64_t max_items,
                                cudaStream_t stream) {
@@ -543,13 +658,14 @@ static int32_t k1_launch_typed(const K1Params& p, bool bulk_ok, int64_t max_item
     if (smem > info.max_smem_optin)
       return fail(TOME_ERR_UNSUPPORTED, "device offers %d bytes of shared memory, need %d",
                   info.max_smem_optin, smem);
-    st = check_cuda(cudaFuncSetAttribute(k1_stream_kernel<T, MODE>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
-                    "cudaFuncSetAttribute");
+    void (*kernel)(K1Params) = pick_stream_kernel<T, MODE>();
+    st = check_cuda(
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+        "cudaFuncSetAttribute");
     if (st != TOME_OK) return st;
     const int grid = static_cast<int>(
         std::max<int64_t>(1, std::min<int64_t>(info.sm_count, max_items)));
-    k1_stream_kernel<T, MODE><<<grid, K1_THREADS, smem, stream>>>(p);
+    kernel<<<grid, K1_THREADS, smem, stream>>>(p);
   } else {
     const int grid = static_cast<int>(std::max<int64_t>(
         1, std::min<int64_t>(static_cast<int64_t>(info.sm_count) * 8, max_items)));
