@@ -110,7 +110,7 @@ int32_t tome_log_softmax_full(const void* logits, int32_t dtype, int64_t rows, i
  *   lengths   device int32 [n_seq]; clamped to [0, seq_len - start]
  *   starts    device int32 [n_seq] or NULL (all zero)
  *   out_*     device fp32 [n_seq * seq_len]; positions outside the window are written as 0
- * Rows outside the windows are never read.  n_seq <= 4096.
+ * Rows outside the windows are never read.  n_seq <= 1024 per call.
  */
 int32_t tome_dual_logprob_kl(const void* policy_logits, const void* ref_logits, int32_t dtype,
                              int64_t n_seq, int64_t seq_len, int64_t vocab, int64_t row_stride,

@@ -122,3 +122,24 @@ def test_caller_workspace_and_size_check(cuda_device):
     with pytest.raises(ValueError):
         tome_b200.lm_head_logprob(hidden.to(cuda_device), weight.to(cuda_device), ids.to(cuda_device),
                                   1.0, workspace=ws[: need - 16])
+
+
+def test_single_cta_tiles_variant(cuda_device):
+    """TOME_K2_PAIR=0 selects the cta_group::1 kernel (read once per process): child process."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import sys, torch; sys.path.insert(0, %r)\n"
+        "import tome_b200; from oracle import oracle; from tome_b200 import synthetic\n"
+        "for rows, k, vocab in ((300, 192, 4096 + 48), (129, 1024, 700)):\n"
+        "    h, w, ids = synthetic.cfg3_lm_head(rows, k, vocab, 'cpu', 5, 0.05)\n"
+        "    lp, lse = tome_b200.lm_head_logprob(h.cuda(), w.cuda(), ids.cuda(), 0.7, check=True)\n"
+        "    o_lp, o_lse = oracle.lm_head_logprob(h, w, ids, 0.7)\n"
+        "    err = float((lp.cpu() - o_lp).abs().max()); print(err); assert err <= 2e-3\n"
+    ) % root
+    env = dict(os.environ, TOME_K2_PAIR="0")
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True,
+                         timeout=600)
+    assert out.returncode == 0, out.stdout + out.stderr

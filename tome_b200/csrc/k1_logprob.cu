@@ -1,10 +1,14 @@
 // K1: streaming log-softmax kernels over materialised logits (HBM-bound).
 //
-// One persistent CTA per SM.  A producer thread streams each logits row through a ring of
-// shared-memory stages with 1-D bulk (TMA) copies that complete on mbarriers; eight consumer
-// warps read the stages with 128-bit shared loads and keep a per-thread online (max, sum-exp)
-// pair in fp32, so every logit is read from HBM exactly once.  The ring runs across row
-// boundaries, so the loads of the next row are in flight while a row is being reduced.
+// Four small persistent CTAs per SM, each working on its own rows.  In every CTA a producer
+// thread streams the row through a two-stage shared-memory ring with 1-D bulk (TMA) copies
+// that complete on mbarriers, in equal chunks of about 25 KB that start on 1 KB boundaries;
+// four consumer warps read the stages with 128-bit shared loads and keep a per-thread online
+// (max, sum-exp) pair in fp32, so every logit is read from HBM exactly once.  The ring runs
+// across row boundaries, so the loads of the next row are in flight while a row is being
+// reduced, and the four CTAs of an SM are never in the same phase, which keeps the exp unit
+// and the memory pipe busy while one of them merges a row.  (Measured: one CTA of 16 warps
+// per SM reached 6.0 TB/s, two of 8 warps 6.6, four of 4 warps 6.85 on 20480 x 151936 bf16.)
 //
 // Three modes share the pipeline:
 //   SELECTIVE  logprob of one target per row             (mlx-impl/node.py:400-404)
@@ -32,13 +36,38 @@ namespace tome {
 
 enum K1Mode { K1_SELECTIVE = 0, K1_DUAL = 1, K1_FULL = 2 };
 
-constexpr int K1_CONSUMER_WARPS = 16;
+// Tuning constants (overridable at compile time for experiments).
+#ifndef K1_CFG_WARPS
+#define K1_CFG_WARPS 4
+#endif
+#ifndef K1_CFG_STAGES
+#define K1_CFG_STAGES 2
+#endif
+#ifndef K1_CFG_CHUNK
+#define K1_CFG_CHUNK 25600
+#endif
+#ifndef K1_CFG_CHUNK_ALIGN
+#define K1_CFG_CHUNK_ALIGN 1024
+#endif
+#ifndef K1_CFG_CTAS_PER_SM
+#define K1_CFG_CTAS_PER_SM 4
+#endif
+#ifndef K1_CFG_L2_HINT
+#define K1_CFG_L2_HINT 1
+#endif
+constexpr int K1_CONSUMER_WARPS = K1_CFG_WARPS;
 constexpr int K1_CONSUMERS = K1_CONSUMER_WARPS * 32;
 constexpr int K1_THREADS = K1_CONSUMERS + 32;
-constexpr int K1_STAGES = 6;
-constexpr int K1_CHUNK_BYTES = 32768;
-constexpr int K1_MAX_SEQ = 4096;
-constexpr int K1_POLY_DEFAULT = 0;
+constexpr int K1_STAGES = K1_CFG_STAGES;
+constexpr int K1_CHUNK_BYTES = K1_CFG_CHUNK;
+constexpr int K1_CTAS_PER_SM = K1_CFG_CTAS_PER_SM;
+// bulk copies start on multiples of this many bytes from the row start (keeps them aligned
+// to whole 128-byte lines when the row pitch is)
+constexpr int K1_CHUNK_ALIGN = K1_CFG_CHUNK_ALIGN;
+static_assert(K1_CHUNK_BYTES % K1_CHUNK_ALIGN == 0 && K1_CHUNK_ALIGN % 16 == 0, "chunk alignment");
+static_assert(K1_CONSUMER_WARPS <= 32, "row-end merge reads one partial per lane");
+constexpr int K1_MAX_SEQ = 1024;
+constexpr int K1_POLY_DEFAULT = 2;
 
 struct K1Params {
   const void* src[2];      // DUAL: policy, reference
@@ -59,6 +88,8 @@ struct K1Params {
   int32_t n_seq;           // DUAL
   int32_t seq_len;         // DUAL
   int32_t* status;         // nullable
+  int32_t chunk_bytes;     // bulk-copy size (multiple of 16, <= K1_CHUNK_BYTES), set by launch
+  int32_t n_chunks;        // bulk copies per row
 };
 
 // ------------------------------------------------------------------ online (max, sum-exp)
@@ -143,12 +174,13 @@ __device__ __forceinline__ float ex2_poly(float x) {
   return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
 
+// Pair number `slot` (0..3) of an 8-logit vector; the first POLY logits of the vector take
+// the polynomial.
 template <int POLY>
 __device__ __forceinline__ float2 ex2_pair(float2 t, int slot) {
-  // slot 0 is the first pair of the vector; POLY of its lanes go to the polynomial
   float2 e;
-  e.x = (POLY >= 1 && slot == 0) ? ex2_poly(t.x) : ex2f(t.x);
-  e.y = (POLY >= 2 && slot == 0) ? ex2_poly(t.y) : ex2f(t.y);
+  e.x = (2 * slot < POLY) ? ex2_poly(t.x) : ex2f(t.x);
+  e.y = (2 * slot + 1 < POLY) ? ex2_poly(t.y) : ex2f(t.y);
   return e;
 }
 
@@ -167,8 +199,8 @@ __device__ __forceinline__ void fast_update(Fast& f, uint4 v, float c, __nv_bflo
   const float2 t3 = __ffma2_rn(make_float2(bf16_lo(v.w), bf16_hi(v.w)), c2, n2);
   const float2 e0 = ex2_pair<POLY>(t0, 0);
   const float2 e1 = ex2_pair<POLY>(t1, 1);
-  const float2 e2 = ex2_pair<POLY>(t2, 1);
-  const float2 e3 = ex2_pair<POLY>(t3, 1);
+  const float2 e2 = ex2_pair<POLY>(t2, 2);
+  const float2 e3 = ex2_pair<POLY>(t3, 3);
   f.a = __fadd2_rn(f.a, __fadd2_rn(e0, e1));
   f.b = __fadd2_rn(f.b, __fadd2_rn(e2, e3));
 }
@@ -391,7 +423,7 @@ __device__ __noinline__ void exact_row(const T* src, int64_t vocab, float c, int
 }
 
 template <typename T, int MODE, int POLY>
-__global__ void __launch_bounds__(K1_THREADS, 1) k1_stream_kernel(const K1Params p) {
+__global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(const K1Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   constexpr int NSUB = (MODE == K1_SELECTIVE) ? 1 : 2;
   constexpr int ES = sizeof(T);
@@ -422,7 +454,8 @@ __global__ void __launch_bounds__(K1_THREADS, 1) k1_stream_kernel(const K1Params
 
   const int64_t row_bytes = p.vocab * ES;
   const int64_t bulk_bytes = row_bytes & ~static_cast<int64_t>(15);
-  const int64_t n_chunks = (bulk_bytes + K1_CHUNK_BYTES - 1) / K1_CHUNK_BYTES;
+  const int64_t n_chunks = p.n_chunks;
+  const int64_t chunk_bytes = p.chunk_bytes;
   const int64_t tail_begin = bulk_bytes / ES;  // first element not covered by bulk copies
 
   if (warp == K1_CONSUMER_WARPS) {
@@ -444,12 +477,11 @@ __global__ void __launch_bounds__(K1_THREADS, 1) k1_stream_kernel(const K1Params
               ok = false;
               break;
             }
-            const int64_t off = k * K1_CHUNK_BYTES;
-            const uint32_t bytes =
-                static_cast<uint32_t>(min(static_cast<int64_t>(K1_CHUNK_BYTES), bulk_bytes - off));
+            const int64_t off = k * chunk_bytes;
+            const uint32_t bytes = static_cast<uint32_t>(min(chunk_bytes, bulk_bytes - off));
             mbar_arrive_expect_tx(full_bar + stage * 8, bytes);
             // FULL re-reads the row in its second pass: keep it in L2 after the first.
-            if (MODE == K1_FULL && sub == 0)
+            if (!K1_CFG_L2_HINT || (MODE == K1_FULL && sub == 0))
               bulk_g2s(smem_base + stage * K1_CHUNK_BYTES, src + off, bytes, full_bar + stage * 8);
             else
               bulk_g2s_hint(smem_base + stage * K1_CHUNK_BYTES, src + off, bytes,
@@ -496,9 +528,8 @@ __global__ void __launch_bounds__(K1_THREADS, 1) k1_stream_kernel(const K1Params
           raise_status(p.status, TOME_DEV_TIMEOUT);
           return;
         }
-        const int64_t off = k * K1_CHUNK_BYTES;
-        const uint32_t bytes =
-            static_cast<uint32_t>(min(static_cast<int64_t>(K1_CHUNK_BYTES), bulk_bytes - off));
+        const int64_t off = k * chunk_bytes;
+        const uint32_t bytes = static_cast<uint32_t>(min(chunk_bytes, bulk_bytes - off));
         const uint32_t nvec = bytes >> 4;
         const uint32_t sbase = smem_base + stage * K1_CHUNK_BYTES;
         uint32_t v = ctid;
@@ -626,13 +657,13 @@ __global__ void __launch_bounds__(K1_PLAIN_THREADS) k1_plain_kernel(const K1Para
 }
 
 // ------------------------------------------------------------------ host side
-// Tuning knob TOME_K1_POLY = 0 | 1 | 2: how many of the 8 logits of a bf16 vector take the
+// Tuning knob TOME_K1_POLY = 0 .. 4: how many of the 8 logits of a bf16 vector take the
 // polynomial exp2 (FMA pipe) instead of ex2.approx (exp unit).  Read once per process.
 static int k1_poly_setting() {
   static const int value = [] {
     const char* e = getenv("TOME_K1_POLY");
     const int v = (e != nullptr) ? atoi(e) : K1_POLY_DEFAULT;
-    return v < 0 ? 0 : (v > 2 ? 2 : v);
+    return v < 0 ? 0 : (v > 4 ? 4 : v);
   }();
   return value;
 }
@@ -643,17 +674,28 @@ static void (*pick_stream_kernel())(K1Params) {
     const int poly = k1_poly_setting();
     if (poly == 1) return k1_stream_kernel<T, MODE, 1>;
     if (poly == 2) return k1_stream_kernel<T, MODE, 2>;
+    if (poly == 3) return k1_stream_kernel<T, MODE, 3>;
+    if (poly == 4) return k1_stream_kernel<T, MODE, 4>;
   }
   return k1_stream_kernel<T, MODE, 0>;
 }
 
 template <typename T, int MODE>
-static int32_t k1_launch_typed(const K1Params& p, bool bulk_ok, int64_t max_items,
+static int32_t k1_launch_typed(const K1Params& p_in, bool bulk_ok, int64_t max_items,
                                cudaStream_t stream) {
   DeviceInfo info;
   int32_t st = current_device_info(&info);
   if (st != TOME_OK) return st;
   if (bulk_ok) {
+    // equal-sized bulk copies: a row is cut into the fewest chunks that fit a stage
+    K1Params p = p_in;
+    constexpr int64_t es = sizeof(T);
+    const int64_t bulk_bytes = (p.vocab * es) & ~static_cast<int64_t>(15);
+    const int64_t n = (bulk_bytes + K1_CHUNK_BYTES - 1) / K1_CHUNK_BYTES;
+    p.n_chunks = static_cast<int32_t>(n);
+    const int64_t al = K1_CHUNK_ALIGN;
+    p.chunk_bytes = (n > 0) ? static_cast<int32_t>(((bulk_bytes + n - 1) / n + al - 1) / al * al)
+                            : K1_CHUNK_ALIGN;
     const int smem = (MODE == K1_DUAL) ? K1Smem::TOTAL_DUAL : K1Smem::TOTAL_PLAIN;
     if (smem > info.max_smem_optin)
       return fail(TOME_ERR_UNSUPPORTED, "device offers %d bytes of shared memory, need %d",
@@ -664,12 +706,12 @@ static int32_t k1_launch_typed(const K1Params& p, bool bulk_ok, int64_t max_item
         "cudaFuncSetAttribute");
     if (st != TOME_OK) return st;
     const int grid = static_cast<int>(
-        std::max<int64_t>(1, std::min<int64_t>(info.sm_count, max_items)));
+        std::max<int64_t>(1, std::min<int64_t>(info.sm_count * K1_CTAS_PER_SM, max_items)));
     kernel<<<grid, K1_THREADS, smem, stream>>>(p);
   } else {
     const int grid = static_cast<int>(std::max<int64_t>(
         1, std::min<int64_t>(static_cast<int64_t>(info.sm_count) * 8, max_items)));
-    k1_plain_kernel<T, MODE><<<grid, K1_PLAIN_THREADS, 0, stream>>>(p);
+    k1_plain_kernel<T, MODE><<<grid, K1_PLAIN_THREADS, 0, stream>>>(p_in);
   }
   return check_cuda(cudaGetLastError(), "k1 launch");
 }

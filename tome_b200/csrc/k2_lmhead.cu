@@ -22,6 +22,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <float.h>
+#include <stdlib.h>
 
 #include <algorithm>
 #include <mutex>
@@ -32,17 +33,29 @@
 
 namespace tome {
 
-constexpr int K2_BM = 128;
-constexpr int K2_BN = 256;
-constexpr int K2_BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
-constexpr int K2_STAGES = 4;
+constexpr int K2_BM = 128;   // rows of the tile held by one CTA (TMEM lanes)
+constexpr int K2_BN = 256;   // columns of a tile
+constexpr int K2_BK = 64;    // 64 bf16 = 128 bytes = one swizzle row
 constexpr int K2_A_BYTES = K2_BM * K2_BK * 2;
-constexpr int K2_B_BYTES = K2_BN * K2_BK * 2;
-constexpr int K2_STAGE_BYTES = K2_A_BYTES + K2_B_BYTES;
 constexpr int K2_THREADS = 192;
 constexpr int K2_EPI_WARPS = 4;
 constexpr int K2_TMEM_COLS = 512;
-constexpr int K2_SMEM_BYTES = K2_STAGES * K2_STAGE_BYTES + 1024 /*alignment slack*/ + 256;
+
+// PAIR = false: one CTA computes a 128 x 256 tile (tcgen05 cta_group::1).
+// PAIR = true : a cluster of two CTAs computes a 256 x 256 tile (cta_group::2); each CTA
+//               loads its own 128 hidden rows and HALF of the weight rows of the tile, the
+//               leader CTA issues the MMAs for both, and each CTA reduces the 128 rows that
+//               land in its own TMEM.  Per CTA that is one third less shared-memory fill
+//               per FLOP, so six stages fit where the single-CTA form has four.
+template <bool PAIR>
+struct K2Cfg {
+  static constexpr int B_ROWS = PAIR ? 128 : 256;  // weight rows this CTA loads per tile
+  static constexpr int B_BYTES = B_ROWS * K2_BK * 2;
+  static constexpr int STAGE_BYTES = K2_A_BYTES + B_BYTES;
+  static constexpr int STAGES = PAIR ? 6 : 4;
+  static constexpr int ITEM_ROWS = PAIR ? 256 : 128;  // rows of a work item's row tile
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256;
+};
 
 struct K2Params {
   int64_t rows;
@@ -56,7 +69,8 @@ struct K2Params {
   float* part_m;           // [n_bands][rows]
   float* part_s;
   float* part_t;
-  int32_t m_tiles, n_tiles, k_blocks;
+  int32_t m_tiles;         // row tiles of ITEM_ROWS rows
+  int32_t n_tiles, k_blocks;
   int32_t nb;              // column tiles per band
   int32_t n_bands;
   int32_t gm;              // row tiles per group
@@ -115,79 +129,110 @@ __device__ __forceinline__ void k2_raise(int32_t* status, int32_t bit) {
   if (status != nullptr) atomicOr(status, bit);
 }
 
+template <bool PAIR>
 __global__ void __launch_bounds__(K2_THREADS, 1)
 k2_lmhead_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b, const K2Params p) {
+  using Cfg = K2Cfg<PAIR>;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int STAGE_BYTES = Cfg::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles want 1024-byte alignment
   uint8_t* smem = smem_raw + (base - raw);
-  const uint32_t bars = base + K2_STAGES * K2_STAGE_BYTES;
+  const uint32_t bars = base + STAGES * STAGE_BYTES;
   const uint32_t full_bar = bars;
-  const uint32_t empty_bar = bars + K2_STAGES * 8;
-  const uint32_t tfull_bar = bars + 2 * K2_STAGES * 8;
+  const uint32_t empty_bar = bars + STAGES * 8;
+  const uint32_t tfull_bar = bars + 2 * STAGES * 8;
   const uint32_t tempty_bar = tfull_bar + 16;
   const uint32_t tmem_slot = tempty_bar + 16;
   volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(smem + K2_STAGES * K2_STAGE_BYTES + 2 * K2_STAGES * 8 + 32);
+      reinterpret_cast<volatile uint32_t*>(smem + STAGES * STAGE_BYTES + 2 * STAGES * 8 + 32);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // the identical smem layout in both CTAs of a pair makes every offset valid in the peer
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = (rank == 0u);
+  const int64_t worker = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
+  const int64_t n_workers = PAIR ? (gridDim.x >> 1) : gridDim.x;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < K2_STAGES; ++i) {
+    for (int i = 0; i < STAGES; ++i) {
       mbar_init(full_bar + i * 8, 1);
       mbar_init(empty_bar + i * 8, 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(tfull_bar + i * 8, 1);
-      mbar_init(tempty_bar + i * 8, K2_EPI_WARPS);
+      mbar_init(tempty_bar + i * 8, PAIR ? 2 * K2_EPI_WARPS : K2_EPI_WARPS);
     }
     fence_mbar_init();
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, K2_TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(tmem_slot, K2_TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, K2_TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      // data of both CTAs of a pair is counted on the LEADER's full barrier
+      const uint32_t full_signal = PAIR ? mapa_shared(full_bar, 0) : full_bar;
       uint32_t it = 0;
       bool ok = true;
-      for (int64_t i = blockIdx.x; i < p.n_items && ok; i += gridDim.x) {
+      for (int64_t i = worker; i < p.n_items && ok; i += n_workers) {
         const K2Item item = k2_decode(p, i);
+        const int32_t row0 = item.mt * Cfg::ITEM_ROWS + static_cast<int32_t>(rank) * K2_BM;
         for (int32_t n = item.n_begin; n < item.n_end && ok; ++n) {
+          const int32_t wrow0 = n * K2_BN + static_cast<int32_t>(rank) * Cfg::B_ROWS;
           for (int32_t kb = 0; kb < p.k_blocks; ++kb, ++it) {
-            const uint32_t stage = it % K2_STAGES;
-            const uint32_t phase = (it / K2_STAGES) & 1u;
+            const uint32_t stage = it % STAGES;
+            const uint32_t phase = (it / STAGES) & 1u;
             if (!mbar_wait(empty_bar + stage * 8, phase ^ 1u)) {
               k2_raise(p.status, TOME_DEV_TIMEOUT);
               ok = false;
               break;
             }
-            const uint32_t sa = base + stage * K2_STAGE_BYTES;
-            mbar_arrive_expect_tx(full_bar + stage * 8, K2_STAGE_BYTES);
-            tma_load_2d(sa, &tmap_a, kb * K2_BK, item.mt * K2_BM, full_bar + stage * 8);
-            tma_load_2d(sa + K2_A_BYTES, &tmap_b, kb * K2_BK, n * K2_BN, full_bar + stage * 8);
+            const uint32_t sa = base + stage * STAGE_BYTES;
+            if (PAIR) {
+              if (leader) mbar_arrive_expect_tx(full_bar + stage * 8, 2 * STAGE_BYTES);
+              tma_load_2d_pair(sa, &tmap_a, kb * K2_BK, row0, full_signal + stage * 8);
+              tma_load_2d_pair(sa + K2_A_BYTES, &tmap_b, kb * K2_BK, wrow0,
+                               full_signal + stage * 8);
+            } else {
+              mbar_arrive_expect_tx(full_bar + stage * 8, STAGE_BYTES);
+              tma_load_2d(sa, &tmap_a, kb * K2_BK, row0, full_bar + stage * 8);
+              tma_load_2d(sa + K2_A_BYTES, &tmap_b, kb * K2_BK, wrow0, full_bar + stage * 8);
+            }
           }
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = k2_idesc(K2_BM, K2_BN);
+    // ------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = k2_idesc(PAIR ? 256 : 128, K2_BN);
+      // completion is signalled to the same barrier in both CTAs of a pair
+      const uint32_t empty_own = PAIR ? mapa_shared(empty_bar, 0) : empty_bar;
+      const uint32_t empty_peer = PAIR ? mapa_shared(empty_bar, 1) : 0u;
+      const uint32_t tfull_own = PAIR ? mapa_shared(tfull_bar, 0) : tfull_bar;
+      const uint32_t tfull_peer = PAIR ? mapa_shared(tfull_bar, 1) : 0u;
       uint32_t it = 0, tc = 0;
       bool ok = true;
-      for (int64_t i = blockIdx.x; i < p.n_items && ok; i += gridDim.x) {
+      for (int64_t i = worker; i < p.n_items && ok; i += n_workers) {
         const K2Item item = k2_decode(p, i);
         for (int32_t n = item.n_begin; n < item.n_end && ok; ++n, ++tc) {
           const uint32_t acc = tc & 1u;
@@ -200,26 +245,44 @@ k2_lmhead_kernel(const __grid_constant__ CUtensorMap tmap_a,
           tc_fence_after_sync();
           const uint32_t d_tmem = tmem_base + acc * K2_BN;
           for (int32_t kb = 0; kb < p.k_blocks; ++kb, ++it) {
-            const uint32_t stage = it % K2_STAGES;
-            const uint32_t phase = (it / K2_STAGES) & 1u;
+            const uint32_t stage = it % STAGES;
+            const uint32_t phase = (it / STAGES) & 1u;
             if (!mbar_wait(full_bar + stage * 8, phase)) {
               k2_raise(p.status, TOME_DEV_TIMEOUT);
               ok = false;
               break;
             }
             tc_fence_after_sync();
-            const uint32_t sa = base + stage * K2_STAGE_BYTES;
+            const uint32_t sa = base + stage * STAGE_BYTES;
             const uint64_t da = k2_smem_desc(sa);
             const uint64_t db = k2_smem_desc(sa + K2_A_BYTES);
 #pragma unroll
             for (int k = 0; k < K2_BK / 16; ++k) {
               // 16 bf16 = 32 bytes further along K inside the swizzle row: +2 in 16-byte units
-              umma_bf16_ss(d_tmem, da + static_cast<uint64_t>(k * 2),
-                           db + static_cast<uint64_t>(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+              const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
+              if (PAIR)
+                umma_bf16_ss_pair(d_tmem, da + static_cast<uint64_t>(k * 2),
+                                  db + static_cast<uint64_t>(k * 2), idesc, accumulate);
+              else
+                umma_bf16_ss(d_tmem, da + static_cast<uint64_t>(k * 2),
+                             db + static_cast<uint64_t>(k * 2), idesc, accumulate);
             }
-            umma_commit(empty_bar + stage * 8);  // frees the stage once these MMAs have read it
+            // frees the stage (in both CTAs) once these MMAs have read it
+            if (PAIR) {
+              umma_commit_pair(empty_own + stage * 8);
+              umma_commit_pair(empty_peer + stage * 8);
+            } else {
+              umma_commit(empty_bar + stage * 8);
+            }
           }
-          if (ok) umma_commit(tfull_bar + acc * 8);  // accumulator complete
+          if (ok) {  // accumulator complete
+            if (PAIR) {
+              umma_commit_pair(tfull_own + acc * 8);
+              umma_commit_pair(tfull_peer + acc * 8);
+            } else {
+              umma_commit(tfull_bar + acc * 8);
+            }
+          }
         }
       }
     }
@@ -228,12 +291,14 @@ k2_lmhead_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+    // accumulators are handed back to the leader's MMA warp
+    const uint32_t tempty_signal = PAIR ? mapa_shared(tempty_bar, 0) : tempty_bar;
     uint32_t tc = 0;
     bool ok = true;
     const float c = p.c;
-    for (int64_t i = blockIdx.x; i < p.n_items && ok; i += gridDim.x) {
+    for (int64_t i = worker; i < p.n_items && ok; i += n_workers) {
       const K2Item item = k2_decode(p, i);
-      const int64_t row = static_cast<int64_t>(item.mt) * K2_BM + q * 32 + lane;
+      const int64_t row = static_cast<int64_t>(item.mt) * Cfg::ITEM_ROWS + rank * K2_BM + q * 32 + lane;
       const bool row_ok = row < p.rows;
       int64_t tloc = -1;  // target column local to this shard, -1 if not owned
       if (row_ok) {
@@ -295,22 +360,28 @@ k2_lmhead_kernel(const __grid_constant__ CUtensorMap tmap_a,
               m = cmax;
               mc = mc_new;
             }
-            const float nmc = -mc;
-            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+            const float2 c2 = make_float2(c, c);
+            const float2 n2 = make_float2(-mc, -mc);
+            float2 a0 = make_float2(0.0f, 0.0f), a1 = make_float2(0.0f, 0.0f);
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
-              a0 += ex2f(fmaf(__uint_as_float(v[j]), c, nmc));
-              a1 += ex2f(fmaf(__uint_as_float(v[j + 1]), c, nmc));
-              a2 += ex2f(fmaf(__uint_as_float(v[j + 2]), c, nmc));
-              a3 += ex2f(fmaf(__uint_as_float(v[j + 3]), c, nmc));
+              const float2 t0 = __ffma2_rn(
+                  make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), c2, n2);
+              const float2 t1 = __ffma2_rn(
+                  make_float2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])), c2, n2);
+              a0 = __fadd2_rn(a0, make_float2(ex2f(t0.x), ex2f(t0.y)));
+              a1 = __fadd2_rn(a1, make_float2(ex2f(t1.x), ex2f(t1.y)));
             }
-            s += (a0 + a1) + (a2 + a3);
+            s += (a0.x + a0.y) + (a1.x + a1.y);
           }
         }
         // accumulator drained: hand it back to the MMA warp
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar + acc * 8);
+        if (lane == 0) {
+          if (PAIR) mbar_arrive_cluster(tempty_signal + acc * 8);
+          else mbar_arrive(tempty_bar + acc * 8);
+        }
       }
       if (row_ok && ok) {
         const int64_t o = static_cast<int64_t>(item.band) * p.rows + row;
@@ -325,9 +396,12 @@ k2_lmhead_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   tc_fence_before_sync();
   __syncthreads();
+  // nobody leaves while the peer may still signal this CTA's barriers or read its smem
+  if (PAIR) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, K2_TMEM_COLS);
+    if (PAIR) tmem_dealloc_pair(tmem_base, K2_TMEM_COLS);
+    else tmem_dealloc(tmem_base, K2_TMEM_COLS);
   }
 }
 
@@ -382,9 +456,11 @@ struct K2Plan {
   int64_t n_items;
 };
 
-static K2Plan k2_plan(int64_t rows, int64_t k, int64_t vocab_local) {
+// item_rows: rows of a work item's row tile (128 single-CTA, 256 CTA pair).  The number of
+// bands, hence the workspace size, does not depend on it.
+static K2Plan k2_plan(int64_t rows, int64_t k, int64_t vocab_local, int item_rows = K2_BM) {
   K2Plan pl;
-  pl.m_tiles = static_cast<int32_t>((rows + K2_BM - 1) / K2_BM);
+  pl.m_tiles = static_cast<int32_t>((rows + item_rows - 1) / item_rows);
   pl.n_tiles = static_cast<int32_t>((vocab_local + K2_BN - 1) / K2_BN);
   pl.k_blocks = static_cast<int32_t>((k + K2_BK - 1) / K2_BK);
   // band: about 16 MB of weight rows, between 2 and 32 column tiles
@@ -394,13 +470,16 @@ static K2Plan k2_plan(int64_t rows, int64_t k, int64_t vocab_local) {
   pl.nb = static_cast<int32_t>(std::min<int64_t>(nb, pl.n_tiles));
   pl.n_bands = (pl.n_tiles + pl.nb - 1) / pl.nb;
   // row-tile group: hidden tiles of a group stay in L2 (about 40 MB)
-  const int64_t a_bytes = static_cast<int64_t>(K2_BM) * k * 2;
+  const int64_t a_bytes = static_cast<int64_t>(item_rows) * k * 2;
   int64_t gm = (40ll << 20) / std::max<int64_t>(a_bytes, 1);
   gm = std::max<int64_t>(1, gm);
   if (gm < pl.m_tiles) {
-    if (gm >= 148) gm = 148;
-    else if (gm >= 74) gm = 74;
-    else if (gm >= 37) gm = 37;
+    // a divisor of the number of concurrent workers (148 CTAs or 74 pairs) keeps a wave
+    // on whole bands
+    const int64_t unit = (item_rows == K2_BM) ? 37 : 37;
+    if (gm >= 4 * unit && item_rows == K2_BM) gm = 4 * unit;
+    else if (gm >= 2 * unit) gm = 2 * unit;
+    else if (gm >= unit) gm = unit;
   } else {
     gm = pl.m_tiles;
   }
@@ -433,6 +512,16 @@ static int32_t k2_check(const void* hidden, const void* weight, int64_t rows, in
   return TOME_OK;
 }
 
+// Tuning knob TOME_K2_PAIR = 0 | 1: single-CTA tiles (cta_group::1) or CTA-pair tiles
+// (cta_group::2, the default).  Read once per process.
+static bool k2_pair_setting() {
+  static const bool value = [] {
+    const char* e = getenv("TOME_K2_PAIR");
+    return (e != nullptr) ? (atoi(e) != 0) : true;
+  }();
+  return value;
+}
+
 // Launches the GEMM+reduce kernel; partial triples land in the workspace.
 static int32_t k2_launch(const void* hidden, const void* weight, int64_t rows, int64_t k,
                          int64_t vocab_local, int64_t vocab_offset, int64_t vocab_check,
@@ -444,12 +533,13 @@ static int32_t k2_launch(const void* hidden, const void* weight, int64_t rows, i
   if (info.cc_major != 10)
     return fail(TOME_ERR_UNSUPPORTED, "the fused LM head needs an sm_100 device (found sm_%d*)",
                 info.cc_major * 10);
-  const K2Plan pl = k2_plan(rows, k, vocab_local);
+  const bool pair = k2_pair_setting();
+  const K2Plan pl = k2_plan(rows, k, vocab_local, pair ? 256 : 128);
   *plan_out = pl;
   CUtensorMap ta, tb;
   st = make_tmap(&ta, hidden, rows, k, K2_BM);
   if (st != TOME_OK) return st;
-  st = make_tmap(&tb, weight, vocab_local, k, K2_BN);
+  st = make_tmap(&tb, weight, vocab_local, k, pair ? K2Cfg<true>::B_ROWS : K2Cfg<false>::B_ROWS);
   if (st != TOME_OK) return st;
   K2Params p = {};
   p.rows = rows;
@@ -473,12 +563,37 @@ static int32_t k2_launch(const void* hidden, const void* weight, int64_t rows, i
   p.gm = pl.gm;
   p.n_items = pl.n_items;
   p.status = dev_status;
-  st = check_cuda(cudaFuncSetAttribute(k2_lmhead_kernel,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, K2_SMEM_BYTES),
+  if (pair) {
+    constexpr int smem = K2Cfg<true>::SMEM_BYTES;
+    st = check_cuda(cudaFuncSetAttribute(k2_lmhead_kernel<true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+                    "cudaFuncSetAttribute(k2 pair)");
+    if (st != TOME_OK) return st;
+    const int pairs = static_cast<int>(
+        std::max<int64_t>(1, std::min<int64_t>(info.sm_count / 2, pl.n_items)));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(K2_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return check_cuda(cudaLaunchKernelEx(&cfg, k2_lmhead_kernel<true>, ta, tb, p),
+                      "k2 pair launch");
+  }
+  constexpr int smem = K2Cfg<false>::SMEM_BYTES;
+  st = check_cuda(cudaFuncSetAttribute(k2_lmhead_kernel<false>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                   "cudaFuncSetAttribute(k2)");
   if (st != TOME_OK) return st;
-  const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(info.sm_count, pl.n_items)));
-  k2_lmhead_kernel<<<grid, K2_THREADS, K2_SMEM_BYTES, stream>>>(ta, tb, p);
+  const int grid =
+      static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(info.sm_count, pl.n_items)));
+  k2_lmhead_kernel<false><<<grid, K2_THREADS, smem, stream>>>(ta, tb, p);
   return check_cuda(cudaGetLastError(), "k2 launch");
 }
 
