@@ -34,8 +34,8 @@ METRIC = "selective_logprob_rows_per_s"
 UNIT = "rows/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the headline kernel, taken from
-# the ncu capture summarised in profiles/ (None until a capture exists).
-NCU_TRAFFIC_BYTES = None
+# the ncu capture summarised in profiles/k1_stream_selective_bf16_2048x151936.md.
+NCU_TRAFFIC_BYTES = 6_258_690_560  # (622.46 + 3.41) MB at 2048 rows, scaled x10 by rows
 
 
 def measured_peaks():
@@ -401,14 +401,47 @@ def run_extra(args, device, rank, world, dist_on, barrier, peaks):
     hidden, weight, ids = synthetic.cfg3_lm_head(16384, 1024, VOCAB, device)
     ws = torch.empty(tome_b200.lm_head_workspace_bytes(16384, 1024, VOCAB), dtype=torch.uint8,
                      device=device)
-    ms, launch = timed(lambda: tome_b200.lm_head_logprob(hidden, weight, ids, 1.0, workspace=ws))
+    sampler3 = ClockSampler(physical_gpu_index(device.index)) if rank == 0 else None
+    total, per = timed_steps(lambda: tome_b200.lm_head_logprob(hidden, weight, ids, 1.0, workspace=ws),
+                             steps, warm, barrier, sampler3)
+    ms, launch = max_over_ranks(total, dist_on, device) / steps, sum(per) / len(per)
     flops = 2.0 * 16384 * VOCAB * 1024
     extra["cfg3_lm_head"] = {"rows": 16384, "hidden": 1024, "ms": ms,
                              "rows_per_s": 16384 / (ms * 1e-3), "TFLOPs": flops / ms / 1e9,
                              "frac_of_measured_bf16": flops / ms / 1e9 / peaks["bf16_tflops"],
+                             "frac_of_measured_bf16_sustained":
+                                 flops / ms / 1e9 / peaks["bf16_tflops_sustained"],
                              "frac_of_nominal_2250": flops / ms / 1e9 / 2250.0,
-                             "launches_per_step": 2}
+                             "launches_per_step": 2,
+                             "clocks": sampler3.summary() if sampler3 is not None else None}
+    # the unfused pipeline on the same inputs, for context: cuBLAS GEMM that materialises the
+    # bf16 logits (4.98 GB), then the streaming selective kernel over them
+    if rank == 0 or dist_on:
+        logits_buf = torch.empty((16384, VOCAB), dtype=torch.bfloat16, device=device)
+        ms_gemm, _ = timed(lambda: torch.matmul(hidden, weight.t(), out=logits_buf))
+
+        def unfused():
+            torch.matmul(hidden, weight.t(), out=logits_buf)
+            tome_b200.local_compute_logprobs(logits_buf, ids, 1.0)
+
+        ms_unfused, _ = timed(unfused)
+        extra["cfg3_lm_head"]["context_cublas_gemm_only_ms"] = ms_gemm
+        extra["cfg3_lm_head"]["context_cublas_gemm_only_TFLOPs"] = flops / ms_gemm / 1e9
+        extra["cfg3_lm_head"]["context_unfused_gemm_then_selective_ms"] = ms_unfused
+        del logits_buf
     del hidden, weight, ids, ws
+    torch.cuda.empty_cache()
+
+    # full-matrix compatibility kernel: the reference's decode-loop shape (64 x V fp32) and a
+    # larger bf16 case; algorithmic bytes = read + write of the matrix
+    for name, rows_f, dt in (("full_fp32_64rows", 64, torch.float32),
+                             ("full_bf16_4096rows", 4096, torch.bfloat16)):
+        xf = (torch.randn((rows_f, VOCAB), device=device, dtype=torch.float32) * 2.0).to(dt)
+        ms_f, launch_f = timed(lambda: tome_b200.fused_log_softmax(xf, 1.0))
+        nbytes = 2 * rows_f * VOCAB * xf.element_size()
+        extra[name] = {"rows": rows_f, "ms": ms_f, "GBps": nbytes / launch_f / 1e6,
+                       "note": "includes torch's allocation of the output matrix"}
+        del xf
     torch.cuda.empty_cache()
 
     # cfg4: vocab-parallel head over the N ranks, strong scaling (total work fixed)
@@ -449,16 +482,20 @@ def run_only(args):
         work, unit = rows * VOCAB * 2 + rows * 8, "GB/s"
     else:
         rows = args.rows or 16384
-        hidden, weight, ids = synthetic.cfg3_lm_head(rows, 1024, VOCAB, device)
-        ws = torch.empty(tome_b200.lm_head_workspace_bytes(rows, 1024, VOCAB), dtype=torch.uint8,
-                         device=device)
+        hidden, weight, ids = synthetic.cfg3_lm_head(rows, args.hidden, VOCAB, device)
+        ws = torch.empty(tome_b200.lm_head_workspace_bytes(rows, args.hidden, VOCAB),
+                         dtype=torch.uint8, device=device)
         fn = lambda: tome_b200.lm_head_logprob(hidden, weight, ids, 1.0, workspace=ws)  # noqa: E731
-        work, unit = 2.0 * rows * VOCAB * 1024, "TFLOP/s"
-    total, per = timed_steps(fn, args.steps, args.warmup, lambda: None)
+        work, unit = 2.0 * rows * VOCAB * args.hidden, "TFLOP/s"
+    sampler = ClockSampler(physical_gpu_index(0))
+    total, per = timed_steps(fn, args.steps, args.warmup, lambda: None, sampler)
     tome_b200.check_device_status(device)
     ms = sum(per) / len(per)
     rate = work / ms / (1e6 if unit == "GB/s" else 1e9)
-    out = {"only": args.only, "rows": rows, "ms": ms, "rate": rate, "unit": unit}
+    sp = sorted(per)
+    out = {"only": args.only, "rows": rows, "ms": ms, "rate": rate, "unit": unit,
+           "ms_first": per[0], "ms_last": per[-1], "ms_min": sp[0], "ms_median": sp[len(sp) // 2],
+           "clocks": sampler.summary()}
     if args.only == "selective":  # the timed kernel's result against a torch reduction
         sample = torch.arange(0, rows, max(1, rows // 256), device=device)
         ref = torch.log_softmax(x[sample].float(), dim=-1).gather(
@@ -478,6 +515,7 @@ def main():
     ap.add_argument("--only", choices=["selective", "lmhead"], default=None,
                     help="profiling aid: run just one kernel's loop (no e2e, extras or CPU leg)")
     ap.add_argument("--rows", type=int, default=None, help="row count for --only (small cases)")
+    ap.add_argument("--hidden", type=int, default=1024, help="hidden size for --only lmhead")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args, int(os.environ.get("RANK", "0")))
