@@ -482,11 +482,11 @@ def run_only(args):
         work, unit = rows * VOCAB * 2 + rows * 8, "GB/s"
     else:
         rows = args.rows or 16384
-        hidden, weight, ids = synthetic.cfg3_lm_head(rows, args.hidden, VOCAB, device)
-        ws = torch.empty(tome_b200.lm_head_workspace_bytes(rows, args.hidden, VOCAB),
+        hidden, weight, ids = synthetic.cfg3_lm_head(rows, args.hidden, args.vocab, device)
+        ws = torch.empty(tome_b200.lm_head_workspace_bytes(rows, args.hidden, args.vocab),
                          dtype=torch.uint8, device=device)
         fn = lambda: tome_b200.lm_head_logprob(hidden, weight, ids, 1.0, workspace=ws)  # noqa: E731
-        work, unit = 2.0 * rows * VOCAB * args.hidden, "TFLOP/s"
+        work, unit = 2.0 * rows * args.vocab * args.hidden, "TFLOP/s"
     sampler = ClockSampler(physical_gpu_index(0))
     total, per = timed_steps(fn, args.steps, args.warmup, lambda: None, sampler)
     tome_b200.check_device_status(device)
@@ -516,6 +516,7 @@ def main():
                     help="profiling aid: run just one kernel's loop (no e2e, extras or CPU leg)")
     ap.add_argument("--rows", type=int, default=None, help="row count for --only (small cases)")
     ap.add_argument("--hidden", type=int, default=1024, help="hidden size for --only lmhead")
+    ap.add_argument("--vocab", type=int, default=VOCAB, help="vocabulary (shard) size for --only")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args, int(os.environ.get("RANK", "0")))

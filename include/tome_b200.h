@@ -139,17 +139,30 @@ int32_t tome_dual_logprob_kl(const void* policy_logits, const void* ref_logits, 
  */
 size_t tome_lmhead_workspace_bytes(int64_t rows, int64_t hidden_dim, int64_t vocab_local);
 
+/* flags of the fused LM-head calls */
+#define TOME_LMHEAD_ROUND_LOGITS_BF16 1 /* round each logit to bf16 before reducing, as the
+                                           reference's materialised bf16 logits are (model.py:538) */
+
 int32_t tome_lmhead_partials(const void* hidden, const void* weight, int64_t rows,
                              int64_t hidden_dim, int64_t vocab_local, int64_t vocab_offset,
-                             const int32_t* targets, float temperature, float* out_m,
-                             float* out_s, float* out_t, void* workspace, size_t workspace_bytes,
-                             int32_t* dev_status, void* stream);
+                             const int32_t* targets, float temperature, int32_t flags,
+                             float* out_m, float* out_s, float* out_t, void* workspace,
+                             size_t workspace_bytes, int32_t* dev_status, void* stream);
 
 int32_t tome_lmhead_logprob(const void* hidden, const void* weight, int64_t rows,
                             int64_t hidden_dim, int64_t vocab, const int32_t* targets,
-                            float temperature, float* out_logprob, float* out_lse,
-                            void* workspace, size_t workspace_bytes, int32_t* dev_status,
-                            void* stream);
+                            float temperature, int32_t flags, float* out_logprob,
+                            float* out_lse, void* workspace, size_t workspace_bytes,
+                            int32_t* dev_status, void* stream);
+
+/*
+ * Final RMSNorm of the model, the step before the head (RMSNorm, mlx-impl/model.py:336-343,
+ * applied at model.py:536): out = bf16(float(x) * rsqrt(mean(x^2) + eps) * float(weight)).
+ *   x, out  device bf16 [rows, dim], contiguous, 16-byte aligned (may not alias), dim % 8 == 0
+ *   weight  device bf16 [dim]
+ */
+int32_t tome_rmsnorm_bf16(const void* x, const void* weight, int64_t rows, int64_t dim, float eps,
+                          void* out, void* stream);
 
 /*
  * tome_lmhead_logprob without a workspace argument and without any allocation.

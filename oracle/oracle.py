@@ -122,6 +122,18 @@ def log_softmax_metal_order(logits, temp: float = 1.0) -> torch.Tensor:
     return (scaled.to(torch.float32) - lse.to(torch.float32)).to(T)
 
 
+def rms_norm(x, weight, eps: float = 1e-6) -> torch.Tensor:
+    """mlx-impl/model.py:336-343 (``mx.fast.rms_norm(x, weight, eps)``), applied to the last
+    hidden states at model.py:536: ``x * rsqrt(mean(x^2) + eps) * weight`` in fp32, rounded once
+    to the input dtype.  (Where MLX's kernel places its casts is not visible from the
+    reference; results can differ from it by one bf16 ulp.)"""
+    if isinstance(x, np.ndarray):
+        x = torch.from_numpy(x)
+    x32 = _f32(x)
+    inv = torch.rsqrt((x32 * x32).mean(dim=-1, keepdim=True) + torch.tensor(eps, dtype=torch.float32))
+    return (x32 * inv * _f32(weight)).to(x.dtype)
+
+
 def lm_head_logits(hidden, weight, round_to_bf16: bool = False) -> torch.Tensor:
     """mlx-impl/model.py:538: ``x @ embed_tokens.weight.T`` with bf16 operands and fp32
     accumulation.  ``round_to_bf16`` reproduces the materialised bf16 logits of the

@@ -57,14 +57,15 @@ def test_argument_errors_are_caught_on_the_host(built_lib):
     assert lib.tome_dual_logprob_kl(fake, fake, 1, 5000, 4, 16, 16, fake, fake, None, 1.0, fake,
                                     fake, fake, None, None) == -9
     # fused head: hidden size must keep rows 16-byte aligned
-    assert lib.tome_lmhead_logprob(fake, fake, 4, 12, 64, fake, 1.0, fake, None, fake, 1 << 20,
+    assert lib.tome_lmhead_logprob(fake, fake, 4, 12, 64, fake, 1.0, 0, fake, None, fake, 1 << 20,
                                    None, None) == -8
     # fused head: workspace too small
     need = lib.tome_lmhead_workspace_bytes(256, 64, 1000)
     assert need > 0
-    assert lib.tome_lmhead_logprob(fake, fake, 256, 64, 1000, fake, 1.0, fake, None, fake,
+    assert lib.tome_lmhead_logprob(fake, fake, 256, 64, 1000, fake, 1.0, 0, fake, None, fake,
                                    need - 1, None, None) == -6
     assert b"workspace" in lib.tome_last_error_string()
+    assert lib.tome_rmsnorm_bf16(fake, fake, 4, 12, 1e-6, fake, None) == -8
     with pytest.raises(_lib.TomeArgumentError):
         _lib.check(-6)
     assert lib.tome_combine_triples(fake, fake, 2, 3, fake, 2, 1, 8, fake, None, None) == -5

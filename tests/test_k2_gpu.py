@@ -124,6 +124,46 @@ def test_caller_workspace_and_size_check(cuda_device):
                                   1.0, workspace=ws[: need - 16])
 
 
+def test_final_rmsnorm_and_model_tail(cuda_device):
+    """RMSNorm kernel against the oracle (one bf16 ulp), then norm + head + log-prob in one
+    call against the oracle's tail of Qwen3.__call__ (model.py:536-538)."""
+    import tome_b200
+    g = torch.Generator().manual_seed(50)
+    x = (torch.randn((300, 1024), generator=g) * 3).to(torch.bfloat16)
+    w = (1.0 + 0.1 * torch.randn((1024,), generator=g)).to(torch.bfloat16)
+    y = tome_b200.rms_norm(x.to(cuda_device), w.to(cuda_device), 1e-6)
+    ref = oracle.rms_norm(x, w, 1e-6)
+    assert y.dtype == torch.bfloat16 and y.shape == x.shape
+    rel = ((y.cpu().float() - ref.float()).abs() / ref.float().abs().clamp_min(1e-3)).max()
+    assert float(rel) <= 2 ** -7, float(rel)   # at most one bf16 ulp
+    assert float((y.cpu() == ref).float().mean()) > 0.99
+    weight = (torch.randn((3000, 1024), generator=g) * 0.02).to(torch.bfloat16)
+    ids = torch.randint(0, 3000, (300,), generator=g, dtype=torch.int32)
+    lp, lse = tome_b200.lm_head_logprob(x.to(cuda_device), weight.to(cuda_device), ids.to(cuda_device),
+                                        0.7, norm_weight=w.to(cuda_device), eps=1e-6)
+    o_lp, o_lse = oracle.lm_head_logprob(ref, weight, ids, 0.7)
+    assert max_abs(lp, o_lp) <= 5e-3 and max_abs(lse, o_lse) <= 5e-3  # norm may differ by an ulp
+
+
+def test_bf16_rounded_logits_switch(cuda_device):
+    """round_logits=True must reproduce the oracle evaluated on bf16-rounded logits (the
+    reference's materialised path), which differs visibly from the un-rounded result."""
+    import tome_b200
+    from tome_b200 import synthetic
+    hidden, weight, ids = synthetic.cfg3_lm_head(260, 512, 5000, "cpu", 51, 0.05)
+    hd, wd, idd = hidden.to(cuda_device), weight.to(cuda_device), ids.to(cuda_device)
+    lp_r, lse_r = tome_b200.lm_head_logprob(hd, wd, idd, 1.0, round_logits=True)
+    o_lp_r, o_lse_r = oracle.lm_head_logprob(hidden, weight, ids, 1.0, round_to_bf16=True)
+    # a logit that sits on a bf16 rounding boundary may round the other way on the GPU
+    # (different fp32 summation order): allow one bf16 ulp of the target logit
+    assert max_abs(lse_r, o_lse_r) <= TOL
+    assert max_abs(lp_r, o_lp_r) <= TOL + 2 ** -6
+    lp_u, _ = tome_b200.lm_head_logprob(hd, wd, idd, 1.0)
+    o_lp_u, _ = oracle.lm_head_logprob(hidden, weight, ids, 1.0)
+    assert max_abs(lp_u, o_lp_u) <= TOL
+    assert max_abs(o_lp_r, o_lp_u) > TOL  # the switch matters
+
+
 def test_single_cta_tiles_variant(cuda_device):
     """TOME_K2_PAIR=0 selects the cta_group::1 kernel (read once per process): child process."""
     import os

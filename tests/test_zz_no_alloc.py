@@ -23,7 +23,7 @@ def _call_pair(lib, hidden, weight, ids, temp, stream):
     ref_lp = torch.empty(rows, dtype=torch.float32, device=dev)
     ref_lse = torch.empty_like(ref_lp)
     st = lib.tome_lmhead_logprob(hidden.data_ptr(), weight.data_ptr(), rows, k, vocab,
-                                 ids.data_ptr(), temp, ref_lp.data_ptr(), ref_lse.data_ptr(),
+                                 ids.data_ptr(), temp, 0, ref_lp.data_ptr(), ref_lse.data_ptr(),
                                  ws.data_ptr(), need, None, stream)
     assert st == 0, lib.tome_last_error_string()
     lp = torch.full((rows,), float("nan"), dtype=torch.float32, device=dev)

@@ -17,6 +17,8 @@ TOME_BF16 = 1
 DEV_TARGET_OUT_OF_RANGE = 1
 DEV_TIMEOUT = 2
 
+LMHEAD_ROUND_LOGITS_BF16 = 1
+
 # name -> (restype, argtypes); mirrors include/tome_b200.h one to one
 SIGNATURES = {
     "tome_version": (c_int32, []),
@@ -32,11 +34,13 @@ SIGNATURES = {
                                        c_void_p, c_void_p, c_void_p, c_void_p]),
     "tome_lmhead_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "tome_lmhead_partials": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
-                                       c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
-                                       c_size_t, c_void_p, c_void_p]),
+                                       c_void_p, c_float, c_int32, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_size_t, c_void_p, c_void_p]),
     "tome_lmhead_logprob": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p,
-                                      c_float, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p,
-                                      c_void_p]),
+                                      c_float, c_int32, c_void_p, c_void_p, c_void_p, c_size_t,
+                                      c_void_p, c_void_p]),
+    "tome_rmsnorm_bf16": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_float, c_void_p,
+                                    c_void_p]),
     "tome_lmhead_static_scratch_bytes": (c_size_t, []),
     "tome_lmhead_logprob_static": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                              c_void_p, c_float, c_void_p, c_void_p, c_void_p,

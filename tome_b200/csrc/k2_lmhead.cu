@@ -22,6 +22,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <float.h>
+#include <stdint.h>
 #include <stdlib.h>
 
 #include <algorithm>
@@ -75,6 +76,7 @@ struct K2Params {
   int32_t n_bands;
   int32_t gm;              // row tiles per group
   int64_t n_items;
+  int32_t round_bf16;      // round every logit to bf16 before the reduction
   int32_t* status;
 };
 
@@ -333,6 +335,13 @@ k2_lmhead_kernel(const __grid_constant__ CUtensorMap tmap_a,
             tmem_ld_wait_dep(buf[ch & 1]);
             if (ch + 1 < n_chunks) tmem_ld32(taddr + (ch + 1) * 32, buf[(ch + 1) & 1]);
             uint32_t(&v)[32] = buf[ch & 1];
+            if (p.round_bf16) {
+              // what the reference reduces are logits already rounded to bf16 (model.py:538)
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                v[j] = __float_as_uint(
+                    __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[j]))));
+            }
             const int32_t valid = n_valid - ch * 32;
             if (valid < 32) {
 #pragma unroll
@@ -456,34 +465,75 @@ struct K2Plan {
   int64_t n_items;
 };
 
-// item_rows: rows of a work item's row tile (128 single-CTA, 256 CTA pair).  The number of
-// bands, hence the workspace size, does not depend on it.
+// Row tiles per group: the hidden tiles of a group (about 40 MB) stay L2-resident while the
+// group sweeps the vocabulary.
+static int32_t k2_group_size(int32_t m_tiles, int64_t k, int item_rows) {
+  const int64_t a_bytes = static_cast<int64_t>(item_rows) * k * 2;
+  int64_t gm = std::max<int64_t>(1, (40ll << 20) / std::max<int64_t>(a_bytes, 1));
+  if (gm >= m_tiles) return m_tiles;
+  // a divisor of the number of concurrent workers keeps a wave on whole bands
+  if (gm >= 148 && item_rows == K2_BM) return 148;
+  if (gm >= 74) return 74;
+  if (gm >= 37) return 37;
+  return static_cast<int32_t>(gm);
+}
+
+// Largest per-worker load (in column tiles) when the items, in launch order, are dealt
+// round-robin to `workers` persistent workers.
+static int64_t k2_makespan(int32_t m_tiles, int32_t n_tiles, int32_t nb, int32_t gm,
+                           int32_t workers) {
+  const int32_t n_bands = (n_tiles + nb - 1) / nb;
+  const int32_t tail = n_tiles - (n_bands - 1) * nb;
+  int64_t loads[256] = {0};
+  const int32_t W = std::min<int32_t>(workers, 256);
+  int64_t idx = 0;
+  auto deal = [&](int64_t len, int64_t size) {
+    if (len <= 0) return;
+    for (int32_t w = 0; w < W; ++w) {
+      const int64_t first = idx + ((w - idx % W) + W) % W;
+      if (first < idx + len) loads[w] += ((idx + len - 1 - first) / W + 1) * size;
+    }
+    idx += len;
+  };
+  for (int32_t g0 = 0; g0 < m_tiles; g0 += gm) {
+    const int64_t gm_here = std::min<int32_t>(gm, m_tiles - g0);
+    deal(static_cast<int64_t>(n_bands - 1) * gm_here, nb);
+    deal(gm_here, tail);
+  }
+  int64_t worst = 0;
+  for (int32_t w = 0; w < W; ++w) worst = std::max(worst, loads[w]);
+  return worst;
+}
+
+// Work decomposition for one problem size.  item_rows: rows of a work item's row tile (128
+// single-CTA, 256 CTA pair).  The number of bands, hence the workspace size, must not depend
+// on the device or on item_rows, so it is planned for 148 workers of 128-row tiles.
 static K2Plan k2_plan(int64_t rows, int64_t k, int64_t vocab_local, int item_rows = K2_BM) {
   K2Plan pl;
-  pl.m_tiles = static_cast<int32_t>((rows + item_rows - 1) / item_rows);
   pl.n_tiles = static_cast<int32_t>((vocab_local + K2_BN - 1) / K2_BN);
   pl.k_blocks = static_cast<int32_t>((k + K2_BK - 1) / K2_BK);
-  // band: about 16 MB of weight rows, between 2 and 32 column tiles
+  // band length: at most about 16 MB of weight rows (2..32 column tiles); among those the
+  // longest one whose round-robin schedule is within 0.2 % of the best balanced
   const int64_t tile_bytes = static_cast<int64_t>(K2_BN) * k * 2;
-  int64_t nb = (16ll << 20) / std::max<int64_t>(tile_bytes, 1);
-  nb = std::max<int64_t>(2, std::min<int64_t>(32, nb));
-  pl.nb = static_cast<int32_t>(std::min<int64_t>(nb, pl.n_tiles));
-  pl.n_bands = (pl.n_tiles + pl.nb - 1) / pl.nb;
-  // row-tile group: hidden tiles of a group stay in L2 (about 40 MB)
-  const int64_t a_bytes = static_cast<int64_t>(item_rows) * k * 2;
-  int64_t gm = (40ll << 20) / std::max<int64_t>(a_bytes, 1);
-  gm = std::max<int64_t>(1, gm);
-  if (gm < pl.m_tiles) {
-    // a divisor of the number of concurrent workers (148 CTAs or 74 pairs) keeps a wave
-    // on whole bands
-    const int64_t unit = (item_rows == K2_BM) ? 37 : 37;
-    if (gm >= 4 * unit && item_rows == K2_BM) gm = 4 * unit;
-    else if (gm >= 2 * unit) gm = 2 * unit;
-    else if (gm >= unit) gm = unit;
-  } else {
-    gm = pl.m_tiles;
+  int64_t nb_max = (16ll << 20) / std::max<int64_t>(tile_bytes, 1);
+  nb_max = std::max<int64_t>(2, std::min<int64_t>(32, nb_max));
+  nb_max = std::min<int64_t>(nb_max, pl.n_tiles);
+  const int32_t plan_tiles = static_cast<int32_t>((rows + K2_BM - 1) / K2_BM);
+  const int32_t plan_gm = k2_group_size(plan_tiles, k, K2_BM);
+  int64_t best = INT64_MAX;
+  const int32_t nb_min = static_cast<int32_t>(std::min<int64_t>(2, nb_max));
+  for (int32_t nb = static_cast<int32_t>(nb_max); nb >= nb_min; --nb)
+    best = std::min(best, k2_makespan(plan_tiles, pl.n_tiles, nb, plan_gm, 148));
+  pl.nb = nb_min;
+  for (int32_t nb = static_cast<int32_t>(nb_max); nb >= nb_min; --nb) {
+    if (k2_makespan(plan_tiles, pl.n_tiles, nb, plan_gm, 148) * 500 <= best * 501) {
+      pl.nb = nb;
+      break;
+    }
   }
-  pl.gm = static_cast<int32_t>(gm);
+  pl.n_bands = (pl.n_tiles + pl.nb - 1) / pl.nb;
+  pl.m_tiles = static_cast<int32_t>((rows + item_rows - 1) / item_rows);
+  pl.gm = k2_group_size(pl.m_tiles, k, item_rows);
   pl.n_items = static_cast<int64_t>(pl.m_tiles) * pl.n_bands;
   return pl;
 }
@@ -512,12 +562,13 @@ static int32_t k2_check(const void* hidden, const void* weight, int64_t rows, in
   return TOME_OK;
 }
 
-// Tuning knob TOME_K2_PAIR = 0 | 1: single-CTA tiles (cta_group::1) or CTA-pair tiles
-// (cta_group::2, the default).  Read once per process.
+// Tuning knob TOME_K2_PAIR = 0 | 1: single-CTA tiles (cta_group::1, the default) or CTA-pair
+// tiles (cta_group::2).  Under the board power cap the single-CTA form measured 1-9 % faster
+// on both head shapes, so it is the default.  Read once per process.
 static bool k2_pair_setting() {
   static const bool value = [] {
     const char* e = getenv("TOME_K2_PAIR");
-    return (e != nullptr) ? (atoi(e) != 0) : true;
+    return (e != nullptr) ? (atoi(e) != 0) : false;
   }();
   return value;
 }
@@ -525,8 +576,9 @@ static bool k2_pair_setting() {
 // Launches the GEMM+reduce kernel; partial triples land in the workspace.
 static int32_t k2_launch(const void* hidden, const void* weight, int64_t rows, int64_t k,
                          int64_t vocab_local, int64_t vocab_offset, int64_t vocab_check,
-                         const int32_t* targets, float temperature, void* workspace,
-                         int32_t* dev_status, cudaStream_t stream, K2Plan* plan_out) {
+                         const int32_t* targets, float temperature, int32_t flags,
+                         void* workspace, int32_t* dev_status, cudaStream_t stream,
+                         K2Plan* plan_out) {
   DeviceInfo info;
   int32_t st = current_device_info(&info);
   if (st != TOME_OK) return st;
@@ -562,6 +614,7 @@ static int32_t k2_launch(const void* hidden, const void* weight, int64_t rows, i
   p.n_bands = pl.n_bands;
   p.gm = pl.gm;
   p.n_items = pl.n_items;
+  p.round_bf16 = (flags & TOME_LMHEAD_ROUND_LOGITS_BF16) ? 1 : 0;
   p.status = dev_status;
   if (pair) {
     constexpr int smem = K2Cfg<true>::SMEM_BYTES;
@@ -611,9 +664,10 @@ extern "C" size_t tome_lmhead_workspace_bytes(int64_t rows, int64_t hidden_dim,
 extern "C" int32_t tome_lmhead_partials(const void* hidden, const void* weight, int64_t rows,
                                         int64_t hidden_dim, int64_t vocab_local,
                                         int64_t vocab_offset, const int32_t* targets,
-                                        float temperature, float* out_m, float* out_s,
-                                        float* out_t, void* workspace, size_t workspace_bytes,
-                                        int32_t* dev_status, void* stream) {
+                                        float temperature, int32_t flags, float* out_m,
+                                        float* out_s, float* out_t, void* workspace,
+                                        size_t workspace_bytes, int32_t* dev_status,
+                                        void* stream) {
   int32_t st = k2_check(hidden, weight, rows, hidden_dim, vocab_local, vocab_offset, targets,
                         temperature, workspace, workspace_bytes);
   if (st != TOME_OK || rows == 0) return st;
@@ -622,7 +676,7 @@ extern "C" int32_t tome_lmhead_partials(const void* hidden, const void* weight, 
   K2Plan pl;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   st = k2_launch(hidden, weight, rows, hidden_dim, vocab_local, vocab_offset, 0, targets,
-                 temperature, workspace, dev_status, s, &pl);
+                 temperature, flags, workspace, dev_status, s, &pl);
   if (st != TOME_OK) return st;
   const float* ws = static_cast<const float*>(workspace);
   const int64_t plane = static_cast<int64_t>(pl.n_bands) * rows;
@@ -632,8 +686,8 @@ extern "C" int32_t tome_lmhead_partials(const void* hidden, const void* weight, 
 
 extern "C" int32_t tome_lmhead_logprob(const void* hidden, const void* weight, int64_t rows,
                                        int64_t hidden_dim, int64_t vocab, const int32_t* targets,
-                                       float temperature, float* out_logprob, float* out_lse,
-                                       void* workspace, size_t workspace_bytes,
+                                       float temperature, int32_t flags, float* out_logprob,
+                                       float* out_lse, void* workspace, size_t workspace_bytes,
                                        int32_t* dev_status, void* stream) {
   int32_t st = k2_check(hidden, weight, rows, hidden_dim, vocab, 0, targets, temperature,
                         workspace, workspace_bytes);
@@ -641,13 +695,82 @@ extern "C" int32_t tome_lmhead_logprob(const void* hidden, const void* weight, i
   if (out_logprob == nullptr) return fail(TOME_ERR_NULL_POINTER, "out_logprob is NULL");
   K2Plan pl;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  st = k2_launch(hidden, weight, rows, hidden_dim, vocab, 0, vocab, targets, temperature,
+  st = k2_launch(hidden, weight, rows, hidden_dim, vocab, 0, vocab, targets, temperature, flags,
                  workspace, dev_status, s, &pl);
   if (st != TOME_OK) return st;
   const float* ws = static_cast<const float*>(workspace);
   const int64_t plane = static_cast<int64_t>(pl.n_bands) * rows;
   return launch_combine(true, ws, ws + plane, rows, pl.n_bands, ws + 2 * plane, rows, pl.n_bands,
                         rows, out_logprob, out_lse, nullptr, s);
+}
+
+// ------------------------------------------------------------------ final RMSNorm
+// y = bf16(float(x) * rsqrt(mean(x^2) + eps) * float(w)), one warp per row, fp32 arithmetic:
+// the model's last step before the head (mlx-impl/model.py:336-343, 536), so that the fused
+// head can be fed from the un-normalised hidden states.
+__global__ void __launch_bounds__(256) k2_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x,
+                                                         const __nv_bfloat16* __restrict__ w,
+                                                         int64_t rows, int64_t dim, float eps,
+                                                         __nv_bfloat16* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t nvec = dim >> 3;  // dim is a multiple of 8
+  for (int64_t row = warp_global; row < rows; row += n_warps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * dim);
+    float ss = 0.0f;
+    for (int64_t v = lane; v < nvec; v += 32) {
+      const uint4 q = xr[v];
+      const uint32_t ws[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float a = __uint_as_float(ws[j] << 16), b = __uint_as_float(ws[j] & 0xffff0000u);
+        ss = fmaf(a, a, ss);
+        ss = fmaf(b, b, ss);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = rsqrtf(ss / static_cast<float>(dim) + eps);
+    uint4* orow = reinterpret_cast<uint4*>(out + row * dim);
+    const uint4* wr = reinterpret_cast<const uint4*>(w);
+    for (int64_t v = lane; v < nvec; v += 32) {
+      const uint4 q = xr[v];
+      const uint4 g = wr[v];
+      const uint32_t xs[4] = {q.x, q.y, q.z, q.w};
+      const uint32_t gs[4] = {g.x, g.y, g.z, g.w};
+      uint32_t os[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float a = __uint_as_float(xs[j] << 16) * inv * __uint_as_float(gs[j] << 16);
+        const float b =
+            __uint_as_float(xs[j] & 0xffff0000u) * inv * __uint_as_float(gs[j] & 0xffff0000u);
+        os[j] = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(a))) |
+                (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(b))) << 16);
+      }
+      orow[v] = make_uint4(os[0], os[1], os[2], os[3]);
+    }
+  }
+}
+
+extern "C" int32_t tome_rmsnorm_bf16(const void* x, const void* weight, int64_t rows, int64_t dim,
+                                     float eps, void* out, void* stream) {
+  if (rows < 0 || dim <= 0)
+    return fail(TOME_ERR_BAD_SHAPE, "rows=%lld dim=%lld", (long long)rows, (long long)dim);
+  if (dim % 8 != 0)
+    return fail(TOME_ERR_UNSUPPORTED, "dim=%lld must be a multiple of 8", (long long)dim);
+  if (!(eps >= 0.0f)) return fail(TOME_ERR_BAD_SHAPE, "eps=%g must be >= 0", eps);
+  if (rows == 0) return TOME_OK;
+  if (x == nullptr || weight == nullptr || out == nullptr)
+    return fail(TOME_ERR_NULL_POINTER, "a required pointer is NULL");
+  if (!aligned16(x) || !aligned16(weight) || !aligned16(out))
+    return fail(TOME_ERR_MISALIGNED, "x, weight and out must be 16-byte aligned");
+  const int64_t want = (rows + 7) / 8;  // 8 warps (rows) per CTA
+  const int grid = static_cast<int>(std::min<int64_t>(want, 148 * 16));
+  k2_rmsnorm_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight), rows, dim,
+      eps, static_cast<__nv_bfloat16*>(out));
+  return check_cuda(cudaGetLastError(), "rmsnorm launch");
 }
 
 // ------------------------------------------------------------------ no-allocation variant
@@ -703,7 +826,7 @@ extern "C" int32_t tome_lmhead_logprob_static(const void* hidden, const void* we
   } else {
     scratch = reinterpret_cast<void*>(static_cast<uintptr_t>(256));  // never used when rows == 0
   }
-  return tome_lmhead_logprob(hidden, weight, rows, hidden_dim, vocab, targets, temperature,
+  return tome_lmhead_logprob(hidden, weight, rows, hidden_dim, vocab, targets, temperature, 0,
                              out_logprob, out_lse, scratch, K2_STATIC_SCRATCH_BYTES, dev_status,
                              stream);
 }

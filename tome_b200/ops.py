@@ -264,9 +264,35 @@ def _workspace(nbytes: int, device: torch.device, workspace: Optional[torch.Tens
     return torch.empty(max(nbytes, 16), dtype=torch.uint8, device=device)
 
 
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """The model's final RMSNorm (mlx-impl/model.py:336-343, applied at :536), bf16 in/out,
+    fp32 arithmetic: ``x * rsqrt(mean(x^2) + eps) * weight``."""
+    _require_cuda("x", x)
+    _require_cuda("weight", weight)
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise TypeError("x and weight must be bfloat16")
+    dim = x.shape[-1]
+    if weight.shape != (dim,):
+        raise ValueError(f"weight must have shape ({dim},)")
+    x2 = x.reshape(-1, dim)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    w = weight if weight.is_contiguous() else weight.contiguous()
+    out = torch.empty_like(x2)
+    with torch.cuda.device(x2.device):
+        status = lib.tome_rmsnorm_bf16(x2.data_ptr(), w.data_ptr(), x2.shape[0], dim, float(eps),
+                                       out.data_ptr(), _stream(x2.device))
+    _lib.check(status)
+    return out.reshape(x.shape)
+
+
+def _head_flags(round_logits: bool) -> int:
+    return _lib.LMHEAD_ROUND_LOGITS_BF16 if round_logits else 0
+
+
 def lm_head_partials(hidden: torch.Tensor, weight_shard: torch.Tensor, vocab_offset: int,
                      ids: torch.Tensor, temp: float = 1.0, *,
-                     workspace: Optional[torch.Tensor] = None):
+                     workspace: Optional[torch.Tensor] = None, round_logits: bool = False):
     """Per-row triple ``(m, s, t)`` of one vocabulary shard of the LM head (fp32 ``[rows]`` each).
 
     ``m = max_j(x_j)/temp``, ``s = sum_j exp(x_j/temp - m)``, ``t = x_target/temp`` if the
@@ -285,7 +311,7 @@ def lm_head_partials(hidden: torch.Tensor, weight_shard: torch.Tensor, vocab_off
     with torch.cuda.device(device):
         status = lib.tome_lmhead_partials(
             h2.data_ptr(), w2.data_ptr(), rows, K, V_local, int(vocab_offset), ids32.data_ptr(),
-            temp, m.data_ptr(), s.data_ptr(), t.data_ptr(), ws.data_ptr(),
+            temp, _head_flags(round_logits), m.data_ptr(), s.data_ptr(), t.data_ptr(), ws.data_ptr(),
             ws.numel() * ws.element_size(), _status_word(device).data_ptr(), _stream(device))
     _lib.check(status)
     return m, s, t
@@ -293,14 +319,22 @@ def lm_head_partials(hidden: torch.Tensor, weight_shard: torch.Tensor, vocab_off
 
 def lm_head_logprob(hidden: torch.Tensor, weight: torch.Tensor, ids: torch.Tensor,
                     temp: float = 1.0, *, workspace: Optional[torch.Tensor] = None,
-                    check: bool = False):
+                    norm_weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                    round_logits: bool = False, check: bool = False):
     """``(logprob, lse)`` of ``ids`` under ``softmax((hidden @ weight.T) / temp)``, fused.
 
     Replaces the LM head matmul (mlx-impl/model.py:538) followed by
     ``local_compute_logprobs`` (mlx-impl/node.py:400-404); the ``[rows, V]`` logits never
     exist in memory.  ``hidden`` is ``[..., K]`` bf16, ``weight`` ``[V, K]`` bf16 (the tied
     embedding), outputs are fp32 with the leading shape of ``hidden``.
+
+    ``norm_weight`` applies the model's final RMSNorm (mlx-impl/model.py:536) to ``hidden``
+    first, which makes the call a replacement for the whole tail of ``Qwen3.__call__``.
+    ``round_logits=True`` rounds every logit to bf16 before it is reduced, as the reference's
+    materialised bf16 logits are; the default reduces the un-rounded fp32 accumulators.
     """
+    if norm_weight is not None:
+        hidden = rms_norm(hidden, norm_weight, eps)
     h2, w2 = _lm_head_inputs(hidden, weight)
     temp = float(temp or 1.0)
     rows, K = h2.shape
@@ -313,8 +347,9 @@ def lm_head_logprob(hidden: torch.Tensor, weight: torch.Tensor, ids: torch.Tenso
     lse = torch.empty(rows, dtype=torch.float32, device=device)
     with torch.cuda.device(device):
         status = lib.tome_lmhead_logprob(
-            h2.data_ptr(), w2.data_ptr(), rows, K, V, ids32.data_ptr(), temp, lp.data_ptr(),
-            lse.data_ptr(), ws.data_ptr(), ws.numel() * ws.element_size(),
+            h2.data_ptr(), w2.data_ptr(), rows, K, V, ids32.data_ptr(), temp,
+            _head_flags(round_logits), lp.data_ptr(), lse.data_ptr(), ws.data_ptr(),
+            ws.numel() * ws.element_size(),
             _status_word(device).data_ptr(), _stream(device))
     _lib.check(status)
     if check:
