@@ -53,6 +53,7 @@ enum tome_status {
 /* bits OR-ed into *dev_status by kernels */
 #define TOME_DEV_TARGET_OUT_OF_RANGE 1
 #define TOME_DEV_TIMEOUT 2
+#define TOME_DEV_RAGGED_OVERFLOW 4 /* windows cover more positions than the packed arrays hold */
 
 /* Library version (TOME_B200_VERSION of the build). */
 int32_t tome_version(void);
@@ -118,6 +119,57 @@ int32_t tome_dual_logprob_kl(const void* policy_logits, const void* ref_logits, 
                              const int32_t* starts, float temperature, float* out_lp_policy,
                              float* out_lp_ref, float* out_kl, int32_t* dev_status,
                              void* stream);
+
+/*
+ * Ragged selective log-softmax, packed to the wire layout: scores the window
+ * [starts[i], starts[i] + lengths[i]) of every sequence of ONE model and writes the results
+ * back to back, sequence after sequence, which is the layout of Completion.ref_log_probs
+ * (scheduler/proto/inference.proto:108-112).  Replaces the per-sequence loop of
+ * _process_ref_logprobs_batched (mlx-impl/node.py:446-458: slice, local_compute_logprobs,
+ * .tolist(), extend).
+ *
+ *   logits          device, [n_seq * seq_len, vocab], row stride row_stride
+ *   targets_packed  device int32 [packed_capacity]: the completion tokens of sequence 0, then of
+ *                   sequence 1, ... (one per scored position)
+ *   packed_capacity entries in targets_packed and in the packed outputs; if the windows cover
+ *                   more positions, only the first packed_capacity are scored and
+ *                   TOME_DEV_RAGGED_OVERFLOW is set
+ *   lengths, starts as in tome_dual_logprob_kl (starts nullable); n_seq <= 1024 per call
+ *   out_logprob_packed  device fp32 [packed_capacity]
+ *   out_lse_packed      device fp32 [packed_capacity] or NULL
+ *   out_offsets     device int32 [n_seq + 1] or NULL: offset of each sequence in the packed
+ *                   arrays (exclusive prefix sums of the clamped lengths)
+ * Rows outside the windows are never read.
+ */
+int32_t tome_ragged_logprob(const void* logits, int32_t dtype, int64_t n_seq, int64_t seq_len,
+                            int64_t vocab, int64_t row_stride, const int32_t* targets_packed,
+                            int64_t packed_capacity, const int32_t* lengths,
+                            const int32_t* starts, float temperature,
+                            float* out_logprob_packed, float* out_lse_packed,
+                            int32_t* out_offsets, int32_t* dev_status, void* stream);
+
+/*
+ * Top-k temperature sampling fused with the sampled token's log-prob, one row per sequence.
+ * Replaces the per-sequence host loop of the rollout (mlx-impl/node.py:593-610):
+ * _sample_token (node.py:894-907: top-k of logits / temperature, categorical draw) followed by
+ * float(fused_log_softmax(...)[b, token]) (node.py:590, 605), without a host round trip.
+ *
+ *   temperature  > 0: draw from softmax over the top_k logits / temperature; the log-prob is of
+ *                the FULL-vocabulary softmax at that temperature.  0: argmax (first maximum),
+ *                scored at temperature 1 (node.py:597-603 with "temperature or 1.0")
+ *   top_k        1..64 (the reference uses 20); clipped to vocab
+ *   seed, offset select the random stream: the draw of row i depends only on
+ *                (seed, offset, i).  The generator is Philox-4x32-10, not MLX's, so parity with
+ *                the reference is distributional, not bitwise
+ *   out_tokens   device int32 [rows]; out_logprob device fp32 [rows]
+ *   out_topk_idx device int32 [rows, top_k] or NULL, out_topk_val device fp32 [rows, top_k] or
+ *                NULL: the top-k (value descending, ties by ascending index), raw logits
+ */
+int32_t tome_sample_topk_logprob(const void* logits, int32_t dtype, int64_t rows, int64_t vocab,
+                                 int64_t row_stride, float temperature, int32_t top_k,
+                                 uint64_t seed, uint64_t offset, int32_t* out_tokens,
+                                 float* out_logprob, int32_t* out_topk_idx, float* out_topk_val,
+                                 int32_t* dev_status, void* stream);
 
 /*
  * Fused LM head + selective log-prob: logits = hidden @ weight^T are formed tile by tile

@@ -191,6 +191,44 @@ def combine_triples(m, s, t):
     return t.sum(dim=0) - lse, lse
 
 
+def ragged_logprobs(logits, targets_per_seq, lengths, temp: float = 1.0, starts=None):
+    """mlx-impl/node.py:446-458, the per-sequence loop of ``_process_ref_logprobs_batched``:
+
+        c_logits = logits[i, p_len - 1 : p_len - 1 + len(c_toks)]
+        lps = local_compute_logprobs(c_logits, c_targets, temperature or 1.0)
+        ... ref_log_probs.extend(lps.tolist())
+
+    ``targets_per_seq[i]`` are the completion tokens of sequence ``i``; returns the list of
+    per-sequence fp32 tensors (what lands in ``Completion.ref_log_probs``)."""
+    n_seq, seq_len, _ = logits.shape
+    lengths = _i64(lengths).reshape(-1)
+    starts_t = torch.zeros_like(lengths) if starts is None else _i64(starts).reshape(-1)
+    out = []
+    for i in range(n_seq):
+        st = int(max(0, min(int(starts_t[i]), seq_len)))
+        ln = int(max(0, min(int(lengths[i]), seq_len - st)))
+        if ln == 0:
+            out.append(torch.zeros(0, dtype=torch.float32))
+            continue
+        lp, _, _ = selective_logprob(logits[i, st:st + ln], _i64(targets_per_seq[i])[:ln], temp or 1.0)
+        out.append(lp)
+    return out
+
+
+def topk_sampling_distribution(logits_row, temperature: float, top_k: int = 20):
+    """The distribution ``_sample_token`` draws from (mlx-impl/node.py:894-907): the ``top_k``
+    largest of ``logits / temperature`` (ties: lower index first, as a stable sort gives) and
+    the categorical probabilities ``softmax(top_logits)`` over them.  Temperature 0 is argmax.
+    Returns ``(indices int64 [k], probabilities float64 [k])`` ordered by descending logit."""
+    x = _f32(logits_row).reshape(-1)
+    k = min(top_k, x.numel())
+    if not temperature or temperature <= 0:
+        return torch.argmax(x).reshape(1), torch.ones(1, dtype=torch.float64)
+    order = torch.sort(x, descending=True, stable=True).indices[:k]
+    top = (x[order] / torch.tensor(float(temperature), dtype=torch.float32)).to(torch.float64)
+    return order, torch.softmax(top, dim=0)
+
+
 def dual_logprob_kl(policy_logits, ref_logits, ids, lengths, temp: float = 1.0,
                     starts=None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """GRPO dual scoring on the ragged completion window of each sequence.

@@ -56,6 +56,10 @@ def test_argument_errors_are_caught_on_the_host(built_lib):
     # dual: too many sequences for one call
     assert lib.tome_dual_logprob_kl(fake, fake, 1, 5000, 4, 16, 16, fake, fake, None, 1.0, fake,
                                     fake, fake, None, None) == -9
+    assert lib.tome_ragged_logprob(fake, 1, 5000, 4, 16, 16, fake, 8, fake, None, 1.0, fake, None,
+                                   None, None, None) == -9
+    assert lib.tome_sample_topk_logprob(fake, 1, 4, 16, 16, 0.7, 0, 1, 0, fake, fake, None, None,
+                                        None, None) == -4
     # fused head: hidden size must keep rows 16-byte aligned
     assert lib.tome_lmhead_logprob(fake, fake, 4, 12, 64, fake, 1.0, 0, fake, None, fake, 1 << 20,
                                    None, None) == -8

@@ -299,6 +299,49 @@ def test_dual_fp32_and_cfg5_shape(cuda_device):
                 ids[:, :8] % 5000, torch.tensor([8, 3], dtype=torch.int32), 1.0, cuda_device, tol=1e-4)
 
 
+# ------------------------------------------------------------------ ragged, packed (wire layout)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_ragged_packed_matches_per_sequence_loop(cuda_device, dtype):
+    import tome_b200
+    g = torch.Generator().manual_seed(60)
+    n_seq, seq_len, vocab = 7, 20, 6000
+    logits = (torch.randn((n_seq, seq_len, vocab), generator=g) * 3).to(dtype)
+    starts = torch.tensor([0, 4, 19, 20, 3, 0, 10], dtype=torch.int32)   # prompt_len - 1
+    lengths = torch.tensor([20, 9, 5, 3, 0, 1, 10], dtype=torch.int32)   # two get clamped
+    clamped = [max(0, min(int(l), seq_len - int(s))) for s, l in zip(starts, lengths)]
+    targets = [torch.randint(0, vocab, (c,), generator=g, dtype=torch.int32) for c in clamped]
+    # poison everything outside the windows: it must never be read
+    poisoned = logits.clone()
+    for i in range(n_seq):
+        mask = torch.ones(seq_len, dtype=torch.bool)
+        mask[int(starts[i]):int(starts[i]) + clamped[i]] = False
+        poisoned[i, mask] = float("nan")
+    packed, offsets, lse = tome_b200.ragged_logprobs(
+        poisoned.to(cuda_device), torch.cat(targets).to(cuda_device), lengths.to(cuda_device), 0.7,
+        starts=starts.to(cuda_device), return_lse=True, check=True)
+    want = oracle.ragged_logprobs(logits, targets, lengths, 0.7, starts)
+    assert offsets.cpu().tolist() == [0] + torch.tensor(clamped).cumsum(0).tolist()
+    assert packed.shape == (sum(clamped),) and not torch.isnan(packed).any()
+    off = offsets.cpu().tolist()
+    for i in range(n_seq):
+        assert max_abs(packed[off[i]:off[i + 1]], want[i]) <= TOL[dtype]
+
+
+def test_ragged_wrong_target_count_is_reported(cuda_device):
+    import tome_b200
+    logits = torch.zeros((2, 4, 64), dtype=torch.float32, device=cuda_device)
+    lengths = torch.tensor([4, 2], dtype=torch.int32, device=cuda_device)
+    tg = torch.zeros(5, dtype=torch.int32, device=cuda_device)  # windows cover 6 positions
+    with pytest.raises(ValueError):  # too many targets: caught on the host after the call
+        tome_b200.ragged_logprobs(logits, torch.cat([tg, tg]), lengths, 1.0, check=True)
+    with pytest.raises(tome_b200.TomeRuntimeError):  # too few: the kernel scores what fits
+        tome_b200.ragged_logprobs(logits, tg, lengths, 1.0, check=True)
+    packed, offsets = tome_b200.ragged_logprobs(logits, tg, lengths, 1.0)
+    assert packed.shape == (5,) and offsets.cpu().tolist() == [0, 4, 6]
+    with pytest.raises(tome_b200.TomeRuntimeError):
+        tome_b200.check_device_status(cuda_device)
+
+
 # ------------------------------------------------------------------ committed fixtures
 @pytest.mark.parametrize("name,dtype", [("selective_bf16.npz", torch.bfloat16),
                                         ("selective_fp32.npz", torch.float32)])

@@ -1,0 +1,99 @@
+"""GPU tests of the fused top-k sampling + log-prob kernel.  The random stream is the
+library's own, so parity with the reference's sampler is checked in distribution; everything
+deterministic (the top-k set and its order, the greedy path, the log-prob of whatever token
+was drawn) is checked exactly against the oracle."""
+import pytest
+import torch
+
+from helpers import TOL, max_abs
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(rows, vocab, dtype, seed, scale=3.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn((rows, vocab), generator=g) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("vocab", [1, 5, 20, 21, 600, 8192, 8193, 151936])
+def test_topk_set_and_logprob(cuda_device, dtype, vocab):
+    import tome_b200
+    x = _case(6, vocab, dtype, 200 + vocab % 89)
+    tok, lp, tk_i, tk_v = tome_b200.sample_topk_logprob(x.to(cuda_device), 0.7, 20, seed=3,
+                                                        return_topk=True)
+    k = min(20, vocab)
+    for r in range(x.shape[0]):
+        idx, probs = oracle.topk_sampling_distribution(x[r], 0.7, 20)
+        assert tk_i[r, :k].cpu().tolist() == idx.tolist()          # exact set AND order
+        assert torch.equal(tk_v[r, :k].cpu(), x[r].float()[idx])   # raw logits, bit-exact
+        assert (tk_i[r, k:] == -1).all()
+        assert int(tok[r]) in idx.tolist()
+    o_lp, _, _ = oracle.selective_logprob(x, tok.cpu(), 0.7)
+    assert max_abs(lp, o_lp) <= TOL[dtype]
+
+
+def test_greedy_is_first_argmax_scored_at_temperature_one(cuda_device):
+    import tome_b200
+    x = _case(9, 5000, torch.bfloat16, 7)
+    x[3, 100] = x[3].max()       # a tie for the maximum: the first index wins
+    x[3, 4000] = x[3].max()
+    tok, lp = tome_b200.sample_topk_logprob(x.to(cuda_device), 0.0)
+    assert tok.cpu().tolist() == torch.argmax(x.float(), dim=-1).tolist()
+    o_lp, _, _ = oracle.selective_logprob(x, tok.cpu(), 1.0)
+    assert max_abs(lp, o_lp) <= 2e-3
+
+
+def test_ties_masks_and_adversarial_orders(cuda_device):
+    """bf16 ties across the k-th place, -inf masks, a constant row, ascending and descending
+    rows (the ascending one makes every new logit a candidate)."""
+    import tome_b200
+    vocab = 30000
+    x = _case(6, vocab, torch.bfloat16, 8, scale=0.25)   # coarse values: many exact ties
+    x[1, : vocab - 7] = float("-inf")                     # fewer finite logits than k
+    x[2, :] = 1.5                                         # constant row
+    x[3] = torch.linspace(-8, 8, vocab).to(torch.bfloat16)            # ascending
+    x[4] = torch.linspace(8, -8, vocab).to(torch.bfloat16)            # descending
+    x[5, ::3] = float("-inf")
+    tok, lp, tk_i, tk_v = tome_b200.sample_topk_logprob(x.to(cuda_device), 1.3, 20, seed=11,
+                                                        return_topk=True)
+    for r in range(6):
+        idx, _ = oracle.topk_sampling_distribution(x[r], 1.3, 20)
+        assert tk_i[r].cpu().tolist() == idx.tolist(), r
+    assert int(tok[1]) >= vocab - 7                       # never a masked token
+    o_lp, _, _ = oracle.selective_logprob(x, tok.cpu(), 1.3)
+    assert max_abs(lp, o_lp) <= 2e-3
+
+
+def test_draws_follow_the_topk_softmax(cuda_device):
+    """20000 independent rows with the same logits: the empirical token frequencies must match
+    softmax(top-k logits / T) (chi-square, 19 degrees of freedom, p = 1e-4 bound 50.0)."""
+    import tome_b200
+    g = torch.Generator().manual_seed(9)
+    row = (torch.randn((1, 4000), generator=g) * 2.0)
+    n = 20000
+    x = row.expand(n, -1).contiguous().to(cuda_device)
+    tok, _ = tome_b200.sample_topk_logprob(x, 0.8, 20, seed=1234, offset=5)
+    idx, probs = oracle.topk_sampling_distribution(row[0], 0.8, 20)
+    counts = torch.stack([(tok.cpu() == int(i)).sum() for i in idx]).double()
+    assert int(counts.sum()) == n
+    chi2 = float((((counts - n * probs) ** 2) / (n * probs)).sum())
+    assert chi2 < 50.0, chi2
+    # reproducible for the same (seed, offset); different for another offset
+    tok2, _ = tome_b200.sample_topk_logprob(x, 0.8, 20, seed=1234, offset=5)
+    tok3, _ = tome_b200.sample_topk_logprob(x, 0.8, 20, seed=1234, offset=6)
+    assert torch.equal(tok, tok2) and not torch.equal(tok, tok3)
+
+
+def test_rollout_step_shape_and_argument_errors(cuda_device):
+    import tome_b200
+    x = _case(64, 151936, torch.bfloat16, 10)             # B = 64 sequences, one decode step
+    tok, lp = tome_b200.sample_topk_logprob(x.to(cuda_device).view(8, 8, -1), 0.7)
+    assert tok.shape == (8, 8) and lp.shape == (8, 8) and tok.dtype == torch.int32
+    o_lp, _, _ = oracle.selective_logprob(x, tok.cpu().reshape(-1), 0.7)
+    assert max_abs(lp.reshape(-1), o_lp) <= 2e-3
+    with pytest.raises(tome_b200.TomeArgumentError):
+        tome_b200.sample_topk_logprob(x.to(cuda_device), 0.7, top_k=65)
+    with pytest.raises(tome_b200.TomeArgumentError):
+        tome_b200.sample_topk_logprob(x.to(cuda_device), -1.0)

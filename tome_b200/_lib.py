@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_float, c_int32, c_int64, c_size_t, c_void_p
+from ctypes import c_char_p, c_float, c_int32, c_int64, c_size_t, c_uint64, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libtome_b200.so")
@@ -16,6 +16,7 @@ TOME_BF16 = 1
 
 DEV_TARGET_OUT_OF_RANGE = 1
 DEV_TIMEOUT = 2
+DEV_RAGGED_OVERFLOW = 4
 
 LMHEAD_ROUND_LOGITS_BF16 = 1
 
@@ -32,6 +33,12 @@ SIGNATURES = {
     "tome_dual_logprob_kl": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int64, c_int64,
                                        c_int64, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
                                        c_void_p, c_void_p, c_void_p, c_void_p]),
+    "tome_ragged_logprob": (c_int32, [c_void_p, c_int32, c_int64, c_int64, c_int64, c_int64,
+                                      c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p,
+                                      c_void_p, c_void_p, c_void_p, c_void_p]),
+    "tome_sample_topk_logprob": (c_int32, [c_void_p, c_int32, c_int64, c_int64, c_int64, c_float,
+                                           c_int32, c_uint64, c_uint64, c_void_p, c_void_p,
+                                           c_void_p, c_void_p, c_void_p, c_void_p]),
     "tome_lmhead_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "tome_lmhead_partials": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                        c_void_p, c_float, c_int32, c_void_p, c_void_p, c_void_p,

@@ -34,7 +34,12 @@
 
 namespace tome {
 
-enum K1Mode { K1_SELECTIVE = 0, K1_DUAL = 1, K1_FULL = 2 };
+enum K1Mode { K1_SELECTIVE = 0, K1_DUAL = 1, K1_FULL = 2, K1_RAGGED = 3 };
+
+// DUAL and RAGGED score only a window [start, start + length) of each sequence.
+__host__ __device__ constexpr bool k1_windowed(int mode) {
+  return mode == K1_DUAL || mode == K1_RAGGED;
+}
 
 // Tuning constants (overridable at compile time for experiments).
 #ifndef K1_CFG_WARPS
@@ -87,6 +92,8 @@ struct K1Params {
   const int32_t* starts;   // DUAL, nullable
   int32_t n_seq;           // DUAL
   int32_t seq_len;         // DUAL
+  int64_t packed_capacity; // RAGGED: entries the packed target/output arrays can hold
+  int32_t* out_offsets;    // RAGGED: int32 [n_seq + 1], start of each sequence in the packed output
   int32_t* status;         // nullable
   int32_t chunk_bytes;     // bulk-copy size (multiple of 16, <= K1_CHUNK_BYTES), set by launch
   int32_t n_chunks;        // bulk copies per row
@@ -378,7 +385,7 @@ __device__ __forceinline__ void emit_row(const K1Params& p, int64_t row, int sub
   }
   float lp = __fdiv_rn(x_t, p.temp) - lse;
   if (!target_ok) lp = __int_as_float(0x7fc00000);
-  if (MODE == K1_SELECTIVE) {
+  if (MODE == K1_SELECTIVE || MODE == K1_RAGGED) {
     p.out0[row] = lp;
     if (p.out1 != nullptr) p.out1[row] = lse;
     if (p.out2 != nullptr) p.out2[row] = target_ok ? x_t : __int_as_float(0x7fc00000);
@@ -425,7 +432,8 @@ __device__ __noinline__ void exact_row(const T* src, int64_t vocab, float c, int
 template <typename T, int MODE, int POLY>
 __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(const K1Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
-  constexpr int NSUB = (MODE == K1_SELECTIVE) ? 1 : 2;
+  constexpr int NSUB = (MODE == K1_DUAL || MODE == K1_FULL) ? 2 : 1;
+  constexpr bool WINDOWED = k1_windowed(MODE);
   constexpr int ES = sizeof(T);
   constexpr int PER_VEC = 16 / ES;
 
@@ -446,9 +454,16 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
     fence_mbar_init();
   }
   int64_t n_items = p.n_rows;
-  if (MODE == K1_DUAL) {
+  if (WINDOWED) {
     n_items = dual_build_prefix(p, cum, reinterpret_cast<int32_t*>(smem + K1Smem::SCRATCH_OFF));
-    dual_zero_masked(p);
+    if (MODE == K1_DUAL) dual_zero_masked(p);
+    if (MODE == K1_RAGGED && blockIdx.x == 0 && p.out_offsets != nullptr)
+      for (int i = threadIdx.x; i <= p.n_seq; i += blockDim.x) p.out_offsets[i] = cum[i];
+    if (MODE == K1_RAGGED && n_items > p.packed_capacity) {
+      // the windows cover more positions than the packed arrays hold: score what fits
+      if (threadIdx.x == 0) raise_status(p.status, TOME_DEV_RAGGED_OVERFLOW);
+      n_items = p.packed_capacity;
+    }
   }
   __syncthreads();
 
@@ -465,7 +480,7 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       uint32_t it = 0;
       bool ok = true;
       for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        const int64_t row = (MODE == K1_DUAL) ? dual_row_of_item(p, cum, item) : item;
+        const int64_t row = WINDOWED ? dual_row_of_item(p, cum, item) : item;
         for (int sub = 0; sub < NSUB && ok; ++sub) {
           const uint8_t* src = reinterpret_cast<const uint8_t*>(
                                    p.src[(MODE == K1_DUAL) ? sub : 0]) + row * p.stride * ES;
@@ -499,7 +514,8 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
   uint32_t red_it = 0;
   float carry = 0.0f;
   for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
-    const int64_t row = (MODE == K1_DUAL) ? dual_row_of_item(p, cum, item) : item;
+    const int64_t row = WINDOWED ? dual_row_of_item(p, cum, item) : item;
+    const int64_t oidx = (MODE == K1_RAGGED) ? item : row;  // where targets/outputs live
     float lse_row = 0.0f;
     for (int sub = 0; sub < NSUB; ++sub) {
       const T* src = reinterpret_cast<const T*>(p.src[(MODE == K1_DUAL) ? sub : 0]) +
@@ -510,7 +526,7 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       float x_t = 0.0f;
       bool target_ok = true;
       if (MODE != K1_FULL && ctid == 0) {
-        const int32_t t = p.targets[row];
+        const int32_t t = p.targets[oidx];
         target_ok = (t >= 0) && (static_cast<int64_t>(t) < p.vocab);
         if (target_ok) x_t = to_float(src[t]);
         else raise_status(p.status, TOME_DEV_TARGET_OUT_OF_RANGE);
@@ -582,7 +598,7 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
           // the true maximum contributes 2^0, so a healthy row has s >= ~1
           if (!(s >= 0.5f && s <= FLT_MAX)) exact_row(src, p.vocab, p.c, lane, m, s);
           if (MODE == K1_FULL) lse_row = finish_lse<MODE>(m, s, p);
-          if (ctid == 0) emit_row<MODE>(p, row, sub, m, s, x_t, target_ok, carry);
+          if (ctid == 0) emit_row<MODE>(p, oidx, sub, m, s, x_t, target_ok, carry);
         }
         ++red_it;
       }
@@ -599,20 +615,28 @@ template <typename T, int MODE>
 __global__ void __launch_bounds__(K1_PLAIN_THREADS) k1_plain_kernel(const K1Params p) {
   __shared__ float2 part[K1_PLAIN_THREADS / 32];
   __shared__ float2 result;
-  __shared__ int32_t cum[(MODE == K1_DUAL) ? (K1_MAX_SEQ + 1) : 1];
-  __shared__ int32_t scratch[(MODE == K1_DUAL) ? K1_PLAIN_THREADS : 1];
+  constexpr bool WINDOWED = k1_windowed(MODE);
+  __shared__ int32_t cum[WINDOWED ? (K1_MAX_SEQ + 1) : 1];
+  __shared__ int32_t scratch[WINDOWED ? K1_PLAIN_THREADS : 1];
   constexpr int NSUB = (MODE == K1_DUAL) ? 2 : 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   int64_t n_items = p.n_rows;
-  if (MODE == K1_DUAL) {
+  if (WINDOWED) {
     n_items = dual_build_prefix(p, cum, scratch);
-    dual_zero_masked(p);
+    if (MODE == K1_DUAL) dual_zero_masked(p);
+    if (MODE == K1_RAGGED && blockIdx.x == 0 && p.out_offsets != nullptr)
+      for (int i = threadIdx.x; i <= p.n_seq; i += blockDim.x) p.out_offsets[i] = cum[i];
+    if (MODE == K1_RAGGED && n_items > p.packed_capacity) {
+      if (threadIdx.x == 0) raise_status(p.status, TOME_DEV_RAGGED_OVERFLOW);
+      n_items = p.packed_capacity;
+    }
     __syncthreads();
   }
   float carry = 0.0f;
   for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
-    const int64_t row = (MODE == K1_DUAL) ? dual_row_of_item(p, cum, item) : item;
+    const int64_t row = WINDOWED ? dual_row_of_item(p, cum, item) : item;
+    const int64_t oidx = (MODE == K1_RAGGED) ? item : row;
     for (int sub = 0; sub < NSUB; ++sub) {
       const T* src = reinterpret_cast<const T*>(p.src[(MODE == K1_DUAL) ? sub : 0]) +
                      row * p.stride;
@@ -635,12 +659,12 @@ __global__ void __launch_bounds__(K1_PLAIN_THREADS) k1_plain_kernel(const K1Para
           float x_t = 0.0f;
           bool target_ok = true;
           if (MODE != K1_FULL) {
-            const int32_t t = p.targets[row];
+            const int32_t t = p.targets[oidx];
             target_ok = (t >= 0) && (static_cast<int64_t>(t) < p.vocab);
             if (target_ok) x_t = to_float(src[t]);
             else raise_status(p.status, TOME_DEV_TARGET_OUT_OF_RANGE);
           }
-          emit_row<MODE>(p, row, sub, m, s, x_t, target_ok, carry);
+          emit_row<MODE>(p, oidx, sub, m, s, x_t, target_ok, carry);
           result = make_float2(m, s);
         }
       }
@@ -696,7 +720,7 @@ static int32_t k1_launch_typed(const K1Params& p_in, bool bulk_ok, int64_t max_i
     const int64_t al = K1_CHUNK_ALIGN;
     p.chunk_bytes = (n > 0) ? static_cast<int32_t>(((bulk_bytes + n - 1) / n + al - 1) / al * al)
                             : K1_CHUNK_ALIGN;
-    const int smem = (MODE == K1_DUAL) ? K1Smem::TOTAL_DUAL : K1Smem::TOTAL_PLAIN;
+    const int smem = k1_windowed(MODE) ? K1Smem::TOTAL_DUAL : K1Smem::TOTAL_PLAIN;
     if (smem > info.max_smem_optin)
       return fail(TOME_ERR_UNSUPPORTED, "device offers %d bytes of shared memory, need %d",
                   info.max_smem_optin, smem);
@@ -857,4 +881,50 @@ extern "C" int32_t tome_dual_logprob_kl(const void* policy_logits, const void* r
   const bool bulk = bulk_eligible(policy_logits, row_stride, dtype) &&
                     bulk_eligible(ref_logits, row_stride, dtype);
   return k1_launch<K1_DUAL>(p, dtype, bulk, rows, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int32_t tome_ragged_logprob(const void* logits, int32_t dtype, int64_t n_seq,
+                                       int64_t seq_len, int64_t vocab, int64_t row_stride,
+                                       const int32_t* targets_packed, int64_t packed_capacity,
+                                       const int32_t* lengths, const int32_t* starts,
+                                       float temperature,
+                                       float* out_logprob_packed, float* out_lse_packed,
+                                       int32_t* out_offsets, int32_t* dev_status, void* stream) {
+  if (n_seq < 0 || seq_len < 0)
+    return fail(TOME_ERR_BAD_SHAPE, "n_seq=%lld seq_len=%lld", (long long)n_seq,
+                (long long)seq_len);
+  if (n_seq > K1_MAX_SEQ)
+    return fail(TOME_ERR_TOO_LARGE, "n_seq=%lld exceeds the limit of %d sequences per call",
+                (long long)n_seq, K1_MAX_SEQ);
+  if (seq_len > 0x7fffffffLL / (n_seq > 0 ? n_seq : 1))
+    return fail(TOME_ERR_TOO_LARGE, "n_seq * seq_len does not fit int32");
+  const int64_t rows = n_seq * seq_len;
+  int32_t st = k1_check_common(logits, dtype, rows, vocab, row_stride, temperature);
+  if (st != TOME_OK) return st;
+  if (packed_capacity < 0)
+    return fail(TOME_ERR_BAD_SHAPE, "packed_capacity=%lld", (long long)packed_capacity);
+  if (rows == 0) return TOME_OK;
+  if (lengths == nullptr ||
+      (packed_capacity > 0 && (targets_packed == nullptr || out_logprob_packed == nullptr)))
+    return fail(TOME_ERR_NULL_POINTER, "a required pointer is NULL");
+  K1Params p = {};
+  p.src[0] = logits;
+  p.n_rows = rows;
+  p.vocab = vocab;
+  p.stride = row_stride;
+  p.targets = targets_packed;
+  p.c = LOG2E / temperature;
+  p.temp = temperature;
+  p.inv_temp = 1.0f / temperature;
+  p.out0 = out_logprob_packed;
+  p.out1 = out_lse_packed;
+  p.lengths = lengths;
+  p.starts = starts;
+  p.n_seq = static_cast<int32_t>(n_seq);
+  p.seq_len = static_cast<int32_t>(seq_len);
+  p.out_offsets = out_offsets;
+  p.packed_capacity = packed_capacity;
+  p.status = dev_status;
+  return k1_launch<K1_RAGGED>(p, dtype, bulk_eligible(logits, row_stride, dtype), rows,
+                              static_cast<cudaStream_t>(stream));
 }

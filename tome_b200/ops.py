@@ -49,6 +49,8 @@ def check_device_status(device=None) -> None:
     problems = []
     if bits & _lib.DEV_TARGET_OUT_OF_RANGE:
         problems.append("a target index lies outside [0, vocab)")
+    if bits & _lib.DEV_RAGGED_OVERFLOW:
+        problems.append("the ragged windows cover more positions than the packed arrays hold")
     if bits & _lib.DEV_TIMEOUT:
         problems.append("a bounded device-side wait ran out (TOME_DEV_TIMEOUT)")
     raise TomeRuntimeError("; ".join(problems) or f"device status {bits}")
@@ -234,6 +236,81 @@ def grpo_dual_logprob_kl(policy_logits: torch.Tensor, ref_logits: torch.Tensor,
     if check:
         check_device_status(device)
     return tuple(outs)
+
+
+def ragged_logprobs(logits: torch.Tensor, targets_packed: torch.Tensor, lengths: torch.Tensor,
+                    temp: float = 1.0, *, starts: Optional[torch.Tensor] = None,
+                    return_lse: bool = False, check: bool = False):
+    """Log-probs of the completion tokens of every sequence of one model, packed back to back.
+
+    The batched form of the loop in ``_process_ref_logprobs_batched`` (mlx-impl/node.py:446-458):
+    for sequence ``i`` the rows ``[starts[i], starts[i] + lengths[i])`` of ``logits[i]`` are
+    scored against ``lengths[i]`` consecutive entries of ``targets_packed`` (the completion
+    tokens), and the fp32 results are written sequence after sequence, the layout of
+    ``Completion.ref_log_probs`` on the wire (scheduler/proto/inference.proto:108-112).
+    ``logits`` is ``[n_seq, seq_len, V]``.  Returns ``(packed, offsets)`` (plus the packed
+    logsumexp with ``return_lse``); ``packed[offsets[i]:offsets[i+1]]`` belongs to sequence
+    ``i``.  Rows outside the windows are never read.
+    """
+    _require_cuda("logits", logits)
+    if logits.dim() != 3:
+        raise ValueError("expected logits of shape [n_seq, seq_len, V]")
+    temp = float(temp or 1.0)
+    n_seq, seq_len, V = logits.shape
+    device = logits.device
+    lg = logits if logits.is_contiguous() else logits.contiguous()
+    tg = _ids32(targets_packed, int(targets_packed.numel()), device)
+    len32 = _ids32(lengths, n_seq, device)
+    st32 = None if starts is None else _ids32(starts, n_seq, device)
+    total = int(tg.numel())
+    out = torch.empty(total, dtype=torch.float32, device=device)
+    lse = torch.empty(total, dtype=torch.float32, device=device) if return_lse else None
+    offsets = torch.empty(n_seq + 1, dtype=torch.int32, device=device)
+    with torch.cuda.device(device):
+        status = lib.tome_ragged_logprob(
+            lg.data_ptr(), _dtype_code(lg), n_seq, seq_len, V, V, tg.data_ptr(), total, len32.data_ptr(),
+            _ptr(st32), temp, out.data_ptr(), _ptr(lse), offsets.data_ptr(),
+            _status_word(device).data_ptr(), _stream(device))
+    _lib.check(status)
+    if check:
+        check_device_status(device)  # raises if the windows needed more than `total` entries
+        if int(offsets[-1].item()) != total:
+            raise ValueError(f"targets_packed holds {total} ids but the windows cover "
+                             f"{int(offsets[-1].item())} positions")
+    return (out, offsets, lse) if return_lse else (out, offsets)
+
+
+def sample_topk_logprob(logits: torch.Tensor, temperature: float, top_k: int = 20, *,
+                        seed: int = 0, offset: int = 0, return_topk: bool = False):
+    """Sample one token per row and score it, on the device, in one pass over the logits.
+
+    The batched replacement of the rollout's per-sequence loop (mlx-impl/node.py:593-610):
+    ``_sample_token`` (node.py:894-907, top-k temperature sampling) plus the gather of the
+    sampled token's log-prob from ``fused_log_softmax`` (node.py:590, 605).  ``temperature``
+    0 means greedy (argmax) scored at temperature 1, as in the reference.  Returns
+    ``(tokens int32 [...], logprobs fp32 [...])`` and, with ``return_topk``, the top-k indices
+    and raw logits.  Draws depend only on ``(seed, offset, row)``; advance ``offset`` per step.
+    """
+    _require_cuda("logits", logits)
+    flat, stride = _rows_view(logits)
+    rows, V = flat.shape
+    device = flat.device
+    tokens = torch.empty(rows, dtype=torch.int32, device=device)
+    lp = torch.empty(rows, dtype=torch.float32, device=device)
+    tk_i = torch.empty((rows, top_k), dtype=torch.int32, device=device) if return_topk else None
+    tk_v = torch.empty((rows, top_k), dtype=torch.float32, device=device) if return_topk else None
+    with torch.cuda.device(device):
+        status = lib.tome_sample_topk_logprob(
+            flat.data_ptr(), _dtype_code(flat), rows, V, stride, float(temperature or 0.0),
+            int(top_k), int(seed) & (2 ** 64 - 1), int(offset) & (2 ** 64 - 1), tokens.data_ptr(),
+            lp.data_ptr(), _ptr(tk_i), _ptr(tk_v), _status_word(device).data_ptr(),
+            _stream(device))
+    _lib.check(status)
+    lead = logits.shape[:-1]
+    if return_topk:
+        return (tokens.reshape(lead), lp.reshape(lead), tk_i.reshape(*lead, top_k),
+                tk_v.reshape(*lead, top_k))
+    return tokens.reshape(lead), lp.reshape(lead)
 
 
 def lm_head_workspace_bytes(rows: int, hidden_dim: int, vocab_local: int) -> int:
