@@ -394,7 +394,32 @@ def run_extra(args, device, rank, world, dist_on, barrier, peaks):
                              "active_rows_per_s": active / (ms * 1e-3),
                              "GBps": nbytes / launch / 1e6,
                              "frac_of_measured_hbm": nbytes / launch / 1e6 / peaks["hbm_gbs"]}
-    del pol, ref, tg, lengths
+    # ragged single-model scoring packed to the wire layout (node.py:446-458), same logits
+    starts = torch.zeros_like(lengths)
+    packed_targets = torch.cat([tg[i, : int(lengths[i])] for i in range(tg.shape[0])])
+    ms_r, launch_r = timed(lambda: tome_b200.ragged_logprobs(ref, packed_targets, lengths, temp,
+                                                             starts=starts))
+    extra["ragged_ref_logprobs"] = {"active_rows": active, "ms": ms_r,
+                                    "active_rows_per_s": active / (ms_r * 1e-3),
+                                    "GBps": active * VOCAB * 2 / launch_r / 1e6}
+    del pol, ref, tg, lengths, packed_targets, starts
+    torch.cuda.empty_cache()
+
+    # fused top-k sampling + log-prob: one decode step of 64 sequences (the reference's
+    # batch), and a large batch
+    for name, rows_s in (("sample_topk_64rows", 64), ("sample_topk_4096rows", 4096)):
+        xs = (torch.randn((rows_s, VOCAB), device=device, dtype=torch.float32) * 3.0).to(
+            torch.bfloat16)
+        step_no = [0]
+
+        def sample_step():
+            step_no[0] += 1
+            tome_b200.sample_topk_logprob(xs, 0.7, 20, seed=7, offset=step_no[0])
+
+        ms_s, launch_s = timed(sample_step)
+        extra[name] = {"rows": rows_s, "ms": ms_s, "rows_per_s": rows_s / (ms_s * 1e-3),
+                       "GBps": rows_s * VOCAB * 2 / launch_s / 1e6}
+        del xs
     torch.cuda.empty_cache()
 
     # cfg3: fused LM head + log-prob, Qwen3-0.6B head shape

@@ -181,13 +181,32 @@ __device__ __forceinline__ float ex2_poly(float x) {
   return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
 
+// The same for two values at once with packed f32x2 arithmetic (12 instructions per pair).
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -126.0f);
+  x.y = fmaxf(x.y, -126.0f);
+  const float2 magic = make_float2(12582912.0f, 12582912.0f);
+  const float2 t = __fadd2_rn(x, magic);
+  const float2 j = __fadd2_rn(t, make_float2(-12582912.0f, -12582912.0f));
+  const float2 fr = __ffma2_rn(j, make_float2(-1.0f, -1.0f), x);
+  float2 p = __ffma2_rn(fr, make_float2(0.0551716648f, 0.0551716648f),
+                        make_float2(0.2426111251f, 0.2426111251f));
+  p = __ffma2_rn(p, fr, make_float2(0.6932609677f, 0.6932609677f));
+  p = __ffma2_rn(p, fr, make_float2(0.9999280572f, 0.9999280572f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
+
 // Pair number `slot` (0..3) of an 8-logit vector; the first POLY logits of the vector take
 // the polynomial.
 template <int POLY>
 __device__ __forceinline__ float2 ex2_pair(float2 t, int slot) {
+  if (2 * slot + 1 < POLY) return ex2_poly2(t);
   float2 e;
   e.x = (2 * slot < POLY) ? ex2_poly(t.x) : ex2f(t.x);
-  e.y = (2 * slot + 1 < POLY) ? ex2_poly(t.y) : ex2f(t.y);
+  e.y = ex2f(t.y);
   return e;
 }
 

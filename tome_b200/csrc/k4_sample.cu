@@ -1,11 +1,13 @@
 // K4: top-k temperature sampling fused with the sampled token's full-vocabulary log-prob.
 //
-// One CTA per row.  A single sweep over the row keeps the online (max, sum-exp) of the full
-// vocabulary AND collects the candidates for the top-k: a threshold derived from the first
-// few thousand logits rejects almost everything with one compare, the survivors (a few
-// hundred for ordinary data) go to a shared-memory list, and an all-pairs ranking picks the
-// exact top-k ordered by (value descending, index ascending).  One thread then draws from the
-// categorical distribution over the top-k with a counter-based generator and writes the
+// One CTA per row.  A single sweep over the row (128-bit loads, no barrier inside) keeps the
+// online (max, sum-exp) of the full vocabulary AND collects the candidates for the top-k: a
+// threshold derived from the first few thousand logits rejects almost everything with one
+// compare, the survivors (a few hundred for ordinary data) go to a shared-memory list, and an
+// all-pairs ranking picks the exact top-k ordered by (value descending, index ascending).  If
+// the list overflows (sorted or heavily tied rows) the k-th best of what was stored becomes a
+// tighter (value, index) threshold and the row is swept again.  One thread then draws from
+// the categorical distribution over the top-k with a counter-based generator and writes the
 // token and its log-prob under the FULL softmax.  No host round trip per sequence.
 //
 // Replaces the per-sequence host loop of the rollout (mlx-impl/node.py:593-610):
@@ -29,10 +31,9 @@ constexpr int K4_THREADS = 512;
 constexpr int K4_WARPS = K4_THREADS / 32;
 constexpr int K4_MAX_K = 64;
 constexpr int K4_CAP = 8192;       // candidate list capacity
-constexpr int K4_TRIGGER = 4096;   // compact when the list is longer than this at a block boundary
-constexpr int K4_BLOCK_ELEMS = 4096;  // elements between two block boundaries (<= CAP - TRIGGER)
 constexpr int K4_SAMPLE = 8192;    // leading logits used to derive the first threshold
 constexpr int K4_RANK_MAX = 1024;  // above this many candidates, compact before ranking
+constexpr int K4_MAX_SWEEPS = 64;  // re-sweeps with a tightened threshold before giving up
 
 struct K4Params {
   const void* logits;
@@ -48,16 +49,13 @@ struct K4Params {
 };
 
 struct K4Smem {
-  uint32_t cand_key[K4_CAP];
-  int32_t cand_idx[K4_CAP];
-  uint32_t top_key[K4_MAX_K];
-  int32_t top_idx[K4_MAX_K];
+  unsigned long long cand[K4_CAP];   // candidates, packed (see k4_pack)
+  unsigned long long top[K4_MAX_K];  // the top-k, best first
+  unsigned long long sort_buf[K4_THREADS];
   float red_f[2 * K4_WARPS];
   int32_t red_i[K4_WARPS];
-  uint32_t sort_buf[K4_THREADS];
   int32_t count;
-  int32_t bcast_i;
-  uint32_t bcast_u;
+  unsigned long long bcast;
 };
 
 // Order-preserving map float -> uint32 (larger float <=> larger key).  NaN maps to 0.
@@ -70,6 +68,19 @@ __device__ __forceinline__ uint32_t k4_key(float x) {
 __device__ __forceinline__ float k4_unkey(uint32_t k) {
   const uint32_t b = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
   return __uint_as_float(b);
+}
+
+// (value, index) as one integer whose numeric order is "larger value first, then lower index":
+// every logit of a row gets a distinct code, so top-k selection has no ties to break.
+__device__ __forceinline__ unsigned long long k4_pack(float x, int64_t idx) {
+  return (static_cast<unsigned long long>(k4_key(x)) << 32) |
+         static_cast<unsigned long long>(0xffffffffu - static_cast<uint32_t>(idx));
+}
+__device__ __forceinline__ float k4_value(unsigned long long pk) {
+  return k4_unkey(static_cast<uint32_t>(pk >> 32));
+}
+__device__ __forceinline__ int32_t k4_index(unsigned long long pk) {
+  return static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(pk));
 }
 
 __device__ __forceinline__ float k4_load(const float* p, int64_t i) { return p[i]; }
@@ -90,59 +101,33 @@ __device__ int32_t k4_block_sum(int32_t v, K4Smem& sm) {
   return t;
 }
 
-// Exact k-th largest key among cand_key[0..n) by bisection on the bits (n >= k).
-__device__ uint32_t k4_kth_key(K4Smem& sm, int32_t n, int32_t k) {
-  uint32_t t = 0;
-  for (int bit = 31; bit >= 0; --bit) {
-    const uint32_t c = t | (1u << bit);
+// Exact k-th largest code among cand[0..n) by bisection on the bits (n >= k, codes distinct).
+__device__ unsigned long long k4_kth(K4Smem& sm, int32_t n, int32_t k) {
+  unsigned long long t = 0;
+  for (int bit = 63; bit >= 0; --bit) {
+    const unsigned long long c = t | (1ull << bit);
     int32_t cnt = 0;
-    for (int32_t i = threadIdx.x; i < n; i += K4_THREADS) cnt += (sm.cand_key[i] >= c) ? 1 : 0;
+    for (int32_t i = threadIdx.x; i < n; i += K4_THREADS) cnt += (sm.cand[i] >= c) ? 1 : 0;
     if (k4_block_sum(cnt, sm) >= k) t = c;
   }
   return t;
 }
 
-// Keeps exactly the k best candidates (value descending, index ascending) in cand[0..k).
-// Returns the key of the k-th; ties at that key beyond the kept ones have larger indices.
-__device__ uint32_t k4_compact(K4Smem& sm, int32_t n, int32_t k) {
-  const uint32_t tkey = k4_kth_key(sm, n, k);
-  int32_t c_gt = 0;
-  for (int32_t i = threadIdx.x; i < n; i += K4_THREADS) c_gt += (sm.cand_key[i] > tkey) ? 1 : 0;
-  const int32_t greater = k4_block_sum(c_gt, sm);
-  const int32_t need_ties = k - greater;  // >= 1
-  // the need_ties-th smallest index among the entries that tie at tkey, by bisection
-  int32_t lo = 0;  // largest value with count(idx < lo) < need_ties ends the search
-  for (int bit = 30; bit >= 0; --bit) {
-    const int32_t c = lo | (1 << bit);
-    int32_t cnt = 0;
-    for (int32_t i = threadIdx.x; i < n; i += K4_THREADS)
-      cnt += (sm.cand_key[i] == tkey && sm.cand_idx[i] < c) ? 1 : 0;
-    if (k4_block_sum(cnt, sm) < need_ties) lo = c;
-  }
-  // keep (key > tkey) or (key == tkey and idx <= lo); each thread stages its survivors in
-  // registers (at most n / THREADS + 1 entries), then the list is rewritten in place
-  uint32_t my_key[K4_CAP / K4_THREADS];
-  int32_t my_idx[K4_CAP / K4_THREADS];
-  int32_t mine = 0;
+// Keeps exactly the k best of cand[0..n) (in arbitrary order) and returns the k-th best code.
+__device__ unsigned long long k4_compact(K4Smem& sm, int32_t n, int32_t k) {
+  const unsigned long long kth = k4_kth(sm, n, k);
+  unsigned long long mine[K4_CAP / K4_THREADS];
+  int32_t n_mine = 0;
   for (int32_t i = threadIdx.x; i < n; i += K4_THREADS) {
-    const uint32_t key = sm.cand_key[i];
-    const int32_t idx = sm.cand_idx[i];
-    if (key > tkey || (key == tkey && idx <= lo)) {
-      my_key[mine] = key;
-      my_idx[mine] = idx;
-      ++mine;
-    }
+    const unsigned long long v = sm.cand[i];
+    if (v >= kth) mine[n_mine++] = v;
   }
   __syncthreads();
   if (threadIdx.x == 0) sm.count = 0;
   __syncthreads();
-  for (int32_t j = 0; j < mine; ++j) {
-    const int32_t slot = atomicAdd(&sm.count, 1);
-    sm.cand_key[slot] = my_key[j];
-    sm.cand_idx[slot] = my_idx[j];
-  }
+  for (int32_t j = 0; j < n_mine; ++j) sm.cand[atomicAdd(&sm.count, 1)] = mine[j];
   __syncthreads();
-  return tkey;
+  return kth;
 }
 
 // Philox-4x32-10: one 128-bit block for (counter, key); returns the first word.
@@ -165,6 +150,53 @@ __device__ uint32_t k4_philox(uint64_t ctr_lo, uint64_t ctr_hi, uint64_t key) {
   return c0;
 }
 
+// One pass over a row: every logit whose code is >= thr is written to the candidate ring (if
+// more than the capacity arrive, later ones overwrite earlier ones and the count tells); with
+// SOFTMAX the per-thread online (max, sum 2^((x - max) * c)) of ALL logits is updated too.
+// No barrier inside.
+template <typename T, bool VEC, bool SOFTMAX>
+__device__ __forceinline__ void k4_sweep(const T* src, int64_t V, float c, unsigned long long thr,
+                                         K4Smem& sm, float& m, float& s) {
+  auto consider = [&](float x, int64_t i) {
+    if (SOFTMAX) {
+      if (x > m) {
+        s *= ex2f((m - x) * c);
+        m = x;
+      }
+      s += ex2f((x - m) * c);
+    }
+    const unsigned long long code = k4_pack(x, i);
+    if (code >= thr) {
+      const uint32_t slot = static_cast<uint32_t>(atomicAdd(&sm.count, 1));
+      sm.cand[slot % K4_CAP] = code;  // one aligned 8-byte store: never a torn entry
+    }
+  };
+  if (VEC) {
+    constexpr int PER = 16 / static_cast<int>(sizeof(T));
+    const int64_t nvec = V / PER;
+    const uint4* vp = reinterpret_cast<const uint4*>(src);
+#pragma unroll 4
+    for (int64_t v = threadIdx.x; v < nvec; v += K4_THREADS) {
+      const uint4 q = __ldg(vp + v);
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+      const int64_t i0 = v * PER;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (sizeof(T) == 4) {
+          consider(__uint_as_float(w[j]), i0 + j);
+        } else {
+          consider(__uint_as_float(w[j] << 16), i0 + 2 * j);
+          consider(__uint_as_float(w[j] & 0xffff0000u), i0 + 2 * j + 1);
+        }
+      }
+    }
+    for (int64_t i = nvec * PER + threadIdx.x; i < V; i += K4_THREADS) consider(k4_load(src, i), i);
+  } else {
+#pragma unroll 8
+    for (int64_t i = threadIdx.x; i < V; i += K4_THREADS) consider(k4_load(src, i), i);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(K4_THREADS) k4_sample_kernel(const K4Params p) {
   extern __shared__ __align__(16) uint8_t k4_smem_raw[];
@@ -181,58 +213,59 @@ __global__ void __launch_bounds__(K4_THREADS) k4_sample_kernel(const K4Params p)
     const int64_t V = p.vocab;
     const int32_t kk = static_cast<int32_t>(min(static_cast<int64_t>(k), V));
 
-    // ---- first threshold: the kk-th largest of the per-thread maxima over the leading
-    //      K4_SAMPLE logits; at least kk logits are >= it, so it bounds the answer from below
+    // ---- first threshold: the kk-th best of the per-thread bests over the leading K4_SAMPLE
+    //      logits; at least kk logits are at least that good, so it bounds the answer from below
     const int64_t n_sample = min(static_cast<int64_t>(K4_SAMPLE), V);
-    uint32_t local = 0u;
-    for (int64_t i = tid; i < n_sample; i += K4_THREADS) local = max(local, k4_key(k4_load(src, i)));
+    unsigned long long local = 0ull;
+    for (int64_t i = tid; i < n_sample; i += K4_THREADS)
+      local = max(local, k4_pack(k4_load(src, i), i));
     sm.sort_buf[tid] = local;
     if (tid == 0) sm.count = 0;
     __syncthreads();
-    // rank of each per-thread maximum among the 512 (ties by thread id): all-pairs
     {
+      // rank of each thread's best among the 512 (threads without a logit hold 0; ties among
+      // those by thread id): all-pairs, V >= kk guarantees kk real entries
       int32_t rank = 0;
       for (int j = 0; j < K4_THREADS; ++j) {
-        const uint32_t o = sm.sort_buf[j];
+        const unsigned long long o = sm.sort_buf[j];
         rank += (o > local || (o == local && j < tid)) ? 1 : 0;
       }
-      // with fewer than kk non-empty threads (tiny vocabularies) the threshold is 0: keep all
-      const int32_t want =
-          min(kk, static_cast<int32_t>(min(n_sample, static_cast<int64_t>(K4_THREADS)))) - 1;
-      if (rank == want) sm.bcast_u = (n_sample >= kk && want == kk - 1) ? local : 0u;
+      if (rank == kk - 1) sm.bcast = local;
     }
     __syncthreads();
-    uint32_t thr = sm.bcast_u;   // candidates satisfy key >= thr (or > thr once strict)
-    bool strict = false;
+    unsigned long long thr = sm.bcast;
     __syncthreads();
 
-    // ---- one sweep: online softmax of the whole row + candidate collection
+    // ---- sweep: online softmax of the whole row + candidate collection; swept again with a
+    //      tighter threshold only if more candidates arrived than the ring holds
     float m = -FLT_MAX, s = 0.0f;
-    for (int64_t base = 0; base < V; base += K4_BLOCK_ELEMS) {
-      const int64_t end = min(V, base + K4_BLOCK_ELEMS);
-      for (int64_t i = base + tid; i < end; i += K4_THREADS) {
-        const float x = k4_load(src, i);
-        if (x > m) {
-          s *= ex2f((m - x) * c);
-          m = x;
-        }
-        s += ex2f((x - m) * c);
-        const uint32_t key = k4_key(x);
-        if (strict ? (key > thr) : (key >= thr)) {
-          const int32_t slot = atomicAdd(&sm.count, 1);
-          if (slot < K4_CAP) {
-            sm.cand_key[slot] = key;
-            sm.cand_idx[slot] = static_cast<int32_t>(i);
-          }
-        }
+    const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0);
+    int32_t n = 0;
+    for (int sweep = 0; sweep < K4_MAX_SWEEPS; ++sweep) {
+      if (sweep == 0) {
+        if (vec) k4_sweep<T, true, true>(src, V, c, thr, sm, m, s);
+        else k4_sweep<T, false, true>(src, V, c, thr, sm, m, s);
+      } else {
+        if (vec) k4_sweep<T, true, false>(src, V, c, thr, sm, m, s);
+        else k4_sweep<T, false, false>(src, V, c, thr, sm, m, s);
       }
       __syncthreads();
-      const int32_t n = sm.count;   // <= TRIGGER + BLOCK_ELEMS <= CAP by construction
+      const int32_t total = sm.count;
       __syncthreads();
-      if (n > K4_TRIGGER) {
-        thr = k4_compact(sm, n, kk);
-        strict = true;  // later ties at thr have larger indices than the kept ones: they lose
+      if (total <= K4_CAP) {
+        n = total;
+        break;
       }
+      // overflow: the ring holds CAP of the candidates (mostly the latest); their kk-th best
+      // is a valid, tighter bound
+      thr = k4_compact(sm, K4_CAP, kk);
+      n = kk;
+      if (sweep + 1 == K4_MAX_SWEEPS) {
+        if (tid == 0 && p.status != nullptr) atomicOr(p.status, TOME_DEV_TIMEOUT);
+        break;  // keeps the kk best of what the ring held
+      }
+      if (tid == 0) sm.count = 0;
+      __syncthreads();
     }
 
     // ---- merge the online softmax across the block
@@ -256,26 +289,16 @@ __global__ void __launch_bounds__(K4_THREADS) k4_sample_kernel(const K4Params p)
     for (int w = 0; w < K4_WARPS; ++w) row_s += sm.red_f[2 * w + 1] * ex2f((sm.red_f[2 * w] - row_m) * c);
     const float lse = __fdiv_rn(row_m, temp) + logf(row_s);
 
-    // ---- exact top-kk of the candidates, ordered (value desc, index asc)
-    int32_t n = sm.count;
-    __syncthreads();
+    // ---- exact top-kk of the candidates, best first
     if (n > K4_RANK_MAX) {
       k4_compact(sm, n, kk);
-      n = sm.count;
-      __syncthreads();
+      n = kk;
     }
     for (int32_t i = tid; i < n; i += K4_THREADS) {
-      const uint32_t key = sm.cand_key[i];
-      const int32_t idx = sm.cand_idx[i];
+      const unsigned long long code = sm.cand[i];
       int32_t rank = 0;
-      for (int32_t j = 0; j < n; ++j) {
-        const uint32_t ok = sm.cand_key[j];
-        rank += (ok > key || (ok == key && sm.cand_idx[j] < idx)) ? 1 : 0;
-      }
-      if (rank < kk) {
-        sm.top_key[rank] = key;
-        sm.top_idx[rank] = idx;
-      }
+      for (int32_t j = 0; j < n; ++j) rank += (sm.cand[j] > code) ? 1 : 0;
+      if (rank < kk) sm.top[rank] = code;
     }
     __syncthreads();
 
@@ -284,31 +307,30 @@ __global__ void __launch_bounds__(K4_THREADS) k4_sample_kernel(const K4Params p)
       int32_t pick = 0;
       if (!greedy && kk > 1) {
         // categorical over the top-kk of logits / temperature
-        const float top = k4_unkey(sm.top_key[0]);
+        const float top = k4_value(sm.top[0]);
         float total = 0.0f;
-        for (int32_t j = 0; j < kk; ++j) total += ex2f((k4_unkey(sm.top_key[j]) - top) * c);
+        for (int32_t j = 0; j < kk; ++j) total += ex2f((k4_value(sm.top[j]) - top) * c);
         const uint32_t r = k4_philox(static_cast<uint64_t>(row), p.offset, p.seed);
         const float u = (static_cast<float>(r >> 8) + 0.5f) * (1.0f / 16777216.0f) * total;
         float acc = 0.0f;
         pick = kk - 1;
         for (int32_t j = 0; j < kk; ++j) {
-          acc += ex2f((k4_unkey(sm.top_key[j]) - top) * c);
+          acc += ex2f((k4_value(sm.top[j]) - top) * c);
           if (u < acc) {
             pick = j;
             break;
           }
         }
       }
-      const int32_t token = sm.top_idx[pick];
-      p.out_tokens[row] = token;
-      p.out_logprob[row] = __fdiv_rn(k4_unkey(sm.top_key[pick]), temp) - lse;
+      p.out_tokens[row] = k4_index(sm.top[pick]);
+      p.out_logprob[row] = __fdiv_rn(k4_value(sm.top[pick]), temp) - lse;
     }
     if (p.out_topk_idx != nullptr || p.out_topk_val != nullptr) {
       for (int32_t j = tid; j < k; j += K4_THREADS) {
         const bool have = j < kk;
-        if (p.out_topk_idx != nullptr) p.out_topk_idx[row * k + j] = have ? sm.top_idx[j] : -1;
+        if (p.out_topk_idx != nullptr) p.out_topk_idx[row * k + j] = have ? k4_index(sm.top[j]) : -1;
         if (p.out_topk_val != nullptr)
-          p.out_topk_val[row * k + j] = have ? k4_unkey(sm.top_key[j]) : -INFINITY;
+          p.out_topk_val[row * k + j] = have ? k4_value(sm.top[j]) : -INFINITY;
       }
     }
     __syncthreads();
@@ -361,7 +383,7 @@ extern "C" int32_t tome_sample_topk_logprob(const void* logits, int32_t dtype, i
   p.status = dev_status;
   const int smem = static_cast<int>(sizeof(K4Smem));
   const int grid = static_cast<int>(
-      std::max<int64_t>(1, std::min<int64_t>(static_cast<int64_t>(info.sm_count) * 2, rows)));
+      std::max<int64_t>(1, std::min<int64_t>(static_cast<int64_t>(info.sm_count) * 3, rows)));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == TOME_F32) {
     st = check_cuda(cudaFuncSetAttribute(k4_sample_kernel<float>,
