@@ -65,6 +65,16 @@ const char* tome_status_string(int32_t status);
 const char* tome_last_error_string(void);
 
 /*
+ * Self-test of the bounded waits: launches a one-CTA kernel that waits on an mbarrier nothing
+ * ever arrives on, gives up after limit_cycles SM clock cycles (<= 2e9), ORs TOME_DEV_TIMEOUT
+ * into *dev_status (nullable) and writes 1 to *out_gave_up (device int32, nullable), then exits
+ * normally.  This is the path every device-side wait of the library takes when it runs out
+ * (no counterpart in the reference).
+ */
+int32_t tome_selftest_bounded_wait(int64_t limit_cycles, int32_t* dev_status,
+                                   int32_t* out_gave_up, void* stream);
+
+/*
  * Selective log-softmax: out_logprob[i] = x[i, targets[i]]/T - logsumexp_j(x[i, j]/T), fp32.
  * Replaces local_compute_logprobs (mlx-impl/node.py:400-404) and the
  * "fused_log_softmax(...) then lp[b, token]" pattern of the policy call sites

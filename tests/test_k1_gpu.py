@@ -164,6 +164,28 @@ def test_out_of_range_target_sets_status_and_nan(cuda_device):
     tome_b200.check_device_status(cuda_device)  # cleared by the failed check
 
 
+def test_bounded_wait_runs_out_and_reports(cuda_device):
+    """A wait on a barrier nothing signals must give up after its limit, set TOME_DEV_TIMEOUT
+    and leave the context usable (no trap, no hang)."""
+    import time
+    import tome_b200
+    from tome_b200 import _lib
+    tome_b200.check_device_status(cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    gave_up = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    t0 = time.perf_counter()
+    st = _lib.lib.tome_selftest_bounded_wait(2_000_000, status.data_ptr(), gave_up.data_ptr(),
+                                             torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 5.0
+    assert int(gave_up) == 1 and int(status) & _lib.DEV_TIMEOUT
+    assert _lib.lib.tome_selftest_bounded_wait(0, None, None, None) == -4
+    # the context still works
+    x, ids = _case(3, 100, torch.float32, 1)
+    _check_selective(x, ids, 1.0, cuda_device)
+
+
 def test_outputs_stay_inside_their_buffers(cuda_device):
     from tome_b200 import _lib
     rows, vocab, pad = 37, 5000, 64
@@ -297,6 +319,28 @@ def test_dual_fp32_and_cfg5_shape(cuda_device):
     _check_dual(pol, ref, ids, lengths, temp, cuda_device)
     _check_dual(pol[:, :8, :5000].float().contiguous(), ref[:, :8, :5000].float().contiguous(),
                 ids[:, :8] % 5000, torch.tensor([8, 3], dtype=torch.int32), 1.0, cuda_device, tol=1e-4)
+
+
+def test_cfg5_full_size_consistency(cuda_device):
+    """cfg5 at full size (2 x 32 x 768 x 151936 bf16, ragged): the dual kernel must agree with
+    two runs of the selective kernel on the active rows, the KL with its formula, masked
+    positions must be zero, and a sample of rows must match the oracle."""
+    import tome_b200
+    from tome_b200 import synthetic
+    pol, ref, tg, lengths, temp = synthetic.cfg5_dual(device=cuda_device)
+    p, r, kl = tome_b200.grpo_dual_logprob_kl(pol, ref, tg, lengths, temp, check=True)
+    pos = torch.arange(768, device=cuda_device)[None, :]
+    active = pos < lengths[:, None]
+    assert float(p[~active].abs().max()) == 0 and float(kl[~active].abs().max()) == 0
+    sel_p = tome_b200.local_compute_logprobs(pol, tg, temp)
+    sel_r = tome_b200.local_compute_logprobs(ref, tg, temp)
+    assert max_abs(p[active], sel_p[active]) <= 1e-5 and max_abs(r[active], sel_r[active]) <= 1e-5
+    d = (r - p)[active]
+    assert max_abs(kl[active], torch.exp(d) - d - 1) <= 1e-6
+    rows = torch.nonzero(active.reshape(-1)).squeeze(1)[::97][:128]
+    flat_p = pol.view(-1, pol.shape[-1])
+    o_lp, _, _ = oracle.selective_logprob(flat_p[rows].cpu(), tg.reshape(-1)[rows].cpu(), temp)
+    assert max_abs(p.reshape(-1)[rows], o_lp) <= 2e-3
 
 
 # ------------------------------------------------------------------ ragged, packed (wire layout)

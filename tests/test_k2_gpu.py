@@ -52,6 +52,31 @@ def test_cfg3_shape_row_slice(cuda_device):
     _run(512, 1024, 151936, 1.0, cuda_device, seed=7, w_scale=0.02)
 
 
+@pytest.mark.parametrize("rows,k,seed,scale", [(16384, 1024, 1003, 0.02), (32768, 4096, 1004, 0.015)])
+def test_full_size_heads_against_an_independent_gpu_reduction(cuda_device, rows, k, seed, scale):
+    """cfg3 / cfg4 at full size: every row's logsumexp and target log-prob against
+    torch.matmul (fp32 accumulate, bf16 logits up-cast) + torch.logsumexp in row chunks, and a
+    64-row sample against the CPU oracle."""
+    import tome_b200
+    from tome_b200 import synthetic
+    hidden, weight, ids = synthetic.cfg3_lm_head(rows, k, 151936, cuda_device, seed, scale)
+    lp, lse = tome_b200.lm_head_logprob(hidden, weight, ids, 1.0, check=True)
+    worst = 0.0
+    for b in range(0, rows, 2048):
+        logits = torch.matmul(hidden[b:b + 2048], weight.t()).float()   # bf16-rounded logits
+        ref_lse = torch.logsumexp(logits, dim=-1)
+        ref_lp = logits.gather(1, ids[b:b + 2048].long()[:, None]).squeeze(1) - ref_lse
+        # the reference path rounds logits to bf16 (ulp 2^-6 at |x| < 8): lse moves by far less
+        # (errors average out), the gathered target logit by up to half an ulp
+        assert max_abs(lse[b:b + 2048], ref_lse) <= 5e-3
+        worst = max(worst, max_abs(lp[b:b + 2048], ref_lp))
+        del logits
+    assert worst <= 5e-3 + 2 ** -7, worst
+    sample = torch.arange(0, rows, rows // 64, device=cuda_device)
+    o_lp, o_lse = oracle.lm_head_logprob(hidden[sample].cpu(), weight.cpu(), ids[sample].cpu(), 1.0)
+    assert max_abs(lp[sample], o_lp) <= TOL and max_abs(lse[sample], o_lse) <= TOL
+
+
 def test_leading_dims_and_golden(cuda_device):
     import tome_b200
     gld = load_golden("lm_head.npz")

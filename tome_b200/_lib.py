@@ -25,6 +25,7 @@ SIGNATURES = {
     "tome_version": (c_int32, []),
     "tome_status_string": (c_char_p, [c_int32]),
     "tome_last_error_string": (c_char_p, []),
+    "tome_selftest_bounded_wait": (c_int32, [c_int64, c_void_p, c_void_p, c_void_p]),
     "tome_selective_logprob": (c_int32, [c_void_p, c_int32, c_int64, c_int64, c_int64, c_void_p,
                                          c_float, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p]),

@@ -2,6 +2,7 @@
 #include <mutex>
 
 #include "host_common.h"
+#include "ptx.cuh"
 
 namespace tome {
 
@@ -54,6 +55,39 @@ int32_t current_device_info(DeviceInfo* out) {
 }
 
 }  // namespace tome
+
+namespace tome {
+
+// Waits on an mbarrier that nothing ever arrives on, with a short limit: exercises the path
+// every bounded wait of the library takes when it runs out (status bit, normal kernel exit).
+__global__ void selftest_bounded_wait_kernel(long long limit_cycles, int32_t* status,
+                                             int32_t* waited_out) {
+  __shared__ __align__(8) unsigned long long bar;
+  const uint32_t addr = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(addr, 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const bool completed = mbar_wait(addr, 0, limit_cycles);
+    if (!completed && status != nullptr) atomicOr(status, TOME_DEV_TIMEOUT);
+    if (waited_out != nullptr) *waited_out = completed ? 0 : 1;
+  }
+}
+
+}  // namespace tome
+
+extern "C" int32_t tome_selftest_bounded_wait(int64_t limit_cycles, int32_t* dev_status,
+                                              int32_t* out_gave_up, void* stream) {
+  using namespace tome;
+  if (limit_cycles <= 0 || limit_cycles > 2000000000LL)
+    return fail(TOME_ERR_BAD_SHAPE, "limit_cycles=%lld must be in (0, 2e9]",
+                (long long)limit_cycles);
+  selftest_bounded_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      limit_cycles, dev_status, out_gave_up);
+  return check_cuda(cudaGetLastError(), "selftest launch");
+}
 
 extern "C" {
 

@@ -55,12 +55,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait for the phase with the given parity to complete.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// Bounded wait for the phase with the given parity to complete: false once `limit` SM clock
+// cycles have passed without it.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
+                                          long long limit = WAIT_LIMIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+    if (clock64() - t0 > limit) return false;
   }
   return true;
 }
