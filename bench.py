@@ -361,13 +361,17 @@ def run_extra(args, device, rank, world, dist_on, barrier, peaks):
         total, per = timed_steps(fn, k, w, barrier)
         return max_over_ranks(total, dist_on, device) / k, sum(per) / len(per)
 
-    # cfg1: fp32 selective [1024 x 151936]; L2 (126 MB) is flushed by a 256 MB write per step
+    # cfg1: fp32 selective [1024 x 151936]; L2 (126 MB) is flushed before every launch by
+    # writing a 256 MB buffer and then reading another one (the read pushes the dirty lines of
+    # the write out, so their write-back does not land inside the timed launch)
     x, ids = synthetic.cfg1_selective_fp32(1024, VOCAB, device)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    flush_rd = torch.zeros(64 << 20, dtype=torch.float32, device=device)
     evs = []
 
     def cfg1_step():
         flush.zero_()
+        flush_rd.sum()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         tome_b200.local_compute_logprobs(x, ids, 1.0)
@@ -382,8 +386,8 @@ def run_extra(args, device, rank, world, dist_on, barrier, peaks):
     extra["cfg1_selective_fp32"] = {"rows": 1024, "ms": ms, "rows_per_s": 1024 / (ms * 1e-3),
                                     "GBps": nbytes / ms / 1e6,
                                     "frac_of_measured_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"],
-                                    "l2": "flushed by a 256 MB write before each launch"}
-    del x, ids, flush
+                                    "l2": "flushed by a 256 MB write + 256 MB read before each launch"}
+    del x, ids, flush, flush_rd
 
     # cfg5: dual scoring + k3 KL, bf16 [32 x 768 x 151936] x 2, ragged lengths, temperature 0.7
     pol, ref, tg, lengths, temp = synthetic.cfg5_dual(32, 768, VOCAB, device)
@@ -502,9 +506,12 @@ def run_only(args):
     torch.cuda.set_device(device)
     if args.only == "selective":
         rows = args.rows or ROWS
-        x, ids = synthetic.cfg2_rollout_bf16(rows, VOCAB, device)
+        if args.fp32:
+            x, ids = synthetic.cfg1_selective_fp32(rows, VOCAB, device)
+        else:
+            x, ids = synthetic.cfg2_rollout_bf16(rows, VOCAB, device)
         fn = lambda: tome_b200.local_compute_logprobs(x, ids, 1.0)  # noqa: E731
-        work, unit = rows * VOCAB * 2 + rows * 8, "GB/s"
+        work, unit = rows * VOCAB * x.element_size() + rows * 8, "GB/s"
     else:
         rows = args.rows or 16384
         hidden, weight, ids = synthetic.cfg3_lm_head(rows, args.hidden, args.vocab, device)
@@ -542,6 +549,7 @@ def main():
     ap.add_argument("--rows", type=int, default=None, help="row count for --only (small cases)")
     ap.add_argument("--hidden", type=int, default=1024, help="hidden size for --only lmhead")
     ap.add_argument("--vocab", type=int, default=VOCAB, help="vocabulary (shard) size for --only")
+    ap.add_argument("--fp32", action="store_true", help="fp32 logits for --only selective")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args, int(os.environ.get("RANK", "0")))
