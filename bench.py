@@ -426,6 +426,25 @@ def run_extra(args, device, rank, world, dist_on, barrier, peaks):
         del xs
     torch.cuda.empty_cache()
 
+    # paged KV gather / update: 64 sequences x 2048 tokens, 8 KV heads x 128, blocks of 16
+    n_blk, Hkv, bs_kv, Dh, Bkv, Lkv = 64 * 128, 8, 16, 128, 64, 2048
+    k_pool = torch.randn((n_blk, Hkv, bs_kv, Dh), device=device, dtype=torch.bfloat16)
+    v_pool = torch.randn_like(k_pool)
+    tables = torch.randperm(n_blk, device=device)[: Bkv * (Lkv // bs_kv)].reshape(Bkv, -1).to(torch.int32)
+    offs = torch.full((Bkv,), Lkv, dtype=torch.int32, device=device)
+    kv_bytes = 2 * 2 * Bkv * Hkv * Lkv * Dh * 2   # K and V, read + write
+    ms_g, launch_g = timed(lambda: tome_b200.gather_paged_kv(tables, offs, k_pool, v_pool, Lkv))
+    k_dense, v_dense = tome_b200.gather_paged_kv(tables, offs, k_pool, v_pool, Lkv)
+    zero_off = torch.zeros_like(offs)
+    ms_u, launch_u = timed(lambda: tome_b200.update_paged_kv(k_dense, v_dense, tables, zero_off,
+                                                             k_pool, v_pool))
+    extra["paged_kv"] = {"shape": "64 seq x 2048 tok x 8 heads x 128, bf16, block 16",
+                         "gather_ms": ms_g, "gather_GBps": kv_bytes / launch_g / 1e6,
+                         "update_ms": ms_u, "update_GBps": kv_bytes / launch_u / 1e6,
+                         "note": "gather time includes torch's allocation of the outputs"}
+    del k_pool, v_pool, tables, k_dense, v_dense
+    torch.cuda.empty_cache()
+
     # cfg3: fused LM head + log-prob, Qwen3-0.6B head shape
     hidden, weight, ids = synthetic.cfg3_lm_head(16384, 1024, VOCAB, device)
     ws = torch.empty(tome_b200.lm_head_workspace_bytes(16384, 1024, VOCAB), dtype=torch.uint8,

@@ -54,6 +54,7 @@ enum tome_status {
 #define TOME_DEV_TARGET_OUT_OF_RANGE 1
 #define TOME_DEV_TIMEOUT 2
 #define TOME_DEV_RAGGED_OVERFLOW 4 /* windows cover more positions than the packed arrays hold */
+#define TOME_DEV_BLOCK_OUT_OF_RANGE 8 /* a block-table entry outside [0, num_blocks) */
 
 /* Library version (TOME_B200_VERSION of the build). */
 int32_t tome_version(void);
@@ -255,6 +256,37 @@ int32_t tome_lmhead_logprob_static(const void* hidden, const void* weight, int64
                                    int64_t hidden_dim, int64_t vocab, const int32_t* targets,
                                    float temperature, float* out_logprob, float* out_lse,
                                    int32_t* dev_status, void* stream);
+
+/*
+ * Paged KV cache: gather and update (byte-exact data movement; adjacent to the log-prob path,
+ * used when the rollout restores or persists a shared prompt prefix).
+ * Pool layout [num_blocks, heads, block_size, head_dim]; block_tables int32 [batch, max_blocks];
+ * elem_bytes 2 (bf16/fp16) or 4; head_dim * elem_bytes must be a multiple of 16.
+ *
+ * tome_gather_paged_kv replaces gather_paged_kv (mlx-impl/paged_kv.py:57-116):
+ *   out[b, h, s, :] = pool[block_tables[b, s / block_size], h, s % block_size, :] for
+ *   s < offsets[b], and 0 for offsets[b] <= s < max_seq_len; out is [batch, heads, max_seq_len,
+ *   head_dim].
+ * tome_update_paged_kv replaces update_paged_kv (mlx-impl/paged_kv.py:6-54), IN PLACE on the
+ * pool (the reference returns new arrays): the first lengths[b] (NULL: new_len) tokens of
+ *   new[b] are written block_size at a time; piece i goes to the START of physical block
+ *   block_tables[b, (offsets[b] + i * block_size) / block_size]; pieces past the end of the
+ *   table are dropped.  Sequences that share a physical block write it concurrently.
+ * A table entry outside [0, num_blocks) is skipped (gather writes zeros) and sets
+ * TOME_DEV_BLOCK_OUT_OF_RANGE.
+ */
+int32_t tome_gather_paged_kv(const int32_t* block_tables, const int32_t* offsets,
+                             const void* k_pool, const void* v_pool, int32_t elem_bytes,
+                             int64_t batch, int64_t heads, int64_t head_dim, int32_t block_size,
+                             int32_t max_blocks, int32_t num_blocks, int64_t max_seq_len,
+                             void* k_out, void* v_out, int32_t* dev_status, void* stream);
+
+int32_t tome_update_paged_kv(const void* k_new, const void* v_new, const int32_t* block_tables,
+                             const int32_t* offsets, const int32_t* lengths, void* k_pool,
+                             void* v_pool, int32_t elem_bytes, int64_t batch, int64_t heads,
+                             int64_t new_len, int64_t head_dim, int32_t block_size,
+                             int32_t max_blocks, int32_t num_blocks, int32_t* dev_status,
+                             void* stream);
 
 /*
  * Combine per-shard triples into log-probs (the step after the vocab-parallel exchange;

@@ -257,3 +257,45 @@ def dual_logprob_kl(policy_logits, ref_logits, ids, lengths, temp: float = 1.0,
         lp_r[i, st:st + ln] = r
         kl[i, st:st + ln] = torch.exp(d) - d - 1.0
     return lp_p, lp_r, kl
+
+
+def gather_paged_kv(block_tables, offsets, k_pool, v_pool, max_seq_len: int):
+    """mlx-impl/paged_kv.py:57-116, thread body restated as loops: for s < offsets[b] the token
+    comes from ``pool[block_tables[b, s // bs], h, s % bs, :]``, otherwise it is zero."""
+    bt = _i64(block_tables)
+    off = _i64(offsets)
+    _, H, bs, D = k_pool.shape
+    B = bt.shape[0]
+    k_out = torch.zeros((B, H, max_seq_len, D), dtype=k_pool.dtype)
+    v_out = torch.zeros_like(k_out)
+    for b in range(B):
+        for s in range(min(int(off[b]), max_seq_len)):
+            phys = int(bt[b, s // bs])
+            k_out[b, :, s, :] = k_pool[phys, :, s % bs, :]
+            v_out[b, :, s, :] = v_pool[phys, :, s % bs, :]
+    return k_out, v_out
+
+
+def update_paged_kv(k_new, v_new, block_tables, offsets, k_pool, v_pool, block_size: int,
+                    lengths=None):
+    """mlx-impl/paged_kv.py:6-54 line by line (each piece of ``block_size`` tokens is written at
+    the START of its physical block, pieces past the table are dropped); returns new pools."""
+    bt = _i64(block_tables)
+    off = _i64(offsets)
+    B, H, S_new, D = k_new.shape
+    ln = _i64(lengths) if lengths is not None else torch.full((B,), S_new, dtype=torch.int64)
+    k_out, v_out = k_pool.clone(), v_pool.clone()
+    for b in range(B):
+        n_write = int(ln[b])
+        for i in range((n_write + block_size - 1) // block_size):
+            logical = (int(off[b]) + i * block_size) // block_size
+            if logical >= bt.shape[1]:
+                break
+            phys = int(bt[b, logical])
+            start, end = i * block_size, min((i + 1) * block_size, n_write)
+            if end - start <= 0:
+                continue
+            piece_k = k_new[b, :, start:end, :]
+            k_out[phys, :, : piece_k.shape[1], :] = piece_k
+            v_out[phys, :, : piece_k.shape[1], :] = v_new[b, :, start:end, :]
+    return k_out, v_out

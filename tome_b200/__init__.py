@@ -11,7 +11,7 @@ import importlib
 
 _OPS = ["check_device_status", "combine_triples", "fused_log_softmax", "grpo_dual_logprob_kl",
         "lm_head_logprob", "lm_head_logprob_static", "lm_head_partials",
-        "lm_head_workspace_bytes", "rms_norm", "ragged_logprobs", "sample_topk_logprob", "local_compute_logprobs", "local_compute_logprobs_host",
+        "lm_head_workspace_bytes", "rms_norm", "ragged_logprobs", "sample_topk_logprob", "gather_paged_kv", "update_paged_kv", "local_compute_logprobs", "local_compute_logprobs_host",
         "selective_log_softmax"]
 _DIST = ["lm_head_logprob_vocab_parallel", "pack_triples", "exchange_triples"]
 _LIB = ["TomeArgumentError", "TomeRuntimeError"]

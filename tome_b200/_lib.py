@@ -17,6 +17,7 @@ TOME_BF16 = 1
 DEV_TARGET_OUT_OF_RANGE = 1
 DEV_TIMEOUT = 2
 DEV_RAGGED_OVERFLOW = 4
+DEV_BLOCK_OUT_OF_RANGE = 8
 
 LMHEAD_ROUND_LOGITS_BF16 = 1
 
@@ -53,6 +54,12 @@ SIGNATURES = {
     "tome_lmhead_logprob_static": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                              c_void_p, c_float, c_void_p, c_void_p, c_void_p,
                                              c_void_p]),
+    "tome_gather_paged_kv": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64,
+                                       c_int64, c_int64, c_int32, c_int32, c_int32, c_int64,
+                                       c_void_p, c_void_p, c_void_p, c_void_p]),
+    "tome_update_paged_kv": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_int32, c_int64, c_int64, c_int64, c_int64,
+                                       c_int32, c_int32, c_int32, c_void_p, c_void_p]),
     "tome_combine_triples": (c_int32, [c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_int64,
                                        c_int32, c_int64, c_void_p, c_void_p, c_void_p]),
 }

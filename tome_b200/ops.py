@@ -51,6 +51,8 @@ def check_device_status(device=None) -> None:
         problems.append("a target index lies outside [0, vocab)")
     if bits & _lib.DEV_RAGGED_OVERFLOW:
         problems.append("the ragged windows cover more positions than the packed arrays hold")
+    if bits & _lib.DEV_BLOCK_OUT_OF_RANGE:
+        problems.append("a paged-KV block-table entry lies outside the pool")
     if bits & _lib.DEV_TIMEOUT:
         problems.append("a bounded device-side wait ran out (TOME_DEV_TIMEOUT)")
     raise TomeRuntimeError("; ".join(problems) or f"device status {bits}")
@@ -483,3 +485,67 @@ def combine_triples(m: torch.Tensor, s: torch.Tensor, t: torch.Tensor):
                                           _stream(device))
     _lib.check(status)
     return lp, lse
+
+
+def _paged_args(block_tables, offsets, k_pool, v_pool):
+    for name, t in (("block_tables", block_tables), ("offsets", offsets), ("k_pool", k_pool),
+                    ("v_pool", v_pool)):
+        _require_cuda(name, t)
+    if k_pool.shape != v_pool.shape or k_pool.dtype != v_pool.dtype or k_pool.dim() != 4:
+        raise ValueError("k_pool and v_pool must be [num_blocks, H, block_size, D] of one dtype")
+    if not (k_pool.is_contiguous() and v_pool.is_contiguous()):
+        raise ValueError("the pools must be contiguous")
+    if k_pool.element_size() not in (2, 4):
+        raise TypeError("pool elements must be 2 or 4 bytes wide")
+    bt = block_tables.to(torch.int32).contiguous()
+    off = offsets.to(torch.int32).contiguous()
+    if bt.dim() != 2 or off.shape != (bt.shape[0],):
+        raise ValueError("block_tables must be [B, max_blocks] and offsets [B]")
+    return bt, off
+
+
+def gather_paged_kv(block_tables: torch.Tensor, offsets: torch.Tensor, k_pool: torch.Tensor,
+                    v_pool: torch.Tensor, max_seq_len: int):
+    """Drop-in for ``gather_paged_kv`` (mlx-impl/paged_kv.py:57-116): dense
+    ``[B, H, max_seq_len, D]`` keys and values from the paged pool, zero past ``offsets[b]``.
+    The sizes the reference passes separately are read from the tensors."""
+    bt, off = _paged_args(block_tables, offsets, k_pool, v_pool)
+    num_blocks, H, block_size, D = k_pool.shape
+    B, max_blocks = bt.shape
+    device = k_pool.device
+    k_out = torch.empty((B, H, max_seq_len, D), dtype=k_pool.dtype, device=device)
+    v_out = torch.empty_like(k_out)
+    with torch.cuda.device(device):
+        status = lib.tome_gather_paged_kv(
+            bt.data_ptr(), off.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+            k_pool.element_size(), B, H, D, block_size, max_blocks, num_blocks, int(max_seq_len),
+            k_out.data_ptr(), v_out.data_ptr(), _status_word(device).data_ptr(), _stream(device))
+    _lib.check(status)
+    return k_out, v_out
+
+
+def update_paged_kv(k_new: torch.Tensor, v_new: torch.Tensor, block_tables: torch.Tensor,
+                    offsets: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                    lengths: Optional[torch.Tensor] = None):
+    """``update_paged_kv`` of mlx-impl/paged_kv.py:6-54 with the pool updated IN PLACE (the
+    reference returns new arrays): the first ``lengths[b]`` tokens of ``k_new[b]``/``v_new[b]``
+    (``[B, H, S_new, D]``) are written into the blocks the table names.  Returns the pools."""
+    bt, off = _paged_args(block_tables, offsets, k_pool, v_pool)
+    _require_cuda("k_new", k_new)
+    _require_cuda("v_new", v_new)
+    num_blocks, H, block_size, D = k_pool.shape
+    B, max_blocks = bt.shape
+    if k_new.shape != v_new.shape or k_new.dim() != 4 or k_new.shape[0] != B or \
+            k_new.shape[1] != H or k_new.shape[3] != D or k_new.dtype != k_pool.dtype:
+        raise ValueError("k_new/v_new must be [B, H, S_new, D] in the pool's dtype")
+    kn = k_new if k_new.is_contiguous() else k_new.contiguous()
+    vn = v_new if v_new.is_contiguous() else v_new.contiguous()
+    ln = None if lengths is None else lengths.to(device=k_pool.device, dtype=torch.int32).contiguous()
+    device = k_pool.device
+    with torch.cuda.device(device):
+        status = lib.tome_update_paged_kv(
+            kn.data_ptr(), vn.data_ptr(), bt.data_ptr(), off.data_ptr(), _ptr(ln),
+            k_pool.data_ptr(), v_pool.data_ptr(), k_pool.element_size(), B, H, kn.shape[2], D,
+            block_size, max_blocks, num_blocks, _status_word(device).data_ptr(), _stream(device))
+    _lib.check(status)
+    return k_pool, v_pool
