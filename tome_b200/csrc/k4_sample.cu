@@ -23,6 +23,7 @@
 #include <algorithm>
 
 #include "host_common.h"
+#include "online.cuh"
 #include "ptx.cuh"
 
 namespace tome {
@@ -31,7 +32,8 @@ constexpr int K4_THREADS = 512;
 constexpr int K4_WARPS = K4_THREADS / 32;
 constexpr int K4_MAX_K = 64;
 constexpr int K4_CAP = 8192;       // candidate list capacity
-constexpr int K4_SAMPLE = 8192;    // leading logits used to derive the first threshold
+constexpr int K4_SAMPLE = 32768;   // leading logits used to derive the first threshold
+constexpr int K4_GROUPS = K4_THREADS / 4;  // sample maxima kept for the threshold
 constexpr int K4_RANK_MAX = 1024;  // above this many candidates, compact before ranking
 constexpr int K4_MAX_SWEEPS = 64;  // re-sweeps with a tightened threshold before giving up
 
@@ -51,7 +53,7 @@ struct K4Params {
 struct K4Smem {
   unsigned long long cand[K4_CAP];   // candidates, packed (see k4_pack)
   unsigned long long top[K4_MAX_K];  // the top-k, best first
-  unsigned long long sort_buf[K4_THREADS];
+  uint32_t sample_key[K4_GROUPS];
   float red_f[2 * K4_WARPS];
   int32_t red_i[K4_WARPS];
   int32_t count;
@@ -150,26 +152,28 @@ __device__ uint32_t k4_philox(uint64_t ctr_lo, uint64_t ctr_hi, uint64_t key) {
   return c0;
 }
 
-// One pass over a row: every logit whose code is >= thr is written to the candidate ring (if
-// more than the capacity arrive, later ones overwrite earlier ones and the count tells); with
-// SOFTMAX the per-thread online (max, sum 2^((x - max) * c)) of ALL logits is updated too.
-// No barrier inside.
+// One pass over a row.  Candidate collection: a 16-byte vector is looked at element by element
+// only if its largest logit reaches the threshold's value (one compare per vector); elements
+// whose code is >= thr go to the candidate ring (if more than the capacity arrive, later ones
+// overwrite earlier ones and the count tells).  With SOFTMAX the per-thread online softmax of
+// ALL logits is updated too: the packed fast path (`fs`) for whole vectors, the exact scalar
+// form (`tail`) for the elements outside them.  No barrier inside.
 template <typename T, bool VEC, bool SOFTMAX>
 __device__ __forceinline__ void k4_sweep(const T* src, int64_t V, float c, unsigned long long thr,
-                                         K4Smem& sm, float& m, float& s) {
-  auto consider = [&](float x, int64_t i) {
-    if (SOFTMAX) {
-      if (x > m) {
-        s *= ex2f((m - x) * c);
-        m = x;
-      }
-      s += ex2f((x - m) * c);
-    }
+                                         K4Smem& sm, Fast& fs, Online& tail) {
+  // thr == 0 means "no threshold": every logit is a candidate
+  const float thr_val = (thr == 0ull) ? __int_as_float(0xff800000) : k4_value(thr);
+  auto candidate = [&](float x, int64_t i) {
     const unsigned long long code = k4_pack(x, i);
     if (code >= thr) {
       const uint32_t slot = static_cast<uint32_t>(atomicAdd(&sm.count, 1));
       sm.cand[slot % K4_CAP] = code;  // one aligned 8-byte store: never a torn entry
     }
+  };
+  auto scalar = [&](int64_t i) {
+    const float x = k4_load(src, i);
+    if (SOFTMAX) online_update_scalar(tail, x, c);
+    if (x >= thr_val) candidate(x, i);
   };
   if (VEC) {
     constexpr int PER = 16 / static_cast<int>(sizeof(T));
@@ -178,23 +182,55 @@ __device__ __forceinline__ void k4_sweep(const T* src, int64_t V, float c, unsig
 #pragma unroll 4
     for (int64_t v = threadIdx.x; v < nvec; v += K4_THREADS) {
       const uint4 q = __ldg(vp + v);
-      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-      const int64_t i0 = v * PER;
+      const float vmax = SOFTMAX ? fast_update<0>(fs, q, c, T()) : vec_max(q, T());
+      if (vmax >= thr_val) {
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        const int64_t i0 = v * PER;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (sizeof(T) == 4) {
-          consider(__uint_as_float(w[j]), i0 + j);
-        } else {
-          consider(__uint_as_float(w[j] << 16), i0 + 2 * j);
-          consider(__uint_as_float(w[j] & 0xffff0000u), i0 + 2 * j + 1);
+        for (int j = 0; j < 4; ++j) {
+          if (sizeof(T) == 4) {
+            candidate(__uint_as_float(w[j]), i0 + j);
+          } else {
+            candidate(__uint_as_float(w[j] << 16), i0 + 2 * j);
+            candidate(__uint_as_float(w[j] & 0xffff0000u), i0 + 2 * j + 1);
+          }
         }
       }
     }
-    for (int64_t i = nvec * PER + threadIdx.x; i < V; i += K4_THREADS) consider(k4_load(src, i), i);
+    for (int64_t i = nvec * PER + threadIdx.x; i < V; i += K4_THREADS) scalar(i);
   } else {
-#pragma unroll 8
-    for (int64_t i = threadIdx.x; i < V; i += K4_THREADS) consider(k4_load(src, i), i);
+#pragma unroll 4
+    for (int64_t i = threadIdx.x; i < V; i += K4_THREADS) scalar(i);
   }
+}
+
+// Block-wide exact (max, sum 2^((x - max) * c)) of a row with plain loads, for rows the fast
+// path cannot represent (see K1_M_FLOOR in online.cuh).  Every thread gets the result.
+template <typename T>
+__device__ void k4_exact_row(const T* src, int64_t V, float c, K4Smem& sm, float& row_m,
+                             float& row_s) {
+  float mx = __int_as_float(0xff800000);
+  for (int64_t i = threadIdx.x; i < V; i += K4_THREADS) mx = fmaxf(mx, k4_load(src, i));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((threadIdx.x & 31) == 0) sm.red_f[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = sm.red_f[0];
+#pragma unroll
+  for (int w = 1; w < K4_WARPS; ++w) mx = fmaxf(mx, sm.red_f[w]);
+  __syncthreads();
+  float sum = 0.0f;
+  for (int64_t i = threadIdx.x; i < V; i += K4_THREADS) sum += ex2f((k4_load(src, i) - mx) * c);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if ((threadIdx.x & 31) == 0) sm.red_f[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  sum = 0.0f;
+#pragma unroll
+  for (int w = 0; w < K4_WARPS; ++w) sum += sm.red_f[w];
+  __syncthreads();
+  row_m = mx;
+  row_s = sum;
 }
 
 template <typename T>
@@ -213,24 +249,42 @@ __global__ void __launch_bounds__(K4_THREADS) k4_sample_kernel(const K4Params p)
     const int64_t V = p.vocab;
     const int32_t kk = static_cast<int32_t>(min(static_cast<int64_t>(k), V));
 
-    // ---- first threshold: the kk-th best of the per-thread bests over the leading K4_SAMPLE
-    //      logits; at least kk logits are at least that good, so it bounds the answer from below
+    // ---- first threshold: the leading K4_SAMPLE logits are cut into 128 groups (4 adjacent
+    //      threads each); the kk-th largest group maximum is a value that at least kk logits
+    //      reach, so it bounds the answer from below.  Values only: ties are kept.
+    const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0);
     const int64_t n_sample = min(static_cast<int64_t>(K4_SAMPLE), V);
-    unsigned long long local = 0ull;
-    for (int64_t i = tid; i < n_sample; i += K4_THREADS)
-      local = max(local, k4_pack(k4_load(src, i), i));
-    sm.sort_buf[tid] = local;
-    if (tid == 0) sm.count = 0;
+    float lmax = __int_as_float(0xff800000);
+    int64_t filled_threads;  // threads that saw at least one logit
+    if (vec) {
+      constexpr int PER = 16 / static_cast<int>(sizeof(T));
+      const int64_t nvec_s = n_sample / PER;
+      const uint4* vp = reinterpret_cast<const uint4*>(src);
+#pragma unroll 4
+      for (int64_t v = tid; v < nvec_s; v += K4_THREADS) lmax = fmaxf(lmax, vec_max(__ldg(vp + v), T()));
+      filled_threads = min(nvec_s, static_cast<int64_t>(K4_THREADS));
+    } else {
+#pragma unroll 4
+      for (int64_t i = tid; i < n_sample; i += K4_THREADS) lmax = fmaxf(lmax, k4_load(src, i));
+      filled_threads = min(n_sample, static_cast<int64_t>(K4_THREADS));
+    }
+    lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, 1));
+    lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, 2));
+    if ((tid & 3) == 0) sm.sample_key[tid >> 2] = k4_key(lmax);
+    if (tid == 0) {
+      sm.count = 0;
+      sm.bcast = 0ull;  // no usable threshold: every logit is a candidate
+    }
     __syncthreads();
-    {
-      // rank of each thread's best among the 512 (threads without a logit hold 0; ties among
-      // those by thread id): all-pairs, V >= kk guarantees kk real entries
+    const int64_t full_groups = filled_threads / 4;  // groups whose four threads all hold data
+    if (tid < K4_GROUPS && full_groups >= kk) {
+      const uint32_t mine = sm.sample_key[tid];
       int32_t rank = 0;
-      for (int j = 0; j < K4_THREADS; ++j) {
-        const unsigned long long o = sm.sort_buf[j];
-        rank += (o > local || (o == local && j < tid)) ? 1 : 0;
+      for (int j = 0; j < K4_GROUPS; ++j) {
+        const uint32_t o = sm.sample_key[j];
+        rank += (o > mine || (o == mine && j < tid)) ? 1 : 0;
       }
-      if (rank == kk - 1) sm.bcast = local;
+      if (rank == kk - 1) sm.bcast = static_cast<unsigned long long>(mine) << 32;
     }
     __syncthreads();
     unsigned long long thr = sm.bcast;
@@ -238,16 +292,18 @@ __global__ void __launch_bounds__(K4_THREADS) k4_sample_kernel(const K4Params p)
 
     // ---- sweep: online softmax of the whole row + candidate collection; swept again with a
     //      tighter threshold only if more candidates arrived than the ring holds
-    float m = -FLT_MAX, s = 0.0f;
-    const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0);
+    Fast fs;
+    fast_init(fs, c);
+    Online tail;
+    online_init(tail);
     int32_t n = 0;
     for (int sweep = 0; sweep < K4_MAX_SWEEPS; ++sweep) {
       if (sweep == 0) {
-        if (vec) k4_sweep<T, true, true>(src, V, c, thr, sm, m, s);
-        else k4_sweep<T, false, true>(src, V, c, thr, sm, m, s);
+        if (vec) k4_sweep<T, true, true>(src, V, c, thr, sm, fs, tail);
+        else k4_sweep<T, false, true>(src, V, c, thr, sm, fs, tail);
       } else {
-        if (vec) k4_sweep<T, true, false>(src, V, c, thr, sm, m, s);
-        else k4_sweep<T, false, false>(src, V, c, thr, sm, m, s);
+        if (vec) k4_sweep<T, true, false>(src, V, c, thr, sm, fs, tail);
+        else k4_sweep<T, false, false>(src, V, c, thr, sm, fs, tail);
       }
       __syncthreads();
       const int32_t total = sm.count;
@@ -270,6 +326,9 @@ __global__ void __launch_bounds__(K4_THREADS) k4_sample_kernel(const K4Params p)
 
     // ---- merge the online softmax across the block
     {
+      const Online vecs = fast_finish(fs, c);
+      const float m = fmaxf(vecs.m, tail.m);
+      const float s = vecs.s * ex2f((vecs.m - m) * c) + tail.s * ex2f((tail.m - m) * c);
       float wm = m;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
@@ -287,6 +346,9 @@ __global__ void __launch_bounds__(K4_THREADS) k4_sample_kernel(const K4Params p)
     for (int w = 0; w < K4_WARPS; ++w) row_m = fmaxf(row_m, sm.red_f[2 * w]);
 #pragma unroll
     for (int w = 0; w < K4_WARPS; ++w) row_s += sm.red_f[2 * w + 1] * ex2f((sm.red_f[2 * w] - row_m) * c);
+    __syncthreads();
+    // the true maximum contributes 2^0, so a healthy row has row_s >= ~1 (see online.cuh)
+    if (!(row_s >= 0.5f && row_s <= FLT_MAX)) k4_exact_row(src, V, c, sm, row_m, row_s);
     const float lse = __fdiv_rn(row_m, temp) + logf(row_s);
 
     // ---- exact top-kk of the candidates, best first
