@@ -77,6 +77,24 @@ def test_full_size_heads_against_an_independent_gpu_reduction(cuda_device, rows,
     assert max_abs(lp[sample], o_lp) <= TOL and max_abs(lse[sample], o_lse) <= TOL
 
 
+def test_peaked_and_large_magnitude_logits(cuda_device):
+    """Weights scaled so that logits reach |x| ~ 100 (300 after the temperature) with a sharply peaked softmax, low
+    temperature on top: the exponent arithmetic (x*c - fl(max*c) with the residual folded
+    back) must stay inside the tolerance relative to the size of the numbers involved."""
+    import tome_b200
+    from tome_b200 import synthetic
+    hidden, weight, ids = synthetic.cfg3_lm_head(256, 512, 6000, "cpu", 52, 1.0)
+    for temp in (1.0, 0.3):
+        lp, lse = tome_b200.lm_head_logprob(hidden.to(cuda_device), weight.to(cuda_device),
+                                            ids.to(cuda_device), temp, check=True)
+        o_lp, o_lse = oracle.lm_head_logprob(hidden, weight, ids, temp)
+        scale = float(o_lse.abs().max())
+        assert scale > 60                       # the case is what it claims to be
+        # fp32 carries ~7 digits: allow 2e-3 absolute or 2e-6 relative to the magnitude
+        tol = max(TOL, 2e-6 * scale * 10)
+        assert max_abs(lse, o_lse) <= tol and max_abs(lp, o_lp) <= 2 * tol, (max_abs(lp, o_lp), tol)
+
+
 def test_leading_dims_and_golden(cuda_device):
     import tome_b200
     gld = load_golden("lm_head.npz")
