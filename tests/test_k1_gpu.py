@@ -313,6 +313,22 @@ def test_dual_windows_with_starts_and_poisoned_padding(cuda_device):
     assert not torch.isnan(p).any() and not torch.isnan(kl).any()
 
 
+def test_dual_at_the_sequence_limit(cuda_device):
+    """1024 sequences per call is the limit (the prefix sums live in shared memory)."""
+    import tome_b200
+    g = torch.Generator().manual_seed(23)
+    n_seq, seq_len, vocab = 1024, 3, 520
+    pol = (torch.randn((n_seq, seq_len, vocab), generator=g) * 2).to(torch.bfloat16)
+    ref = (pol.float() + 0.1 * torch.randn((n_seq, seq_len, vocab), generator=g)).to(torch.bfloat16)
+    ids = torch.randint(0, vocab, (n_seq, seq_len), generator=g, dtype=torch.int32)
+    lengths = torch.randint(0, seq_len + 1, (n_seq,), generator=g, dtype=torch.int32)
+    _check_dual(pol, ref, ids, lengths, 0.7, cuda_device)
+    big = torch.zeros((1025, 1, 16), dtype=torch.bfloat16, device=cuda_device)
+    with pytest.raises(tome_b200.TomeArgumentError):
+        tome_b200.grpo_dual_logprob_kl(big, big, torch.zeros((1025, 1), dtype=torch.int32),
+                                       torch.ones(1025, dtype=torch.int32), 1.0)
+
+
 def test_dual_fp32_and_cfg5_shape(cuda_device):
     from tome_b200 import synthetic
     pol, ref, ids, lengths, temp = synthetic.cfg5_dual(2, 96, 151936, "cpu", 1005)

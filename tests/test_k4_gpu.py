@@ -97,3 +97,23 @@ def test_rollout_step_shape_and_argument_errors(cuda_device):
         tome_b200.sample_topk_logprob(x.to(cuda_device), 0.7, top_k=65)
     with pytest.raises(tome_b200.TomeArgumentError):
         tome_b200.sample_topk_logprob(x.to(cuda_device), -1.0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_unaligned_rows_and_extreme_k(cuda_device, dtype):
+    """A vocabulary that is not a multiple of the vector width makes every other row start off
+    a 16-byte boundary (scalar path); top_k = 1 and top_k = 64 are the ends of the range."""
+    import tome_b200
+    x = _case(7, 1003, dtype, 21)
+    for k in (1, 64):
+        tok, lp, tk_i, tk_v = tome_b200.sample_topk_logprob(x.to(cuda_device), 0.9, k, seed=5,
+                                                            return_topk=True)
+        for r in range(7):
+            idx, _ = oracle.topk_sampling_distribution(x[r], 0.9, k)
+            assert tk_i[r].cpu().tolist() == idx.tolist()
+        o_lp, _, _ = oracle.selective_logprob(x, tok.cpu(), 0.9)
+        assert max_abs(lp, o_lp) <= TOL[dtype]
+    # a sliced view: odd base offset as well
+    view = x.to(cuda_device)[:, 1:1000]
+    tok, lp = tome_b200.sample_topk_logprob(view, 0.0)
+    assert tok.cpu().tolist() == torch.argmax(x[:, 1:1000].float(), dim=-1).tolist()
