@@ -583,8 +583,16 @@ static int32_t k1_launch_typed(const K1Params& p_in, bool bulk_ok, int64_t max_i
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
         "cudaFuncSetAttribute");
     if (st != TOME_OK) return st;
+    int64_t ctas_per_sm = K1_CTAS_PER_SM;
+    if (MODE == K1_FULL) {
+      // the second pass over a row should find it in L2: keep the rows in flight (one per CTA)
+      // under ~100 MB, but never fewer than two CTAs per SM (measured: 4.2 -> 4.9 TB/s on bf16)
+      const int64_t row_bytes = std::max<int64_t>(1, p.vocab * es);
+      ctas_per_sm = std::max<int64_t>(
+          2, std::min<int64_t>(K1_CTAS_PER_SM, (100ll << 20) / (row_bytes * info.sm_count)));
+    }
     const int grid = static_cast<int>(
-        std::max<int64_t>(1, std::min<int64_t>(info.sm_count * K1_CTAS_PER_SM, max_items)));
+        std::max<int64_t>(1, std::min<int64_t>(info.sm_count * ctas_per_sm, max_items)));
     kernel<<<grid, K1_THREADS, smem, stream>>>(p);
   } else {
     const int grid = static_cast<int>(std::max<int64_t>(
