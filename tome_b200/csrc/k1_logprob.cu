@@ -420,7 +420,8 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
           uint8_t* drow = reinterpret_cast<uint8_t*>(dst) + off;
           for (; v < nvec; v += K1_CONSUMERS) {
             const uint4 a = lds128(sbase + v * 16);
-            stg128(drow + static_cast<size_t>(v) * 16, full_out_vec(a, p.inv_temp, lse_row, T()));
+            stg128_streaming(drow + static_cast<size_t>(v) * 16,
+                             full_out_vec(a, p.inv_temp, lse_row, T()));
           }
         }
         __syncwarp();

@@ -138,6 +138,13 @@ __device__ __forceinline__ void stg128(void* p, uint4 v) {
                : "memory");
 }
 
+// 128-bit store of data that will not be read again soon (evict-first in the caches).
+__device__ __forceinline__ void stg128_streaming(void* p, uint4 v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
