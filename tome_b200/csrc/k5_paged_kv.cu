@@ -50,14 +50,14 @@ __global__ void __launch_bounds__(256) k5_gather_kernel(const K5Params p) {
       if (phys >= 0 && phys < p.num_blocks) {
         const int64_t src = ((static_cast<int64_t>(phys) * p.H + h) * p.block_size + in_blk) *
                                 p.vec_per_row + dv;
-        kq = p.k_src[src];
-        vq = p.v_src[src];
+        kq = __ldcs(p.k_src + src);  // every byte is touched once: stream through the caches
+        vq = __ldcs(p.v_src + src);
       } else {
         k5_raise(p.status, TOME_DEV_BLOCK_OUT_OF_RANGE);
       }
     }
-    p.k_dst[i] = kq;
-    p.v_dst[i] = vq;
+    __stcs(p.k_dst + i, kq);
+    __stcs(p.v_dst + i, vq);
   }
 }
 
@@ -87,8 +87,8 @@ __global__ void __launch_bounds__(256) k5_update_kernel(const K5Params p) {
     }
     const int64_t dst = ((static_cast<int64_t>(phys) * p.H + h) * p.block_size + in_blk) *
                             p.vec_per_row + dv;
-    p.k_dst[dst] = p.k_src[i];
-    p.v_dst[dst] = p.v_src[i];
+    __stcs(p.k_dst + dst, __ldcs(p.k_src + i));
+    __stcs(p.v_dst + dst, __ldcs(p.v_src + i));
   }
 }
 
