@@ -62,10 +62,18 @@ def lm_head_logprob_vocab_parallel(hidden: torch.Tensor, weight_shard: torch.Ten
         rank = dist.get_rank(group)
     else:
         world, rank = 1, 0
-    m, s, t = ops.lm_head_partials(hidden, weight_shard, vocab_offset, ids, temp,
-                                   workspace=workspace)
-    buf = pack_triples(m, s, t, rank, world, out=packed)
-    m_all, s_all, t_sum = exchange_triples(buf, group)
-    lp, lse = ops.combine_triples(m_all.contiguous(), s_all.contiguous(), t_sum.contiguous())
+    rows = hidden.numel() // hidden.shape[-1]
+    if packed is None:
+        packed = torch.zeros((2 * world + 1, rows), dtype=torch.float32, device=hidden.device)
+    else:
+        if packed.shape != (2 * world + 1, rows) or packed.dtype != torch.float32 or \
+                not packed.is_contiguous():
+            raise ValueError(f"packed must be a contiguous fp32 [{2 * world + 1}, {rows}] tensor")
+        packed.zero_()
+    # the kernel writes this rank's slots of the exchange buffer directly
+    ops.lm_head_partials(hidden, weight_shard, vocab_offset, ids, temp, workspace=workspace,
+                         out=(packed[rank], packed[world + rank], packed[2 * world]))
+    m_all, s_all, t_sum = exchange_triples(packed, group)
+    lp, lse = ops.combine_triples(m_all, s_all, t_sum)
     lead = hidden.shape[:-1]
     return lp.reshape(lead), lse.reshape(lead)

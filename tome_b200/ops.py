@@ -371,12 +371,15 @@ def _head_flags(round_logits: bool) -> int:
 
 def lm_head_partials(hidden: torch.Tensor, weight_shard: torch.Tensor, vocab_offset: int,
                      ids: torch.Tensor, temp: float = 1.0, *,
-                     workspace: Optional[torch.Tensor] = None, round_logits: bool = False):
+                     workspace: Optional[torch.Tensor] = None, round_logits: bool = False,
+                     out: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None):
     """Per-row triple ``(m, s, t)`` of one vocabulary shard of the LM head (fp32 ``[rows]`` each).
 
     ``m = max_j(x_j)/temp``, ``s = sum_j exp(x_j/temp - m)``, ``t = x_target/temp`` if the
     shard owns the target else 0, for ``x = hidden @ weight_shard.T``; no logits are stored.
     ``ids`` are global vocabulary indices; ``vocab_offset`` is the global index of shard row 0.
+    ``out`` may name three contiguous fp32 ``[rows]`` tensors to write into (for instance rows of
+    the exchange buffer of the vocab-parallel path).
     """
     h2, w2 = _lm_head_inputs(hidden, weight_shard)
     temp = float(temp or 1.0)
@@ -386,7 +389,14 @@ def lm_head_partials(hidden: torch.Tensor, weight_shard: torch.Tensor, vocab_off
     ids32 = _ids32(ids, rows, device)
     nbytes = lm_head_workspace_bytes(rows, K, V_local)
     ws = _workspace(nbytes, device, workspace)
-    m, s, t = (torch.empty(rows, dtype=torch.float32, device=device) for _ in range(3))
+    if out is None:
+        m, s, t = (torch.empty(rows, dtype=torch.float32, device=device) for _ in range(3))
+    else:
+        m, s, t = out
+        for x in (m, s, t):
+            if x.dtype != torch.float32 or x.shape != (rows,) or not x.is_contiguous() or \
+                    x.device != device:
+                raise ValueError("out must hold three contiguous fp32 [rows] tensors on the device")
     with torch.cuda.device(device):
         status = lib.tome_lmhead_partials(
             h2.data_ptr(), w2.data_ptr(), rows, K, V_local, int(vocab_offset), ids32.data_ptr(),
