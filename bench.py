@@ -232,6 +232,22 @@ def run_reference(args, rank: int):
 
 # ---------------------------------------------------------------------------- GPU legs
 def run_ours(args):
+    # stdout must carry exactly one JSON line: libraries that print to file descriptor 1 (NCCL's
+    # version banner, for one) are sent to stderr for the duration of the run
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        line = _run_ours(args)
+    finally:
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        os.close(real_stdout)
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def _run_ours(args):
     import torch
     import tome_b200
     from tome_b200 import synthetic
@@ -344,8 +360,7 @@ def run_ours(args):
         import torch.distributed as dist
         dist.barrier(device_ids=[local])
         dist.destroy_process_group()
-    if rank == 0:
-        print(json.dumps(line), flush=True)
+    return line if rank == 0 else None
 
 
 def run_extra(args, device, rank, world, dist_on, barrier, peaks):
