@@ -463,7 +463,8 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
 }
 
 // ------------------------------------------------------------------ plain-load kernel
-// Same arithmetic with ordinary loads; any alignment, any pitch.  One CTA per row at a time.
+// Same arithmetic with ordinary loads; any alignment, any pitch.  One CTA per row at a time;
+// each row is read with 128-bit loads from its first 16-byte boundary on.
 constexpr int K1_PLAIN_THREADS = 256;
 
 template <typename T, int MODE>
@@ -495,9 +496,23 @@ __global__ void __launch_bounds__(K1_PLAIN_THREADS) k1_plain_kernel(const K1Para
     for (int sub = 0; sub < NSUB; ++sub) {
       const T* src = reinterpret_cast<const T*>(p.src[(MODE == K1_DUAL) ? sub : 0]) +
                      row * p.stride;
-      Online st;
-      online_init(st);
-      for (int64_t j = threadIdx.x; j < p.vocab; j += K1_PLAIN_THREADS)
+      // a row may start anywhere: scalar loads up to the first 16-byte boundary, 128-bit
+      // loads for the aligned body (packed fast path), scalar loads for what is left
+      constexpr int64_t PER = 16 / static_cast<int64_t>(sizeof(T));
+      const uintptr_t addr = reinterpret_cast<uintptr_t>(src);
+      const int64_t head = min(p.vocab, static_cast<int64_t>(((16 - (addr & 15)) & 15) / sizeof(T)));
+      const int64_t nvec = (p.vocab - head) / PER;
+      const int64_t tail_begin = head + nvec * PER;
+      const uint4* body = reinterpret_cast<const uint4*>(src + head);
+      Fast fs;
+      fast_init(fs, p.c);
+#pragma unroll 4
+      for (int64_t v = threadIdx.x; v < nvec; v += K1_PLAIN_THREADS)
+        fast_update<0>(fs, __ldg(body + v), p.c, T());
+      Online st = fast_finish(fs, p.c);
+      for (int64_t j = threadIdx.x; j < head; j += K1_PLAIN_THREADS)
+        online_update_scalar(st, to_float(src[j]), p.c);
+      for (int64_t j = tail_begin + threadIdx.x; j < p.vocab; j += K1_PLAIN_THREADS)
         online_update_scalar(st, to_float(src[j]), p.c);
       online_warp_reduce(st, p.c);
       if (lane == 0) part[warp] = make_float2(st.m, st.s);
@@ -510,6 +525,8 @@ __global__ void __launch_bounds__(K1_PLAIN_THREADS) k1_plain_kernel(const K1Para
         float s = ms.y * ex2f((ms.x - m) * p.c);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        // the true maximum contributes 2^0, so a healthy row has s >= ~1 (see online.cuh)
+        if (!(s >= 0.5f && s <= FLT_MAX)) exact_row(src, p.vocab, p.c, lane, m, s);
         if (lane == 0) {
           float x_t = 0.0f;
           bool target_ok = true;
