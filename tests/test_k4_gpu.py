@@ -117,3 +117,50 @@ def test_unaligned_rows_and_extreme_k(cuda_device, dtype):
     view = x.to(cuda_device)[:, 1:1000]
     tok, lp = tome_b200.sample_topk_logprob(view, 0.0)
     assert tok.cpu().tolist() == torch.argmax(x[:, 1:1000].float(), dim=-1).tolist()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("vocab", [24, 600, 4096 + 8, 40000])
+def test_large_batches_take_the_streaming_path(cuda_device, dtype, vocab):
+    """From 1024 rows on, the batch goes through the TMA-pipelined kernel; rows it cannot
+    finish (sorted, constant or heavily tied ones overflow its small candidate ring) come back
+    marked and are redone by the one-CTA-per-row kernel.  Both must give the oracle's top-k."""
+    import tome_b200
+    rows = 1200
+    x = _case(rows, vocab, dtype, 300 + vocab % 71)
+    x[5] = torch.linspace(-8, 8, vocab).to(dtype)          # ascending: overflows the ring
+    x[6, :] = 0.5                                           # constant
+    x[7, : vocab // 2] = float("-inf")
+    tok, lp, tk_i, tk_v = tome_b200.sample_topk_logprob(x.to(cuda_device), 0.7, 20, seed=8, offset=2,
+                                                        return_topk=True)
+    assert int(tok.min()) >= 0                              # no row left marked
+    k = min(20, vocab)
+    for r in list(range(12)) + list(range(rows - 5, rows)) + [400, 777]:
+        idx, _ = oracle.topk_sampling_distribution(x[r], 0.7, 20)
+        assert tk_i[r, :k].cpu().tolist() == idx.tolist(), r
+        assert torch.equal(tk_v[r, :k].cpu(), x[r].float()[idx])
+        assert int(tok[r]) in idx.tolist()
+    o_lp, _, _ = oracle.selective_logprob(x, tok.cpu(), 0.7)
+    assert max_abs(lp, o_lp) <= TOL[dtype]
+    # greedy on the same batch
+    tok0, lp0 = tome_b200.sample_topk_logprob(x.to(cuda_device), 0.0)
+    assert tok0.cpu().tolist() == torch.argmax(x.float(), dim=-1).tolist()
+    o_lp0, _, _ = oracle.selective_logprob(x, tok0.cpu(), 1.0)
+    assert max_abs(lp0, o_lp0) <= TOL[dtype]
+
+
+def test_streaming_path_draws_follow_the_topk_softmax(cuda_device):
+    import tome_b200
+    g = torch.Generator().manual_seed(10)
+    row = (torch.randn((1, 4096), generator=g) * 2.0).to(torch.bfloat16)
+    n = 20000
+    x = row.expand(n, -1).contiguous().to(cuda_device)
+    tok, _ = tome_b200.sample_topk_logprob(x, 0.8, 20, seed=99, offset=1)
+    idx, probs = oracle.topk_sampling_distribution(row[0], 0.8, 20)
+    counts = torch.stack([(tok.cpu() == int(i)).sum() for i in idx]).double()
+    assert int(counts.sum()) == n
+    chi2 = float((((counts - n * probs) ** 2) / (n * probs)).sum())
+    assert chi2 < 50.0, chi2
+    # the same draws as the one-CTA-per-row kernel makes for the same (seed, offset, row)
+    tok_small, _ = tome_b200.sample_topk_logprob(x[:512], 0.8, 20, seed=99, offset=1)
+    assert torch.equal(tok[:512], tok_small)

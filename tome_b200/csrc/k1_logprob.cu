@@ -30,12 +30,14 @@
 #include <type_traits>
 
 #include "host_common.h"
+#include "k1_sample.h"
 #include "online.cuh"
 #include "ptx.cuh"
+#include "sampling.cuh"
 
 namespace tome {
 
-enum K1Mode { K1_SELECTIVE = 0, K1_DUAL = 1, K1_FULL = 2, K1_RAGGED = 3 };
+enum K1Mode { K1_SELECTIVE = 0, K1_DUAL = 1, K1_FULL = 2, K1_RAGGED = 3, K1_SAMPLE = 4 };
 
 // DUAL and RAGGED score only a window [start, start + length) of each sequence.
 __host__ __device__ constexpr bool k1_windowed(int mode) {
@@ -95,6 +97,12 @@ struct K1Params {
   int32_t seq_len;         // DUAL
   int64_t packed_capacity; // RAGGED: entries the packed target/output arrays can hold
   int32_t* out_offsets;    // RAGGED: int32 [n_seq + 1], start of each sequence in the packed output
+  int32_t* out_tokens;     // SAMPLE: int32 [rows]; -1 marks a row left to the one-CTA-per-row kernel
+  int32_t* out_topk_idx;   // SAMPLE: nullable, [rows, top_k]
+  float* out_topk_val;     // SAMPLE: nullable, [rows, top_k]
+  uint64_t seed, offset;   // SAMPLE: random stream
+  int32_t top_k;           // SAMPLE: 1..64
+  int32_t greedy;          // SAMPLE: temperature 0 -> argmax, scored at temperature 1
   int32_t* status;         // nullable
   int32_t chunk_bytes;     // bulk-copy size (multiple of 16, <= K1_CHUNK_BYTES), set by launch
   int32_t n_chunks;        // bulk copies per row
@@ -264,7 +272,21 @@ struct K1Smem {
   static constexpr int SCRATCH_OFF = CUM_OFF + (K1_MAX_SEQ + 1) * 4 + 12;
   static constexpr int TOTAL_DUAL = SCRATCH_OFF + K1_THREADS * 4;
   static constexpr int TOTAL_PLAIN = CUM_OFF;
+  static constexpr int SAMPLE_OFF = (CUM_OFF + 7) & ~7;                  // SAMPLE: K1SampleSmem
 };
+
+// SAMPLE mode: candidate ring and top-k of the row a CTA is working on.
+constexpr int K1_SAMPLE_CAP = 512;
+constexpr int K1_SAMPLE_SUBSET = 64;  // candidates used for the cheap pre-filter (>= top_k)
+constexpr int K1_SAMPLE_GROUPS = K1_CONSUMERS / 2;
+struct K1SampleSmem {
+  unsigned long long cand[K1_SAMPLE_CAP];
+  unsigned long long top[64];
+  unsigned long long thr;
+  uint32_t gkey[K1_SAMPLE_GROUPS];
+  int32_t count;
+};
+static_assert(K1_SAMPLE_GROUPS >= 64, "the threshold needs at least top_k (<= 64) groups");
 
 // Exact two-pass (max, sum 2^((x - max) * c)) of one row with plain loads, by one full warp.
 // Only used for rows the streaming arithmetic cannot represent (see K1_M_FLOOR).
@@ -379,7 +401,7 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       // the one thread that finishes the row fetches the target logit early
       float x_t = 0.0f;
       bool target_ok = true;
-      if (MODE != K1_FULL && ctid == 0) {
+      if (MODE != K1_FULL && MODE != K1_SAMPLE && ctid == 0) {
         const int32_t t = p.targets[oidx];
         target_ok = (t >= 0) && (static_cast<int64_t>(t) < p.vocab);
         if (target_ok) x_t = to_float(src[t]);
@@ -390,6 +412,70 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       fast_init(fs, p.c);
       T* dst = nullptr;
       if (MODE == K1_FULL) dst = reinterpret_cast<T*>(p.out_full) + row * p.out_stride;
+
+      // SAMPLE: a value that at least top_k logits reach, from the row's first chunk: the
+      // top_k-th largest of 64 group maxima (2 adjacent threads per group).  Ties are kept.
+      K1SampleSmem& smp = *reinterpret_cast<K1SampleSmem*>(smem + K1Smem::SAMPLE_OFF);
+      unsigned long long thr = 0ull;
+      float thr_val = __int_as_float(0xff800000);
+      const int32_t kk = static_cast<int32_t>(min(static_cast<int64_t>(p.top_k), p.vocab));
+      if (MODE == K1_SAMPLE) {
+        uint32_t nvec0 = 0;
+        float lmax = __int_as_float(0xff800000);
+        if (n_chunks > 0) {
+          const uint32_t stage = it % K1_STAGES;
+          const uint32_t phase = (it / K1_STAGES) & 1u;
+          if (!mbar_wait(full_bar + stage * 8, phase)) {
+            raise_status(p.status, TOME_DEV_TIMEOUT);
+            return;
+          }
+          nvec0 = static_cast<uint32_t>(min(chunk_bytes, bulk_bytes)) >> 4;
+          const uint32_t sbase = smem_base + stage * K1_CHUNK_BYTES;
+          for (uint32_t v = ctid; v < nvec0; v += K1_CONSUMERS)
+            lmax = fmaxf(lmax, vec_max(lds128(sbase + v * 16), T()));
+        }
+        lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, 1));
+        if ((ctid & 1) == 0) smp.gkey[ctid >> 1] = k4_key(lmax);
+        if (ctid == 0) {
+          smp.count = 0;
+          smp.thr = 0ull;
+        }
+        named_bar_sync(2, K1_CONSUMERS);
+        const int32_t full_groups =
+            static_cast<int32_t>(min(nvec0, static_cast<uint32_t>(K1_CONSUMERS))) / 2;
+        if (ctid < K1_SAMPLE_GROUPS && full_groups >= kk) {
+          const uint32_t mine = smp.gkey[ctid];
+          int32_t rank = 0;
+          for (int j = 0; j < K1_SAMPLE_GROUPS; ++j) {
+            const uint32_t o = smp.gkey[j];
+            rank += (o > mine || (o == mine && j < ctid)) ? 1 : 0;
+          }
+          if (rank == kk - 1) smp.thr = static_cast<unsigned long long>(mine) << 32;
+        }
+        named_bar_sync(2, K1_CONSUMERS);
+        thr = smp.thr;
+        if (thr != 0ull) thr_val = k4_value(thr);
+      }
+      // SAMPLE: the logits of a vector that reach the threshold join the candidate ring
+      auto push = [&](float x, int64_t i) {
+        if (x >= thr_val) {
+          const unsigned long long code = k4_pack(x, i);
+          if (code >= thr)
+            smp.cand[static_cast<uint32_t>(atomicAdd(&smp.count, 1)) % K1_SAMPLE_CAP] = code;
+        }
+      };
+      auto collect = [&](uint4 q, int64_t i0) {
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (sizeof(T) == 4) {
+            push(__uint_as_float(w[j]), i0 + j);
+          } else {
+            push(__uint_as_float(w[j] << 16), i0 + 2 * j);
+            push(__uint_as_float(w[j] & 0xffff0000u), i0 + 2 * j + 1);
+          }
+        }
+      };
 
       for (int64_t k = 0; k < n_chunks; ++k, ++it) {
         const uint32_t stage = it % K1_STAGES;
@@ -409,13 +495,26 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
             const uint4 b = lds128(sbase + (v + K1_CONSUMERS) * 16);
             const uint4 cc = lds128(sbase + (v + 2 * K1_CONSUMERS) * 16);
             const uint4 d = lds128(sbase + (v + 3 * K1_CONSUMERS) * 16);
-            fast_update<POLY>(fs, a, p.c, T());
-            fast_update<POLY>(fs, b, p.c, T());
-            fast_update<POLY>(fs, cc, p.c, T());
-            fast_update<POLY>(fs, d, p.c, T());
+            const float ma = fast_update<POLY>(fs, a, p.c, T());
+            const float mb = fast_update<POLY>(fs, b, p.c, T());
+            const float mc = fast_update<POLY>(fs, cc, p.c, T());
+            const float md = fast_update<POLY>(fs, d, p.c, T());
+            if (MODE == K1_SAMPLE) {
+              const int64_t e0 = (off >> 4) * PER_VEC;  // first element of this chunk
+              if (ma >= thr_val) collect(a, e0 + static_cast<int64_t>(v) * PER_VEC);
+              if (mb >= thr_val) collect(b, e0 + static_cast<int64_t>(v + K1_CONSUMERS) * PER_VEC);
+              if (mc >= thr_val)
+                collect(cc, e0 + static_cast<int64_t>(v + 2 * K1_CONSUMERS) * PER_VEC);
+              if (md >= thr_val)
+                collect(d, e0 + static_cast<int64_t>(v + 3 * K1_CONSUMERS) * PER_VEC);
+            }
           }
-          for (; v < nvec; v += K1_CONSUMERS)
-            fast_update<POLY>(fs, lds128(sbase + v * 16), p.c, T());
+          for (; v < nvec; v += K1_CONSUMERS) {
+            const uint4 a = lds128(sbase + v * 16);
+            const float ma = fast_update<POLY>(fs, a, p.c, T());
+            if (MODE == K1_SAMPLE && ma >= thr_val)
+              collect(a, (off >> 4) * PER_VEC + static_cast<int64_t>(v) * PER_VEC);
+          }
         } else {
           uint8_t* drow = reinterpret_cast<uint8_t*>(dst) + off;
           for (; v < nvec; v += K1_CONSUMERS) {
@@ -434,6 +533,7 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
         for (int64_t j = tail_begin; j < p.vocab; ++j) {
           if (reduce_pass) online_update_scalar(st, to_float(src[j]), p.c);
           else dst[j] = full_out_scalar(src[j], p.inv_temp, lse_row);
+          if (MODE == K1_SAMPLE) push(to_float(src[j]), j);
         }
       }
 
@@ -453,9 +553,92 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
           // the true maximum contributes 2^0, so a healthy row has s >= ~1
           if (!(s >= 0.5f && s <= FLT_MAX)) exact_row(src, p.vocab, p.c, lane, m, s);
           if (MODE == K1_FULL) lse_row = finish_lse<MODE>(m, s, p);
-          if (ctid == 0) emit_row<MODE>(p, oidx, sub, m, s, x_t, target_ok, carry);
+          if (MODE == K1_SAMPLE) lse_row = finish_lse<MODE>(m, s, p);  // kept by warp 0
+          if (MODE != K1_SAMPLE && ctid == 0)
+            emit_row<MODE>(p, oidx, sub, m, s, x_t, target_ok, carry);
         }
         ++red_it;
+        if (MODE == K1_SAMPLE) {
+          // every candidate of the row is in the ring (the barrier above followed the last chunk)
+          int32_t n = *reinterpret_cast<volatile int32_t*>(&smp.count);
+          const bool overflow = n > K1_SAMPLE_CAP;
+          constexpr int MINE = K1_SAMPLE_CAP / K1_CONSUMERS;
+          unsigned long long code[MINE];
+          if (!overflow) {
+#pragma unroll
+            for (int q = 0; q < MINE; ++q) {
+              const int32_t i = ctid + q * K1_CONSUMERS;
+              code[q] = (i < n) ? smp.cand[i] : 0ull;  // 0: below every real code
+            }
+          }
+          if (!overflow && n > 2 * K1_SAMPLE_SUBSET) {
+            // cheap filter first: the kk-th best of the first SUBSET candidates is a bound the
+            // final top-kk must reach; only the candidates that reach it are ranked in full
+            if (ctid < K1_SAMPLE_SUBSET) {
+              const unsigned long long mine = code[0];
+              int32_t r = 0;
+#pragma unroll 4
+              for (int32_t j = 0; j < K1_SAMPLE_SUBSET; ++j) r += (smp.cand[j] > mine) ? 1 : 0;
+              if (r == kk - 1) smp.thr = mine;
+            }
+            named_bar_sync(2, K1_CONSUMERS);
+            const unsigned long long thr2 = smp.thr;
+            if (ctid == 0) smp.count = 0;
+            named_bar_sync(2, K1_CONSUMERS);
+#pragma unroll
+            for (int q = 0; q < MINE; ++q) {
+              if (code[q] >= thr2 && code[q] != 0ull)
+                smp.cand[atomicAdd(&smp.count, 1)] = code[q];
+            }
+            named_bar_sync(2, K1_CONSUMERS);
+            n = *reinterpret_cast<volatile int32_t*>(&smp.count);
+#pragma unroll
+            for (int q = 0; q < MINE; ++q) {
+              const int32_t i = ctid + q * K1_CONSUMERS;
+              code[q] = (i < n) ? smp.cand[i] : 0ull;
+            }
+          }
+          if (!overflow) {
+            // each thread ranks its candidates in ONE pipelined pass over the list; codes are
+            // distinct, rank r goes to top[r]
+            int32_t rank[MINE];
+#pragma unroll
+            for (int q = 0; q < MINE; ++q) rank[q] = 0;
+#pragma unroll 4
+            for (int32_t j = 0; j < n; ++j) {
+              const unsigned long long o = smp.cand[j];
+#pragma unroll
+              for (int q = 0; q < MINE; ++q) rank[q] += (o > code[q]) ? 1 : 0;
+            }
+#pragma unroll
+            for (int q = 0; q < MINE; ++q)
+              if (ctid + q * K1_CONSUMERS < n && rank[q] < kk) smp.top[rank[q]] = code[q];
+          }
+          named_bar_sync(2, K1_CONSUMERS);
+          if (overflow) {
+            // more candidates than the ring holds (sorted or heavily tied row): leave the row
+            // to the one-CTA-per-row kernel, which re-sweeps with tighter thresholds
+            if (ctid == 0) p.out_tokens[row] = -1;
+          } else {
+            if (ctid == 0) {
+              const int32_t pick = p.greedy ? 0 : k4_draw(smp.top, kk, p.c, row, p.seed, p.offset);
+              p.out_tokens[row] = k4_index(smp.top[pick]);
+              p.out0[row] = __fdiv_rn(k4_value(smp.top[pick]), p.temp) - lse_row;
+            }
+            if (p.out_topk_idx != nullptr || p.out_topk_val != nullptr) {
+              for (int32_t j = ctid; j < p.top_k; j += K1_CONSUMERS) {
+                const bool have = j < kk;
+                if (p.out_topk_idx != nullptr)
+                  p.out_topk_idx[row * p.top_k + j] = have ? k4_index(smp.top[j]) : -1;
+                if (p.out_topk_val != nullptr)
+                  p.out_topk_val[row * p.top_k + j] =
+                      have ? k4_value(smp.top[j]) : __int_as_float(0xff800000);
+              }
+            }
+          }
+          // top[] is next written several barriers from here, cand[]/count/thr after the next
+          // row's first barrier: nobody can overtake the readers above
+        }
       }
     }
   }
@@ -592,7 +775,10 @@ static int32_t k1_launch_typed(const K1Params& p_in, bool bulk_ok, int64_t max_i
     const int64_t al = K1_CHUNK_ALIGN;
     p.chunk_bytes = (n > 0) ? static_cast<int32_t>(((bulk_bytes + n - 1) / n + al - 1) / al * al)
                             : K1_CHUNK_ALIGN;
-    const int smem = k1_windowed(MODE) ? K1Smem::TOTAL_DUAL : K1Smem::TOTAL_PLAIN;
+    const int smem = k1_windowed(MODE) ? K1Smem::TOTAL_DUAL
+                     : (MODE == K1_SAMPLE)
+                         ? K1Smem::SAMPLE_OFF + static_cast<int>(sizeof(K1SampleSmem))
+                         : K1Smem::TOTAL_PLAIN;
     if (smem > info.max_smem_optin)
       return fail(TOME_ERR_UNSUPPORTED, "device offers %d bytes of shared memory, need %d",
                   info.max_smem_optin, smem);
@@ -808,3 +994,39 @@ extern "C" int32_t tome_ragged_logprob(const void* logits, int32_t dtype, int64_
   return k1_launch<K1_RAGGED>(p, dtype, bulk_eligible(logits, row_stride, dtype), rows,
                               static_cast<cudaStream_t>(stream));
 }
+
+namespace tome {
+
+bool k1_sample_eligible(const void* logits, int32_t dtype, int64_t vocab, int64_t row_stride) {
+  const int64_t es = (dtype == TOME_F32) ? 4 : 2;
+  return bulk_eligible(logits, row_stride, dtype) && vocab * es >= 16;
+}
+
+int32_t k1_launch_sample(const void* logits, int32_t dtype, int64_t rows, int64_t vocab,
+                         int64_t row_stride, float temperature, int32_t top_k, uint64_t seed,
+                         uint64_t offset, int32_t* out_tokens, float* out_logprob,
+                         int32_t* out_topk_idx, float* out_topk_val, int32_t* dev_status,
+                         cudaStream_t stream) {
+  const bool greedy = !(temperature > 0.0f);
+  const float temp = greedy ? 1.0f : temperature;
+  K1Params p = {};
+  p.src[0] = logits;
+  p.n_rows = rows;
+  p.vocab = vocab;
+  p.stride = row_stride;
+  p.c = LOG2E / temp;
+  p.temp = temp;
+  p.inv_temp = 1.0f / temp;
+  p.out0 = out_logprob;
+  p.out_tokens = out_tokens;
+  p.out_topk_idx = out_topk_idx;
+  p.out_topk_val = out_topk_val;
+  p.seed = seed;
+  p.offset = offset;
+  p.top_k = top_k;
+  p.greedy = greedy ? 1 : 0;
+  p.status = dev_status;
+  return k1_launch<K1_SAMPLE>(p, dtype, true, rows, stream);
+}
+
+}  // namespace tome

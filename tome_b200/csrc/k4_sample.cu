@@ -23,8 +23,10 @@
 #include <algorithm>
 
 #include "host_common.h"
+#include "k1_sample.h"
 #include "online.cuh"
 #include "ptx.cuh"
+#include "sampling.cuh"
 
 namespace tome {
 
@@ -35,7 +37,8 @@ constexpr int K4_CAP = 8192;       // candidate list capacity
 constexpr int K4_SAMPLE = 32768;   // leading logits used to derive the first threshold
 constexpr int K4_GROUPS = K4_THREADS / 4;  // sample maxima kept for the threshold
 constexpr int K4_RANK_MAX = 1024;  // above this many candidates, compact before ranking
-constexpr int K4_MAX_SWEEPS = 64;  // re-sweeps with a tightened threshold before giving up
+constexpr int K4_MAX_SWEEPS = 64;
+constexpr int64_t K4_STREAM_MIN_ROWS = 1024;  // from here on the streaming kernel takes the batch  // re-sweeps with a tightened threshold before giving up
 
 struct K4Params {
   const void* logits;
@@ -47,6 +50,7 @@ struct K4Params {
   float* out_logprob;
   int32_t* out_topk_idx;  // nullable, [rows, top_k]
   float* out_topk_val;    // nullable, [rows, top_k]
+  int32_t only_flagged;   // redo only the rows whose token is -1 (left over by the streaming kernel)
   int32_t* status;
 };
 
@@ -59,31 +63,6 @@ struct K4Smem {
   int32_t count;
   unsigned long long bcast;
 };
-
-// Order-preserving map float -> uint32 (larger float <=> larger key).  NaN maps to 0.
-__device__ __forceinline__ uint32_t k4_key(float x) {
-  if (x != x) return 0u;
-  const uint32_t b = __float_as_uint(x);
-  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
-}
-
-__device__ __forceinline__ float k4_unkey(uint32_t k) {
-  const uint32_t b = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
-  return __uint_as_float(b);
-}
-
-// (value, index) as one integer whose numeric order is "larger value first, then lower index":
-// every logit of a row gets a distinct code, so top-k selection has no ties to break.
-__device__ __forceinline__ unsigned long long k4_pack(float x, int64_t idx) {
-  return (static_cast<unsigned long long>(k4_key(x)) << 32) |
-         static_cast<unsigned long long>(0xffffffffu - static_cast<uint32_t>(idx));
-}
-__device__ __forceinline__ float k4_value(unsigned long long pk) {
-  return k4_unkey(static_cast<uint32_t>(pk >> 32));
-}
-__device__ __forceinline__ int32_t k4_index(unsigned long long pk) {
-  return static_cast<int32_t>(0xffffffffu - static_cast<uint32_t>(pk));
-}
 
 __device__ __forceinline__ float k4_load(const float* p, int64_t i) { return p[i]; }
 __device__ __forceinline__ float k4_load(const __nv_bfloat16* p, int64_t i) {
@@ -130,26 +109,6 @@ __device__ unsigned long long k4_compact(K4Smem& sm, int32_t n, int32_t k) {
   for (int32_t j = 0; j < n_mine; ++j) sm.cand[atomicAdd(&sm.count, 1)] = mine[j];
   __syncthreads();
   return kth;
-}
-
-// Philox-4x32-10: one 128-bit block for (counter, key); returns the first word.
-__device__ uint32_t k4_philox(uint64_t ctr_lo, uint64_t ctr_hi, uint64_t key) {
-  uint32_t c0 = static_cast<uint32_t>(ctr_lo), c1 = static_cast<uint32_t>(ctr_lo >> 32);
-  uint32_t c2 = static_cast<uint32_t>(ctr_hi), c3 = static_cast<uint32_t>(ctr_hi >> 32);
-  uint32_t k0 = static_cast<uint32_t>(key), k1 = static_cast<uint32_t>(key >> 32);
-#pragma unroll
-  for (int r = 0; r < 10; ++r) {
-    const uint64_t p0 = static_cast<uint64_t>(0xD2511F53u) * c0;
-    const uint64_t p1 = static_cast<uint64_t>(0xCD9E8D57u) * c2;
-    const uint32_t n0 = static_cast<uint32_t>(p1 >> 32) ^ c1 ^ k0;
-    const uint32_t n1 = static_cast<uint32_t>(p1);
-    const uint32_t n2 = static_cast<uint32_t>(p0 >> 32) ^ c3 ^ k1;
-    const uint32_t n3 = static_cast<uint32_t>(p0);
-    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
-    k0 += 0x9E3779B9u;
-    k1 += 0xBB67AE85u;
-  }
-  return c0;
 }
 
 // One pass over a row.  Candidate collection: a 16-byte vector is looked at element by element
@@ -245,6 +204,7 @@ __global__ void __launch_bounds__(K4_THREADS) k4_sample_kernel(const K4Params p)
   const float c = LOG2E / temp;
 
   for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    if (p.only_flagged && p.out_tokens[row] != -1) continue;  // uniform across the CTA
     const T* src = reinterpret_cast<const T*>(p.logits) + row * p.stride;
     const int64_t V = p.vocab;
     const int32_t kk = static_cast<int32_t>(min(static_cast<int64_t>(k), V));
@@ -356,34 +316,33 @@ __global__ void __launch_bounds__(K4_THREADS) k4_sample_kernel(const K4Params p)
       k4_compact(sm, n, kk);
       n = kk;
     }
-    for (int32_t i = tid; i < n; i += K4_THREADS) {
-      const unsigned long long code = sm.cand[i];
-      int32_t rank = 0;
-      for (int32_t j = 0; j < n; ++j) rank += (sm.cand[j] > code) ? 1 : 0;
-      if (rank < kk) sm.top[rank] = code;
+    {
+      // n <= K4_RANK_MAX here: each thread ranks its (at most two) candidates in one pipelined
+      // pass over the list
+      constexpr int MINE = K4_RANK_MAX / K4_THREADS;
+      unsigned long long code[MINE];
+      int32_t rank[MINE];
+#pragma unroll
+      for (int q = 0; q < MINE; ++q) {
+        const int32_t i = tid + q * K4_THREADS;
+        code[q] = (i < n) ? sm.cand[i] : ~0ull;  // ~0 outranks everything: never placed
+        rank[q] = 0;
+      }
+#pragma unroll 4
+      for (int32_t j = 0; j < n; ++j) {
+        const unsigned long long o = sm.cand[j];
+#pragma unroll
+        for (int q = 0; q < MINE; ++q) rank[q] += (o > code[q]) ? 1 : 0;
+      }
+#pragma unroll
+      for (int q = 0; q < MINE; ++q)
+        if (tid + q * K4_THREADS < n && rank[q] < kk) sm.top[rank[q]] = code[q];
     }
     __syncthreads();
 
     // ---- draw, score, write
     if (tid == 0) {
-      int32_t pick = 0;
-      if (!greedy && kk > 1) {
-        // categorical over the top-kk of logits / temperature
-        const float top = k4_value(sm.top[0]);
-        float total = 0.0f;
-        for (int32_t j = 0; j < kk; ++j) total += ex2f((k4_value(sm.top[j]) - top) * c);
-        const uint32_t r = k4_philox(static_cast<uint64_t>(row), p.offset, p.seed);
-        const float u = (static_cast<float>(r >> 8) + 0.5f) * (1.0f / 16777216.0f) * total;
-        float acc = 0.0f;
-        pick = kk - 1;
-        for (int32_t j = 0; j < kk; ++j) {
-          acc += ex2f((k4_value(sm.top[j]) - top) * c);
-          if (u < acc) {
-            pick = j;
-            break;
-          }
-        }
-      }
+      const int32_t pick = greedy ? 0 : k4_draw(sm.top, kk, c, row, p.seed, p.offset);
       p.out_tokens[row] = k4_index(sm.top[pick]);
       p.out_logprob[row] = __fdiv_rn(k4_value(sm.top[pick]), temp) - lse;
     }
@@ -429,7 +388,18 @@ extern "C" int32_t tome_sample_topk_logprob(const void* logits, int32_t dtype, i
   DeviceInfo info;
   int32_t st = current_device_info(&info);
   if (st != TOME_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // Large batches stream through the TMA pipeline of the selective kernel (several times the
+  // throughput); the rows it could not finish come back marked -1 and are redone below.
+  const bool streamed = rows >= K4_STREAM_MIN_ROWS && k1_sample_eligible(logits, dtype, vocab, row_stride);
+  if (streamed) {
+    st = k1_launch_sample(logits, dtype, rows, vocab, row_stride, temperature, top_k, seed,
+                          offset, out_tokens, out_logprob, out_topk_idx, out_topk_val, dev_status,
+                          s);
+    if (st != TOME_OK) return st;
+  }
   K4Params p = {};
+  p.only_flagged = streamed ? 1 : 0;
   p.logits = logits;
   p.rows = rows;
   p.vocab = vocab;
@@ -446,7 +416,6 @@ extern "C" int32_t tome_sample_topk_logprob(const void* logits, int32_t dtype, i
   const int smem = static_cast<int>(sizeof(K4Smem));
   const int grid = static_cast<int>(
       std::max<int64_t>(1, std::min<int64_t>(static_cast<int64_t>(info.sm_count) * 3, rows)));
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == TOME_F32) {
     st = check_cuda(cudaFuncSetAttribute(k4_sample_kernel<float>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
