@@ -13,6 +13,17 @@ from oracle import oracle
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=["small_batches_split", "one_cta_per_row"])
+def small_batch_path(request, monkeypatch):
+    """Few rows normally share each row among a cluster of CTAs; the second run of every test
+    switches that off so the same cases also reach the streaming and plain-load kernels."""
+    if request.param == "one_cta_per_row":
+        monkeypatch.setenv("TOME_K1_SPLIT", "0")
+    else:
+        monkeypatch.delenv("TOME_K1_SPLIT", raising=False)
+    return request.param
+
+
 def _case(rows, vocab, dtype, seed, scale=3.0):
     g = torch.Generator().manual_seed(seed)
     x = (torch.randn((rows, vocab), generator=g) * scale).to(dtype)
@@ -432,3 +443,38 @@ def test_golden_dual(cuda_device):
     assert max_abs(p, torch.from_numpy(gld["lp_policy"])) <= 2e-3
     assert max_abs(r, torch.from_numpy(gld["lp_ref"])) <= 2e-3
     assert max_abs(kl, torch.from_numpy(gld["kl"])) <= 4e-3
+
+
+@pytest.mark.parametrize("split", ["2", "4", "8"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_selective_every_cluster_size(cuda_device, monkeypatch, split, dtype):
+    """Each cluster size on rows whose vector count does not divide by it, aligned and not."""
+    monkeypatch.setenv("TOME_K1_SPLIT", split)
+    for rows, vocab in ((5, 151936), (3, 4099), (2, 9), (4, 1)):
+        x, ids = _case(rows, vocab, dtype, seed=700 + vocab % 97)
+        _check_selective(x, ids, 0.7, cuda_device)
+    base, ids = _case(6, 1000 + 3, dtype, seed=77)
+    view = base[:, 3:]  # rows start off the 16-byte grid
+    ids = ids % view.shape[1]
+    import tome_b200
+    lp = tome_b200.selective_log_softmax(base.to(cuda_device)[:, 3:], ids.to(cuda_device), 1.3,
+                                         check=True)
+    o_lp, _, _ = oracle.selective_logprob(view.contiguous(), ids, 1.3)
+    assert max_abs(lp, o_lp) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("split", ["2", "4", "8"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_full_every_cluster_size(cuda_device, monkeypatch, split, dtype):
+    import tome_b200
+    monkeypatch.setenv("TOME_K1_SPLIT", split)
+    tol = 1e-4 if dtype == torch.float32 else 0.0625 + 1e-6
+    for rows, vocab in ((5, 151936), (3, 4099), (2, 9), (4, 1)):
+        x, _ = _case(rows, vocab, dtype, seed=900 + vocab % 89, scale=1.0)
+        out = tome_b200.fused_log_softmax(x.to(cuda_device), 0.7)
+        assert max_abs(out.float(), oracle.log_softmax_metal_order(x, 0.7).float()) <= tol
+    # input rows off the 16-byte grid while the output rows are on it
+    base, _ = _case(6, 1024 + 3, dtype, seed=78, scale=1.0)
+    out = tome_b200.fused_log_softmax(base.to(cuda_device)[:, 3:], 1.0)
+    ref = oracle.log_softmax_metal_order(base[:, 3:].contiguous(), 1.0)
+    assert out.shape == ref.shape and max_abs(out.float(), ref.float()) <= tol
