@@ -11,6 +11,17 @@ from oracle import oracle
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=["small_batches_split", "one_cta_per_row"])
+def small_batch_path(request, monkeypatch):
+    """Few long rows normally share each row among a cluster of CTAs; the second run of every
+    test switches that off so the same cases also reach the one-CTA-per-row kernel."""
+    if request.param == "one_cta_per_row":
+        monkeypatch.setenv("TOME_K4_SPLIT", "0")
+    else:
+        monkeypatch.delenv("TOME_K4_SPLIT", raising=False)
+    return request.param
+
+
 def _case(rows, vocab, dtype, seed, scale=3.0):
     g = torch.Generator().manual_seed(seed)
     return (torch.randn((rows, vocab), generator=g) * scale).to(dtype)
@@ -164,3 +175,29 @@ def test_streaming_path_draws_follow_the_topk_softmax(cuda_device):
     # the same draws as the one-CTA-per-row kernel makes for the same (seed, offset, row)
     tok_small, _ = tome_b200.sample_topk_logprob(x[:512], 0.8, 20, seed=99, offset=1)
     assert torch.equal(tok[:512], tok_small)
+
+
+@pytest.mark.parametrize("split", ["2", "4", "8"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_split_rows_give_the_same_tokens_as_one_cta_per_row(cuda_device, monkeypatch, split, dtype):
+    """The cluster path must return the identical top-k lists and tokens (the draw depends on
+    the row's top-k only); the log-prob may differ by the summation order."""
+    import tome_b200
+    vocab = 151936 - 3                      # rows off the 16-byte grid from the second one on
+    x = _case(5, vocab, dtype, 4242)
+    x[1, : vocab - 11] = float("-inf")      # whole parts without a finite logit
+    x[2] = torch.linspace(-8, 8, vocab).to(dtype)   # ascending: the top-k sits in the last part
+    x[3, 16:] = x[3, 16:].clamp(max=0.5)    # heavy ties at the cap
+    xd = x.to(cuda_device)
+    monkeypatch.setenv("TOME_K4_SPLIT", "0")
+    t0, lp0, i0, v0 = tome_b200.sample_topk_logprob(xd, 0.8, 20, seed=5, offset=9, return_topk=True)
+    monkeypatch.setenv("TOME_K4_SPLIT", split)
+    t1, lp1, i1, v1 = tome_b200.sample_topk_logprob(xd, 0.8, 20, seed=5, offset=9, return_topk=True,
+                                                    check=True)
+    assert torch.equal(i0, i1) and torch.equal(v0, v1) and torch.equal(t0, t1)
+    assert max_abs(lp0, lp1) <= 1e-5
+    for r in range(x.shape[0]):
+        idx, _ = oracle.topk_sampling_distribution(x[r], 0.8, 20)
+        assert i1[r, : len(idx)].cpu().tolist() == idx.tolist()
+    o_lp, _, _ = oracle.selective_logprob(x, t1.cpu(), 0.8)
+    assert max_abs(lp1, o_lp) <= TOL[dtype]

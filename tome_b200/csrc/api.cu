@@ -1,5 +1,6 @@
 // Version, status text and per-device property cache of the C ABI.
 #include <mutex>
+#include <vector>
 
 #include "host_common.h"
 #include "ptx.cuh"
@@ -52,6 +53,43 @@ int32_t current_device_info(DeviceInfo* out) {
   }
   *out = info;
   return TOME_OK;
+}
+
+int max_active_clusters(const void* kernel, int threads, int dyn_smem, int cluster) {
+  struct Entry {
+    int device;
+    const void* kernel;
+    int cluster;
+    int value;
+  };
+  static std::mutex mu;
+  static std::vector<Entry> cache;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    for (const Entry& e : cache)
+      if (e.device == dev && e.kernel == kernel && e.cluster == cluster) return e.value;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(cluster), 1, 1);
+  cfg.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
+  cfg.dynamicSmemBytes = static_cast<size_t>(dyn_smem);
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = static_cast<unsigned>(cluster);
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+    cudaGetLastError();  // the query's failure is not the caller's error
+    n = 0;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  cache.push_back({dev, kernel, cluster, n});
+  return n;
 }
 
 }  // namespace tome

@@ -26,6 +26,10 @@ struct DeviceInfo {
 // Properties of the current device (cached per device id; thread-safe).
 int32_t current_device_info(DeviceInfo* out);
 
+// How many clusters of `cluster` CTAs (threads x dyn_smem each) of `kernel` the current device
+// can hold at once; 0 if the query fails.  Cached per (device, kernel, cluster); thread-safe.
+int max_active_clusters(const void* kernel, int threads, int dyn_smem, int cluster);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline bool temperature_ok(float t) { return t > 0.0f && t <= 3.0e38f; }

@@ -831,21 +831,23 @@ __global__ void __launch_bounds__(K1_SPLIT_THREADS) k1_split_kernel(const K1Para
   }
 }
 
-// TOME_K1_SPLIT=0 switches the split off, 2/4/8 forces that cluster size (read at every call:
-// tests use it to reach the one-CTA-per-row kernels with few rows).
-static int k1_split_factor(int64_t rows, int sm_count) {
+// Cluster size for a batch too small to fill the GPU with one CTA per row: the largest of 8
+// and 4 whose clusters are all resident at once (measured on V = 151936: 4.7 vs 17 us for one
+// fp32 row, 13 vs 19 us for 128 rows; clusters of 2 do not pay).  0: do not split.
+// TOME_K1_SPLIT=0 switches the split off, 2/4/8 forces that size (read at every call: tests
+// use it to reach the one-CTA-per-row kernels with few rows).
+template <typename T, int MODE>
+static int k1_split_factor(int64_t rows) {
   const char* e = getenv("TOME_K1_SPLIT");
   if (e != nullptr) {
     const int v = atoi(e);
     const bool valid = (v == 2 || v == 4 || v == 8) && rows * v <= 0x7fffffffLL;
     return valid ? v : 0;
   }
-  // measured on V = 151936: clusters of 8 and 4 beat one CTA per row (4.7 vs 17 us for one fp32
-  // row, 13 vs 19 us for 128), clusters of 2 do not
-  const int64_t slots = static_cast<int64_t>(sm_count) * (2048 / K1_SPLIT_THREADS);
-  int split = K1_SPLIT_MAX;
-  while (split > 2 && rows * split > slots) split >>= 1;
-  return split > 2 ? split : 0;
+  const void* kernel = reinterpret_cast<const void*>(k1_split_kernel<T, MODE>);
+  for (int split = K1_SPLIT_MAX; split >= 4; split >>= 1)
+    if (rows <= max_active_clusters(kernel, K1_SPLIT_THREADS, 0, split)) return split;
+  return 0;
 }
 
 template <typename T, int MODE>
@@ -896,7 +898,7 @@ static int32_t k1_launch_typed(const K1Params& p_in, bool bulk_ok, int64_t max_i
   int32_t st = current_device_info(&info);
   if (st != TOME_OK) return st;
   if constexpr (MODE == K1_SELECTIVE || MODE == K1_FULL) {
-    const int split = k1_split_factor(p_in.n_rows, info.sm_count);
+    const int split = k1_split_factor<T, MODE>(p_in.n_rows);
     if (split > 1) return k1_launch_split<T, MODE>(p_in, split, stream);
   }
   if (bulk_ok) {

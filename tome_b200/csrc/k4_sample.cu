@@ -20,6 +20,8 @@
 #include <cuda_bf16.h>
 #include <float.h>
 
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "host_common.h"
@@ -37,8 +39,10 @@ constexpr int K4_CAP = 8192;       // candidate list capacity
 constexpr int K4_SAMPLE = 32768;   // leading logits used to derive the first threshold
 constexpr int K4_GROUPS = K4_THREADS / 4;  // sample maxima kept for the threshold
 constexpr int K4_RANK_MAX = 1024;  // above this many candidates, compact before ranking
-constexpr int K4_MAX_SWEEPS = 64;
-constexpr int64_t K4_STREAM_MIN_ROWS = 1024;  // from here on the streaming kernel takes the batch  // re-sweeps with a tightened threshold before giving up
+constexpr int K4_MAX_SWEEPS = 64;   // re-sweeps with a tightened threshold before giving up
+constexpr int64_t K4_STREAM_MIN_ROWS = 1024;  // from here on the streaming kernel takes the batch
+constexpr int K4_SPLIT_MAX = 8;               // CTAs of a cluster that may share one row
+constexpr int64_t K4_SPLIT_MIN_VOCAB = 16384; // shorter rows stay with one CTA
 
 struct K4Params {
   const void* logits;
@@ -62,6 +66,10 @@ struct K4Smem {
   int32_t red_i[K4_WARPS];
   int32_t count;
   unsigned long long bcast;
+  // split rows: the first CTA of the cluster receives every other rank's top-k and (m, s)
+  unsigned long long inbox[K4_SPLIT_MAX * K4_MAX_K];
+  float2 inbox_ms[K4_SPLIT_MAX];
+  int32_t inbox_n[K4_SPLIT_MAX];
 };
 
 __device__ __forceinline__ float k4_load(const float* p, int64_t i) { return p[i]; }
@@ -111,6 +119,30 @@ __device__ unsigned long long k4_compact(K4Smem& sm, int32_t n, int32_t k) {
   return kth;
 }
 
+// Exact top-kk of cand[0..n), best first, into top[] (n <= K4_RANK_MAX, codes distinct): each
+// thread ranks its (at most two) candidates in one pipelined pass over the list.
+__device__ __forceinline__ void k4_rank_top(K4Smem& sm, int32_t n, int32_t kk) {
+  const int tid = threadIdx.x;
+  constexpr int MINE = K4_RANK_MAX / K4_THREADS;
+  unsigned long long code[MINE];
+  int32_t rank[MINE];
+#pragma unroll
+  for (int q = 0; q < MINE; ++q) {
+    const int32_t i = tid + q * K4_THREADS;
+    code[q] = (i < n) ? sm.cand[i] : ~0ull;  // ~0 outranks everything: never placed
+    rank[q] = 0;
+  }
+#pragma unroll 4
+  for (int32_t j = 0; j < n; ++j) {
+    const unsigned long long o = sm.cand[j];
+#pragma unroll
+    for (int q = 0; q < MINE; ++q) rank[q] += (o > code[q]) ? 1 : 0;
+  }
+#pragma unroll
+  for (int q = 0; q < MINE; ++q)
+    if (tid + q * K4_THREADS < n && rank[q] < kk) sm.top[rank[q]] = code[q];
+}
+
 // One pass over a row.  Candidate collection: a 16-byte vector is looked at element by element
 // only if its largest logit reaches the threshold's value (one compare per vector); elements
 // whose code is >= thr go to the candidate ring (if more than the capacity arrive, later ones
@@ -118,12 +150,13 @@ __device__ unsigned long long k4_compact(K4Smem& sm, int32_t n, int32_t k) {
 // ALL logits is updated too: the packed fast path (`fs`) for whole vectors, the exact scalar
 // form (`tail`) for the elements outside them.  No barrier inside.
 template <typename T, bool VEC, bool SOFTMAX>
-__device__ __forceinline__ void k4_sweep(const T* src, int64_t V, float c, unsigned long long thr,
-                                         K4Smem& sm, Fast& fs, Online& tail) {
+__device__ __forceinline__ void k4_sweep(const T* src, int64_t V, int64_t base, float c,
+                                         unsigned long long thr, K4Smem& sm, Fast& fs,
+                                         Online& tail) {
   // thr == 0 means "no threshold": every logit is a candidate
   const float thr_val = (thr == 0ull) ? __int_as_float(0xff800000) : k4_value(thr);
   auto candidate = [&](float x, int64_t i) {
-    const unsigned long long code = k4_pack(x, i);
+    const unsigned long long code = k4_pack(x, base + i);  // index within the whole row
     if (code >= thr) {
       const uint32_t slot = static_cast<uint32_t>(atomicAdd(&sm.count, 1));
       sm.cand[slot % K4_CAP] = code;  // one aligned 8-byte store: never a torn entry
@@ -192,13 +225,154 @@ __device__ void k4_exact_row(const T* src, int64_t V, float c, K4Smem& sm, float
   row_s = sum;
 }
 
+// Works through `V` logits starting at `src` (a whole row, or one CTA's part of a split row;
+// `base` = index of src[0] within the row).  Afterwards sm.top[0 .. kk) holds the exact top-kk
+// of the part, best first (kk = min(k, V)), and every thread has the part's (max, sum-exp).
+template <typename T>
+__device__ void k4_segment(const T* src, const int64_t V, const int64_t base, const int32_t k,
+                           const float c, K4Smem& sm, int32_t* status, int32_t& kk_out,
+                           float& m_out, float& s_out) {
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int32_t kk = static_cast<int32_t>(min(static_cast<int64_t>(k), V));
+  kk_out = kk;
+
+  // ---- first threshold: the leading K4_SAMPLE logits are cut into 128 groups (4 adjacent
+  //      threads each); the kk-th largest group maximum is a value that at least kk logits
+  //      reach, so it bounds the answer from below.  Values only: ties are kept.
+  const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0);
+  const int64_t n_sample = min(static_cast<int64_t>(K4_SAMPLE), V);
+  float lmax = __int_as_float(0xff800000);
+  int64_t filled_threads;  // threads that saw at least one logit
+  if (vec) {
+    constexpr int PER = 16 / static_cast<int>(sizeof(T));
+    const int64_t nvec_s = n_sample / PER;
+    const uint4* vp = reinterpret_cast<const uint4*>(src);
+#pragma unroll 4
+    for (int64_t v = tid; v < nvec_s; v += K4_THREADS) lmax = fmaxf(lmax, vec_max(__ldg(vp + v), T()));
+    filled_threads = min(nvec_s, static_cast<int64_t>(K4_THREADS));
+  } else {
+#pragma unroll 4
+    for (int64_t i = tid; i < n_sample; i += K4_THREADS) lmax = fmaxf(lmax, k4_load(src, i));
+    filled_threads = min(n_sample, static_cast<int64_t>(K4_THREADS));
+  }
+  lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, 1));
+  lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, 2));
+  if ((tid & 3) == 0) sm.sample_key[tid >> 2] = k4_key(lmax);
+  if (tid == 0) {
+    sm.count = 0;
+    sm.bcast = 0ull;  // no usable threshold: every logit is a candidate
+  }
+  __syncthreads();
+  const int64_t full_groups = filled_threads / 4;  // groups whose four threads all hold data
+  if (tid < K4_GROUPS && full_groups >= kk && kk > 0) {
+    const uint32_t mine = sm.sample_key[tid];
+    int32_t rank = 0;
+    for (int j = 0; j < K4_GROUPS; ++j) {
+      const uint32_t o = sm.sample_key[j];
+      rank += (o > mine || (o == mine && j < tid)) ? 1 : 0;
+    }
+    if (rank == kk - 1) sm.bcast = static_cast<unsigned long long>(mine) << 32;
+  }
+  __syncthreads();
+  unsigned long long thr = sm.bcast;
+  __syncthreads();
+
+  // ---- sweep: online softmax of the whole part + candidate collection; swept again with a
+  //      tighter threshold only if more candidates arrived than the ring holds
+  Fast fs;
+  fast_init(fs, c);
+  Online tail;
+  online_init(tail);
+  int32_t n = 0;
+  for (int sweep = 0; sweep < K4_MAX_SWEEPS; ++sweep) {
+    if (sweep == 0) {
+      if (vec) k4_sweep<T, true, true>(src, V, base, c, thr, sm, fs, tail);
+      else k4_sweep<T, false, true>(src, V, base, c, thr, sm, fs, tail);
+    } else {
+      if (vec) k4_sweep<T, true, false>(src, V, base, c, thr, sm, fs, tail);
+      else k4_sweep<T, false, false>(src, V, base, c, thr, sm, fs, tail);
+    }
+    __syncthreads();
+    const int32_t total = sm.count;
+    __syncthreads();
+    if (total <= K4_CAP) {
+      n = total;
+      break;
+    }
+    // overflow: the ring holds CAP of the candidates (mostly the latest); their kk-th best
+    // is a valid, tighter bound
+    thr = k4_compact(sm, K4_CAP, kk);
+    n = kk;
+    if (sweep + 1 == K4_MAX_SWEEPS) {
+      if (tid == 0 && status != nullptr) atomicOr(status, TOME_DEV_TIMEOUT);
+      break;  // keeps the kk best of what the ring held
+    }
+    if (tid == 0) sm.count = 0;
+    __syncthreads();
+  }
+
+  // ---- merge the online softmax across the block
+  {
+    const Online vecs = fast_finish(fs, c);
+    const float m = fmaxf(vecs.m, tail.m);
+    const float s = vecs.s * ex2f((vecs.m - m) * c) + tail.s * ex2f((tail.m - m) * c);
+    float wm = m;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
+    float ws = s * ex2f((m - wm) * c);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ws += __shfl_xor_sync(0xffffffffu, ws, o);
+    if (lane == 0) {
+      sm.red_f[2 * warp] = wm;
+      sm.red_f[2 * warp + 1] = ws;
+    }
+  }
+  __syncthreads();
+  float row_m = -FLT_MAX, row_s = 0.0f;
+#pragma unroll
+  for (int w = 0; w < K4_WARPS; ++w) row_m = fmaxf(row_m, sm.red_f[2 * w]);
+#pragma unroll
+  for (int w = 0; w < K4_WARPS; ++w) row_s += sm.red_f[2 * w + 1] * ex2f((sm.red_f[2 * w] - row_m) * c);
+  __syncthreads();
+  // the true maximum contributes 2^0, so a healthy part has row_s >= ~1 (see online.cuh)
+  if (V > 0 && !(row_s >= 0.5f && row_s <= FLT_MAX)) k4_exact_row(src, V, c, sm, row_m, row_s);
+  m_out = row_m;
+  s_out = row_s;
+
+  // ---- exact top-kk of the candidates, best first
+  if (n > K4_RANK_MAX) {
+    k4_compact(sm, n, kk);
+    n = kk;
+  }
+  k4_rank_top(sm, n, kk);
+  __syncthreads();
+}
+
+// One thread draws the token and scores it; all write the optional top-k outputs.
+__device__ void k4_finish_row(const K4Params& p, K4Smem& sm, int64_t row, int32_t kk, float c,
+                              float temp, bool greedy, float lse) {
+  const int tid = threadIdx.x;
+  const int32_t k = p.top_k;
+  if (tid == 0) {
+    const int32_t pick = greedy ? 0 : k4_draw(sm.top, kk, c, row, p.seed, p.offset);
+    p.out_tokens[row] = k4_index(sm.top[pick]);
+    p.out_logprob[row] = __fdiv_rn(k4_value(sm.top[pick]), temp) - lse;
+  }
+  if (p.out_topk_idx != nullptr || p.out_topk_val != nullptr) {
+    for (int32_t j = tid; j < k; j += K4_THREADS) {
+      const bool have = j < kk;
+      if (p.out_topk_idx != nullptr) p.out_topk_idx[row * k + j] = have ? k4_index(sm.top[j]) : -1;
+      if (p.out_topk_val != nullptr)
+        p.out_topk_val[row * k + j] = have ? k4_value(sm.top[j]) : -INFINITY;
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(K4_THREADS) k4_sample_kernel(const K4Params p) {
   extern __shared__ __align__(16) uint8_t k4_smem_raw[];
   K4Smem& sm = *reinterpret_cast<K4Smem*>(k4_smem_raw);
-  const int tid = threadIdx.x;
-  const int lane = tid & 31, warp = tid >> 5;
-  const int32_t k = p.top_k;
   const bool greedy = !(p.temperature > 0.0f);
   const float temp = greedy ? 1.0f : p.temperature;  // temperature of the reported log-prob
   const float c = LOG2E / temp;
@@ -206,156 +380,87 @@ __global__ void __launch_bounds__(K4_THREADS) k4_sample_kernel(const K4Params p)
   for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
     if (p.only_flagged && p.out_tokens[row] != -1) continue;  // uniform across the CTA
     const T* src = reinterpret_cast<const T*>(p.logits) + row * p.stride;
-    const int64_t V = p.vocab;
-    const int32_t kk = static_cast<int32_t>(min(static_cast<int64_t>(k), V));
-
-    // ---- first threshold: the leading K4_SAMPLE logits are cut into 128 groups (4 adjacent
-    //      threads each); the kk-th largest group maximum is a value that at least kk logits
-    //      reach, so it bounds the answer from below.  Values only: ties are kept.
-    const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0);
-    const int64_t n_sample = min(static_cast<int64_t>(K4_SAMPLE), V);
-    float lmax = __int_as_float(0xff800000);
-    int64_t filled_threads;  // threads that saw at least one logit
-    if (vec) {
-      constexpr int PER = 16 / static_cast<int>(sizeof(T));
-      const int64_t nvec_s = n_sample / PER;
-      const uint4* vp = reinterpret_cast<const uint4*>(src);
-#pragma unroll 4
-      for (int64_t v = tid; v < nvec_s; v += K4_THREADS) lmax = fmaxf(lmax, vec_max(__ldg(vp + v), T()));
-      filled_threads = min(nvec_s, static_cast<int64_t>(K4_THREADS));
-    } else {
-#pragma unroll 4
-      for (int64_t i = tid; i < n_sample; i += K4_THREADS) lmax = fmaxf(lmax, k4_load(src, i));
-      filled_threads = min(n_sample, static_cast<int64_t>(K4_THREADS));
-    }
-    lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, 1));
-    lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, 2));
-    if ((tid & 3) == 0) sm.sample_key[tid >> 2] = k4_key(lmax);
-    if (tid == 0) {
-      sm.count = 0;
-      sm.bcast = 0ull;  // no usable threshold: every logit is a candidate
-    }
-    __syncthreads();
-    const int64_t full_groups = filled_threads / 4;  // groups whose four threads all hold data
-    if (tid < K4_GROUPS && full_groups >= kk) {
-      const uint32_t mine = sm.sample_key[tid];
-      int32_t rank = 0;
-      for (int j = 0; j < K4_GROUPS; ++j) {
-        const uint32_t o = sm.sample_key[j];
-        rank += (o > mine || (o == mine && j < tid)) ? 1 : 0;
-      }
-      if (rank == kk - 1) sm.bcast = static_cast<unsigned long long>(mine) << 32;
-    }
-    __syncthreads();
-    unsigned long long thr = sm.bcast;
-    __syncthreads();
-
-    // ---- sweep: online softmax of the whole row + candidate collection; swept again with a
-    //      tighter threshold only if more candidates arrived than the ring holds
-    Fast fs;
-    fast_init(fs, c);
-    Online tail;
-    online_init(tail);
-    int32_t n = 0;
-    for (int sweep = 0; sweep < K4_MAX_SWEEPS; ++sweep) {
-      if (sweep == 0) {
-        if (vec) k4_sweep<T, true, true>(src, V, c, thr, sm, fs, tail);
-        else k4_sweep<T, false, true>(src, V, c, thr, sm, fs, tail);
-      } else {
-        if (vec) k4_sweep<T, true, false>(src, V, c, thr, sm, fs, tail);
-        else k4_sweep<T, false, false>(src, V, c, thr, sm, fs, tail);
-      }
-      __syncthreads();
-      const int32_t total = sm.count;
-      __syncthreads();
-      if (total <= K4_CAP) {
-        n = total;
-        break;
-      }
-      // overflow: the ring holds CAP of the candidates (mostly the latest); their kk-th best
-      // is a valid, tighter bound
-      thr = k4_compact(sm, K4_CAP, kk);
-      n = kk;
-      if (sweep + 1 == K4_MAX_SWEEPS) {
-        if (tid == 0 && p.status != nullptr) atomicOr(p.status, TOME_DEV_TIMEOUT);
-        break;  // keeps the kk best of what the ring held
-      }
-      if (tid == 0) sm.count = 0;
-      __syncthreads();
-    }
-
-    // ---- merge the online softmax across the block
-    {
-      const Online vecs = fast_finish(fs, c);
-      const float m = fmaxf(vecs.m, tail.m);
-      const float s = vecs.s * ex2f((vecs.m - m) * c) + tail.s * ex2f((tail.m - m) * c);
-      float wm = m;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
-      float ws = s * ex2f((m - wm) * c);
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ws += __shfl_xor_sync(0xffffffffu, ws, o);
-      if (lane == 0) {
-        sm.red_f[2 * warp] = wm;
-        sm.red_f[2 * warp + 1] = ws;
-      }
-    }
-    __syncthreads();
-    float row_m = -FLT_MAX, row_s = 0.0f;
-#pragma unroll
-    for (int w = 0; w < K4_WARPS; ++w) row_m = fmaxf(row_m, sm.red_f[2 * w]);
-#pragma unroll
-    for (int w = 0; w < K4_WARPS; ++w) row_s += sm.red_f[2 * w + 1] * ex2f((sm.red_f[2 * w] - row_m) * c);
-    __syncthreads();
-    // the true maximum contributes 2^0, so a healthy row has row_s >= ~1 (see online.cuh)
-    if (!(row_s >= 0.5f && row_s <= FLT_MAX)) k4_exact_row(src, V, c, sm, row_m, row_s);
+    int32_t kk;
+    float row_m, row_s;
+    k4_segment(src, p.vocab, 0, p.top_k, c, sm, p.status, kk, row_m, row_s);
     const float lse = __fdiv_rn(row_m, temp) + logf(row_s);
-
-    // ---- exact top-kk of the candidates, best first
-    if (n > K4_RANK_MAX) {
-      k4_compact(sm, n, kk);
-      n = kk;
-    }
-    {
-      // n <= K4_RANK_MAX here: each thread ranks its (at most two) candidates in one pipelined
-      // pass over the list
-      constexpr int MINE = K4_RANK_MAX / K4_THREADS;
-      unsigned long long code[MINE];
-      int32_t rank[MINE];
-#pragma unroll
-      for (int q = 0; q < MINE; ++q) {
-        const int32_t i = tid + q * K4_THREADS;
-        code[q] = (i < n) ? sm.cand[i] : ~0ull;  // ~0 outranks everything: never placed
-        rank[q] = 0;
-      }
-#pragma unroll 4
-      for (int32_t j = 0; j < n; ++j) {
-        const unsigned long long o = sm.cand[j];
-#pragma unroll
-        for (int q = 0; q < MINE; ++q) rank[q] += (o > code[q]) ? 1 : 0;
-      }
-#pragma unroll
-      for (int q = 0; q < MINE; ++q)
-        if (tid + q * K4_THREADS < n && rank[q] < kk) sm.top[rank[q]] = code[q];
-    }
-    __syncthreads();
-
-    // ---- draw, score, write
-    if (tid == 0) {
-      const int32_t pick = greedy ? 0 : k4_draw(sm.top, kk, c, row, p.seed, p.offset);
-      p.out_tokens[row] = k4_index(sm.top[pick]);
-      p.out_logprob[row] = __fdiv_rn(k4_value(sm.top[pick]), temp) - lse;
-    }
-    if (p.out_topk_idx != nullptr || p.out_topk_val != nullptr) {
-      for (int32_t j = tid; j < k; j += K4_THREADS) {
-        const bool have = j < kk;
-        if (p.out_topk_idx != nullptr) p.out_topk_idx[row * k + j] = have ? k4_index(sm.top[j]) : -1;
-        if (p.out_topk_val != nullptr)
-          p.out_topk_val[row * k + j] = have ? k4_value(sm.top[j]) : -INFINITY;
-      }
-    }
+    k4_finish_row(p, sm, row, kk, c, temp, greedy, lse);
     __syncthreads();
   }
+}
+
+// Small batches: a cluster of `split` CTAs shares each row.  Every CTA finds the top-k and the
+// (max, sum-exp) of its part; the parts meet in the first CTA's shared memory, which ranks the
+// at most split * k survivors, merges the sums and draws.  Same tokens as the kernel above
+// (the draw depends on the row's top-k only).  grid = rows * split, one row per cluster.
+template <typename T>
+__global__ void __launch_bounds__(K4_THREADS, 2) k4_sample_split_kernel(const K4Params p,
+                                                                     const int split) {
+  extern __shared__ __align__(16) uint8_t k4_smem_raw[];
+  K4Smem& sm = *reinterpret_cast<K4Smem*>(k4_smem_raw);
+  const int tid = threadIdx.x;
+  const bool greedy = !(p.temperature > 0.0f);
+  const float temp = greedy ? 1.0f : p.temperature;
+  const float c = LOG2E / temp;
+  const uint32_t rank = cluster_ctarank();
+  const int64_t row = static_cast<int64_t>(blockIdx.x) / split;
+  const T* src = reinterpret_cast<const T*>(p.logits) + row * p.stride;
+  // parts begin on multiples of 8 logits, so they are as aligned as the row itself
+  const int64_t units = p.vocab / 8;
+  const int64_t begin = (units * rank / split) * 8;
+  const int64_t end = (rank + 1 == static_cast<uint32_t>(split)) ? p.vocab
+                                                                 : (units * (rank + 1) / split) * 8;
+  int32_t kk;
+  float part_m, part_s;
+  k4_segment(src + begin, end - begin, begin, p.top_k, c, sm, p.status, kk, part_m, part_s);
+  if (rank != 0) {
+    const uint32_t inbox = mapa_shared(smem_u32(&sm.inbox[rank * K4_MAX_K]), 0);
+    if (tid < kk) st_cluster_u64(inbox + tid * 8, sm.top[tid]);
+    if (tid == 0) {
+      st_cluster_f32x2(mapa_shared(smem_u32(&sm.inbox_ms[rank]), 0), part_m, part_s);
+      st_cluster_u32(mapa_shared(smem_u32(&sm.inbox_n[rank]), 0), static_cast<uint32_t>(kk));
+    }
+  }
+  cluster_sync_all();  // release/acquire: the first CTA sees what the others stored
+  if (rank != 0) return;
+  // gather the survivors of every part into the candidate list (at most split * k codes)
+  if (tid == 0) sm.count = 0;
+  __syncthreads();
+  if (tid < kk) sm.cand[atomicAdd(&sm.count, 1)] = sm.top[tid];
+  for (int r = 1; r < split; ++r)
+    if (tid < sm.inbox_n[r]) sm.cand[atomicAdd(&sm.count, 1)] = sm.inbox[r * K4_MAX_K + tid];
+  // a part without a finite logit (maximum -inf, sum NaN) adds nothing to the row's sum
+  const float ninf = __int_as_float(0xff800000);
+  float row_m = part_m;
+  for (int r = 1; r < split; ++r) row_m = fmaxf(row_m, sm.inbox_ms[r].x);
+  float row_s = (part_m == ninf) ? 0.0f : part_s * ex2f((part_m - row_m) * c);
+  for (int r = 1; r < split; ++r) {
+    const float2 ms = sm.inbox_ms[r];
+    if (ms.x != ninf) row_s += ms.y * ex2f((ms.x - row_m) * c);
+  }
+  __syncthreads();
+  const int32_t n = sm.count;
+  const int32_t kk_row = static_cast<int32_t>(min(static_cast<int64_t>(p.top_k), p.vocab));
+  __syncthreads();
+  k4_rank_top(sm, n, kk_row);
+  __syncthreads();
+  const float lse = __fdiv_rn(row_m, temp) + logf(row_s);
+  k4_finish_row(p, sm, row, kk_row, c, temp, greedy, lse);
+}
+
+// Cluster size for a batch too small to fill the GPU with one CTA per row: the largest of 8
+// and 4 whose clusters are all resident at once (0: do not split).
+// TOME_K4_SPLIT=0 switches the split off, 2/4/8 forces a size (read at every call; tests).
+static int k4_split_factor(const void* kernel, int smem, int64_t rows, int64_t vocab) {
+  if (vocab < K4_SPLIT_MIN_VOCAB) return 0;
+  const char* e = getenv("TOME_K4_SPLIT");
+  if (e != nullptr) {
+    const int v = atoi(e);
+    return ((v == 2 || v == 4 || v == 8) && rows * v <= 0x7fffffffLL) ? v : 0;
+  }
+  for (int split = K4_SPLIT_MAX; split >= 4; split >>= 1)
+    if (rows <= max_active_clusters(kernel, K4_THREADS, smem, split)) return split;
+  return 0;
 }
 
 }  // namespace tome
@@ -414,6 +519,31 @@ extern "C" int32_t tome_sample_topk_logprob(const void* logits, int32_t dtype, i
   p.out_topk_val = out_topk_val;
   p.status = dev_status;
   const int smem = static_cast<int>(sizeof(K4Smem));
+  void (*split_kernel)(K4Params, int) = (dtype == TOME_F32)
+                                            ? k4_sample_split_kernel<float>
+                                            : k4_sample_split_kernel<__nv_bfloat16>;
+  st = check_cuda(
+      cudaFuncSetAttribute(split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+      "cudaFuncSetAttribute(k4 split)");
+  if (st != TOME_OK) return st;
+  const int split =
+      streamed ? 0
+               : k4_split_factor(reinterpret_cast<const void*>(split_kernel), smem, rows, vocab);
+  if (split > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(rows * split), 1, 1);
+    cfg.blockDim = dim3(K4_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = static_cast<unsigned>(split);
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return check_cuda(cudaLaunchKernelEx(&cfg, split_kernel, p, split), "k4 split launch");
+  }
   const int grid = static_cast<int>(
       std::max<int64_t>(1, std::min<int64_t>(static_cast<int64_t>(info.sm_count) * 3, rows)));
   if (dtype == TOME_F32) {

@@ -283,7 +283,8 @@ def ragged_logprobs(logits: torch.Tensor, targets_packed: torch.Tensor, lengths:
 
 
 def sample_topk_logprob(logits: torch.Tensor, temperature: float, top_k: int = 20, *,
-                        seed: int = 0, offset: int = 0, return_topk: bool = False):
+                        seed: int = 0, offset: int = 0, return_topk: bool = False,
+                        check: bool = False):
     """Sample one token per row and score it, on the device, in one pass over the logits.
 
     The batched replacement of the rollout's per-sequence loop (mlx-impl/node.py:593-610):
@@ -292,6 +293,7 @@ def sample_topk_logprob(logits: torch.Tensor, temperature: float, top_k: int = 2
     0 means greedy (argmax) scored at temperature 1, as in the reference.  Returns
     ``(tokens int32 [...], logprobs fp32 [...])`` and, with ``return_topk``, the top-k indices
     and raw logits.  Draws depend only on ``(seed, offset, row)``; advance ``offset`` per step.
+    ``check=True`` synchronises and raises if the kernels reported a device status.
     """
     _require_cuda("logits", logits)
     flat, stride = _rows_view(logits)
@@ -308,6 +310,8 @@ def sample_topk_logprob(logits: torch.Tensor, temperature: float, top_k: int = 2
             lp.data_ptr(), _ptr(tk_i), _ptr(tk_v), _status_word(device).data_ptr(),
             _stream(device))
     _lib.check(status)
+    if check:
+        check_device_status(device)
     lead = logits.shape[:-1]
     if return_topk:
         return (tokens.reshape(lead), lp.reshape(lead), tk_i.reshape(*lead, top_k),
