@@ -13,14 +13,16 @@ from oracle import oracle
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=["small_batches_split", "one_cta_per_row"])
+@pytest.fixture(autouse=True, params=["small_batches_split", "one_cta_per_row", "two_pass_full"])
 def small_batch_path(request, monkeypatch):
     """Few rows normally share each row among a cluster of CTAs; the second run of every test
-    switches that off so the same cases also reach the streaming and plain-load kernels."""
-    if request.param == "one_cta_per_row":
+    switches that off so the same cases also reach the streaming, cluster-resident and
+    plain-load kernels; the third also sends the full-matrix mode to the two-pass pipeline."""
+    monkeypatch.delenv("TOME_K1_SPLIT", raising=False)
+    monkeypatch.delenv("TOME_K1_FULL_CLUSTER", raising=False)
+    if request.param != "small_batches_split":
         monkeypatch.setenv("TOME_K1_SPLIT", "0")
-    else:
-        monkeypatch.delenv("TOME_K1_SPLIT", raising=False)
+        monkeypatch.setenv("TOME_K1_FULL_CLUSTER", "0" if request.param == "two_pass_full" else "1")
     return request.param
 
 
@@ -478,3 +480,25 @@ def test_full_every_cluster_size(cuda_device, monkeypatch, split, dtype):
     out = tome_b200.fused_log_softmax(base.to(cuda_device)[:, 3:], 1.0)
     ref = oracle.log_softmax_metal_order(base[:, 3:].contiguous(), 1.0)
     assert out.shape == ref.shape and max_abs(out.float(), ref.float()) <= tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("vocab", [8, 24, 7000, 7680 * 6, 7680 * 6 + 8, 151936, 151936 + 4, 300000])
+def test_full_cluster_resident_sizes(cuda_device, monkeypatch, dtype, vocab):
+    """Row lengths around every cluster size of the resident kernel (1, 2, 4, 8 CTAs per row,
+    and beyond what 8 can hold), more rows than clusters so that slots are reused."""
+    import tome_b200
+    monkeypatch.setenv("TOME_K1_SPLIT", "0")
+    monkeypatch.setenv("TOME_K1_FULL_CLUSTER", "1")
+    rows = 700 if vocab <= 7000 else (330 if vocab < 100000 else 160)
+    x, _ = _case(rows, vocab, dtype, seed=31 + vocab % 83, scale=1.0)
+    x[3, : vocab // 2] = float("-inf")          # a part of a row without a finite logit
+    x[5] = -1.0e30                              # far below the streaming floor: exact fallback
+    xd = x.to(cuda_device)
+    out = tome_b200.fused_log_softmax(xd, 0.7)
+    ref = oracle.log_softmax_metal_order(x, 0.7)
+    tol = 1e-4 if dtype == torch.float32 else 0.0625 + 1e-6
+    finite = torch.isfinite(ref.float())
+    assert torch.equal(torch.isfinite(out.float()).cpu(), finite)
+    assert max_abs(out.float().cpu()[finite], ref.float()[finite]) <= tol
+    tome_b200.check_device_status(cuda_device)

@@ -67,6 +67,32 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   return true;
 }
 
+// Same wait with cluster-scope acquire: what another CTA of the cluster stored to this CTA's
+// shared memory before its (release.cluster) arrive is visible afterwards.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
+                                                  long long limit = WAIT_LIMIT_CYCLES) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if (clock64() - t0 > limit) return false;
+  }
+  return true;
+}
+
 // ---------------------------------------------------------------- bulk copies (TMA)
 // 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier.
 // Both addresses 16-byte aligned, bytes a multiple of 16.
