@@ -509,6 +509,35 @@ def run_extra(args, device, rank, world, dist_on, barrier, peaks):
         del xf
     torch.cuda.empty_cache()
 
+    # one decode step of the reference's rollout (64 sequences x V fp32 logits, node.py:590-605)
+    # replayed from a CUDA graph, so the numbers are the kernels' own time without the host
+    # cost of the Python call: selective log-prob, sampling + log-prob, full matrix
+    if rank == 0 or dist_on:
+        xd = torch.randn((64, VOCAB), device=device, dtype=torch.float32) * 3.0
+        idd = torch.randint(0, VOCAB, (64,), device=device, dtype=torch.int32)
+        calls = {"selective_us": lambda: tome_b200.local_compute_logprobs(xd, idd, 0.7),
+                 "sample_topk_us": lambda: tome_b200.sample_topk_logprob(xd, 0.7, 20, seed=7,
+                                                                         offset=1),
+                 "full_matrix_us": lambda: tome_b200.fused_log_softmax(xd, 0.7)}
+        step = {"shape": "64 x 151936 fp32", "how": "20 calls per CUDA graph, 20 replays"}
+        side = torch.cuda.Stream()
+        for key, call in calls.items():
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    call()
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(20):
+                        call()
+            torch.cuda.synchronize()
+            ms_g, _ = timed(graph.replay, k=20, w=3)
+            step[key] = ms_g / 20 * 1e3
+            del graph
+        extra["decode_step_64rows_graph"] = step
+        del xd, idd
+    torch.cuda.empty_cache()
+
     # cfg4: vocab-parallel head over the N ranks, strong scaling (total work fixed)
     hidden, weight, ids = synthetic.cfg4_vocab_parallel(32768, 4096, VOCAB, device)
     b, e = synthetic.shard_bounds(VOCAB, rank, world)

@@ -101,8 +101,34 @@ def _ids32(ids: torch.Tensor, n: int, device: torch.device) -> torch.Tensor:
     return ids.contiguous()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(device: torch.device) -> int:
+    """Handle of torch's current stream on ``device`` (the fast accessor when torch has it)."""
+    if _raw_stream is not None:
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        return _raw_stream(index)
     return torch.cuda.current_stream(device).cuda_stream
+
+
+class _NoSwitch:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def _on(device: torch.device):
+    """Context in which ``device`` is the current CUDA device; free when it already is (the
+    library launches on the current device, and switching costs several microseconds)."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(device)
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -128,7 +154,7 @@ def selective_log_softmax(logits: torch.Tensor, ids: torch.Tensor, temp: float =
     out = torch.empty(rows, dtype=torch.float32, device=device)
     lse = torch.empty(rows, dtype=torch.float32, device=device) if return_lse else None
     raw = torch.empty(rows, dtype=torch.float32, device=device) if return_target_logit else None
-    with torch.cuda.device(device):
+    with _on(device):
         status = lib.tome_selective_logprob(
             flat.data_ptr(), _dtype_code(flat), rows, V, stride, ids32.data_ptr(), temp,
             out.data_ptr(), _ptr(lse), _ptr(raw), _status_word(device).data_ptr(), _stream(device))
@@ -191,7 +217,7 @@ def fused_log_softmax(logits: torch.Tensor, temperature: float = 1.0, *,
     rows, V = flat.shape
     device = flat.device
     out = torch.empty((rows, V), dtype=flat.dtype, device=device)
-    with torch.cuda.device(device):
+    with _on(device):
         status = lib.tome_log_softmax_full(
             flat.data_ptr(), _dtype_code(flat), rows, V, stride, temperature, out.data_ptr(), V,
             None, _status_word(device).data_ptr(), _stream(device))
@@ -228,7 +254,7 @@ def grpo_dual_logprob_kl(policy_logits: torch.Tensor, ref_logits: torch.Tensor,
     len32 = _ids32(lengths, n_seq, device)
     st32 = None if starts is None else _ids32(starts, n_seq, device)
     outs = [torch.empty((n_seq, seq_len), dtype=torch.float32, device=device) for _ in range(3)]
-    with torch.cuda.device(device):
+    with _on(device):
         status = lib.tome_dual_logprob_kl(
             pol.data_ptr(), ref.data_ptr(), _dtype_code(pol), n_seq, seq_len, V, V,
             ids32.data_ptr(), len32.data_ptr(), _ptr(st32), temp, outs[0].data_ptr(),
@@ -268,7 +294,7 @@ def ragged_logprobs(logits: torch.Tensor, targets_packed: torch.Tensor, lengths:
     out = torch.empty(total, dtype=torch.float32, device=device)
     lse = torch.empty(total, dtype=torch.float32, device=device) if return_lse else None
     offsets = torch.empty(n_seq + 1, dtype=torch.int32, device=device)
-    with torch.cuda.device(device):
+    with _on(device):
         status = lib.tome_ragged_logprob(
             lg.data_ptr(), _dtype_code(lg), n_seq, seq_len, V, V, tg.data_ptr(), total, len32.data_ptr(),
             _ptr(st32), temp, out.data_ptr(), _ptr(lse), offsets.data_ptr(),
@@ -303,7 +329,7 @@ def sample_topk_logprob(logits: torch.Tensor, temperature: float, top_k: int = 2
     lp = torch.empty(rows, dtype=torch.float32, device=device)
     tk_i = torch.empty((rows, top_k), dtype=torch.int32, device=device) if return_topk else None
     tk_v = torch.empty((rows, top_k), dtype=torch.float32, device=device) if return_topk else None
-    with torch.cuda.device(device):
+    with _on(device):
         status = lib.tome_sample_topk_logprob(
             flat.data_ptr(), _dtype_code(flat), rows, V, stride, float(temperature or 0.0),
             int(top_k), int(seed) & (2 ** 64 - 1), int(offset) & (2 ** 64 - 1), tokens.data_ptr(),
@@ -362,7 +388,7 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.
         x2 = x2.contiguous()
     w = weight if weight.is_contiguous() else weight.contiguous()
     out = torch.empty_like(x2)
-    with torch.cuda.device(x2.device):
+    with _on(x2.device):
         status = lib.tome_rmsnorm_bf16(x2.data_ptr(), w.data_ptr(), x2.shape[0], dim, float(eps),
                                        out.data_ptr(), _stream(x2.device))
     _lib.check(status)
@@ -401,7 +427,7 @@ def lm_head_partials(hidden: torch.Tensor, weight_shard: torch.Tensor, vocab_off
             if x.dtype != torch.float32 or x.shape != (rows,) or not x.is_contiguous() or \
                     x.device != device:
                 raise ValueError("out must hold three contiguous fp32 [rows] tensors on the device")
-    with torch.cuda.device(device):
+    with _on(device):
         status = lib.tome_lmhead_partials(
             h2.data_ptr(), w2.data_ptr(), rows, K, V_local, int(vocab_offset), ids32.data_ptr(),
             temp, _head_flags(round_logits), m.data_ptr(), s.data_ptr(), t.data_ptr(), ws.data_ptr(),
@@ -438,7 +464,7 @@ def lm_head_logprob(hidden: torch.Tensor, weight: torch.Tensor, ids: torch.Tenso
     ws = _workspace(nbytes, device, workspace)
     lp = torch.empty(rows, dtype=torch.float32, device=device)
     lse = torch.empty(rows, dtype=torch.float32, device=device)
-    with torch.cuda.device(device):
+    with _on(device):
         status = lib.tome_lmhead_logprob(
             h2.data_ptr(), w2.data_ptr(), rows, K, V, ids32.data_ptr(), temp,
             _head_flags(round_logits), lp.data_ptr(), lse.data_ptr(), ws.data_ptr(),
@@ -472,7 +498,7 @@ def lm_head_logprob_static(hidden: torch.Tensor, weight: torch.Tensor, ids: torc
         raise TypeError("out_lse must be a contiguous float32 tensor")
     rows, K = hidden.shape
     device = hidden.device
-    with torch.cuda.device(device):
+    with _on(device):
         status = lib.tome_lmhead_logprob_static(
             hidden.data_ptr(), weight.data_ptr(), rows, K, weight.shape[0], ids.data_ptr(),
             float(temp or 1.0), out_logprob.data_ptr(), _ptr(out_lse),
@@ -493,7 +519,7 @@ def combine_triples(m: torch.Tensor, s: torch.Tensor, t: torch.Tensor):
     device = m.device
     lp = torch.empty(rows, dtype=torch.float32, device=device)
     lse = torch.empty(rows, dtype=torch.float32, device=device)
-    with torch.cuda.device(device):
+    with _on(device):
         status = lib.tome_combine_triples(m.data_ptr(), s.data_ptr(), rows, parts, t.data_ptr(),
                                           rows, t.shape[0], rows, lp.data_ptr(), lse.data_ptr(),
                                           _stream(device))
@@ -529,7 +555,7 @@ def gather_paged_kv(block_tables: torch.Tensor, offsets: torch.Tensor, k_pool: t
     device = k_pool.device
     k_out = torch.empty((B, H, max_seq_len, D), dtype=k_pool.dtype, device=device)
     v_out = torch.empty_like(k_out)
-    with torch.cuda.device(device):
+    with _on(device):
         status = lib.tome_gather_paged_kv(
             bt.data_ptr(), off.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
             k_pool.element_size(), B, H, D, block_size, max_blocks, num_blocks, int(max_seq_len),
@@ -556,7 +582,7 @@ def update_paged_kv(k_new: torch.Tensor, v_new: torch.Tensor, block_tables: torc
     vn = v_new if v_new.is_contiguous() else v_new.contiguous()
     ln = None if lengths is None else lengths.to(device=k_pool.device, dtype=torch.int32).contiguous()
     device = k_pool.device
-    with torch.cuda.device(device):
+    with _on(device):
         status = lib.tome_update_paged_kv(
             kn.data_ptr(), vn.data_ptr(), bt.data_ptr(), off.data_ptr(), _ptr(ln),
             k_pool.data_ptr(), v_pool.data_ptr(), k_pool.element_size(), B, H, kn.shape[2], D,
