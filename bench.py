@@ -511,8 +511,9 @@ def run_extra(args, device, rank, world, dist_on, barrier, peaks):
 
     # one decode step of the reference's rollout (64 sequences x V fp32 logits, node.py:590-605)
     # replayed from a CUDA graph, so the numbers are the kernels' own time without the host
-    # cost of the Python call: selective log-prob, sampling + log-prob, full matrix
-    if rank == 0 or dist_on:
+    # cost of the Python call: selective log-prob, sampling + log-prob, full matrix.  Single
+    # process only: a process group's watchdog thread must not meet a stream capture.
+    if not dist_on:
         xd = torch.randn((64, VOCAB), device=device, dtype=torch.float32) * 3.0
         idd = torch.randint(0, VOCAB, (64,), device=device, dtype=torch.int32)
         calls = {"selective_us": lambda: tome_b200.local_compute_logprobs(xd, idd, 0.7),
