@@ -578,6 +578,22 @@ def run_only(args):
             x, ids = synthetic.cfg2_rollout_bf16(rows, VOCAB, device)
         fn = lambda: tome_b200.local_compute_logprobs(x, ids, 1.0)  # noqa: E731
         work, unit = rows * VOCAB * x.element_size() + rows * 8, "GB/s"
+    elif args.only in ("full", "sample"):
+        rows = args.rows or 2048
+        x = torch.randn((rows, args.vocab), device=device, dtype=torch.float32) * 3.0
+        if not args.fp32:
+            x = x.to(torch.bfloat16)
+        if args.only == "full":  # algorithmic bytes: the matrix in and out
+            fn = lambda: tome_b200.fused_log_softmax(x, 1.0)  # noqa: E731
+            work, unit = 2 * rows * args.vocab * x.element_size(), "GB/s"
+        else:
+            draws = [0]
+
+            def fn():
+                draws[0] += 1
+                return tome_b200.sample_topk_logprob(x, 0.7, 20, seed=7, offset=draws[0])
+
+            work, unit = rows * args.vocab * x.element_size(), "GB/s"
     else:
         rows = args.rows or 16384
         hidden, weight, ids = synthetic.cfg3_lm_head(rows, args.hidden, args.vocab, device)
@@ -610,12 +626,12 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--skip-extra", action="store_true", help="headline workload only")
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg")
-    ap.add_argument("--only", choices=["selective", "lmhead"], default=None,
+    ap.add_argument("--only", choices=["selective", "lmhead", "full", "sample"], default=None,
                     help="profiling aid: run just one kernel's loop (no e2e, extras or CPU leg)")
     ap.add_argument("--rows", type=int, default=None, help="row count for --only (small cases)")
     ap.add_argument("--hidden", type=int, default=1024, help="hidden size for --only lmhead")
     ap.add_argument("--vocab", type=int, default=VOCAB, help="vocabulary (shard) size for --only")
-    ap.add_argument("--fp32", action="store_true", help="fp32 logits for --only selective")
+    ap.add_argument("--fp32", action="store_true", help="fp32 logits for --only selective / full / sample")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args, int(os.environ.get("RANK", "0")))
