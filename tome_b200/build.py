@@ -16,7 +16,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libtome_b200.so")
 
-SOURCES = ["api.cu", "k1_logprob.cu", "combine.cu", "k2_lmhead.cu", "k4_sample.cu", "k5_paged_kv.cu"]
+SOURCES = ["api.cu", "k1_logprob.cu", "k1_small.cu", "k1_full.cu", "combine.cu", "k2_lmhead.cu",
+           "k4_sample.cu", "k5_paged_kv.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -10,7 +10,7 @@
 // and the memory pipe busy while one of them merges a row.  (Measured: one CTA of 16 warps
 // per SM reached 6.0 TB/s, two of 8 warps 6.6, four of 4 warps 6.85 on 20480 x 151936 bf16.)
 //
-// Three modes share the pipeline:
+// These modes share the pipeline:
 //   SELECTIVE  logprob of one target per row             (mlx-impl/node.py:400-404)
 //   DUAL       policy + reference rows of a ragged window, plus the k3 KL estimate
 //              (window = completion slice, mlx-impl/node.py:446-451)
@@ -18,250 +18,16 @@
 //              the reference's Metal kernel (mlx-impl/model.py:16-66); the row is streamed
 //              twice (the second pass is served mostly by L2)
 //
+//   SAMPLE     top-k sampling + log-prob of the drawn token for large batches (see below)
+//
 // Inputs that do not meet the bulk-copy alignment rules (base or row pitch not a multiple
-// of 16 bytes) take a plain-load kernel with the same arithmetic.
-#include <cuda_bf16.h>
-#include <float.h>
-#include <math.h>
-
-#include <stdlib.h>
-
-#include <algorithm>
-#include <type_traits>
-
-#include "host_common.h"
+// of 16 bytes) take a plain-load kernel with the same arithmetic.  Small batches and long
+// fp32 rows of the FULL mode have kernels of their own (k1_small.cu, k1_full.cu).
+#include "k1_common.cuh"
 #include "k1_sample.h"
-#include "online.cuh"
-#include "ptx.cuh"
 #include "sampling.cuh"
 
 namespace tome {
-
-enum K1Mode { K1_SELECTIVE = 0, K1_DUAL = 1, K1_FULL = 2, K1_RAGGED = 3, K1_SAMPLE = 4 };
-
-// DUAL and RAGGED score only a window [start, start + length) of each sequence.
-__host__ __device__ constexpr bool k1_windowed(int mode) {
-  return mode == K1_DUAL || mode == K1_RAGGED;
-}
-
-// Tuning constants (overridable at compile time for experiments).
-#ifndef K1_CFG_WARPS
-#define K1_CFG_WARPS 4
-#endif
-#ifndef K1_CFG_STAGES
-#define K1_CFG_STAGES 2
-#endif
-#ifndef K1_CFG_CHUNK
-#define K1_CFG_CHUNK 25600
-#endif
-#ifndef K1_CFG_CHUNK_ALIGN
-#define K1_CFG_CHUNK_ALIGN 1024
-#endif
-#ifndef K1_CFG_CTAS_PER_SM
-#define K1_CFG_CTAS_PER_SM 4
-#endif
-#ifndef K1_CFG_L2_HINT
-#define K1_CFG_L2_HINT 1
-#endif
-constexpr int K1_CONSUMER_WARPS = K1_CFG_WARPS;
-constexpr int K1_CONSUMERS = K1_CONSUMER_WARPS * 32;
-constexpr int K1_THREADS = K1_CONSUMERS + 32;
-constexpr int K1_STAGES = K1_CFG_STAGES;
-constexpr int K1_CHUNK_BYTES = K1_CFG_CHUNK;
-constexpr int K1_CTAS_PER_SM = K1_CFG_CTAS_PER_SM;
-// bulk copies start on multiples of this many bytes from the row start (keeps them aligned
-// to whole 128-byte lines when the row pitch is)
-constexpr int K1_CHUNK_ALIGN = K1_CFG_CHUNK_ALIGN;
-static_assert(K1_CHUNK_BYTES % K1_CHUNK_ALIGN == 0 && K1_CHUNK_ALIGN % 16 == 0, "chunk alignment");
-static_assert(K1_CONSUMER_WARPS <= 32, "row-end merge reads one partial per lane");
-constexpr int K1_MAX_SEQ = 1024;
-constexpr int K1_POLY_DEFAULT = 2;
-
-struct K1Params {
-  const void* src[2];      // DUAL: policy, reference
-  int64_t n_rows;          // SELECTIVE/FULL: rows; DUAL: n_seq * seq_len (dense row count)
-  int64_t vocab;
-  int64_t stride;          // elements between rows
-  const int32_t* targets;  // SELECTIVE, DUAL
-  float c;                 // log2(e) / temperature
-  float temp;
-  float inv_temp;
-  float* out0;             // SELECTIVE: logprob   DUAL: policy logprob   FULL: lse (nullable)
-  float* out1;             // SELECTIVE: lse (nullable)   DUAL: reference logprob
-  float* out2;             // SELECTIVE: raw target logit (nullable)   DUAL: k3 KL
-  void* out_full;          // FULL
-  int64_t out_stride;      // FULL
-  const int32_t* lengths;  // DUAL
-  const int32_t* starts;   // DUAL, nullable
-  int32_t n_seq;           // DUAL
-  int32_t seq_len;         // DUAL
-  int64_t packed_capacity; // RAGGED: entries the packed target/output arrays can hold
-  int32_t* out_offsets;    // RAGGED: int32 [n_seq + 1], start of each sequence in the packed output
-  int32_t* out_tokens;     // SAMPLE: int32 [rows]; -1 marks a row left to the one-CTA-per-row kernel
-  int32_t* out_topk_idx;   // SAMPLE: nullable, [rows, top_k]
-  float* out_topk_val;     // SAMPLE: nullable, [rows, top_k]
-  uint64_t seed, offset;   // SAMPLE: random stream
-  int32_t top_k;           // SAMPLE: 1..64
-  int32_t greedy;          // SAMPLE: temperature 0 -> argmax, scored at temperature 1
-  int32_t* status;         // nullable
-  int32_t chunk_bytes;     // bulk-copy size (multiple of 16, <= K1_CHUNK_BYTES), set by launch
-  int32_t n_chunks;        // bulk copies per row
-};
-
-// ------------------------------------------------------------------ FULL mode output
-// out = T(float(x) * inv_temp) - T(lse), subtraction in T (mlx-impl/model.py:57-60)
-__device__ __forceinline__ uint32_t full_out_bf16x2(uint32_t w, float inv_temp,
-                                                    __nv_bfloat16 lse_t) {
-  const __nv_bfloat16 a = __float2bfloat16_rn(bf16_lo(w) * inv_temp);
-  const __nv_bfloat16 b = __float2bfloat16_rn(bf16_hi(w) * inv_temp);
-  const __nv_bfloat16 ra = __hsub(a, lse_t);
-  const __nv_bfloat16 rb = __hsub(b, lse_t);
-  return static_cast<uint32_t>(__bfloat16_as_ushort(ra)) |
-         (static_cast<uint32_t>(__bfloat16_as_ushort(rb)) << 16);
-}
-
-__device__ __forceinline__ uint4 full_out_vec(uint4 v, float inv_temp, float lse, __nv_bfloat16) {
-  const __nv_bfloat16 lse_t = __float2bfloat16_rn(lse);
-  uint4 o;
-  o.x = full_out_bf16x2(v.x, inv_temp, lse_t);
-  o.y = full_out_bf16x2(v.y, inv_temp, lse_t);
-  o.z = full_out_bf16x2(v.z, inv_temp, lse_t);
-  o.w = full_out_bf16x2(v.w, inv_temp, lse_t);
-  return o;
-}
-
-__device__ __forceinline__ uint4 full_out_vec(uint4 v, float inv_temp, float lse, float) {
-  uint4 o;
-  o.x = __float_as_uint(__fsub_rn(__fmul_rn(__uint_as_float(v.x), inv_temp), lse));
-  o.y = __float_as_uint(__fsub_rn(__fmul_rn(__uint_as_float(v.y), inv_temp), lse));
-  o.z = __float_as_uint(__fsub_rn(__fmul_rn(__uint_as_float(v.z), inv_temp), lse));
-  o.w = __float_as_uint(__fsub_rn(__fmul_rn(__uint_as_float(v.w), inv_temp), lse));
-  return o;
-}
-
-__device__ __forceinline__ float full_out_scalar(float x, float inv_temp, float lse) {
-  return __fsub_rn(__fmul_rn(x, inv_temp), lse);
-}
-
-__device__ __forceinline__ __nv_bfloat16 full_out_scalar(__nv_bfloat16 x, float inv_temp,
-                                                         float lse) {
-  return __hsub(__float2bfloat16_rn(__bfloat162float(x) * inv_temp), __float2bfloat16_rn(lse));
-}
-
-// ------------------------------------------------------------------ row results
-// lse of x/T from the raw maximum m and s = sum 2^((x - m) * c).
-template <int MODE>
-__device__ __forceinline__ float finish_lse(float m, float s, const K1Params& p) {
-  // SELECTIVE/DUAL follow node.py:401 (true division); FULL follows the Metal kernel
-  // (multiplication by the reciprocal, model.py:27).
-  const float ms = (MODE == K1_FULL) ? __fmul_rn(m, p.inv_temp) : __fdiv_rn(m, p.temp);
-  return ms + logf(s);
-}
-
-__device__ __forceinline__ void raise_status(int32_t* status, int32_t bit) {
-  if (status != nullptr) atomicOr(status, bit);
-}
-
-// DUAL: window of sequence i, clamped to the sequence.
-__device__ __forceinline__ void dual_window(const K1Params& p, int i, int& start, int& len) {
-  start = (p.starts != nullptr) ? p.starts[i] : 0;
-  start = max(0, min(start, p.seq_len));
-  len = max(0, min(p.lengths[i], p.seq_len - start));
-}
-
-// DUAL: dense row of the a-th active position; cum[] = exclusive prefix sums of the lengths.
-__device__ __forceinline__ int64_t dual_row_of_item(const K1Params& p, const int32_t* cum,
-                                                    int64_t a) {
-  int lo = 0, hi = p.n_seq;  // find i with cum[i] <= a < cum[i+1]
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (cum[mid] <= a) lo = mid; else hi = mid;
-  }
-  int start = (p.starts != nullptr) ? p.starts[lo] : 0;
-  start = max(0, min(start, p.seq_len));
-  return static_cast<int64_t>(lo) * p.seq_len + start + (a - cum[lo]);
-}
-
-// Block-wide exclusive prefix sum of the window lengths into cum[0..n_seq]; returns the total.
-__device__ int64_t dual_build_prefix(const K1Params& p, int32_t* cum, int32_t* scratch) {
-  const int n = p.n_seq;
-  const int nt = blockDim.x;
-  const int per = (n + nt - 1) / nt;
-  const int b = min(n, static_cast<int>(threadIdx.x) * per);
-  const int e = min(n, b + per);
-  int32_t local = 0;
-  for (int i = b; i < e; ++i) {
-    int st, ln;
-    dual_window(p, i, st, ln);
-    local += ln;
-  }
-  scratch[threadIdx.x] = local;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int32_t run = 0;
-    for (int t = 0; t < nt; ++t) {
-      const int32_t v = scratch[t];
-      scratch[t] = run;
-      run += v;
-    }
-    cum[n] = run;
-  }
-  __syncthreads();
-  int32_t run = scratch[threadIdx.x];
-  for (int i = b; i < e; ++i) {
-    int st, ln;
-    dual_window(p, i, st, ln);
-    cum[i] = run;
-    run += ln;
-  }
-  __syncthreads();
-  return cum[n];
-}
-
-// DUAL: zero the outputs of every position outside its sequence's window.
-__device__ void dual_zero_masked(const K1Params& p) {
-  const int64_t total = p.n_rows;
-  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
-       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int i = static_cast<int>(idx / p.seq_len);
-    const int pos = static_cast<int>(idx - static_cast<int64_t>(i) * p.seq_len);
-    int st, ln;
-    dual_window(p, i, st, ln);
-    if (pos < st || pos >= st + ln) {
-      p.out0[idx] = 0.0f;
-      p.out1[idx] = 0.0f;
-      p.out2[idx] = 0.0f;
-    }
-  }
-}
-
-// Writes the per-row results once the row's (m, s) and raw target logit are known.
-// Called by one thread.  `carry` holds the policy logprob between the two DUAL sub-rows.
-template <int MODE>
-__device__ __forceinline__ void emit_row(const K1Params& p, int64_t row, int sub, float m, float s,
-                                         float x_t, bool target_ok, float& carry) {
-  const float lse = finish_lse<MODE>(m, s, p);
-  if (MODE == K1_FULL) {
-    if (p.out0 != nullptr) p.out0[row] = lse;
-    return;
-  }
-  float lp = __fdiv_rn(x_t, p.temp) - lse;
-  if (!target_ok) lp = __int_as_float(0x7fc00000);
-  if (MODE == K1_SELECTIVE || MODE == K1_RAGGED) {
-    p.out0[row] = lp;
-    if (p.out1 != nullptr) p.out1[row] = lse;
-    if (p.out2 != nullptr) p.out2[row] = target_ok ? x_t : __int_as_float(0x7fc00000);
-  } else {
-    if (sub == 0) {
-      carry = lp;
-      p.out0[row] = lp;
-    } else {
-      const float d = lp - carry;  // r - p
-      p.out1[row] = lp;
-      p.out2[row] = expf(d) - d - 1.0f;
-    }
-  }
-}
 
 // ------------------------------------------------------------------ bulk-copy pipeline kernel
 // FULL mode runs two CTAs per SM (see the launch code), so each can afford a deeper ring.
@@ -298,23 +64,6 @@ struct K1SampleSmem {
   int32_t count;
 };
 static_assert(K1_SAMPLE_GROUPS >= 64, "the threshold needs at least top_k (<= 64) groups");
-
-// Exact two-pass (max, sum 2^((x - max) * c)) of one row with plain loads, by one full warp.
-// Only used for rows the streaming arithmetic cannot represent (see K1_M_FLOOR).
-template <typename T>
-__device__ __noinline__ void exact_row(const T* src, int64_t vocab, float c, int lane, float& m,
-                                       float& s) {
-  float mx = __int_as_float(0xff800000);  // -inf
-  for (int64_t j = lane; j < vocab; j += 32) mx = fmaxf(mx, to_float(src[j]));
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  float sum = 0.0f;
-  for (int64_t j = lane; j < vocab; j += 32) sum += ex2f((to_float(src[j]) - mx) * c);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  m = mx;
-  s = sum;
-}
 
 template <typename T, int MODE, int POLY>
 __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(const K1Params p) {
@@ -752,398 +501,6 @@ __global__ void __launch_bounds__(K1_PLAIN_THREADS) k1_plain_kernel(const K1Para
   }
 }
 
-// ------------------------------------------------------------------ small batches
-// With fewer rows than SMs a one-CTA-per-row launch leaves most of the GPU idle and the call
-// takes as long as one CTA needs for a whole row.  Here a cluster of `split` CTAs shares a
-// row: each streams 1/split of it with 128-bit loads, the per-CTA (m, s) pairs meet in the
-// shared memory of the cluster's first CTA, which merges them and writes the row's result.
-constexpr int K1_SPLIT_THREADS = 512;
-constexpr int K1_SPLIT_MAX = 8;  // portable cluster size
-
-template <typename T, int MODE>
-__global__ void __launch_bounds__(K1_SPLIT_THREADS) k1_split_kernel(const K1Params p,
-                                                                    const int split) {
-  static_assert(MODE == K1_SELECTIVE || MODE == K1_FULL, "modes with one result set per row");
-  __shared__ float2 part[K1_SPLIT_THREADS / 32];
-  __shared__ __align__(8) float2 slot[K1_SPLIT_MAX];  // one pair per rank of the cluster
-  __shared__ float2 result;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_ctarank();
-  const int64_t row = static_cast<int64_t>(blockIdx.x) / split;
-  const T* src = reinterpret_cast<const T*>(p.src[0]) + row * p.stride;
-  constexpr int64_t PER = 16 / static_cast<int64_t>(sizeof(T));
-  const uintptr_t addr = reinterpret_cast<uintptr_t>(src);
-  const int64_t head = min(p.vocab, static_cast<int64_t>(((16 - (addr & 15)) & 15) / sizeof(T)));
-  const int64_t nvec = (p.vocab - head) / PER;
-  const int64_t tail_begin = head + nvec * PER;
-  const uint4* body = reinterpret_cast<const uint4*>(src + head);
-  const int64_t v_begin = nvec * rank / split;
-  const int64_t v_end = nvec * (rank + 1) / split;
-  Fast fs;
-  fast_init(fs, p.c);
-#pragma unroll 4
-  for (int64_t v = v_begin + threadIdx.x; v < v_end; v += K1_SPLIT_THREADS)
-    fast_update<0>(fs, __ldg(body + v), p.c, T());
-  Online st = fast_finish(fs, p.c);
-  if (rank == 0) {  // the unaligned ends of the row
-    for (int64_t j = threadIdx.x; j < head; j += K1_SPLIT_THREADS)
-      online_update_scalar(st, to_float(src[j]), p.c);
-    for (int64_t j = tail_begin + threadIdx.x; j < p.vocab; j += K1_SPLIT_THREADS)
-      online_update_scalar(st, to_float(src[j]), p.c);
-  }
-  online_warp_reduce(st, p.c);
-  if (lane == 0) part[warp] = make_float2(st.m, st.s);
-  __syncthreads();
-  if (warp == 0) {
-    const float2 ms = (lane < K1_SPLIT_THREADS / 32) ? part[lane] : make_float2(-FLT_MAX, 0.0f);
-    Online cta = {ms.x, ms.y};
-    online_warp_reduce(cta, p.c);
-    // SELECTIVE: only the first CTA finishes the row; FULL: every CTA needs the row's lse
-    const int receivers = (MODE == K1_FULL) ? split : 1;
-    if (lane < receivers) st_cluster_f32x2(mapa_shared(smem_u32(&slot[rank]), lane), cta.m, cta.s);
-  }
-  cluster_sync_all();  // release/acquire: the pairs are visible where they were sent
-  if (MODE == K1_SELECTIVE && rank != 0) return;
-  if (warp == 0) {
-    const float2 ms = (lane < split) ? slot[lane] : make_float2(-FLT_MAX, 0.0f);
-    Online all = {ms.x, ms.y};
-    online_warp_reduce(all, p.c);
-    float m = all.m, s = all.s;
-    if (!(s >= 0.5f && s <= FLT_MAX)) exact_row(src, p.vocab, p.c, lane, m, s);
-    if (lane == 0) {
-      float x_t = 0.0f;
-      bool target_ok = true;
-      if (MODE == K1_SELECTIVE) {
-        const int32_t t = p.targets[row];
-        target_ok = (t >= 0) && (static_cast<int64_t>(t) < p.vocab);
-        if (target_ok) x_t = to_float(src[t]);
-        else raise_status(p.status, TOME_DEV_TARGET_OUT_OF_RANGE);
-      }
-      float carry = 0.0f;
-      if (MODE == K1_SELECTIVE || rank == 0) emit_row<MODE>(p, row, 0, m, s, x_t, target_ok, carry);
-      result = make_float2(m, s);
-    }
-  }
-  if (MODE != K1_FULL) return;
-  __syncthreads();
-  // second pass over this CTA's part of the row (just read: it comes from L2)
-  const float lse = finish_lse<MODE>(result.x, result.y, p);
-  T* dst = reinterpret_cast<T*>(p.out_full) + row * p.out_stride;
-  const bool dst_vec = ((reinterpret_cast<uintptr_t>(dst + head) & 15) == 0);
-  if (dst_vec) {
-    uint4* out = reinterpret_cast<uint4*>(dst + head);
-#pragma unroll 4
-    for (int64_t v = v_begin + threadIdx.x; v < v_end; v += K1_SPLIT_THREADS)
-      out[v] = full_out_vec(__ldg(body + v), p.inv_temp, lse, T());
-  } else {
-    for (int64_t j = head + v_begin * PER + threadIdx.x; j < head + v_end * PER;
-         j += K1_SPLIT_THREADS)
-      dst[j] = full_out_scalar(src[j], p.inv_temp, lse);
-  }
-  if (rank == 0) {
-    for (int64_t j = threadIdx.x; j < head; j += K1_SPLIT_THREADS)
-      dst[j] = full_out_scalar(src[j], p.inv_temp, lse);
-    for (int64_t j = tail_begin + threadIdx.x; j < p.vocab; j += K1_SPLIT_THREADS)
-      dst[j] = full_out_scalar(src[j], p.inv_temp, lse);
-  }
-}
-
-// Cluster size for a batch too small to fill the GPU with one CTA per row: the largest of 8
-// and 4 whose clusters are all resident at once (measured on V = 151936: 4.7 vs 17 us for one
-// fp32 row, 13 vs 19 us for 128 rows; clusters of 2 do not pay).  0: do not split.
-// TOME_K1_SPLIT=0 switches the split off, 2/4/8 forces that size (read at every call: tests
-// use it to reach the one-CTA-per-row kernels with few rows).
-template <typename T, int MODE>
-static int k1_split_factor(int64_t rows) {
-  const char* e = getenv("TOME_K1_SPLIT");
-  if (e != nullptr) {
-    const int v = atoi(e);
-    const bool valid = (v == 2 || v == 4 || v == 8) && rows * v <= 0x7fffffffLL;
-    return valid ? v : 0;
-  }
-  const void* kernel = reinterpret_cast<const void*>(k1_split_kernel<T, MODE>);
-  for (int split = K1_SPLIT_MAX; split >= 4; split >>= 1)
-    if (rows <= max_active_clusters(kernel, K1_SPLIT_THREADS, 0, split)) return split;
-  return 0;
-}
-
-template <typename T, int MODE>
-static int32_t k1_launch_split(const K1Params& p, int split, cudaStream_t stream) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(p.n_rows * split), 1, 1);
-  cfg.blockDim = dim3(K1_SPLIT_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = static_cast<unsigned>(split);
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
-  return check_cuda(cudaLaunchKernelEx(&cfg, k1_split_kernel<T, MODE>, p, split), "k1 split launch");
-}
-
-// ------------------------------------------------------------------ full matrix, large batches
-// The two-pass FULL mode of the pipeline kernel re-reads each row from L2, which holds only as
-// long as the rows in flight fit there (fp32 rows of an LM vocabulary do not: measured DRAM
-// traffic was 3 units per 2 algorithmic).  Here a row never leaves the SMs between the passes:
-// a cluster of C CTAs shares it, each CTA's part stays RESIDENT in its shared-memory ring.
-//   pass 1: the consumers fold the chunks into (m, s) as they land, without releasing them;
-//   exchange: each CTA sends its pair to the others (st.shared::cluster + mbarrier arrive with
-//             release.cluster), waits for theirs (acquire.cluster), every CTA computes the lse;
-//   pass 2: the consumers turn the resident chunks into outputs, store them (streaming
-//           stores) and only now release each slot, which the producer refills with the
-//           next row's chunk: loads of row r+1 overlap the stores of row r.
-// DRAM traffic: the row once in, once out.  Two CTAs per SM so one can compute while the other
-// waits for its exchange.
-#ifndef KF_CFG_WARPS
-#define KF_CFG_WARPS 8
-#endif
-#ifndef KF_CFG_SLOTS
-#define KF_CFG_SLOTS 7
-#endif
-#ifndef KF_CFG_CHUNK
-#define KF_CFG_CHUNK 15360
-#endif
-#ifndef KF_CFG_CTAS_PER_SM
-#define KF_CFG_CTAS_PER_SM 2
-#endif
-#ifndef KF_CFG_WANT_SPARE
-#define KF_CFG_WANT_SPARE 1
-#endif
-constexpr int KF_CONSUMER_WARPS = KF_CFG_WARPS;
-constexpr int KF_CONSUMERS = KF_CONSUMER_WARPS * 32;
-constexpr int KF_THREADS = KF_CONSUMERS + 32;
-constexpr int KF_SLOTS = KF_CFG_SLOTS;
-constexpr int KF_CHUNK_BYTES = KF_CFG_CHUNK;
-constexpr int KF_MAX_CLUSTER = 8;
-constexpr int KF_CTAS_PER_SM = KF_CFG_CTAS_PER_SM;
-constexpr int KF_WANT_SPARE = KF_CFG_WANT_SPARE;  // free slots preferred (at least one is required)
-
-struct KFSmem {
-  static constexpr int DATA = KF_SLOTS * KF_CHUNK_BYTES;
-  static constexpr int FULL_BAR = DATA;                       // SLOTS mbarriers
-  static constexpr int EMPTY_BAR = FULL_BAR + KF_SLOTS * 8;   // SLOTS mbarriers
-  static constexpr int XCHG_BAR = EMPTY_BAR + KF_SLOTS * 8;   // 2 mbarriers (row parity)
-  static constexpr int PART = XCHG_BAR + 16;                  // [2][WARPS] float2
-  static constexpr int PAIRS = PART + 2 * KF_CONSUMER_WARPS * 8;   // [2][MAX_CLUSTER] float2
-  static constexpr int LSE = PAIRS + 2 * KF_MAX_CLUSTER * 8;       // [2] float
-  static constexpr int TOTAL = LSE + 8;
-};
-
-template <typename T>
-__global__ void __launch_bounds__(KF_THREADS, KF_CTAS_PER_SM)
-k1_full_cluster_kernel(const K1Params p, const int cluster, const int chunks_per_cta) {
-  extern __shared__ __align__(1024) uint8_t smem[];
-  constexpr int ES = sizeof(T);
-  const uint32_t smem_base = smem_u32(smem);
-  const uint32_t full_bar = smem_base + KFSmem::FULL_BAR;
-  const uint32_t empty_bar = smem_base + KFSmem::EMPTY_BAR;
-  const uint32_t xchg_bar = smem_base + KFSmem::XCHG_BAR;
-  float2* part = reinterpret_cast<float2*>(smem + KFSmem::PART);
-  float2* pairs = reinterpret_cast<float2*>(smem + KFSmem::PAIRS);
-  volatile float* lse_box = reinterpret_cast<volatile float*>(smem + KFSmem::LSE);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_ctarank();
-  const int64_t n_clusters = gridDim.x / cluster;
-  const int64_t first_row = blockIdx.x / cluster;
-
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < KF_SLOTS; ++i) {
-      mbar_init(full_bar + i * 8, 1);
-      mbar_init(empty_bar + i * 8, KF_CONSUMER_WARPS);
-    }
-    mbar_init(xchg_bar, cluster > 1 ? cluster - 1 : 1);
-    mbar_init(xchg_bar + 8, cluster > 1 ? cluster - 1 : 1);
-    fence_mbar_init();
-  }
-  __syncthreads();
-  if (cluster > 1) cluster_sync_all();  // nobody arrives on a barrier that is not there yet
-
-  // this CTA's part of a row: chunks [rank * chunks_per_cta, (rank + 1) * chunks_per_cta) of
-  // chunk_bytes each (the last chunks of a row may be short or empty)
-  const int64_t bulk_bytes = (p.vocab * ES) & ~static_cast<int64_t>(15);
-  const int64_t chunk_bytes = p.chunk_bytes;
-  const int64_t part_begin = static_cast<int64_t>(rank) * chunks_per_cta * chunk_bytes;
-  int my_chunks = 0;
-  for (int k = 0; k < chunks_per_cta; ++k)
-    if (part_begin + k * chunk_bytes < bulk_bytes) ++my_chunks;
-  const int64_t tail_begin = bulk_bytes / ES;  // elements past the last 16-byte boundary
-  const bool owns_tail = (rank == static_cast<uint32_t>(cluster) - 1);
-
-  if (warp == KF_CONSUMER_WARPS) {
-    // ---------------- producer
-    if (lane == 0) {
-      const uint64_t policy = policy_evict_first();  // every byte is read once
-      uint32_t it = 0;
-      bool ok = true;
-      for (int64_t row = first_row; row < p.n_rows && ok; row += n_clusters) {
-        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.src[0]) + row * p.stride * ES +
-                             part_begin;
-        for (int k = 0; k < my_chunks; ++k, ++it) {
-          const uint32_t slot = it % KF_SLOTS;
-          const uint32_t phase = (it / KF_SLOTS) & 1u;
-          if (!mbar_wait(empty_bar + slot * 8, phase ^ 1u)) {
-            raise_status(p.status, TOME_DEV_TIMEOUT);
-            ok = false;
-            break;
-          }
-          const int64_t off = k * chunk_bytes;
-          const uint32_t bytes =
-              static_cast<uint32_t>(min(chunk_bytes, bulk_bytes - part_begin - off));
-          mbar_arrive_expect_tx(full_bar + slot * 8, bytes);
-          bulk_g2s_hint(smem_base + slot * KF_CHUNK_BYTES, src + off, bytes, full_bar + slot * 8,
-                        policy);
-        }
-      }
-    }
-    return;
-  }
-
-  // ---------------- consumers
-  // A consumer whose wait ran out stops touching data but stays in step with its cluster (the
-  // peers keep storing into this CTA's shared memory until their last row).
-  const int ctid = threadIdx.x;
-  uint32_t it = 0;
-  uint32_t row_it = 0;
-  bool dead = false;
-  for (int64_t row = first_row; row < p.n_rows; row += n_clusters, ++row_it) {
-    const T* src = reinterpret_cast<const T*>(p.src[0]) + row * p.stride;
-    T* dst = reinterpret_cast<T*>(p.out_full) + row * p.out_stride;
-    const uint32_t par = row_it & 1u;
-    // ---- pass 1: (m, s) of this CTA's part, chunks stay where they are
-    Fast fs;
-    fast_init(fs, p.c);
-    for (int k = 0; k < my_chunks; ++k) {
-      const uint32_t slot = (it + k) % KF_SLOTS;
-      const uint32_t phase = ((it + k) / KF_SLOTS) & 1u;
-      if (!dead && !mbar_wait(full_bar + slot * 8, phase)) {
-        raise_status(p.status, TOME_DEV_TIMEOUT);
-        dead = true;
-      }
-      if (dead) break;
-      const uint32_t bytes = static_cast<uint32_t>(
-          min(chunk_bytes, bulk_bytes - part_begin - k * chunk_bytes));
-      const uint32_t nvec = bytes >> 4;
-      const uint32_t sbase = smem_base + slot * KF_CHUNK_BYTES;
-#pragma unroll 4
-      for (uint32_t v = ctid; v < nvec; v += KF_CONSUMERS)
-        fast_update<0>(fs, lds128(sbase + v * 16), p.c, T());
-    }
-    Online st = fast_finish(fs, p.c);
-    if (owns_tail && ctid == 0)
-      for (int64_t j = tail_begin; j < p.vocab; ++j) online_update_scalar(st, to_float(src[j]), p.c);
-    online_warp_reduce(st, p.c);
-    if (lane == 0) part[par * KF_CONSUMER_WARPS + warp] = make_float2(st.m, st.s);
-    named_bar_sync(1, KF_CONSUMERS);
-    if (warp == 0) {
-      const float2 w = (lane < KF_CONSUMER_WARPS) ? part[par * KF_CONSUMER_WARPS + lane]
-                                                  : make_float2(-FLT_MAX, 0.0f);
-      Online cta = {w.x, w.y};
-      online_warp_reduce(cta, p.c);
-      // ---- exchange: lane q sends this CTA's pair to rank q, then all wait for the others
-      if (lane < cluster) {
-        if (static_cast<uint32_t>(lane) == rank) {
-          pairs[par * KF_MAX_CLUSTER + rank] = make_float2(cta.m, cta.s);
-        } else {
-          st_cluster_f32x2(mapa_shared(smem_u32(&pairs[par * KF_MAX_CLUSTER + rank]), lane),
-                           cta.m, cta.s);
-          mbar_arrive_cluster(mapa_shared(xchg_bar + par * 8, lane));
-        }
-      }
-      __syncwarp();
-      bool ok = true;
-      if (cluster > 1) ok = mbar_wait_cluster(xchg_bar + par * 8, (row_it >> 1) & 1u);
-      const float2 o = (lane < cluster) ? pairs[par * KF_MAX_CLUSTER + lane]
-                                        : make_float2(-FLT_MAX, 0.0f);
-      Online all = {o.x, o.y};
-      online_warp_reduce(all, p.c);
-      float m = all.m, s = all.s;
-      if (!(s >= 0.5f && s <= FLT_MAX)) exact_row(src, p.vocab, p.c, lane, m, s);
-      float lse = finish_lse<K1_FULL>(m, s, p);
-      if (!ok) {  // a peer never delivered: report, poison the row, keep the CTA in step
-        raise_status(p.status, TOME_DEV_TIMEOUT);
-        lse = __int_as_float(0x7fc00000);
-      }
-      if (lane == 0) {
-        lse_box[par] = lse;
-        if (rank == 0 && p.out0 != nullptr) p.out0[row] = lse;
-      }
-    }
-    named_bar_sync(1, KF_CONSUMERS);
-    const float lse = lse_box[par];
-    // ---- pass 2: outputs from the resident chunks; a slot is released once it is written out
-    for (int k = 0; k < my_chunks; ++k, ++it) {
-      const uint32_t slot = it % KF_SLOTS;
-      const int64_t off = part_begin + k * chunk_bytes;
-      const uint32_t bytes = static_cast<uint32_t>(min(chunk_bytes, bulk_bytes - off));
-      const uint32_t nvec = dead ? 0u : (bytes >> 4);
-      const uint32_t sbase = smem_base + slot * KF_CHUNK_BYTES;
-      uint8_t* drow = reinterpret_cast<uint8_t*>(dst) + off;
-#pragma unroll 4
-      for (uint32_t v = ctid; v < nvec; v += KF_CONSUMERS)
-        stg128_streaming(drow + static_cast<size_t>(v) * 16,
-                         full_out_vec(lds128(sbase + v * 16), p.inv_temp, lse, T()));
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty_bar + slot * 8);
-    }
-    if (owns_tail && ctid == 0)
-      for (int64_t j = tail_begin; j < p.vocab; ++j)
-        dst[j] = full_out_scalar(src[j], p.inv_temp, lse);
-  }
-}
-
-// Cluster size and chunking with which a row stays resident in the cluster's rings
-// (false: the row is too long for 8 CTAs).  One slot is kept free for prefetching.
-static bool kf_plan(int64_t bulk_bytes, int* cluster, int* chunks_per_cta, int32_t* chunk_bytes) {
-  for (int pass = 0; pass < 2; ++pass)
-  for (int c = 1; c <= KF_MAX_CLUSTER; c <<= 1) {
-    const int64_t n = std::max<int64_t>(1, (bulk_bytes + static_cast<int64_t>(c) * KF_CHUNK_BYTES - 1) /
-                                               (static_cast<int64_t>(c) * KF_CHUNK_BYTES));
-    if (n > KF_SLOTS - (pass == 0 ? KF_WANT_SPARE : 1)) continue;
-    const int64_t total = n * c;
-    const int64_t al = K1_CHUNK_ALIGN;
-    const int64_t cb = std::max<int64_t>(al, ((bulk_bytes + total - 1) / total + al - 1) / al * al);
-    if (cb > KF_CHUNK_BYTES) continue;
-    *cluster = c;
-    *chunks_per_cta = static_cast<int>(n);
-    *chunk_bytes = static_cast<int32_t>(cb);
-    return true;
-  }
-  return false;
-}
-
-template <typename T>
-static int32_t k1_launch_full_cluster(const K1Params& p_in, int cluster, int chunks_per_cta,
-                                      int32_t chunk_bytes, int sm_count, cudaStream_t stream) {
-  K1Params p = p_in;
-  p.chunk_bytes = chunk_bytes;
-  auto kernel = k1_full_cluster_kernel<T>;
-  int32_t st = check_cuda(
-      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KFSmem::TOTAL),
-      "cudaFuncSetAttribute(full cluster)");
-  if (st != TOME_OK) return st;
-  int resident = max_active_clusters(reinterpret_cast<const void*>(kernel), KF_THREADS,
-                                     KFSmem::TOTAL, cluster);
-  if (resident <= 0) resident = std::max(1, sm_count * KF_CTAS_PER_SM / cluster);
-  const int64_t n_clusters = std::max<int64_t>(1, std::min<int64_t>(resident, p.n_rows));
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(n_clusters * cluster), 1, 1);
-  cfg.blockDim = dim3(KF_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = KFSmem::TOTAL;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = static_cast<unsigned>(cluster);
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
-  return check_cuda(cudaLaunchKernelEx(&cfg, kernel, p, cluster, chunks_per_cta),
-                    "k1 full cluster launch");
-}
-
 // ------------------------------------------------------------------ host side
 // Tuning knob TOME_K1_POLY = 0 .. 4: how many of the 8 logits of a bf16 vector take the
 // polynomial exp2 (FMA pipe) instead of ex2.approx (exp unit).  Read once per process.
@@ -1174,27 +531,18 @@ static int32_t k1_launch_typed(const K1Params& p_in, bool bulk_ok, int64_t max_i
   DeviceInfo info;
   int32_t st = current_device_info(&info);
   if (st != TOME_OK) return st;
+  constexpr int32_t dtype = std::is_same<T, float>::value ? TOME_F32 : TOME_BF16;
   if constexpr (MODE == K1_SELECTIVE || MODE == K1_FULL) {
-    const int split = k1_split_factor<T, MODE>(p_in.n_rows);
-    if (split > 1) return k1_launch_split<T, MODE>(p_in, split, stream);
+    // few rows: a cluster of CTAs shares each row (k1_small.cu)
+    bool taken = false;
+    st = k1_small_batch_launch(p_in, dtype, MODE, stream, &taken);
+    if (taken || st != TOME_OK) return st;
   }
   if constexpr (MODE == K1_FULL) {
-    // The cluster-resident kernel pays an exchange per row; it wins where the pipeline kernel's
-    // second pass would miss L2, i.e. when the rows in flight there (two per SM) exceed ~100 MB,
-    // and only for fp32 (measured at V = 128256 / 151936: fp32 4.6 / 4.5 -> 5.1 / 5.6 TB/s,
-    // bf16 5.1 / 5.0 -> 4.4 / 4.9).  TOME_K1_FULL_CLUSTER=0 / 1 forces the pipeline / the
-    // resident kernel (tests reach both with every dtype).
-    const char* e = getenv("TOME_K1_FULL_CLUSTER");
-    int cluster = 0, chunks_per_cta = 0;
-    int32_t chunk_bytes = 0;
-    const int64_t bulk_bytes = (p_in.vocab * static_cast<int64_t>(sizeof(T))) & ~15ll;
-    const bool misses_l2 = 2 * static_cast<int64_t>(info.sm_count) * p_in.vocab *
-                               static_cast<int64_t>(sizeof(T)) > (100ll << 20);
-    const bool want = (e != nullptr) ? (atoi(e) != 0) : (sizeof(T) == 4 && misses_l2);
-    if (bulk_ok && want && bulk_bytes >= 16 &&
-        kf_plan(bulk_bytes, &cluster, &chunks_per_cta, &chunk_bytes))
-      return k1_launch_full_cluster<T>(p_in, cluster, chunks_per_cta, chunk_bytes, info.sm_count,
-                                       stream);
+    // long fp32 rows: the cluster-resident kernel (k1_full.cu)
+    bool taken = false;
+    st = k1_full_resident_launch(p_in, dtype, bulk_ok, info.sm_count, stream, &taken);
+    if (taken || st != TOME_OK) return st;
   }
   if (bulk_ok) {
     // equal-sized bulk copies: a row is cut into the fewest chunks that fit a stage
