@@ -4,15 +4,26 @@ Nothing in the product imports this file.  Only ``tests/``, ``__graft_entry__.sm
 the CPU-baseline / reference legs of ``bench.py`` use it, and only as the checker or as the
 timed CPU baseline.
 
-PARITY UNPINNED.  The reference computes this path with MLX (``mlx>=0.30.6``, unpinned in
-the reference's pyproject.toml and not vendored), which is not installed here and cannot be
-installed offline; its Metal kernel cannot run on Linux at all.  The reference holds no
-golden vectors or known-answer tests for the path (its only numeric test,
-mlx-impl/tests/test_logprob_comparison.py:84-102, draws unseeded random logits and compares
-against ``logits - mx.logsumexp(logits)`` within 5e-3).  This oracle is therefore pinned to
-the reference by FORMULA only; it is cross-checked against float64 and against
-``torch.log_softmax`` in tests/test_oracle.py, and the committed fixtures under
-tests/golden/ were produced by this file (tests/golden/make_golden.py).
+PARITY.  Pinned for the full-matrix kernel and the policy call site, unpinned for the rest:
+
+* ``log_softmax_metal_order`` (mlx-impl/model.py:14-89) and, through it, the policy call site
+  ``fused_log_softmax(...)[b, token]`` (mlx-impl/node.py:590, 605) are pinned to OUTPUTS OF THE
+  REFERENCE'S OWN KERNEL: oracle/build_ref.py compiles the reference's Metal kernel body,
+  unmodified and from where it lies in the reference checkout, around a CPU emulation of the
+  Metal execution model (oracle/metal_emulation.cpp); tests/golden/metal_kernel.npz holds what
+  it computes (tests/golden/make_metal_golden.py), and tests/test_metal_reference.py holds this
+  file against it (fp32: within 4e-6, bf16: bit-exact on the fixture).  Not the reference's in
+  that run: Apple's fast::exp / fast::log are libm's, simdgroup sums add in butterfly order.
+* PARITY UNPINNED for ``local_compute_logprobs`` (node.py:400-404) and everything built on it:
+  the reference computes those with MLX array ops (``mlx>=0.30.6``, unpinned in the
+  reference's pyproject.toml and not vendored), MLX is not installed here and cannot be
+  installed offline, and the reference holds no golden vectors or known-answer tests for the
+  path (its only numeric test, mlx-impl/tests/test_logprob_comparison.py:84-102, draws unseeded
+  random logits and compares against ``logits - mx.logsumexp(logits)`` within 5e-3).  Those
+  functions are pinned by FORMULA only, cross-checked against float64 and
+  ``torch.log_softmax`` in tests/test_oracle.py and against the pinned function above (the two
+  differ by one rounding: division by T against multiplication by 1/T); the other fixtures
+  under tests/golden/ were produced by this file (tests/golden/make_golden.py).
 
 Each function names the reference lines it follows.
 """

@@ -7,7 +7,8 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import TOL, from_bits, load_golden, max_abs
+from helpers import (METAL_CASES, TOL, from_bits, load_golden, max_abs, metal_case_inputs,
+                     metal_case_view)
 from oracle import oracle
 
 pytestmark = pytest.mark.gpu
@@ -502,3 +503,25 @@ def test_full_cluster_resident_sizes(cuda_device, monkeypatch, dtype, vocab):
     assert torch.equal(torch.isfinite(out.float()).cpu(), finite)
     assert max_abs(out.float().cpu()[finite], ref.float()[finite]) <= tol
     tome_b200.check_device_status(cuda_device)
+
+
+@pytest.mark.parametrize("case_no", range(len(METAL_CASES)))
+def test_against_outputs_of_the_reference_metal_kernel(cuda_device, case_no):
+    """tests/golden/metal_kernel.npz: what the reference's own kernel body computes for these
+    inputs (run on the CPU under an emulation of the Metal execution model)."""
+    import tome_b200
+    golden = load_golden("metal_kernel.npz")
+    dtype_name, rows, vocab, temp = METAL_CASES[case_no]
+    dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype_name]
+    logits, targets = metal_case_inputs(dtype_name, rows, vocab, case_no)
+    want = from_bits(golden[f"out_{case_no}"], dtype)
+    got = metal_case_view(tome_b200.fused_log_softmax(logits.to(cuda_device), temp).cpu(), vocab)
+    if dtype == torch.float32:
+        assert max_abs(got, want) <= 1e-4
+        # the policy call site gathers the kernel's output at the sampled token
+        lp = tome_b200.fused_log_softmax(logits.to(cuda_device), temp,
+                                         targets=targets.to(cuda_device), check=True)
+        assert max_abs(lp, torch.from_numpy(golden[f"at_target_{case_no}"].copy())) <= 1e-4
+    else:
+        assert max_abs(got.float(), want.float()) <= 0.0625 + 1e-6      # one bf16 ulp near -12
+        assert float((got == want).float().mean()) >= 0.99
