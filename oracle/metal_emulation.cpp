@@ -222,7 +222,51 @@ int run(const T* logits, float temperature, T* out, int rows, int V) {
   return 0;
 }
 
+// ---------------------------------------------------------------- paged KV gather
+// mlx-impl/paged_kv.py:57-116: a Metal body assembled as a Python f-string; build_ref.py
+// replaces its `{B}`-style fields by the `_arg` parameters below and its `{{ }}` by braces.
+// One thread per output element, no barriers, so the grid is walked with plain loops.
+template <typename T>
+void gather_body(const int32_t* block_tables, const int32_t* offsets, const T* k_pool,
+                 const T* v_pool, T* k_out, T* v_out, const uint max_seq_len,
+                 const uint3 thread_position_in_grid, const uint B_arg, const uint H_arg,
+                 const uint D_arg, const uint block_size_arg, const uint max_blocks_arg) {
+#include "gather_paged_kv_body.inc"
+}
+
+template <typename T>
+void gather_run(const int32_t* block_tables, const int32_t* offsets, const T* k_pool,
+                const T* v_pool, T* k_out, T* v_out, uint B, uint H, uint D, uint block_size,
+                uint max_blocks, uint max_seq_len) {
+  for (uint x = 0; x < B; ++x)  // grid=(B, H, max_seq_len * D), paged_kv.py:110
+    for (uint y = 0; y < H; ++y)
+      for (uint z = 0; z < max_seq_len * D; ++z)
+        gather_body<T>(block_tables, offsets, k_pool, v_pool, k_out, v_out, max_seq_len,
+                       uint3{x, y, z}, B, H, D, block_size, max_blocks);
+}
+
 }  // namespace
+
+// Pools [num_blocks, H, block_size, D], outputs [B, H, max_seq_len, D]; elem_bytes 2 or 4 (the
+// kernel only copies, so elements travel as integers of their width).
+extern "C" int metal_gather_paged_kv(const int32_t* block_tables, const int32_t* offsets,
+                                     const void* k_pool, const void* v_pool, void* k_out,
+                                     void* v_out, int elem_bytes, int B, int H, int D,
+                                     int block_size, int max_blocks, int max_seq_len) {
+  if (elem_bytes == 2) {
+    gather_run<uint16_t>(block_tables, offsets, static_cast<const uint16_t*>(k_pool),
+                         static_cast<const uint16_t*>(v_pool), static_cast<uint16_t*>(k_out),
+                         static_cast<uint16_t*>(v_out), B, H, D, block_size, max_blocks, max_seq_len);
+    return 0;
+  }
+  if (elem_bytes == 4) {
+    gather_run<uint32_t>(block_tables, offsets, static_cast<const uint32_t*>(k_pool),
+                         static_cast<const uint32_t*>(v_pool), static_cast<uint32_t*>(k_out),
+                         static_cast<uint32_t*>(v_out), B, H, D, block_size, max_blocks, max_seq_len);
+    return 0;
+  }
+  return -1;
+}
 
 // logits / out: [rows, V] row-contiguous (ensure_row_contiguous=True, model.py:73).
 extern "C" int metal_fused_log_softmax_f32(const float* logits, float temperature, float* out,

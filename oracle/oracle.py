@@ -14,6 +14,7 @@ PARITY.  Pinned for the full-matrix kernel and the policy call site, unpinned fo
   it computes (tests/golden/make_metal_golden.py), and tests/test_metal_reference.py holds this
   file against it (fp32: within 4e-6, bf16: bit-exact on the fixture).  Not the reference's in
   that run: Apple's fast::exp / fast::log are libm's, simdgroup sums add in butterfly order.
+  ``gather_paged_kv`` is pinned the same way (mlx-impl/paged_kv.py:57-116, byte-exact).
 * PARITY UNPINNED for ``local_compute_logprobs`` (node.py:400-404) and everything built on it:
   the reference computes those with MLX array ops (``mlx>=0.30.6``, unpinned in the
   reference's pyproject.toml and not vendored), MLX is not installed here and cannot be

@@ -52,7 +52,7 @@ def run_reference_kernel(lib, logits: torch.Tensor, temp: float) -> torch.Tensor
     return t if logits.dtype == torch.float32 else t.view(torch.bfloat16)
 
 
-def main():
+def main():  # noqa: D103
     lib = load_reference_kernel()
     arrays = {}
     for n, (dtype_name, rows, vocab, temp) in enumerate(METAL_CASES):
@@ -67,8 +67,34 @@ def main():
             kept, at_target = kept.numpy(), at_target.numpy()
         arrays[f"out_{n}"] = kept
         arrays[f"at_target_{n}"] = at_target
+    arrays.update(paged_gather_case(lib))
     np.savez_compressed(os.path.join(HERE, "metal_kernel.npz"), **arrays)
-    print(f"wrote {len(METAL_CASES)} cases")
+    print(f"wrote {len(METAL_CASES)} log-softmax cases and the paged-KV gather case")
+
+
+def paged_gather_case(lib):
+    """mlx-impl/paged_kv.py:57-116 run on a small pool: sequences of length 0, mid-block, a
+    whole number of blocks and the full table; inputs are stored with the outputs."""
+    g = torch.Generator().manual_seed(20260)
+    B, H, D, bs, max_blocks, max_seq_len, num_blocks = 4, 2, 8, 4, 5, 20, 11
+    k_pool = torch.randint(0, 65536, (num_blocks, H, bs, D), generator=g, dtype=torch.int32)
+    v_pool = torch.randint(0, 65536, (num_blocks, H, bs, D), generator=g, dtype=torch.int32)
+    k_pool, v_pool = k_pool.numpy().astype(np.uint16), v_pool.numpy().astype(np.uint16)
+    tables = torch.randint(0, num_blocks, (B, max_blocks), generator=g, dtype=torch.int32).numpy()
+    offsets = np.array([0, 7, 12, 20], dtype=np.int32)
+    k_out = np.full((B, H, max_seq_len, D), 0xFFFF, dtype=np.uint16)
+    v_out = np.full_like(k_out, 0xFFFF)
+
+    def ptr(a):
+        return a.ctypes.data_as(ctypes.c_void_p)
+
+    rc = lib.metal_gather_paged_kv(ptr(tables), ptr(offsets), ptr(k_pool), ptr(v_pool), ptr(k_out),
+                                   ptr(v_out), 2, B, H, D, bs, max_blocks, max_seq_len)
+    if rc != 0:
+        raise RuntimeError("the emulated gather kernel failed")
+    return {"gather_k_pool": k_pool, "gather_v_pool": v_pool, "gather_tables": tables,
+            "gather_offsets": offsets, "gather_k_out": k_out, "gather_v_out": v_out,
+            "gather_max_seq_len": np.int32(max_seq_len)}
 
 
 if __name__ == "__main__":

@@ -80,3 +80,20 @@ def test_bad_table_entries_are_reported_not_followed(cuda_device):
     with pytest.raises(tome_b200.TomeArgumentError):                  # head_dim * 2 bytes % 16 != 0
         bad = torch.zeros((4, 1, 16, 4), dtype=torch.bfloat16, device=cuda_device)
         tome_b200.gather_paged_kv(tables.to(cuda_device), offsets.to(cuda_device), bad, bad, 8)
+
+
+def test_gather_against_output_of_the_reference_metal_kernel(cuda_device):
+    """tests/golden/metal_kernel.npz holds what the reference's own gather kernel body
+    (mlx-impl/paged_kv.py:57-116, compiled for the CPU by oracle/build_ref.py) produces."""
+    import tome_b200
+    from helpers import from_bits, load_golden
+    gold = load_golden("metal_kernel.npz")
+    as_bf16 = lambda name: from_bits(gold[name], torch.bfloat16)  # noqa: E731
+    k_out, v_out = tome_b200.gather_paged_kv(
+        torch.from_numpy(gold["gather_tables"].copy()).to(cuda_device),
+        torch.from_numpy(gold["gather_offsets"].copy()).to(cuda_device),
+        as_bf16("gather_k_pool").to(cuda_device), as_bf16("gather_v_pool").to(cuda_device),
+        int(gold["gather_max_seq_len"]))
+    tome_b200.check_device_status(cuda_device)
+    assert torch.equal(k_out.cpu().view(torch.int16), as_bf16("gather_k_out").view(torch.int16))
+    assert torch.equal(v_out.cpu().view(torch.int16), as_bf16("gather_v_out").view(torch.int16))

@@ -77,3 +77,14 @@ def test_the_built_reference_kernel_reproduces_the_fixture(golden):
         kept = metal_case_view(t, vocab)
         same = (kept == want) | (torch.isnan(kept.float()) & torch.isnan(want.float()))
         assert bool(same.all())
+
+
+def test_paged_gather_restatement_matches_the_reference_kernel(golden):
+    """mlx-impl/paged_kv.py:57-116 compiled for the CPU (same recipe) against the oracle's loop."""
+    as_bf16 = lambda a: from_bits(a, torch.bfloat16)  # noqa: E731
+    k_out, v_out = oracle.gather_paged_kv(
+        torch.from_numpy(golden["gather_tables"].copy()), torch.from_numpy(golden["gather_offsets"].copy()),
+        as_bf16(golden["gather_k_pool"]), as_bf16(golden["gather_v_pool"]),
+        int(golden["gather_max_seq_len"]))
+    assert torch.equal(k_out.view(torch.int16), as_bf16(golden["gather_k_out"]).view(torch.int16))
+    assert torch.equal(v_out.view(torch.int16), as_bf16(golden["gather_v_out"]).view(torch.int16))
