@@ -6,7 +6,10 @@ gather kernel's f-string), writes them to scratch files under ``oracle/_ref/`` a
 of the reference is stored in this repository: ``oracle/_ref/`` is git-ignored, and the scratch
 copies of the bodies are deleted once the library is linked.
 
-    python oracle/build_ref.py [path/to/reference]        (default: $TOME_REFERENCE or /root/reference)
+    python oracle/build_ref.py [path/to/reference]
+
+Without an argument the checkout is looked for in $TOME_REFERENCE, then in a directory named
+``reference`` beside this repository.
 """
 from __future__ import annotations
 
@@ -47,7 +50,8 @@ def extract_gather_body(reference_root: str) -> str:
 
 def build(reference_root: str | None = None) -> str | None:
     """Returns the library path, or None when no reference checkout is available."""
-    root = reference_root or os.environ.get("TOME_REFERENCE", "/root/reference")
+    beside = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    root = reference_root or os.environ.get("TOME_REFERENCE", beside)
     if not os.path.isdir(os.path.join(root, "mlx-impl")):
         return None
     os.makedirs(OUT_DIR, exist_ok=True)
