@@ -483,14 +483,18 @@ def test_full_every_cluster_size(cuda_device, monkeypatch, split, dtype):
     assert out.shape == ref.shape and max_abs(out.float(), ref.float()) <= tol
 
 
+@pytest.mark.parametrize("form", ["1", "s1", "s2", "s4", "s8"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("vocab", [8, 24, 7000, 7680 * 6, 7680 * 6 + 8, 151936, 151936 + 4, 300000])
-def test_full_cluster_resident_sizes(cuda_device, monkeypatch, dtype, vocab):
-    """Row lengths around every cluster size of the resident kernel (1, 2, 4, 8 CTAs per row,
-    and beyond what 8 can hold), more rows than clusters so that slots are reused."""
+def test_full_cluster_kernel_sizes(cuda_device, monkeypatch, small_batch_path, form, dtype, vocab):
+    """Row lengths around every cluster size of the resident form (1, 2, 4, 8 CTAs per row, and
+    beyond what 8 can hold) and the streamed form with every cluster size; more rows than
+    clusters so that ring slots are reused."""
     import tome_b200
+    if small_batch_path != "small_batches_split":
+        pytest.skip("the environment is set by this test: one run is enough")
     monkeypatch.setenv("TOME_K1_SPLIT", "0")
-    monkeypatch.setenv("TOME_K1_FULL_CLUSTER", "1")
+    monkeypatch.setenv("TOME_K1_FULL_CLUSTER", form)
     rows = 700 if vocab <= 7000 else (330 if vocab < 100000 else 160)
     x, _ = _case(rows, vocab, dtype, seed=31 + vocab % 83, scale=1.0)
     x[3, : vocab // 2] = float("-inf")          # a part of a row without a finite logit

@@ -267,9 +267,9 @@ __device__ __noinline__ void exact_row(const T* src, int64_t vocab, float c, int
 int32_t k1_small_batch_launch(const K1Params& p, int32_t dtype, int mode, cudaStream_t stream,
                               bool* taken);
 
-// Full matrix with the row resident in a cluster's shared memory (k1_full.cu): same contract.
+// Full matrix with each row shared by a cluster of CTAs (k1_full.cu): same contract.
 // bulk_ok: logits and output meet the bulk-copy alignment rules.
-int32_t k1_full_resident_launch(const K1Params& p, int32_t dtype, bool bulk_ok, int sm_count,
+int32_t k1_full_cluster_launch(const K1Params& p, int32_t dtype, bool bulk_ok, int sm_count,
                                 cudaStream_t stream, bool* taken);
 
 }  // namespace tome

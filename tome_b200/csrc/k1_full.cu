@@ -1,22 +1,26 @@
-// K1, full-matrix mode for rows too long for L2: the row stays resident in the shared memory
-// of a cluster of CTAs between the two passes.
+// K1, full-matrix mode for rows of more than ~100 KB: a cluster of CTAs shares each row, so
+// that few enough rows are in flight for the second pass to be served by L2 (streamed form),
+// or the row stays in the cluster's shared memory between the passes (resident form).
 #include "k1_common.cuh"
 
 namespace tome {
 
 // ------------------------------------------------------------------ full matrix, large batches
 // The two-pass FULL mode of the pipeline kernel re-reads each row from L2, which holds only as
-// long as the rows in flight fit there (fp32 rows of an LM vocabulary do not: measured DRAM
-// traffic was 3 units per 2 algorithmic).  Here a row never leaves the SMs between the passes:
-// a cluster of C CTAs shares it, each CTA's part stays RESIDENT in its shared-memory ring.
-//   pass 1: the consumers fold the chunks into (m, s) as they land, without releasing them;
+// long as the rows in flight (two per SM) fit there; fp32 rows of an LM vocabulary do not
+// (measured DRAM traffic: 3 units per 2 algorithmic), bf16 rows barely.  Here a cluster of C
+// CTAs shares a row, which divides the rows in flight by C:
+//   pass 1: the consumers fold the chunks of their CTA's part into (m, s) as they land;
 //   exchange: each CTA sends its pair to the others (st.shared::cluster + mbarrier arrive with
 //             release.cluster), waits for theirs (acquire.cluster), every CTA computes the lse;
-//   pass 2: the consumers turn the resident chunks into outputs, store them (streaming
-//           stores) and only now release each slot, which the producer refills with the
-//           next row's chunk: loads of row r+1 overlap the stores of row r.
-// DRAM traffic: the row once in, once out.  Two CTAs per SM so one can compute while the other
-// waits for its exchange.
+//   pass 2: the consumers turn the chunks into outputs and store them (streaming stores).
+// Streamed form (default): the ring is an ordinary pipeline, the producer fetches every chunk
+// once per pass and the second fetch comes from L2.  Resident form: the part fits the ring,
+// pass 1 does not release its slots and pass 2 reads them again from shared memory, releasing
+// each slot once it is written out, so the row crosses the memory system exactly once.  The
+// resident form measured slower than the streamed one (its clusters are larger, so the
+// exchange is paid on smaller parts) and is kept as an option.
+// Two CTAs per SM so that one computes while the other waits for its exchange.
 #ifndef KF_CFG_WARPS
 #define KF_CFG_WARPS 8
 #endif
@@ -54,7 +58,8 @@ struct KFSmem {
 
 template <typename T>
 __global__ void __launch_bounds__(KF_THREADS, KF_CTAS_PER_SM)
-k1_full_cluster_kernel(const K1Params p, const int cluster, const int chunks_per_cta) {
+k1_full_cluster_kernel(const K1Params p, const int cluster, const int chunks_per_cta,
+                       const int resident) {
   extern __shared__ __align__(1024) uint8_t smem[];
   constexpr int ES = sizeof(T);
   const uint32_t smem_base = smem_u32(smem);
@@ -101,20 +106,27 @@ k1_full_cluster_kernel(const K1Params p, const int cluster, const int chunks_per
       for (int64_t row = first_row; row < p.n_rows && ok; row += n_clusters) {
         const uint8_t* src = reinterpret_cast<const uint8_t*>(p.src[0]) + row * p.stride * ES +
                              part_begin;
-        for (int k = 0; k < my_chunks; ++k, ++it) {
-          const uint32_t slot = it % KF_SLOTS;
-          const uint32_t phase = (it / KF_SLOTS) & 1u;
-          if (!mbar_wait(empty_bar + slot * 8, phase ^ 1u)) {
-            raise_status(p.status, TOME_DEV_TIMEOUT);
-            ok = false;
-            break;
+        // resident: every chunk is fetched once; streamed: once per pass, the second time
+        // (served by L2) marked as the last use
+        for (int pass = 0; pass < (resident ? 1 : 2) && ok; ++pass) {
+          for (int k = 0; k < my_chunks; ++k, ++it) {
+            const uint32_t slot = it % KF_SLOTS;
+            const uint32_t phase = (it / KF_SLOTS) & 1u;
+            if (!mbar_wait(empty_bar + slot * 8, phase ^ 1u)) {
+              raise_status(p.status, TOME_DEV_TIMEOUT);
+              ok = false;
+              break;
+            }
+            const int64_t off = k * chunk_bytes;
+            const uint32_t bytes =
+                static_cast<uint32_t>(min(chunk_bytes, bulk_bytes - part_begin - off));
+            mbar_arrive_expect_tx(full_bar + slot * 8, bytes);
+            if (resident || pass == 1)
+              bulk_g2s_hint(smem_base + slot * KF_CHUNK_BYTES, src + off, bytes,
+                            full_bar + slot * 8, policy);
+            else
+              bulk_g2s(smem_base + slot * KF_CHUNK_BYTES, src + off, bytes, full_bar + slot * 8);
           }
-          const int64_t off = k * chunk_bytes;
-          const uint32_t bytes =
-              static_cast<uint32_t>(min(chunk_bytes, bulk_bytes - part_begin - off));
-          mbar_arrive_expect_tx(full_bar + slot * 8, bytes);
-          bulk_g2s_hint(smem_base + slot * KF_CHUNK_BYTES, src + off, bytes, full_bar + slot * 8,
-                        policy);
         }
       }
     }
@@ -150,7 +162,12 @@ k1_full_cluster_kernel(const K1Params p, const int cluster, const int chunks_per
 #pragma unroll 4
       for (uint32_t v = ctid; v < nvec; v += KF_CONSUMERS)
         fast_update<0>(fs, lds128(sbase + v * 16), p.c, T());
+      if (!resident) {  // streamed: the slot is refilled for the second pass
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar + slot * 8);
+      }
     }
+    if (!resident) it += static_cast<uint32_t>(my_chunks);  // the second pass has chunks of its own
     Online st = fast_finish(fs, p.c);
     if (owns_tail && ctid == 0)
       for (int64_t j = tail_begin; j < p.vocab; ++j) online_update_scalar(st, to_float(src[j]), p.c);
@@ -196,6 +213,10 @@ k1_full_cluster_kernel(const K1Params p, const int cluster, const int chunks_per
     // ---- pass 2: outputs from the resident chunks; a slot is released once it is written out
     for (int k = 0; k < my_chunks; ++k, ++it) {
       const uint32_t slot = it % KF_SLOTS;
+      if (!resident && !dead && !mbar_wait(full_bar + slot * 8, (it / KF_SLOTS) & 1u)) {
+        raise_status(p.status, TOME_DEV_TIMEOUT);
+        dead = true;
+      }
       const int64_t off = part_begin + k * chunk_bytes;
       const uint32_t bytes = static_cast<uint32_t>(min(chunk_bytes, bulk_bytes - off));
       const uint32_t nvec = dead ? 0u : (bytes >> 4);
@@ -234,9 +255,27 @@ static bool kf_plan(int64_t bulk_bytes, int* cluster, int* chunks_per_cta, int32
   return false;
 }
 
+// Chunking for a cluster of `cluster` CTAs that streams its parts twice (no residency limit).
+static void kf_plan_streamed(int64_t bulk_bytes, int cluster, int* chunks_per_cta,
+                             int32_t* chunk_bytes) {
+  const int64_t per_cta = (bulk_bytes + cluster - 1) / cluster;
+  const int64_t n = std::max<int64_t>(1, (per_cta + KF_CHUNK_BYTES - 1) / KF_CHUNK_BYTES);
+  const int64_t total = n * cluster;
+  const int64_t al = K1_CHUNK_ALIGN;
+  int64_t cb = std::max<int64_t>(al, ((bulk_bytes + total - 1) / total + al - 1) / al * al);
+  int64_t chunks = n;
+  if (cb > KF_CHUNK_BYTES) {  // rounding pushed a chunk over the slot size: one more chunk
+    chunks = n + 1;
+    cb = std::max<int64_t>(al, ((bulk_bytes + chunks * cluster - 1) / (chunks * cluster) + al - 1) / al * al);
+  }
+  *chunks_per_cta = static_cast<int>(chunks);
+  *chunk_bytes = static_cast<int32_t>(std::min<int64_t>(cb, KF_CHUNK_BYTES));
+}
+
 template <typename T>
 static int32_t k1_launch_full_cluster(const K1Params& p_in, int cluster, int chunks_per_cta,
-                                      int32_t chunk_bytes, int sm_count, cudaStream_t stream) {
+                                      int32_t chunk_bytes, bool keep_resident, int sm_count,
+                                      cudaStream_t stream) {
   K1Params p = p_in;
   p.chunk_bytes = chunk_bytes;
   auto kernel = k1_full_cluster_kernel<T>;
@@ -260,33 +299,50 @@ static int32_t k1_launch_full_cluster(const K1Params& p_in, int cluster, int chu
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  return check_cuda(cudaLaunchKernelEx(&cfg, kernel, p, cluster, chunks_per_cta),
+  return check_cuda(cudaLaunchKernelEx(&cfg, kernel, p, cluster, chunks_per_cta,
+                                       keep_resident ? 1 : 0),
                     "k1 full cluster launch");
 }
 
-int32_t k1_full_resident_launch(const K1Params& p, int32_t dtype, bool bulk_ok, int sm_count,
-                                cudaStream_t stream, bool* taken) {
+int32_t k1_full_cluster_launch(const K1Params& p, int32_t dtype, bool bulk_ok, int sm_count,
+                               cudaStream_t stream, bool* taken) {
   *taken = false;
-  // The cluster-resident kernel pays an exchange per row; it wins where the pipeline kernel's
-  // second pass would miss L2, i.e. when the rows in flight there (two per SM) exceed ~100 MB,
-  // and only for fp32 (measured at V = 128256 / 151936: fp32 4.6 / 4.5 -> 5.1 / 5.6 TB/s,
-  // bf16 5.1 / 5.0 -> 4.4 / 4.9).  TOME_K1_FULL_CLUSTER=0 / 1 forces the pipeline / the
-  // resident kernel (tests reach both with every dtype).
+  // The pipeline kernel keeps two rows per SM in flight and its second pass is served by L2
+  // only while those rows fit there; sharing a row among the CTAs of a cluster divides the
+  // rows in flight by the cluster size at the price of one exchange per row.  Measured
+  // (read + write, GB/s; pipeline / best cluster form): 128 KB rows 5350 / 5550 (1 CTA),
+  // 262 KB 5380 / 5790 (2), 304 KB bf16 4990 / 5110 (2), 513 KB 4590 / 5750 (4), 608 KB fp32
+  // 4530 / 5720 (4), 1 MB 4300 / 5700 (8); rows of 64 KB and less are better off in the
+  // pipeline kernel.  Default: streamed form, the smallest cluster whose CTAs get at most
+  // 160 KB (fp32) or 200 KB (bf16) of a row.  TOME_K1_FULL_CLUSTER forces a form: 0 = pipeline
+  // kernel, 1 = resident, s1 / s2 / s4 / s8 = streamed by clusters of that size (tests reach
+  // all of them).
   const int64_t es = (dtype == TOME_F32) ? 4 : 2;
   const char* e = getenv("TOME_K1_FULL_CLUSTER");
   int cluster = 0, chunks_per_cta = 0;
   int32_t chunk_bytes = 0;
   const int64_t bulk_bytes = (p.vocab * es) & ~15ll;
-  const bool misses_l2 = 2 * static_cast<int64_t>(sm_count) * p.vocab * es > (100ll << 20);
-  const bool want = (e != nullptr) ? (atoi(e) != 0) : (es == 4 && misses_l2);
-  if (!(bulk_ok && want && bulk_bytes >= 16 &&
-        kf_plan(bulk_bytes, &cluster, &chunks_per_cta, &chunk_bytes)))
-    return TOME_OK;
+  if (!bulk_ok || bulk_bytes < 16) return TOME_OK;
+  bool keep_resident = false;
+  if (e != nullptr && e[0] == 's') {
+    cluster = atoi(e + 1);
+    if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return TOME_OK;
+  } else if (e != nullptr) {
+    if (atoi(e) == 0 || !kf_plan(bulk_bytes, &cluster, &chunks_per_cta, &chunk_bytes)) return TOME_OK;
+    keep_resident = true;
+  } else {
+    if (bulk_bytes <= 100 * 1024) return TOME_OK;
+    const int64_t per_cta = (es == 4 ? 160 : 200) * 1024;
+    cluster = 1;
+    while (cluster < KF_MAX_CLUSTER && bulk_bytes > per_cta * cluster) cluster <<= 1;
+  }
+  if (!keep_resident) kf_plan_streamed(bulk_bytes, cluster, &chunks_per_cta, &chunk_bytes);
   *taken = true;
   if (dtype == TOME_F32)
-    return k1_launch_full_cluster<float>(p, cluster, chunks_per_cta, chunk_bytes, sm_count, stream);
-  return k1_launch_full_cluster<__nv_bfloat16>(p, cluster, chunks_per_cta, chunk_bytes, sm_count,
-                                               stream);
+    return k1_launch_full_cluster<float>(p, cluster, chunks_per_cta, chunk_bytes, keep_resident,
+                                         sm_count, stream);
+  return k1_launch_full_cluster<__nv_bfloat16>(p, cluster, chunks_per_cta, chunk_bytes,
+                                               keep_resident, sm_count, stream);
 }
 
 }  // namespace tome

@@ -539,9 +539,9 @@ static int32_t k1_launch_typed(const K1Params& p_in, bool bulk_ok, int64_t max_i
     if (taken || st != TOME_OK) return st;
   }
   if constexpr (MODE == K1_FULL) {
-    // long fp32 rows: the cluster-resident kernel (k1_full.cu)
+    // rows of more than ~100 KB: a cluster of CTAs shares each row (k1_full.cu)
     bool taken = false;
-    st = k1_full_resident_launch(p_in, dtype, bulk_ok, info.sm_count, stream, &taken);
+    st = k1_full_cluster_launch(p_in, dtype, bulk_ok, info.sm_count, stream, &taken);
     if (taken || st != TOME_OK) return st;
   }
   if (bulk_ok) {

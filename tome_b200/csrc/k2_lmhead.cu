@@ -508,7 +508,36 @@ static int64_t k2_makespan(int32_t m_tiles, int32_t n_tiles, int32_t nb, int32_t
 // Work decomposition for one problem size.  item_rows: rows of a work item's row tile (128
 // single-CTA, 256 CTA pair).  The number of bands, hence the workspace size, must not depend
 // on the device or on item_rows, so it is planned for 148 workers of 128-row tiles.
+static K2Plan k2_plan_uncached(int64_t rows, int64_t k, int64_t vocab_local, int item_rows);
+
+// The band search costs tens of microseconds of host time; callers come back with the same
+// few shapes, so the last plans are kept (thread-safe, a handful of entries).
 static K2Plan k2_plan(int64_t rows, int64_t k, int64_t vocab_local, int item_rows = K2_BM) {
+  struct Entry {
+    int64_t rows, k, vocab;
+    int item_rows;
+    K2Plan plan;
+  };
+  constexpr int SLOTS = 16;
+  static std::mutex mu;
+  static Entry cache[SLOTS];
+  static int used = 0, next = 0;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < used; ++i)
+      if (cache[i].rows == rows && cache[i].k == k && cache[i].vocab == vocab_local &&
+          cache[i].item_rows == item_rows)
+        return cache[i].plan;
+  }
+  const K2Plan pl = k2_plan_uncached(rows, k, vocab_local, item_rows);
+  std::lock_guard<std::mutex> lock(mu);
+  cache[next] = Entry{rows, k, vocab_local, item_rows, pl};
+  next = (next + 1) % SLOTS;
+  used = std::min(used + 1, SLOTS);
+  return pl;
+}
+
+static K2Plan k2_plan_uncached(int64_t rows, int64_t k, int64_t vocab_local, int item_rows) {
   K2Plan pl;
   pl.n_tiles = static_cast<int32_t>((vocab_local + K2_BN - 1) / K2_BN);
   pl.k_blocks = static_cast<int32_t>((k + K2_BK - 1) / K2_BK);
