@@ -462,6 +462,48 @@ def run_extra(args, device, rank, world, dist_on, barrier, peaks):
     del k_pool, v_pool, tables, k_dense, v_dense
     torch.cuda.empty_cache()
 
+    # full-matrix compatibility kernel: the reference's decode-loop shape (64 x V fp32) and a
+    # larger bf16 case; algorithmic bytes = read + write of the matrix
+    for name, rows_f, dt in (("full_fp32_64rows", 64, torch.float32),
+                             ("full_bf16_4096rows", 4096, torch.bfloat16)):
+        xf = (torch.randn((rows_f, VOCAB), device=device, dtype=torch.float32) * 2.0).to(dt)
+        of = torch.empty_like(xf)
+        ms_f, launch_f = timed(lambda: tome_b200.fused_log_softmax(xf, 1.0, out=of))
+        nbytes = 2 * rows_f * VOCAB * xf.element_size()
+        extra[name] = {"rows": rows_f, "ms": ms_f, "GBps": nbytes / launch_f / 1e6}
+        del xf, of
+    torch.cuda.empty_cache()
+
+    # one decode step of the reference's rollout (64 sequences x V fp32 logits, node.py:590-605)
+    # replayed from a CUDA graph, so the numbers are the kernels' own time without the host
+    # cost of the Python call: selective log-prob, sampling + log-prob, full matrix.  Single
+    # process only: a process group's watchdog thread must not meet a stream capture.
+    if not dist_on:
+        xd = torch.randn((64, VOCAB), device=device, dtype=torch.float32) * 3.0
+        idd = torch.randint(0, VOCAB, (64,), device=device, dtype=torch.int32)
+        calls = {"selective_us": lambda: tome_b200.local_compute_logprobs(xd, idd, 0.7),
+                 "sample_topk_us": lambda: tome_b200.sample_topk_logprob(xd, 0.7, 20, seed=7,
+                                                                         offset=1),
+                 "full_matrix_us": lambda: tome_b200.fused_log_softmax(xd, 0.7)}
+        step = {"shape": "64 x 151936 fp32", "how": "20 calls per CUDA graph, 20 replays"}
+        side = torch.cuda.Stream()
+        for key, call in calls.items():
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    call()
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(20):
+                        call()
+            torch.cuda.synchronize()
+            ms_g, _ = timed(graph.replay, k=20, w=3)
+            step[key] = ms_g / 20 * 1e3
+            del graph
+        extra["decode_step_64rows_graph"] = step
+        del xd, idd
+    torch.cuda.empty_cache()
+
     # cfg3: fused LM head + log-prob, Qwen3-0.6B head shape
     hidden, weight, ids = synthetic.cfg3_lm_head(16384, 1024, VOCAB, device)
     ws = torch.empty(tome_b200.lm_head_workspace_bytes(16384, 1024, VOCAB), dtype=torch.uint8,
@@ -495,48 +537,6 @@ def run_extra(args, device, rank, world, dist_on, barrier, peaks):
         extra["cfg3_lm_head"]["context_unfused_gemm_then_selective_ms"] = ms_unfused
         del logits_buf
     del hidden, weight, ids, ws
-    torch.cuda.empty_cache()
-
-    # full-matrix compatibility kernel: the reference's decode-loop shape (64 x V fp32) and a
-    # larger bf16 case; algorithmic bytes = read + write of the matrix
-    for name, rows_f, dt in (("full_fp32_64rows", 64, torch.float32),
-                             ("full_bf16_4096rows", 4096, torch.bfloat16)):
-        xf = (torch.randn((rows_f, VOCAB), device=device, dtype=torch.float32) * 2.0).to(dt)
-        ms_f, launch_f = timed(lambda: tome_b200.fused_log_softmax(xf, 1.0))
-        nbytes = 2 * rows_f * VOCAB * xf.element_size()
-        extra[name] = {"rows": rows_f, "ms": ms_f, "GBps": nbytes / launch_f / 1e6,
-                       "note": "includes torch's allocation of the output matrix"}
-        del xf
-    torch.cuda.empty_cache()
-
-    # one decode step of the reference's rollout (64 sequences x V fp32 logits, node.py:590-605)
-    # replayed from a CUDA graph, so the numbers are the kernels' own time without the host
-    # cost of the Python call: selective log-prob, sampling + log-prob, full matrix.  Single
-    # process only: a process group's watchdog thread must not meet a stream capture.
-    if not dist_on:
-        xd = torch.randn((64, VOCAB), device=device, dtype=torch.float32) * 3.0
-        idd = torch.randint(0, VOCAB, (64,), device=device, dtype=torch.int32)
-        calls = {"selective_us": lambda: tome_b200.local_compute_logprobs(xd, idd, 0.7),
-                 "sample_topk_us": lambda: tome_b200.sample_topk_logprob(xd, 0.7, 20, seed=7,
-                                                                         offset=1),
-                 "full_matrix_us": lambda: tome_b200.fused_log_softmax(xd, 0.7)}
-        step = {"shape": "64 x 151936 fp32", "how": "20 calls per CUDA graph, 20 replays"}
-        side = torch.cuda.Stream()
-        for key, call in calls.items():
-            with torch.cuda.stream(side):
-                for _ in range(3):
-                    call()
-                torch.cuda.synchronize()
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=side):
-                    for _ in range(20):
-                        call()
-            torch.cuda.synchronize()
-            ms_g, _ = timed(graph.replay, k=20, w=3)
-            step[key] = ms_g / 20 * 1e3
-            del graph
-        extra["decode_step_64rows_graph"] = step
-        del xd, idd
     torch.cuda.empty_cache()
 
     # cfg4: vocab-parallel head over the N ranks, strong scaling (total work fixed)

@@ -272,6 +272,18 @@ def test_full_log_softmax_matches_metal_order(cuda_device, dtype, shape):
             assert float(exact) > 0.99 or max_abs(out.float(), ref.float()) <= 0.0625 + 1e-6
 
 
+def test_full_log_softmax_into_a_given_buffer(cuda_device):
+    import tome_b200
+    x, _ = _case(5, 4097, torch.float32, 91, scale=1.0)
+    xd = x.to(cuda_device)
+    out = torch.full_like(xd, 7.0)
+    got = tome_b200.fused_log_softmax(xd, 0.7, out=out)
+    assert got.data_ptr() == out.data_ptr()
+    assert max_abs(out, oracle.log_softmax_metal_order(x, 0.7)) <= 1e-4
+    with pytest.raises(ValueError):
+        tome_b200.fused_log_softmax(xd, 0.7, out=out[:, :100])
+
+
 def test_full_log_softmax_reference_unit_test_shape(cuda_device):
     # mlx-impl/tests/test_logprob_comparison.py:84-102 with its 5e-3 tolerance
     import tome_b200

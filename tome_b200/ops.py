@@ -200,14 +200,16 @@ def local_compute_logprobs_host(logits_host: torch.Tensor, ids_host: torch.Tenso
 
 
 def fused_log_softmax(logits: torch.Tensor, temperature: float = 1.0, *,
-                      targets: Optional[torch.Tensor] = None, check: bool = False) -> torch.Tensor:
+                      targets: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                      check: bool = False) -> torch.Tensor:
     """Drop-in for ``fused_log_softmax`` of mlx-impl/model.py:77-89.
 
     Without ``targets`` it returns the full ``[..., V]`` log-softmax in the dtype of
     ``logits`` with the Metal kernel's order of operations (scale by ``1/temperature``, round
     to the dtype, subtract the rounded logsumexp).  With ``targets`` it returns only the fp32
     log-probs of those columns, which turns the call sites' ``lp[b, token]`` pattern
-    (mlx-impl/node.py:590-605) into one call that never writes the matrix.
+    (mlx-impl/node.py:590-605) into one call that never writes the matrix.  ``out`` (same shape
+    and dtype as ``logits``, contiguous) receives the matrix instead of a fresh allocation.
     """
     if targets is not None:
         return selective_log_softmax(logits, targets, temperature, check=check)
@@ -216,7 +218,11 @@ def fused_log_softmax(logits: torch.Tensor, temperature: float = 1.0, *,
     flat, stride = _rows_view(logits)
     rows, V = flat.shape
     device = flat.device
-    out = torch.empty((rows, V), dtype=flat.dtype, device=device)
+    if out is None:
+        out = torch.empty((rows, V), dtype=flat.dtype, device=device)
+    elif (out.shape != logits.shape or out.dtype != flat.dtype or out.device != device
+          or not out.is_contiguous()):
+        raise ValueError("out must be a contiguous tensor with the shape, dtype and device of logits")
     with _on(device):
         status = lib.tome_log_softmax_full(
             flat.data_ptr(), _dtype_code(flat), rows, V, stride, temperature, out.data_ptr(), V,
