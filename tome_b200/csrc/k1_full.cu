@@ -283,10 +283,11 @@ static int32_t k1_launch_full_cluster(const K1Params& p_in, int cluster, int chu
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KFSmem::TOTAL),
       "cudaFuncSetAttribute(full cluster)");
   if (st != TOME_OK) return st;
-  int resident = max_active_clusters(reinterpret_cast<const void*>(kernel), KF_THREADS,
-                                     KFSmem::TOTAL, cluster);
-  if (resident <= 0) resident = std::max(1, sm_count * KF_CTAS_PER_SM / cluster);
-  const int64_t n_clusters = std::max<int64_t>(1, std::min<int64_t>(resident, p.n_rows));
+  // persistent clusters: as many as the device holds at once
+  int fit = max_active_clusters(reinterpret_cast<const void*>(kernel), KF_THREADS, KFSmem::TOTAL,
+                                cluster);
+  if (fit <= 0) fit = std::max(1, sm_count * KF_CTAS_PER_SM / cluster);
+  const int64_t n_clusters = std::max<int64_t>(1, std::min<int64_t>(fit, p.n_rows));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(n_clusters * cluster), 1, 1);
   cfg.blockDim = dim3(KF_THREADS, 1, 1);
