@@ -25,10 +25,10 @@ namespace tome {
 #define KF_CFG_WARPS 8
 #endif
 #ifndef KF_CFG_SLOTS
-#define KF_CFG_SLOTS 7
+#define KF_CFG_SLOTS 4
 #endif
 #ifndef KF_CFG_CHUNK
-#define KF_CFG_CHUNK 15360
+#define KF_CFG_CHUNK 25600
 #endif
 #ifndef KF_CFG_CTAS_PER_SM
 #define KF_CFG_CTAS_PER_SM 2
@@ -314,8 +314,9 @@ int32_t k1_full_cluster_launch(const K1Params& p, int32_t dtype, bool bulk_ok, i
   // (read + write, GB/s; pipeline / best cluster form): 128 KB rows 5350 / 5550 (1 CTA),
   // 262 KB 5380 / 5790 (2), 304 KB bf16 4990 / 5110 (2), 513 KB 4590 / 5750 (4), 608 KB fp32
   // 4530 / 5720 (4), 1 MB 4300 / 5700 (8); rows of 64 KB and less are better off in the
-  // pipeline kernel.  Default: streamed form, the smallest cluster whose CTAs get at most
-  // 160 KB (fp32) or 200 KB (bf16) of a row.  TOME_K1_FULL_CLUSTER forces a form: 0 = pipeline
+  // pipeline kernel (the figures are of a 7 x 15 KB ring; the 4 x 25 KB ring in use now is
+  // a few per cent faster still).  Default: streamed form, the smallest cluster whose CTAs get at most
+  // 160 KB of a row.  TOME_K1_FULL_CLUSTER forces a form: 0 = pipeline
   // kernel, 1 = resident, s1 / s2 / s4 / s8 = streamed by clusters of that size (tests reach
   // all of them).
   const int64_t es = (dtype == TOME_F32) ? 4 : 2;
@@ -332,8 +333,8 @@ int32_t k1_full_cluster_launch(const K1Params& p, int32_t dtype, bool bulk_ok, i
     if (atoi(e) == 0 || !kf_plan(bulk_bytes, &cluster, &chunks_per_cta, &chunk_bytes)) return TOME_OK;
     keep_resident = true;
   } else {
-    if (bulk_bytes <= 100 * 1024) return TOME_OK;
-    const int64_t per_cta = (es == 4 ? 160 : 200) * 1024;
+    if (bulk_bytes <= 80 * 1024) return TOME_OK;
+    const int64_t per_cta = 160 * 1024;
     cluster = 1;
     while (cluster < KF_MAX_CLUSTER && bulk_bytes > per_cta * cluster) cluster <<= 1;
   }
