@@ -132,11 +132,13 @@ def test_unaligned_rows_and_extreme_k(cuda_device, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("vocab", [24, 600, 4096 + 8, 40000])
-def test_large_batches_take_the_streaming_path(cuda_device, dtype, vocab):
-    """From 1024 rows on, the batch goes through the TMA-pipelined kernel; rows it cannot
-    finish (sorted, constant or heavily tied ones overflow its small candidate ring) come back
-    marked and are redone by the one-CTA-per-row kernel.  Both must give the oracle's top-k."""
+def test_large_batches_take_the_streaming_path(cuda_device, monkeypatch, dtype, vocab):
+    """Large bf16 batches go through the TMA-pipelined kernel (forced here for fp32 too); rows
+    it cannot finish (sorted, constant or heavily tied ones overflow its small candidate ring)
+    come back marked and are redone by the one-CTA-per-row kernel.  Both must give the
+    oracle's top-k."""
     import tome_b200
+    monkeypatch.setenv("TOME_K4_STREAM", "1")
     rows = 1200
     x = _case(rows, vocab, dtype, 300 + vocab % 71)
     x[5] = torch.linspace(-8, 8, vocab).to(dtype)          # ascending: overflows the ring
@@ -160,7 +162,7 @@ def test_large_batches_take_the_streaming_path(cuda_device, dtype, vocab):
     assert max_abs(lp0, o_lp0) <= TOL[dtype]
 
 
-def test_streaming_path_draws_follow_the_topk_softmax(cuda_device):
+def test_streaming_path_draws_follow_the_topk_softmax(cuda_device, monkeypatch):
     import tome_b200
     g = torch.Generator().manual_seed(10)
     row = (torch.randn((1, 4096), generator=g) * 2.0).to(torch.bfloat16)
@@ -175,6 +177,9 @@ def test_streaming_path_draws_follow_the_topk_softmax(cuda_device):
     # the same draws as the one-CTA-per-row kernel makes for the same (seed, offset, row)
     tok_small, _ = tome_b200.sample_topk_logprob(x[:512], 0.8, 20, seed=99, offset=1)
     assert torch.equal(tok[:512], tok_small)
+    monkeypatch.setenv("TOME_K4_STREAM", "0")
+    tok_all, _ = tome_b200.sample_topk_logprob(x, 0.8, 20, seed=99, offset=1)
+    assert torch.equal(tok, tok_all)
 
 
 @pytest.mark.parametrize("split", ["2", "4", "8"])
