@@ -183,6 +183,22 @@ int32_t tome_sample_topk_logprob(const void* logits, int32_t dtype, int64_t rows
                                  int32_t* dev_status, void* stream);
 
 /*
+ * The same call with caller-owned scratch, which lets large batches take a three-kernel path
+ * whose pass over the logits is a plain streaming pass (per-row threshold, streaming pass
+ * that collects the candidates, rank + draw).  Same results as tome_sample_topk_logprob: the
+ * draw depends on the row's top-k only.  tome_sample_workspace_bytes returns the bytes that
+ * path needs for the batch, or 0 if the batch would not take it (then workspace may be NULL).
+ * workspace must be 16-byte aligned; its contents need no initialisation.
+ */
+size_t tome_sample_workspace_bytes(int64_t rows, int64_t vocab);
+int32_t tome_sample_topk_logprob_ws(const void* logits, int32_t dtype, int64_t rows,
+                                    int64_t vocab, int64_t row_stride, float temperature,
+                                    int32_t top_k, uint64_t seed, uint64_t offset,
+                                    int32_t* out_tokens, float* out_logprob,
+                                    int32_t* out_topk_idx, float* out_topk_val, void* workspace,
+                                    size_t ws_bytes, int32_t* dev_status, void* stream);
+
+/*
  * Fused LM head + selective log-prob: logits = hidden @ weight^T are formed tile by tile
  * on the tensor cores and reduced on the fly; no logits buffer exists.
  * Replaces "x @ embed_tokens.weight.T" (mlx-impl/model.py:538) followed by

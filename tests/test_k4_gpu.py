@@ -206,3 +206,30 @@ def test_split_rows_give_the_same_tokens_as_one_cta_per_row(cuda_device, monkeyp
         assert i1[r, : len(idx)].cpu().tolist() == idx.tolist()
     o_lp, _, _ = oracle.selective_logprob(x, t1.cpu(), 0.8)
     assert max_abs(lp1, o_lp) <= TOL[dtype]
+
+
+def test_workspace_entry_point_checks_its_scratch(cuda_device, monkeypatch):
+    """The scratch-taking entry point: size query, too-small and misaligned scratch are refused
+    before anything is launched, and without scratch the call still works (row kernel)."""
+    import tome_b200
+    from tome_b200 import _lib
+    lib = _lib.lib
+    rows, vocab = 400, 8192
+    assert lib.tome_sample_workspace_bytes(rows, vocab) > rows * 256 * 8
+    assert lib.tome_sample_workspace_bytes(8, vocab) == 0          # small batch: no scratch
+    assert lib.tome_sample_workspace_bytes(rows, 1000) == 0        # short rows: row kernel
+    x = _case(rows, vocab, torch.bfloat16, 77).to(cuda_device)
+    tok = torch.empty(rows, dtype=torch.int32, device=cuda_device)
+    lp = torch.empty(rows, dtype=torch.float32, device=cuda_device)
+    ws = torch.empty(4096, dtype=torch.uint8, device=cuda_device)
+    args = (x.data_ptr(), _lib.TOME_BF16, rows, vocab, vocab, 0.7, 20, 1, 2, tok.data_ptr(),
+            lp.data_ptr(), None, None)
+    assert lib.tome_sample_topk_logprob_ws(*args, ws.data_ptr(), 4096, None, None) == -6
+    need = lib.tome_sample_workspace_bytes(rows, vocab)
+    big = torch.empty(need + 16, dtype=torch.uint8, device=cuda_device)
+    assert lib.tome_sample_topk_logprob_ws(*args, big.data_ptr() + 4, need, None, None) == -2
+    assert lib.tome_sample_topk_logprob_ws(*args, None, 0, None, None) == 0
+    t_row = tok.clone()
+    assert lib.tome_sample_topk_logprob_ws(*args, big.data_ptr(), need, None, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(t_row, tok)

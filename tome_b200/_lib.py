@@ -41,6 +41,11 @@ SIGNATURES = {
     "tome_sample_topk_logprob": (c_int32, [c_void_p, c_int32, c_int64, c_int64, c_int64, c_float,
                                            c_int32, c_uint64, c_uint64, c_void_p, c_void_p,
                                            c_void_p, c_void_p, c_void_p, c_void_p]),
+    "tome_sample_workspace_bytes": (c_size_t, [c_int64, c_int64]),
+    "tome_sample_topk_logprob_ws": (c_int32, [c_void_p, c_int32, c_int64, c_int64, c_int64,
+                                              c_float, c_int32, c_uint64, c_uint64, c_void_p,
+                                              c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
+                                              c_void_p, c_void_p]),
     "tome_lmhead_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "tome_lmhead_partials": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                        c_void_p, c_float, c_int32, c_void_p, c_void_p, c_void_p,

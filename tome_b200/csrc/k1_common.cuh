@@ -77,12 +77,10 @@ struct K1Params {
   int32_t seq_len;         // DUAL
   int64_t packed_capacity; // RAGGED: entries the packed target/output arrays can hold
   int32_t* out_offsets;    // RAGGED: int32 [n_seq + 1], start of each sequence in the packed output
-  int32_t* out_tokens;     // SAMPLE: int32 [rows]; -1 marks a row left to the one-CTA-per-row kernel
-  int32_t* out_topk_idx;   // SAMPLE: nullable, [rows, top_k]
-  float* out_topk_val;     // SAMPLE: nullable, [rows, top_k]
-  uint64_t seed, offset;   // SAMPLE: random stream
-  int32_t top_k;           // SAMPLE: 1..64
-  int32_t greedy;          // SAMPLE: temperature 0 -> argmax, scored at temperature 1
+  const float* row_thr;    // SAMPLE: per-row value threshold
+  int32_t* cand_count;     // SAMPLE: per-row number of candidates appended (may exceed cand_cap)
+  unsigned long long* cand;  // SAMPLE: [rows, cand_cap] packed candidates (see sampling.cuh)
+  int32_t cand_cap;
   int32_t* status;         // nullable
   int32_t chunk_bytes;     // bulk-copy size (multiple of 16, <= K1_CHUNK_BYTES), set by launch
   int32_t n_chunks;        // bulk copies per row

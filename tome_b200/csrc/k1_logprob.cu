@@ -40,6 +40,15 @@ namespace tome {
 constexpr int K1_FULL_STAGES = K1_CFG_FULL_STAGES;
 __host__ __device__ constexpr int k1_stages(int mode) { return mode == K1_FULL ? K1_FULL_STAGES : K1_STAGES; }
 
+// SAMPLE mode: the row's candidates are gathered in shared memory (a global atomic per
+// candidate stalls its warp for a memory round trip: 312 us for 4096 bf16 rows against 190 us
+// in the selective mode) and copied out once per row.
+constexpr int K1_SAMPLE_LIST = 256;
+struct K1SampleSmem {
+  unsigned long long cand[K1_SAMPLE_LIST];
+  int32_t count[2];  // by row parity: the other one is reset while this one is read
+};
+
 template <int STAGES>
 struct K1SmemT {
   static constexpr int DATA = STAGES * K1_CHUNK_BYTES;
@@ -52,18 +61,6 @@ struct K1SmemT {
   static constexpr int SAMPLE_OFF = (CUM_OFF + 7) & ~7;                  // SAMPLE: K1SampleSmem
 };
 
-// SAMPLE mode: candidate ring and top-k of the row a CTA is working on.
-constexpr int K1_SAMPLE_CAP = 512;
-constexpr int K1_SAMPLE_SUBSET = 64;  // candidates used for the cheap pre-filter (>= top_k)
-constexpr int K1_SAMPLE_GROUPS = K1_CONSUMERS / 2;
-struct K1SampleSmem {
-  unsigned long long cand[K1_SAMPLE_CAP];
-  unsigned long long top[64];
-  unsigned long long thr;
-  uint32_t gkey[K1_SAMPLE_GROUPS];
-  int32_t count;
-};
-static_assert(K1_SAMPLE_GROUPS >= 64, "the threshold needs at least top_k (<= 64) groups");
 
 template <typename T, int MODE, int POLY>
 __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(const K1Params p) {
@@ -90,6 +87,11 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       mbar_init(empty_bar + i * 8, K1_CONSUMER_WARPS);
     }
     fence_mbar_init();
+    if (MODE == K1_SAMPLE) {
+      K1SampleSmem* smp0 = reinterpret_cast<K1SampleSmem*>(smem + Smem::SAMPLE_OFF);
+      smp0->count[0] = 0;
+      smp0->count[1] = 0;
+    }
   }
   int64_t n_items = p.n_rows;
   if (WINDOWED) {
@@ -179,55 +181,16 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       T* dst = nullptr;
       if (MODE == K1_FULL) dst = reinterpret_cast<T*>(p.out_full) + row * p.out_stride;
 
-      // SAMPLE: a value that at least top_k logits reach, from the row's first chunk: the
-      // top_k-th largest of 64 group maxima (2 adjacent threads per group).  Ties are kept.
+      // SAMPLE: logits that reach the row's threshold (found by an earlier kernel) are appended
+      // to the row's candidate list in global memory; a later kernel ranks them and draws.
       K1SampleSmem& smp = *reinterpret_cast<K1SampleSmem*>(smem + Smem::SAMPLE_OFF);
-      unsigned long long thr = 0ull;
-      float thr_val = __int_as_float(0xff800000);
-      const int32_t kk = static_cast<int32_t>(min(static_cast<int64_t>(p.top_k), p.vocab));
-      if (MODE == K1_SAMPLE) {
-        uint32_t nvec0 = 0;
-        float lmax = __int_as_float(0xff800000);
-        if (n_chunks > 0) {
-          const uint32_t stage = it % STAGES;
-          const uint32_t phase = (it / STAGES) & 1u;
-          if (!mbar_wait(full_bar + stage * 8, phase)) {
-            raise_status(p.status, TOME_DEV_TIMEOUT);
-            return;
-          }
-          nvec0 = static_cast<uint32_t>(min(chunk_bytes, bulk_bytes)) >> 4;
-          const uint32_t sbase = smem_base + stage * K1_CHUNK_BYTES;
-          for (uint32_t v = ctid; v < nvec0; v += K1_CONSUMERS)
-            lmax = fmaxf(lmax, vec_max(lds128(sbase + v * 16), T()));
-        }
-        lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, 1));
-        if ((ctid & 1) == 0) smp.gkey[ctid >> 1] = k4_key(lmax);
-        if (ctid == 0) {
-          smp.count = 0;
-          smp.thr = 0ull;
-        }
-        named_bar_sync(2, K1_CONSUMERS);
-        const int32_t full_groups =
-            static_cast<int32_t>(min(nvec0, static_cast<uint32_t>(K1_CONSUMERS))) / 2;
-        if (ctid < K1_SAMPLE_GROUPS && full_groups >= kk) {
-          const uint32_t mine = smp.gkey[ctid];
-          int32_t rank = 0;
-          for (int j = 0; j < K1_SAMPLE_GROUPS; ++j) {
-            const uint32_t o = smp.gkey[j];
-            rank += (o > mine || (o == mine && j < ctid)) ? 1 : 0;
-          }
-          if (rank == kk - 1) smp.thr = static_cast<unsigned long long>(mine) << 32;
-        }
-        named_bar_sync(2, K1_CONSUMERS);
-        thr = smp.thr;
-        if (thr != 0ull) thr_val = k4_value(thr);
-      }
-      // SAMPLE: the logits of a vector that reach the threshold join the candidate ring
+      int32_t* smp_count = &smp.count[red_it & 1u];
+      float thr_val = __int_as_float(0x7f800000);  // +inf: nothing qualifies
+      if (MODE == K1_SAMPLE) thr_val = p.row_thr[row];
       auto push = [&](float x, int64_t i) {
         if (x >= thr_val) {
-          const unsigned long long code = k4_pack(x, i);
-          if (code >= thr)
-            smp.cand[static_cast<uint32_t>(atomicAdd(&smp.count, 1)) % K1_SAMPLE_CAP] = code;
+          const int32_t slot = atomicAdd(smp_count, 1);
+          if (slot < K1_SAMPLE_LIST) smp.cand[slot] = k4_pack(x, i);
         }
       };
       auto collect = [&](uint4 q, int64_t i0) {
@@ -319,92 +282,24 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
           // the true maximum contributes 2^0, so a healthy row has s >= ~1
           if (!(s >= 0.5f && s <= FLT_MAX)) exact_row(src, p.vocab, p.c, lane, m, s);
           if (MODE == K1_FULL) lse_row = finish_lse<MODE>(m, s, p);
-          if (MODE == K1_SAMPLE) lse_row = finish_lse<MODE>(m, s, p);  // kept by warp 0
+          if (MODE == K1_SAMPLE && ctid == 0) p.out1[row] = finish_lse<MODE>(m, s, p);
           if (MODE != K1_SAMPLE && ctid == 0)
             emit_row<MODE>(p, oidx, sub, m, s, x_t, target_ok, carry);
         }
-        ++red_it;
         if (MODE == K1_SAMPLE) {
-          // every candidate of the row is in the ring (the barrier above followed the last chunk)
-          int32_t n = *reinterpret_cast<volatile int32_t*>(&smp.count);
-          const bool overflow = n > K1_SAMPLE_CAP;
-          constexpr int MINE = K1_SAMPLE_CAP / K1_CONSUMERS;
-          unsigned long long code[MINE];
-          if (!overflow) {
-#pragma unroll
-            for (int q = 0; q < MINE; ++q) {
-              const int32_t i = ctid + q * K1_CONSUMERS;
-              code[q] = (i < n) ? smp.cand[i] : 0ull;  // 0: below every real code
-            }
-          }
-          if (!overflow && n > 2 * K1_SAMPLE_SUBSET) {
-            // cheap filter first: the kk-th best of the first SUBSET candidates is a bound the
-            // final top-kk must reach; only the candidates that reach it are ranked in full
-            if (ctid < K1_SAMPLE_SUBSET) {
-              const unsigned long long mine = code[0];
-              int32_t r = 0;
-#pragma unroll 4
-              for (int32_t j = 0; j < K1_SAMPLE_SUBSET; ++j) r += (smp.cand[j] > mine) ? 1 : 0;
-              if (r == kk - 1) smp.thr = mine;
-            }
-            named_bar_sync(2, K1_CONSUMERS);
-            const unsigned long long thr2 = smp.thr;
-            if (ctid == 0) smp.count = 0;
-            named_bar_sync(2, K1_CONSUMERS);
-#pragma unroll
-            for (int q = 0; q < MINE; ++q) {
-              if (code[q] >= thr2 && code[q] != 0ull)
-                smp.cand[atomicAdd(&smp.count, 1)] = code[q];
-            }
-            named_bar_sync(2, K1_CONSUMERS);
-            n = *reinterpret_cast<volatile int32_t*>(&smp.count);
-#pragma unroll
-            for (int q = 0; q < MINE; ++q) {
-              const int32_t i = ctid + q * K1_CONSUMERS;
-              code[q] = (i < n) ? smp.cand[i] : 0ull;
-            }
-          }
-          if (!overflow) {
-            // each thread ranks its candidates in ONE pipelined pass over the list; codes are
-            // distinct, rank r goes to top[r]
-            int32_t rank[MINE];
-#pragma unroll
-            for (int q = 0; q < MINE; ++q) rank[q] = 0;
-#pragma unroll 4
-            for (int32_t j = 0; j < n; ++j) {
-              const unsigned long long o = smp.cand[j];
-#pragma unroll
-              for (int q = 0; q < MINE; ++q) rank[q] += (o > code[q]) ? 1 : 0;
-            }
-#pragma unroll
-            for (int q = 0; q < MINE; ++q)
-              if (ctid + q * K1_CONSUMERS < n && rank[q] < kk) smp.top[rank[q]] = code[q];
+          // every consumer has passed the barrier above, so the list is complete: copy it out,
+          // reset the other counter for the next row, and let nobody start that row before
+          const int32_t n = *reinterpret_cast<volatile int32_t*>(smp_count);
+          const int32_t keep = min(n, min(K1_SAMPLE_LIST, p.cand_cap));
+          for (int32_t i = ctid; i < keep; i += K1_CONSUMERS)
+            p.cand[row * p.cand_cap + i] = smp.cand[i];
+          if (ctid == 0) {
+            p.cand_count[row] = (n > keep) ? p.cand_cap + 1 : n;  // more than kept: overflow
+            smp.count[(red_it & 1u) ^ 1u] = 0;
           }
           named_bar_sync(2, K1_CONSUMERS);
-          if (overflow) {
-            // more candidates than the ring holds (sorted or heavily tied row): leave the row
-            // to the one-CTA-per-row kernel, which re-sweeps with tighter thresholds
-            if (ctid == 0) p.out_tokens[row] = -1;
-          } else {
-            if (ctid == 0) {
-              const int32_t pick = p.greedy ? 0 : k4_draw(smp.top, kk, p.c, row, p.seed, p.offset);
-              p.out_tokens[row] = k4_index(smp.top[pick]);
-              p.out0[row] = __fdiv_rn(k4_value(smp.top[pick]), p.temp) - lse_row;
-            }
-            if (p.out_topk_idx != nullptr || p.out_topk_val != nullptr) {
-              for (int32_t j = ctid; j < p.top_k; j += K1_CONSUMERS) {
-                const bool have = j < kk;
-                if (p.out_topk_idx != nullptr)
-                  p.out_topk_idx[row * p.top_k + j] = have ? k4_index(smp.top[j]) : -1;
-                if (p.out_topk_val != nullptr)
-                  p.out_topk_val[row * p.top_k + j] =
-                      have ? k4_value(smp.top[j]) : __int_as_float(0xff800000);
-              }
-            }
-          }
-          // top[] is next written several barriers from here, cand[]/count/thr after the next
-          // row's first barrier: nobody can overtake the readers above
         }
+        ++red_it;
       }
     }
   }
@@ -784,28 +679,22 @@ bool k1_sample_eligible(const void* logits, int32_t dtype, int64_t vocab, int64_
 }
 
 int32_t k1_launch_sample(const void* logits, int32_t dtype, int64_t rows, int64_t vocab,
-                         int64_t row_stride, float temperature, int32_t top_k, uint64_t seed,
-                         uint64_t offset, int32_t* out_tokens, float* out_logprob,
-                         int32_t* out_topk_idx, float* out_topk_val, int32_t* dev_status,
-                         cudaStream_t stream) {
-  const bool greedy = !(temperature > 0.0f);
-  const float temp = greedy ? 1.0f : temperature;
+                         int64_t row_stride, float temperature, const float* row_thr,
+                         int32_t* cand_count, unsigned long long* cand, int32_t cand_cap,
+                         float* out_lse, int32_t* dev_status, cudaStream_t stream) {
   K1Params p = {};
   p.src[0] = logits;
   p.n_rows = rows;
   p.vocab = vocab;
   p.stride = row_stride;
-  p.c = LOG2E / temp;
-  p.temp = temp;
-  p.inv_temp = 1.0f / temp;
-  p.out0 = out_logprob;
-  p.out_tokens = out_tokens;
-  p.out_topk_idx = out_topk_idx;
-  p.out_topk_val = out_topk_val;
-  p.seed = seed;
-  p.offset = offset;
-  p.top_k = top_k;
-  p.greedy = greedy ? 1 : 0;
+  p.c = LOG2E / temperature;
+  p.temp = temperature;
+  p.inv_temp = 1.0f / temperature;
+  p.out1 = out_lse;
+  p.row_thr = row_thr;
+  p.cand_count = cand_count;
+  p.cand = cand;
+  p.cand_cap = cand_cap;
   p.status = dev_status;
   return k1_launch<K1_SAMPLE>(p, dtype, true, rows, stream);
 }

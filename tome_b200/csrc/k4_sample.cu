@@ -1,6 +1,6 @@
 // K4: top-k temperature sampling fused with the sampled token's full-vocabulary log-prob.
 //
-// One CTA per row.  A single sweep over the row (128-bit loads, no barrier inside) keeps the
+// Base form (k4_sample_kernel): one CTA per row.  A single sweep over the row (128-bit loads, no barrier inside) keeps the
 // online (max, sum-exp) of the full vocabulary AND collects the candidates for the top-k: a
 // threshold derived from the first few thousand logits rejects almost everything with one
 // compare, the survivors (a few hundred for ordinary data) go to a shared-memory list, and an
@@ -40,7 +40,10 @@ constexpr int K4_SAMPLE = 32768;   // leading logits used to derive the first th
 constexpr int K4_GROUPS = K4_THREADS / 4;  // sample maxima kept for the threshold
 constexpr int K4_RANK_MAX = 1024;  // above this many candidates, compact before ranking
 constexpr int K4_MAX_SWEEPS = 64;   // re-sweeps with a tightened threshold before giving up
-constexpr int64_t K4_STREAM_MIN_ROWS = 1024;  // from here on the streaming kernel takes bf16 batches
+constexpr int64_t K4_STREAM_MIN_ROWS = 320;    // from here on a batch takes the three-kernel path
+constexpr int64_t K4_STREAM_MIN_VOCAB = 4096;  // its threshold kernel wants full groups
+constexpr int K4_LIST_CAP = 256;               // candidates kept per row on that path
+constexpr int K4_LIST_THREADS = 128;
 constexpr int K4_SPLIT_MAX = 8;               // CTAs of a cluster that may share one row
 constexpr int64_t K4_SPLIT_MIN_VOCAB = 16384; // shorter rows stay with one CTA
 
@@ -448,6 +451,129 @@ __global__ void __launch_bounds__(K4_THREADS, 2) k4_sample_split_kernel(const K4
   k4_finish_row(p, sm, row, kk_row, c, temp, greedy, lse);
 }
 
+// ------------------------------------------------------------------ large batches
+// Three kernels, so that the pass over the logits is a plain streaming pass:
+//   1. k4_threshold_kernel: per row, the kk-th largest of 128 group maxima over the leading
+//      K4_SAMPLE logits (a value that at least kk logits reach); zeroes the row's counter;
+//   2. the streaming kernel's SAMPLE mode (k1_logprob.cu): one pass at HBM speed that keeps
+//      (max, sum-exp) and appends the logits reaching the threshold to the row's list;
+//   3. k4_finish_kernel: ranks the row's list (exact top-kk), draws, scores, writes.
+// A row whose list overflowed (sorted or heavily tied rows) is marked with token -1 and redone
+// by k4_sample_kernel (only_flagged).  Same tokens as the other kernels of this file.
+template <typename T>
+__global__ void __launch_bounds__(K4_LIST_THREADS)
+k4_threshold_kernel(const T* logits, int64_t rows, int64_t vocab, int64_t stride, int32_t kk,
+                    float* row_thr, int32_t* cand_count) {
+  __shared__ uint32_t keys[K4_LIST_THREADS];
+  constexpr int PER = 16 / static_cast<int>(sizeof(T));
+  const int tid = threadIdx.x;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* vp = reinterpret_cast<const uint4*>(logits + row * stride);
+    const int64_t nvec = min(static_cast<int64_t>(K4_SAMPLE), vocab) / PER;  // >= K4_LIST_THREADS
+    float lmax = __int_as_float(0xff800000);
+#pragma unroll 8
+    for (int64_t v = tid; v < nvec; v += K4_LIST_THREADS) lmax = fmaxf(lmax, vec_max(__ldg(vp + v), T()));
+    keys[tid] = k4_key(lmax);
+    if (tid == 0) cand_count[row] = 0;
+    __syncthreads();
+    const uint32_t mine = keys[tid];
+    int32_t rank = 0;
+#pragma unroll 8
+    for (int j = 0; j < K4_LIST_THREADS; ++j) {
+      const uint32_t o = keys[j];
+      rank += (o > mine || (o == mine && j < tid)) ? 1 : 0;
+    }
+    if (rank == kk - 1) row_thr[row] = lmax;
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(K4_LIST_THREADS)
+k4_finish_kernel(const K4Params p, const float* lse, const int32_t* cand_count,
+                 const unsigned long long* cand) {
+  __shared__ unsigned long long list[K4_LIST_CAP];
+  __shared__ unsigned long long top[K4_MAX_K];
+  const int tid = threadIdx.x;
+  const bool greedy = !(p.temperature > 0.0f);
+  const float temp = greedy ? 1.0f : p.temperature;
+  const float c = LOG2E / temp;
+  const int32_t k = p.top_k;
+  const int32_t kk = static_cast<int32_t>(min(static_cast<int64_t>(k), p.vocab));
+  for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    const int32_t n = cand_count[row];
+    if (n > K4_LIST_CAP || n < kk) {  // overflow (or a row of NaNs): left to the row kernel
+      if (tid == 0) p.out_tokens[row] = -1;
+      continue;
+    }
+    constexpr int MINE = K4_LIST_CAP / K4_LIST_THREADS;
+    unsigned long long code[MINE];
+    int32_t rank[MINE];
+#pragma unroll
+    for (int q = 0; q < MINE; ++q) {
+      const int32_t i = tid + q * K4_LIST_THREADS;
+      code[q] = (i < n) ? cand[row * K4_LIST_CAP + i] : ~0ull;
+      if (i < n) list[i] = code[q];
+      rank[q] = 0;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int32_t j = 0; j < n; ++j) {
+      const unsigned long long o = list[j];
+#pragma unroll
+      for (int q = 0; q < MINE; ++q) rank[q] += (o > code[q]) ? 1 : 0;
+    }
+#pragma unroll
+    for (int q = 0; q < MINE; ++q)
+      if (tid + q * K4_LIST_THREADS < n && rank[q] < kk) top[rank[q]] = code[q];
+    __syncthreads();
+    if (tid == 0) {
+      const int32_t pick = greedy ? 0 : k4_draw(top, kk, c, row, p.seed, p.offset);
+      p.out_tokens[row] = k4_index(top[pick]);
+      p.out_logprob[row] = __fdiv_rn(k4_value(top[pick]), temp) - lse[row];
+    }
+    if (p.out_topk_idx != nullptr || p.out_topk_val != nullptr) {
+      for (int32_t j = tid; j < k; j += K4_LIST_THREADS) {
+        const bool have = j < kk;
+        if (p.out_topk_idx != nullptr) p.out_topk_idx[row * k + j] = have ? k4_index(top[j]) : -1;
+        if (p.out_topk_val != nullptr)
+          p.out_topk_val[row * k + j] = have ? k4_value(top[j]) : -INFINITY;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// Scratch layout of the three-kernel path: thresholds, logsumexps and counters per row, then
+// the candidate lists.
+struct K4Workspace {
+  float* thr;
+  float* lse;
+  int32_t* count;
+  unsigned long long* cand;
+};
+static size_t k4_workspace_bytes(int64_t rows) {
+  const size_t head = (static_cast<size_t>(rows) * 12 + 15) & ~static_cast<size_t>(15);
+  return head + static_cast<size_t>(rows) * K4_LIST_CAP * sizeof(unsigned long long);
+}
+static K4Workspace k4_workspace(void* base, int64_t rows) {
+  K4Workspace w;
+  uint8_t* b = static_cast<uint8_t*>(base);
+  w.thr = reinterpret_cast<float*>(b);
+  w.lse = w.thr + rows;
+  w.count = reinterpret_cast<int32_t*>(w.lse + rows);
+  w.cand = reinterpret_cast<unsigned long long*>(
+      b + ((static_cast<size_t>(rows) * 12 + 15) & ~static_cast<size_t>(15)));
+  return w;
+}
+
+// Whether a batch takes the three-kernel path (given scratch): large batches of rows that the
+// streaming kernel can read.  TOME_K4_STREAM = 1 / 0 forces it on (where possible) / off.
+static bool k4_wants_stream(int64_t rows, int64_t vocab) {
+  if (vocab < K4_STREAM_MIN_VOCAB) return false;
+  if (const char* e = getenv("TOME_K4_STREAM")) return atoi(e) != 0;
+  return rows >= K4_STREAM_MIN_ROWS;
+}
+
 // Cluster size for a batch too small to fill the GPU with one CTA per row: the largest of 8
 // and 4 whose clusters are all resident at once (0: do not split).
 // TOME_K4_SPLIT=0 switches the split off, 2/4/8 forces a size (read at every call; tests).
@@ -467,12 +593,12 @@ static int k4_split_factor(const void* kernel, int smem, int64_t rows, int64_t v
 
 using namespace tome;
 
-extern "C" int32_t tome_sample_topk_logprob(const void* logits, int32_t dtype, int64_t rows,
-                                            int64_t vocab, int64_t row_stride, float temperature,
-                                            int32_t top_k, uint64_t seed, uint64_t offset,
-                                            int32_t* out_tokens, float* out_logprob,
-                                            int32_t* out_topk_idx, float* out_topk_val,
-                                            int32_t* dev_status, void* stream) {
+static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, int64_t vocab,
+                              int64_t row_stride, float temperature, int32_t top_k,
+                              uint64_t seed, uint64_t offset, int32_t* out_tokens,
+                              float* out_logprob, int32_t* out_topk_idx, float* out_topk_val,
+                              void* workspace, size_t ws_bytes, int32_t* dev_status,
+                              void* stream) {
   if (dtype != TOME_F32 && dtype != TOME_BF16)
     return fail(TOME_ERR_BAD_DTYPE, "dtype %d is neither TOME_F32 nor TOME_BF16", dtype);
   if (rows < 0 || vocab <= 0 || vocab > 0x7fffffffLL)
@@ -494,20 +620,13 @@ extern "C" int32_t tome_sample_topk_logprob(const void* logits, int32_t dtype, i
   int32_t st = current_device_info(&info);
   if (st != TOME_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // Large batches stream through the TMA pipeline of the selective kernel (several times the
-  // throughput); the rows it could not finish come back marked -1 and are redone below.
-  // Measured (V = 151936): bf16 1024 rows 158 vs 166 us, 8192 rows 0.89 vs 1.33 ms; fp32 rows
-  // are quicker in the kernel below at every size (8192 rows: 2.19 vs 1.74 ms), so they stay
-  // there.  TOME_K4_STREAM = 1 / 0 forces the streaming kernel on (where the rows are
-  // eligible) / off, whatever the size and dtype (tests).
-  bool streamed = dtype == TOME_BF16 && rows >= K4_STREAM_MIN_ROWS;
-  if (const char* e = getenv("TOME_K4_STREAM")) streamed = atoi(e) != 0;
-  streamed = streamed && k1_sample_eligible(logits, dtype, vocab, row_stride);
+  const bool streamed = workspace != nullptr && k4_wants_stream(rows, vocab) &&
+                        k1_sample_eligible(logits, dtype, vocab, row_stride);
   if (streamed) {
-    st = k1_launch_sample(logits, dtype, rows, vocab, row_stride, temperature, top_k, seed,
-                          offset, out_tokens, out_logprob, out_topk_idx, out_topk_val, dev_status,
-                          s);
-    if (st != TOME_OK) return st;
+    if (ws_bytes < k4_workspace_bytes(rows))
+      return fail(TOME_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes, %zu needed", ws_bytes,
+                  k4_workspace_bytes(rows));
+    if (!aligned16(workspace)) return fail(TOME_ERR_MISALIGNED, "workspace is not 16-byte aligned");
   }
   K4Params p = {};
   p.only_flagged = streamed ? 1 : 0;
@@ -524,6 +643,27 @@ extern "C" int32_t tome_sample_topk_logprob(const void* logits, int32_t dtype, i
   p.out_topk_idx = out_topk_idx;
   p.out_topk_val = out_topk_val;
   p.status = dev_status;
+  if (streamed) {
+    const K4Workspace w = k4_workspace(workspace, rows);
+    const float lse_temp = (temperature > 0.0f) ? temperature : 1.0f;
+    const int32_t kk = static_cast<int32_t>(std::min<int64_t>(top_k, vocab));
+    const int grid_rows = static_cast<int>(
+        std::min<int64_t>(rows, static_cast<int64_t>(info.sm_count) * 16));
+    if (dtype == TOME_F32)
+      k4_threshold_kernel<float><<<grid_rows, K4_LIST_THREADS, 0, s>>>(
+          static_cast<const float*>(logits), rows, vocab, row_stride, kk, w.thr, w.count);
+    else
+      k4_threshold_kernel<__nv_bfloat16><<<grid_rows, K4_LIST_THREADS, 0, s>>>(
+          static_cast<const __nv_bfloat16*>(logits), rows, vocab, row_stride, kk, w.thr, w.count);
+    st = check_cuda(cudaGetLastError(), "k4 threshold launch");
+    if (st != TOME_OK) return st;
+    st = k1_launch_sample(logits, dtype, rows, vocab, row_stride, lse_temp, w.thr, w.count, w.cand,
+                          K4_LIST_CAP, w.lse, dev_status, s);
+    if (st != TOME_OK) return st;
+    k4_finish_kernel<<<grid_rows, K4_LIST_THREADS, 0, s>>>(p, w.lse, w.count, w.cand);
+    st = check_cuda(cudaGetLastError(), "k4 finish launch");
+    if (st != TOME_OK) return st;
+  }
   const int smem = static_cast<int>(sizeof(K4Smem));
   void (*split_kernel)(K4Params, int) = (dtype == TOME_F32)
                                             ? k4_sample_split_kernel<float>
@@ -566,4 +706,33 @@ extern "C" int32_t tome_sample_topk_logprob(const void* logits, int32_t dtype, i
     k4_sample_kernel<__nv_bfloat16><<<grid, K4_THREADS, smem, s>>>(p);
   }
   return check_cuda(cudaGetLastError(), "k4 launch");
+}
+
+extern "C" int32_t tome_sample_topk_logprob(const void* logits, int32_t dtype, int64_t rows,
+                                            int64_t vocab, int64_t row_stride, float temperature,
+                                            int32_t top_k, uint64_t seed, uint64_t offset,
+                                            int32_t* out_tokens, float* out_logprob,
+                                            int32_t* out_topk_idx, float* out_topk_val,
+                                            int32_t* dev_status, void* stream) {
+  return k4_sample_impl(logits, dtype, rows, vocab, row_stride, temperature, top_k, seed, offset,
+                        out_tokens, out_logprob, out_topk_idx, out_topk_val, nullptr, 0,
+                        dev_status, stream);
+}
+
+extern "C" size_t tome_sample_workspace_bytes(int64_t rows, int64_t vocab) {
+  if (rows <= 0 || vocab <= 0 || !k4_wants_stream(rows, vocab)) return 0;
+  return k4_workspace_bytes(rows);
+}
+
+extern "C" int32_t tome_sample_topk_logprob_ws(const void* logits, int32_t dtype, int64_t rows,
+                                               int64_t vocab, int64_t row_stride,
+                                               float temperature, int32_t top_k, uint64_t seed,
+                                               uint64_t offset, int32_t* out_tokens,
+                                               float* out_logprob, int32_t* out_topk_idx,
+                                               float* out_topk_val, void* workspace,
+                                               size_t ws_bytes, int32_t* dev_status,
+                                               void* stream) {
+  return k4_sample_impl(logits, dtype, rows, vocab, row_stride, temperature, top_k, seed, offset,
+                        out_tokens, out_logprob, out_topk_idx, out_topk_val, workspace, ws_bytes,
+                        dev_status, stream);
 }

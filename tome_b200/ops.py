@@ -335,12 +335,15 @@ def sample_topk_logprob(logits: torch.Tensor, temperature: float, top_k: int = 2
     lp = torch.empty(rows, dtype=torch.float32, device=device)
     tk_i = torch.empty((rows, top_k), dtype=torch.int32, device=device) if return_topk else None
     tk_v = torch.empty((rows, top_k), dtype=torch.float32, device=device) if return_topk else None
+    # large batches take a streaming three-kernel path that needs scratch (0: not this batch)
+    nbytes = int(lib.tome_sample_workspace_bytes(rows, V))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=device) if nbytes else None
     with _on(device):
-        status = lib.tome_sample_topk_logprob(
+        status = lib.tome_sample_topk_logprob_ws(
             flat.data_ptr(), _dtype_code(flat), rows, V, stride, float(temperature or 0.0),
             int(top_k), int(seed) & (2 ** 64 - 1), int(offset) & (2 ** 64 - 1), tokens.data_ptr(),
-            lp.data_ptr(), _ptr(tk_i), _ptr(tk_v), _status_word(device).data_ptr(),
-            _stream(device))
+            lp.data_ptr(), _ptr(tk_i), _ptr(tk_v), _ptr(ws), nbytes,
+            _status_word(device).data_ptr(), _stream(device))
     _lib.check(status)
     if check:
         check_device_status(device)
