@@ -44,9 +44,9 @@ __host__ __device__ constexpr int k1_stages(int mode) { return mode == K1_FULL ?
 // candidate stalls its warp for a memory round trip: 312 us for 4096 bf16 rows against 190 us
 // in the selective mode) and copied out once per row.
 constexpr int K1_SAMPLE_LIST = 256;
-struct K1SampleSmem {
-  unsigned long long cand[K1_SAMPLE_LIST];
-  int32_t count[2];  // by row parity: the other one is reset while this one is read
+struct K1SampleSmem {  // list and counter are double-buffered by row parity
+  unsigned long long cand[2][K1_SAMPLE_LIST];
+  int32_t count[2];
 };
 
 template <int STAGES>
@@ -185,12 +185,13 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       // to the row's candidate list in global memory; a later kernel ranks them and draws.
       K1SampleSmem& smp = *reinterpret_cast<K1SampleSmem*>(smem + Smem::SAMPLE_OFF);
       int32_t* smp_count = &smp.count[red_it & 1u];
+      unsigned long long* smp_list = smp.cand[red_it & 1u];
       float thr_val = __int_as_float(0x7f800000);  // +inf: nothing qualifies
       if (MODE == K1_SAMPLE) thr_val = p.row_thr[row];
       auto push = [&](float x, int64_t i) {
         if (x >= thr_val) {
           const int32_t slot = atomicAdd(smp_count, 1);
-          if (slot < K1_SAMPLE_LIST) smp.cand[slot] = k4_pack(x, i);
+          if (slot < K1_SAMPLE_LIST) smp_list[slot] = k4_pack(x, i);
         }
       };
       auto collect = [&](uint4 q, int64_t i0) {
@@ -286,18 +287,19 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
           if (MODE != K1_SAMPLE && ctid == 0)
             emit_row<MODE>(p, oidx, sub, m, s, x_t, target_ok, carry);
         }
-        if (MODE == K1_SAMPLE) {
-          // every consumer has passed the barrier above, so the list is complete: copy it out,
-          // reset the other counter for the next row, and let nobody start that row before
+        if (MODE == K1_SAMPLE && warp == 0) {
+          // Every consumer has passed the barrier above, so this row's list is complete; warp 0
+          // copies it out while the others go on.  The next row fills the other list, which this
+          // warp finished copying before it arrived at that barrier; this list and its counter
+          // are next used two rows from here, after a barrier this warp has yet to arrive at.
           const int32_t n = *reinterpret_cast<volatile int32_t*>(smp_count);
           const int32_t keep = min(n, min(K1_SAMPLE_LIST, p.cand_cap));
-          for (int32_t i = ctid; i < keep; i += K1_CONSUMERS)
-            p.cand[row * p.cand_cap + i] = smp.cand[i];
-          if (ctid == 0) {
+          for (int32_t i = lane; i < keep; i += 32) p.cand[row * p.cand_cap + i] = smp_list[i];
+          __syncwarp();
+          if (lane == 0) {
             p.cand_count[row] = (n > keep) ? p.cand_cap + 1 : n;  // more than kept: overflow
-            smp.count[(red_it & 1u) ^ 1u] = 0;
+            *smp_count = 0;
           }
-          named_bar_sync(2, K1_CONSUMERS);
         }
         ++red_it;
       }

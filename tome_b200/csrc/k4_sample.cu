@@ -58,6 +58,7 @@ struct K4Params {
   int32_t* out_topk_idx;  // nullable, [rows, top_k]
   float* out_topk_val;    // nullable, [rows, top_k]
   int32_t only_flagged;   // redo only the rows whose token is -1 (left over by the streaming kernel)
+  int32_t* marked;        // with only_flagged: how many rows were marked (0: nothing to do)
   int32_t* status;
 };
 
@@ -380,6 +381,7 @@ __global__ void __launch_bounds__(K4_THREADS) k4_sample_kernel(const K4Params p)
   const float temp = greedy ? 1.0f : p.temperature;  // temperature of the reported log-prob
   const float c = LOG2E / temp;
 
+  if (p.only_flagged && p.marked != nullptr && *p.marked == 0) return;
   for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
     if (p.only_flagged && p.out_tokens[row] != -1) continue;  // uniform across the CTA
     const T* src = reinterpret_cast<const T*>(p.logits) + row * p.stride;
@@ -463,8 +465,9 @@ __global__ void __launch_bounds__(K4_THREADS, 2) k4_sample_split_kernel(const K4
 template <typename T>
 __global__ void __launch_bounds__(K4_LIST_THREADS)
 k4_threshold_kernel(const T* logits, int64_t rows, int64_t vocab, int64_t stride, int32_t kk,
-                    float* row_thr, int32_t* cand_count) {
+                    float* row_thr, int32_t* cand_count, int32_t* marked) {
   __shared__ uint32_t keys[K4_LIST_THREADS];
+  if (blockIdx.x == 0 && threadIdx.x == 0) *marked = 0;
   constexpr int PER = 16 / static_cast<int>(sizeof(T));
   const int tid = threadIdx.x;
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -502,7 +505,10 @@ k4_finish_kernel(const K4Params p, const float* lse, const int32_t* cand_count,
   for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
     const int32_t n = cand_count[row];
     if (n > K4_LIST_CAP || n < kk) {  // overflow (or a row of NaNs): left to the row kernel
-      if (tid == 0) p.out_tokens[row] = -1;
+      if (tid == 0) {
+        p.out_tokens[row] = -1;
+        atomicAdd(p.marked, 1);
+      }
       continue;
     }
     constexpr int MINE = K4_LIST_CAP / K4_LIST_THREADS;
@@ -549,11 +555,15 @@ struct K4Workspace {
   float* thr;
   float* lse;
   int32_t* count;
+  int32_t* marked;  // one counter for the batch
   unsigned long long* cand;
 };
+static size_t k4_workspace_head(int64_t rows) {
+  return (static_cast<size_t>(rows) * 12 + 4 + 15) & ~static_cast<size_t>(15);
+}
 static size_t k4_workspace_bytes(int64_t rows) {
-  const size_t head = (static_cast<size_t>(rows) * 12 + 15) & ~static_cast<size_t>(15);
-  return head + static_cast<size_t>(rows) * K4_LIST_CAP * sizeof(unsigned long long);
+  return k4_workspace_head(rows) +
+         static_cast<size_t>(rows) * K4_LIST_CAP * sizeof(unsigned long long);
 }
 static K4Workspace k4_workspace(void* base, int64_t rows) {
   K4Workspace w;
@@ -561,8 +571,8 @@ static K4Workspace k4_workspace(void* base, int64_t rows) {
   w.thr = reinterpret_cast<float*>(b);
   w.lse = w.thr + rows;
   w.count = reinterpret_cast<int32_t*>(w.lse + rows);
-  w.cand = reinterpret_cast<unsigned long long*>(
-      b + ((static_cast<size_t>(rows) * 12 + 15) & ~static_cast<size_t>(15)));
+  w.marked = w.count + rows;
+  w.cand = reinterpret_cast<unsigned long long*>(b + k4_workspace_head(rows));
   return w;
 }
 
@@ -645,16 +655,18 @@ static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, i
   p.status = dev_status;
   if (streamed) {
     const K4Workspace w = k4_workspace(workspace, rows);
+    p.marked = w.marked;
     const float lse_temp = (temperature > 0.0f) ? temperature : 1.0f;
     const int32_t kk = static_cast<int32_t>(std::min<int64_t>(top_k, vocab));
     const int grid_rows = static_cast<int>(
         std::min<int64_t>(rows, static_cast<int64_t>(info.sm_count) * 16));
     if (dtype == TOME_F32)
       k4_threshold_kernel<float><<<grid_rows, K4_LIST_THREADS, 0, s>>>(
-          static_cast<const float*>(logits), rows, vocab, row_stride, kk, w.thr, w.count);
+          static_cast<const float*>(logits), rows, vocab, row_stride, kk, w.thr, w.count, w.marked);
     else
       k4_threshold_kernel<__nv_bfloat16><<<grid_rows, K4_LIST_THREADS, 0, s>>>(
-          static_cast<const __nv_bfloat16*>(logits), rows, vocab, row_stride, kk, w.thr, w.count);
+          static_cast<const __nv_bfloat16*>(logits), rows, vocab, row_stride, kk, w.thr, w.count,
+          w.marked);
     st = check_cuda(cudaGetLastError(), "k4 threshold launch");
     if (st != TOME_OK) return st;
     st = k1_launch_sample(logits, dtype, rows, vocab, row_stride, lse_temp, w.thr, w.count, w.cand,
