@@ -62,6 +62,33 @@ struct K1SmemT {
 };
 
 
+// SAMPLE: a logit that reaches the row's threshold joins the row's candidate list.
+__device__ __forceinline__ void sample_push(float x, int64_t i, float thr_val, int32_t* count,
+                                            unsigned long long* list) {
+  if (x >= thr_val) {
+    const int32_t slot = atomicAdd(count, 1);
+    if (slot < K1_SAMPLE_LIST) list[slot] = k4_pack(x, i);
+  }
+}
+
+// The elements of one 16-byte vector (first element index i0).  Rare (about a hundred vectors
+// of a row qualify), so it is kept out of line: inlined at its five call sites it bloats the
+// hot loop.
+template <typename T>
+__device__ __noinline__ void sample_collect(uint4 q, int64_t i0, float thr_val, int32_t* count,
+                                            unsigned long long* list) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (sizeof(T) == 4) {
+      sample_push(__uint_as_float(w[j]), i0 + j, thr_val, count, list);
+    } else {
+      sample_push(__uint_as_float(w[j] << 16), i0 + 2 * j, thr_val, count, list);
+      sample_push(__uint_as_float(w[j] & 0xffff0000u), i0 + 2 * j + 1, thr_val, count, list);
+    }
+  }
+}
+
 template <typename T, int MODE, int POLY>
 __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(const K1Params p) {
   constexpr int STAGES = k1_stages(MODE);
@@ -188,23 +215,9 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       unsigned long long* smp_list = smp.cand[red_it & 1u];
       float thr_val = __int_as_float(0x7f800000);  // +inf: nothing qualifies
       if (MODE == K1_SAMPLE) thr_val = p.row_thr[row];
-      auto push = [&](float x, int64_t i) {
-        if (x >= thr_val) {
-          const int32_t slot = atomicAdd(smp_count, 1);
-          if (slot < K1_SAMPLE_LIST) smp_list[slot] = k4_pack(x, i);
-        }
-      };
+      auto push = [&](float x, int64_t i) { sample_push(x, i, thr_val, smp_count, smp_list); };
       auto collect = [&](uint4 q, int64_t i0) {
-        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (sizeof(T) == 4) {
-            push(__uint_as_float(w[j]), i0 + j);
-          } else {
-            push(__uint_as_float(w[j] << 16), i0 + 2 * j);
-            push(__uint_as_float(w[j] & 0xffff0000u), i0 + 2 * j + 1);
-          }
-        }
+        sample_collect<T>(q, i0, thr_val, smp_count, smp_list);
       };
 
       for (int64_t k = 0; k < n_chunks; ++k, ++it) {
