@@ -78,8 +78,9 @@ struct K1Params {
   int64_t packed_capacity; // RAGGED: entries the packed target/output arrays can hold
   int32_t* out_offsets;    // RAGGED: int32 [n_seq + 1], start of each sequence in the packed output
   const float* row_thr;    // SAMPLE: per-row value threshold
-  int32_t* cand_count;     // SAMPLE: per-row number of candidates appended (may exceed cand_cap)
-  unsigned long long* cand;  // SAMPLE: [rows, cand_cap] packed candidates (see sampling.cuh)
+  int32_t* cand_count;     // SAMPLE: per-row number of vectors appended (cand_cap + 1: overflow)
+  uint4* cand_vec;         // SAMPLE: [rows, cand_cap] 16-byte vectors holding a candidate
+  int32_t* cand_idx;       // SAMPLE: [rows, cand_cap] their positions in the row, in 16-byte units
   int32_t cand_cap;
   int32_t* status;         // nullable
   int32_t chunk_bytes;     // bulk-copy size (multiple of 16, <= K1_CHUNK_BYTES), set by launch

@@ -40,13 +40,15 @@ namespace tome {
 constexpr int K1_FULL_STAGES = K1_CFG_FULL_STAGES;
 __host__ __device__ constexpr int k1_stages(int mode) { return mode == K1_FULL ? K1_FULL_STAGES : K1_STAGES; }
 
-// SAMPLE mode: the row's candidates are gathered in shared memory (a global atomic per
-// candidate stalls its warp for a memory round trip: 312 us for 4096 bf16 rows against 190 us
-// in the selective mode) and copied out once per row.
+// SAMPLE mode: the 16-byte vectors holding a logit that reaches the row's threshold are gathered
+// in shared memory, whole (one shared-memory atomic and two stores per vector; unpacking them
+// here cost ~600 warp-cycles per vector, and a global atomic per candidate a memory round
+// trip), and copied out once per row.
 constexpr int K1_SAMPLE_LIST = 256;
-struct K1SampleSmem {  // list and counter are double-buffered by row parity
-  unsigned long long cand[2][K1_SAMPLE_LIST];
-  int32_t count[2];
+struct K1SampleSmem {
+  uint4 vec[K1_SAMPLE_LIST];
+  int32_t idx[K1_SAMPLE_LIST];  // index of the vector within the row (16-byte units)
+  int32_t count[2];             // by row parity: the other one is reset while this one is read
 };
 
 template <int STAGES>
@@ -58,36 +60,9 @@ struct K1SmemT {
   static constexpr int SCRATCH_OFF = CUM_OFF + (K1_MAX_SEQ + 1) * 4 + 12;
   static constexpr int TOTAL_DUAL = SCRATCH_OFF + K1_THREADS * 4;
   static constexpr int TOTAL_PLAIN = CUM_OFF;
-  static constexpr int SAMPLE_OFF = (CUM_OFF + 7) & ~7;                  // SAMPLE: K1SampleSmem
+  static constexpr int SAMPLE_OFF = (CUM_OFF + 15) & ~15;                // SAMPLE: K1SampleSmem
 };
 
-
-// SAMPLE: a logit that reaches the row's threshold joins the row's candidate list.
-__device__ __forceinline__ void sample_push(float x, int64_t i, float thr_val, int32_t* count,
-                                            unsigned long long* list) {
-  if (x >= thr_val) {
-    const int32_t slot = atomicAdd(count, 1);
-    if (slot < K1_SAMPLE_LIST) list[slot] = k4_pack(x, i);
-  }
-}
-
-// The elements of one 16-byte vector (first element index i0).  Rare (about a hundred vectors
-// of a row qualify), so it is kept out of line: inlined at its five call sites it bloats the
-// hot loop.
-template <typename T>
-__device__ __noinline__ void sample_collect(uint4 q, int64_t i0, float thr_val, int32_t* count,
-                                            unsigned long long* list) {
-  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    if (sizeof(T) == 4) {
-      sample_push(__uint_as_float(w[j]), i0 + j, thr_val, count, list);
-    } else {
-      sample_push(__uint_as_float(w[j] << 16), i0 + 2 * j, thr_val, count, list);
-      sample_push(__uint_as_float(w[j] & 0xffff0000u), i0 + 2 * j + 1, thr_val, count, list);
-    }
-  }
-}
 
 template <typename T, int MODE, int POLY>
 __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(const K1Params p) {
@@ -208,16 +183,18 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       T* dst = nullptr;
       if (MODE == K1_FULL) dst = reinterpret_cast<T*>(p.out_full) + row * p.out_stride;
 
-      // SAMPLE: logits that reach the row's threshold (found by an earlier kernel) are appended
-      // to the row's candidate list in global memory; a later kernel ranks them and draws.
+      // SAMPLE: vectors holding a logit that reaches the row's threshold (found by an earlier
+      // kernel) are appended to the row's list; a later kernel unpacks, ranks and draws.
       K1SampleSmem& smp = *reinterpret_cast<K1SampleSmem*>(smem + Smem::SAMPLE_OFF);
       int32_t* smp_count = &smp.count[red_it & 1u];
-      unsigned long long* smp_list = smp.cand[red_it & 1u];
       float thr_val = __int_as_float(0x7f800000);  // +inf: nothing qualifies
       if (MODE == K1_SAMPLE) thr_val = p.row_thr[row];
-      auto push = [&](float x, int64_t i) { sample_push(x, i, thr_val, smp_count, smp_list); };
-      auto collect = [&](uint4 q, int64_t i0) {
-        sample_collect<T>(q, i0, thr_val, smp_count, smp_list);
+      auto collect = [&](uint4 q, int64_t vec_index) {
+        const int32_t slot = atomicAdd(smp_count, 1);
+        if (slot < K1_SAMPLE_LIST) {
+          smp.vec[slot] = q;
+          smp.idx[slot] = static_cast<int32_t>(vec_index);
+        }
       };
 
       for (int64_t k = 0; k < n_chunks; ++k, ++it) {
@@ -243,20 +220,17 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
             const float mc = fast_update<POLY>(fs, cc, p.c, T());
             const float md = fast_update<POLY>(fs, d, p.c, T());
             if (MODE == K1_SAMPLE) {
-              const int64_t e0 = (off >> 4) * PER_VEC;  // first element of this chunk
-              if (ma >= thr_val) collect(a, e0 + static_cast<int64_t>(v) * PER_VEC);
-              if (mb >= thr_val) collect(b, e0 + static_cast<int64_t>(v + K1_CONSUMERS) * PER_VEC);
-              if (mc >= thr_val)
-                collect(cc, e0 + static_cast<int64_t>(v + 2 * K1_CONSUMERS) * PER_VEC);
-              if (md >= thr_val)
-                collect(d, e0 + static_cast<int64_t>(v + 3 * K1_CONSUMERS) * PER_VEC);
+              const int64_t v0 = (off >> 4) + v;  // this thread's first vector within the row
+              if (ma >= thr_val) collect(a, v0);
+              if (mb >= thr_val) collect(b, v0 + K1_CONSUMERS);
+              if (mc >= thr_val) collect(cc, v0 + 2 * K1_CONSUMERS);
+              if (md >= thr_val) collect(d, v0 + 3 * K1_CONSUMERS);
             }
           }
           for (; v < nvec; v += K1_CONSUMERS) {
             const uint4 a = lds128(sbase + v * 16);
             const float ma = fast_update<POLY>(fs, a, p.c, T());
-            if (MODE == K1_SAMPLE && ma >= thr_val)
-              collect(a, (off >> 4) * PER_VEC + static_cast<int64_t>(v) * PER_VEC);
+            if (MODE == K1_SAMPLE && ma >= thr_val) collect(a, (off >> 4) + v);
           }
         } else {
           uint8_t* drow = reinterpret_cast<uint8_t*>(dst) + off;
@@ -276,7 +250,18 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
         for (int64_t j = tail_begin; j < p.vocab; ++j) {
           if (reduce_pass) online_update_scalar(st, to_float(src[j]), p.c);
           else dst[j] = full_out_scalar(src[j], p.inv_temp, lse_row);
-          if (MODE == K1_SAMPLE) push(to_float(src[j]), j);
+        }
+        if (MODE == K1_SAMPLE && tail_begin < p.vocab) {
+          // the tail travels as one vector padded with -inf (tail_begin is a multiple of PER_VEC)
+          __align__(16) T pad[PER_VEC];
+          float tail_max = __int_as_float(0xff800000);
+          for (int j = 0; j < PER_VEC; ++j) {
+            const bool have = tail_begin + j < p.vocab;
+            const float x = have ? to_float(src[tail_begin + j]) : __int_as_float(0xff800000);
+            pad[j] = have ? src[tail_begin + j] : from_float_neg_inf(T());
+            tail_max = fmaxf(tail_max, x);
+          }
+          if (tail_max >= thr_val) collect(*reinterpret_cast<const uint4*>(pad), tail_begin / PER_VEC);
         }
       }
 
@@ -300,19 +285,20 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
           if (MODE != K1_SAMPLE && ctid == 0)
             emit_row<MODE>(p, oidx, sub, m, s, x_t, target_ok, carry);
         }
-        if (MODE == K1_SAMPLE && warp == 0) {
-          // Every consumer has passed the barrier above, so this row's list is complete; warp 0
-          // copies it out while the others go on.  The next row fills the other list, which this
-          // warp finished copying before it arrived at that barrier; this list and its counter
-          // are next used two rows from here, after a barrier this warp has yet to arrive at.
+        if (MODE == K1_SAMPLE) {
+          // every consumer has passed the barrier above, so the list is complete: copy it out,
+          // reset the other counter for the next row, and let nobody start that row before
           const int32_t n = *reinterpret_cast<volatile int32_t*>(smp_count);
           const int32_t keep = min(n, min(K1_SAMPLE_LIST, p.cand_cap));
-          for (int32_t i = lane; i < keep; i += 32) p.cand[row * p.cand_cap + i] = smp_list[i];
-          __syncwarp();
-          if (lane == 0) {
-            p.cand_count[row] = (n > keep) ? p.cand_cap + 1 : n;  // more than kept: overflow
-            *smp_count = 0;
+          for (int32_t i = ctid; i < keep; i += K1_CONSUMERS) {
+            p.cand_vec[row * p.cand_cap + i] = smp.vec[i];
+            p.cand_idx[row * p.cand_cap + i] = smp.idx[i];
           }
+          if (ctid == 0) {
+            p.cand_count[row] = (n > keep) ? p.cand_cap + 1 : n;  // more than kept: overflow
+            smp.count[(red_it & 1u) ^ 1u] = 0;
+          }
+          named_bar_sync(2, K1_CONSUMERS);
         }
         ++red_it;
       }
@@ -695,8 +681,9 @@ bool k1_sample_eligible(const void* logits, int32_t dtype, int64_t vocab, int64_
 
 int32_t k1_launch_sample(const void* logits, int32_t dtype, int64_t rows, int64_t vocab,
                          int64_t row_stride, float temperature, const float* row_thr,
-                         int32_t* cand_count, unsigned long long* cand, int32_t cand_cap,
-                         float* out_lse, int32_t* dev_status, cudaStream_t stream) {
+                         int32_t* cand_count, uint4* cand_vec, int32_t* cand_idx,
+                         int32_t cand_cap, float* out_lse, int32_t* dev_status,
+                         cudaStream_t stream) {
   K1Params p = {};
   p.src[0] = logits;
   p.n_rows = rows;
@@ -708,7 +695,8 @@ int32_t k1_launch_sample(const void* logits, int32_t dtype, int64_t rows, int64_
   p.out1 = out_lse;
   p.row_thr = row_thr;
   p.cand_count = cand_count;
-  p.cand = cand;
+  p.cand_vec = cand_vec;
+  p.cand_idx = cand_idx;
   p.cand_cap = cand_cap;
   p.status = dev_status;
   return k1_launch<K1_SAMPLE>(p, dtype, true, rows, stream);

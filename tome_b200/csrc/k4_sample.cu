@@ -491,11 +491,14 @@ k4_threshold_kernel(const T* logits, int64_t rows, int64_t vocab, int64_t stride
   }
 }
 
+template <typename T>
 __global__ void __launch_bounds__(K4_LIST_THREADS)
-k4_finish_kernel(const K4Params p, const float* lse, const int32_t* cand_count,
-                 const unsigned long long* cand) {
+k4_finish_kernel(const K4Params p, const float* row_thr, const float* lse,
+                 const int32_t* cand_count, const uint4* cand_vec, const int32_t* cand_idx) {
   __shared__ unsigned long long list[K4_LIST_CAP];
   __shared__ unsigned long long top[K4_MAX_K];
+  __shared__ int32_t list_n;
+  constexpr int PER = 16 / static_cast<int>(sizeof(T));
   const int tid = threadIdx.x;
   const bool greedy = !(p.temperature > 0.0f);
   const float temp = greedy ? 1.0f : p.temperature;
@@ -503,12 +506,37 @@ k4_finish_kernel(const K4Params p, const float* lse, const int32_t* cand_count,
   const int32_t k = p.top_k;
   const int32_t kk = static_cast<int32_t>(min(static_cast<int64_t>(k), p.vocab));
   for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
-    const int32_t n = cand_count[row];
-    if (n > K4_LIST_CAP || n < kk) {  // overflow (or a row of NaNs): left to the row kernel
+    const int32_t n_vec = cand_count[row];
+    if (tid == 0) list_n = 0;
+    __syncthreads();
+    // unpack the row's vectors: the logits that reach the threshold are the candidates
+    if (n_vec <= K4_LIST_CAP) {
+      const float thr = row_thr[row];
+      for (int32_t i = tid; i < n_vec; i += K4_LIST_THREADS) {
+        const uint4 q = cand_vec[row * K4_LIST_CAP + i];
+        const int64_t e0 = static_cast<int64_t>(cand_idx[row * K4_LIST_CAP + i]) * PER;
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+          const float x = (sizeof(T) == 4)
+                              ? __uint_as_float(w[j])
+                              : __uint_as_float((j & 1) ? (w[j >> 1] & 0xffff0000u) : (w[j >> 1] << 16));
+          if (e0 + j < p.vocab && x >= thr) {
+            const int32_t slot = atomicAdd(&list_n, 1);
+            if (slot < K4_LIST_CAP) list[slot] = k4_pack(x, e0 + j);
+          }
+        }
+      }
+    }
+    __syncthreads();
+    const int32_t n = list_n;
+    if (n_vec > K4_LIST_CAP || n > K4_LIST_CAP || n < kk) {
+      // overflow (sorted or heavily tied rows) or a row of NaNs: left to the row kernel
       if (tid == 0) {
         p.out_tokens[row] = -1;
         atomicAdd(p.marked, 1);
       }
+      __syncthreads();
       continue;
     }
     constexpr int MINE = K4_LIST_CAP / K4_LIST_THREADS;
@@ -517,11 +545,9 @@ k4_finish_kernel(const K4Params p, const float* lse, const int32_t* cand_count,
 #pragma unroll
     for (int q = 0; q < MINE; ++q) {
       const int32_t i = tid + q * K4_LIST_THREADS;
-      code[q] = (i < n) ? cand[row * K4_LIST_CAP + i] : ~0ull;
-      if (i < n) list[i] = code[q];
+      code[q] = (i < n) ? list[i] : ~0ull;
       rank[q] = 0;
     }
-    __syncthreads();
 #pragma unroll 4
     for (int32_t j = 0; j < n; ++j) {
       const unsigned long long o = list[j];
@@ -556,14 +582,15 @@ struct K4Workspace {
   float* lse;
   int32_t* count;
   int32_t* marked;  // one counter for the batch
-  unsigned long long* cand;
+  uint4* cand_vec;  // [rows, K4_LIST_CAP] vectors holding a candidate
+  int32_t* cand_idx;
 };
 static size_t k4_workspace_head(int64_t rows) {
   return (static_cast<size_t>(rows) * 12 + 4 + 15) & ~static_cast<size_t>(15);
 }
 static size_t k4_workspace_bytes(int64_t rows) {
   return k4_workspace_head(rows) +
-         static_cast<size_t>(rows) * K4_LIST_CAP * sizeof(unsigned long long);
+         static_cast<size_t>(rows) * K4_LIST_CAP * (sizeof(uint4) + sizeof(int32_t));
 }
 static K4Workspace k4_workspace(void* base, int64_t rows) {
   K4Workspace w;
@@ -572,7 +599,8 @@ static K4Workspace k4_workspace(void* base, int64_t rows) {
   w.lse = w.thr + rows;
   w.count = reinterpret_cast<int32_t*>(w.lse + rows);
   w.marked = w.count + rows;
-  w.cand = reinterpret_cast<unsigned long long*>(b + k4_workspace_head(rows));
+  w.cand_vec = reinterpret_cast<uint4*>(b + k4_workspace_head(rows));
+  w.cand_idx = reinterpret_cast<int32_t*>(w.cand_vec + rows * K4_LIST_CAP);
   return w;
 }
 
@@ -669,10 +697,15 @@ static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, i
           w.marked);
     st = check_cuda(cudaGetLastError(), "k4 threshold launch");
     if (st != TOME_OK) return st;
-    st = k1_launch_sample(logits, dtype, rows, vocab, row_stride, lse_temp, w.thr, w.count, w.cand,
-                          K4_LIST_CAP, w.lse, dev_status, s);
+    st = k1_launch_sample(logits, dtype, rows, vocab, row_stride, lse_temp, w.thr, w.count,
+                          w.cand_vec, w.cand_idx, K4_LIST_CAP, w.lse, dev_status, s);
     if (st != TOME_OK) return st;
-    k4_finish_kernel<<<grid_rows, K4_LIST_THREADS, 0, s>>>(p, w.lse, w.count, w.cand);
+    if (dtype == TOME_F32)
+      k4_finish_kernel<float><<<grid_rows, K4_LIST_THREADS, 0, s>>>(p, w.thr, w.lse, w.count,
+                                                                    w.cand_vec, w.cand_idx);
+    else
+      k4_finish_kernel<__nv_bfloat16><<<grid_rows, K4_LIST_THREADS, 0, s>>>(
+          p, w.thr, w.lse, w.count, w.cand_vec, w.cand_idx);
     st = check_cuda(cudaGetLastError(), "k4 finish launch");
     if (st != TOME_OK) return st;
   }

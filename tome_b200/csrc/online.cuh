@@ -180,6 +180,10 @@ __device__ __forceinline__ void online_update_scalar(Online& st, float x, float 
 
 __device__ __forceinline__ float to_float(float x) { return x; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ float from_float_neg_inf(float) { return __int_as_float(0xff800000); }
+__device__ __forceinline__ __nv_bfloat16 from_float_neg_inf(__nv_bfloat16) {
+  return __ushort_as_bfloat16(static_cast<unsigned short>(0xff80));
+}
 
 // Merge the 32 per-thread states of a warp; every lane gets the result.
 __device__ __forceinline__ void online_warp_reduce(Online& st, float c) {
