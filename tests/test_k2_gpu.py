@@ -226,3 +226,11 @@ def test_single_cta_tiles_variant(cuda_device):
     out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True,
                          timeout=600)
     assert out.returncode == 0, out.stdout + out.stderr
+
+
+def test_alternating_shapes_reuse_cached_plans(cuda_device):
+    """Band plans are cached by shape (more shapes here than the cache holds, revisited in a
+    different order): every call must still get the plan of its own shape."""
+    shapes = [(128 * i + 7 * i, 64 + 8 * (i % 3), 256 * (i % 5 + 1) + 16 * i) for i in range(1, 20)]
+    for rows, k, vocab in shapes + shapes[::-3] + shapes[:4]:
+        _run(rows, k, vocab, 1.0, cuda_device, seed=rows % 17)
