@@ -495,6 +495,7 @@ def test_full_every_cluster_size(cuda_device, monkeypatch, split, dtype):
     assert out.shape == ref.shape and max_abs(out.float(), ref.float()) <= tol
 
 
+@pytest.mark.parametrize("small_batch_path", ["small_batches_split"], indirect=True)  # env set below
 @pytest.mark.parametrize("form", ["1", "s1", "s2", "s4", "s8"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("vocab", [8, 24, 7000, 7680 * 6, 7680 * 6 + 8, 151936, 151936 + 4, 300000])
@@ -503,8 +504,6 @@ def test_full_cluster_kernel_sizes(cuda_device, monkeypatch, small_batch_path, f
     beyond what 8 can hold) and the streamed form with every cluster size; more rows than
     clusters so that ring slots are reused."""
     import tome_b200
-    if small_batch_path != "small_batches_split":
-        pytest.skip("the environment is set by this test: one run is enough")
     monkeypatch.setenv("TOME_K1_SPLIT", "0")
     monkeypatch.setenv("TOME_K1_FULL_CLUSTER", form)
     rows = 700 if vocab <= 7000 else (330 if vocab < 100000 else 160)
