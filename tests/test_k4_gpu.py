@@ -233,3 +233,31 @@ def test_workspace_entry_point_checks_its_scratch(cuda_device, monkeypatch):
     assert lib.tome_sample_topk_logprob_ws(*args, big.data_ptr(), need, None, None) == 0
     torch.cuda.synchronize()
     assert torch.equal(t_row, tok)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_three_kernel_path_when_every_row_overflows(cuda_device, monkeypatch, dtype):
+    """Sorted, constant and fully masked rows overflow the per-row lists of the large-batch
+    path; every such row must come back from the row kernel with the same answer."""
+    import tome_b200
+    rows, vocab = 400, 20000
+    x = torch.empty((rows, vocab), dtype=dtype)
+    x[0::4] = torch.linspace(-8, 8, vocab).to(dtype)       # ascending
+    x[1::4] = 0.25                                          # constant
+    x[2::4] = torch.linspace(8, -8, vocab).to(dtype)       # descending: top-k in the sample
+    x[3::4] = float("-inf")
+    x[3::4, 17] = 1.0                                       # a single finite logit
+    xd = x.to(cuda_device)
+    monkeypatch.setenv("TOME_K4_STREAM", "0")
+    t0, lp0, i0, _ = tome_b200.sample_topk_logprob(xd, 0.9, 20, seed=4, offset=7, return_topk=True)
+    monkeypatch.setenv("TOME_K4_STREAM", "1")
+    t1, lp1, i1, _ = tome_b200.sample_topk_logprob(xd, 0.9, 20, seed=4, offset=7, return_topk=True,
+                                                   check=True)
+    assert int(t1.min()) >= 0
+    assert torch.equal(t0, t1) and torch.equal(i0, i1)
+    # rows that did not overflow were summed by the streaming pass (bf16: two of eight
+    # exponentials by polynomial), the others by the row kernel
+    assert max_abs(lp0, lp1) <= (1e-5 if dtype == torch.float32 else 1e-4)
+    for r in range(4):
+        idx, _ = oracle.topk_sampling_distribution(x[r], 0.9, 20)
+        assert i1[r, : len(idx)].cpu().tolist() == idx.tolist()
