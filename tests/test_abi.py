@@ -84,3 +84,15 @@ def test_cpu_tensors_are_rejected_not_emulated(built_lib):
         tome_b200.local_compute_logprobs(x, ids, 1.0)
     with pytest.raises(tome_b200.TomeRuntimeError):
         tome_b200.fused_log_softmax(x, 1.0)
+
+
+def test_sampling_workspace_query_needs_no_gpu(built_lib, monkeypatch):
+    from tome_b200 import _lib
+    monkeypatch.delenv("TOME_K4_STREAM", raising=False)
+    q = _lib.lib.tome_sample_workspace_bytes
+    assert q(8, 151936) == 0 and q(4096, 100) == 0 and q(0, 151936) == 0
+    per_row = 256 * (16 + 4)
+    assert q(4096, 151936) >= 4096 * per_row
+    assert q(4096, 151936) < 4096 * (per_row + 64)
+    monkeypatch.setenv("TOME_K4_STREAM", "0")
+    assert q(4096, 151936) == 0
