@@ -55,6 +55,7 @@ enum tome_status {
 #define TOME_DEV_TIMEOUT 2
 #define TOME_DEV_RAGGED_OVERFLOW 4 /* windows cover more positions than the packed arrays hold */
 #define TOME_DEV_BLOCK_OUT_OF_RANGE 8 /* a block-table entry outside [0, num_blocks) */
+#define TOME_DEV_NO_CANDIDATE 16 /* sampling: a row without a single logit that is not NaN */
 
 /* Library version (TOME_B200_VERSION of the build). */
 int32_t tome_version(void);
@@ -264,7 +265,9 @@ int32_t tome_rmsnorm_bf16(const void* x, const void* weight, int64_t rows, int64
  *     two calls that overlap in time on the same GPU (different streams, or different host
  *     threads) race on it: serialise them on one stream.
  *   - Calls no cudaMalloc, cudaFree or other allocating routine.
- * Arguments and results are those of tome_lmhead_logprob.
+ * Arguments and results are those of tome_lmhead_logprob, without `flags` (the logits are
+ * always reduced un-rounded; TOME_LMHEAD_ROUND_LOGITS_BF16 needs the workspace variant) and
+ * without the workspace pair.
  */
 size_t tome_lmhead_static_scratch_bytes(void);
 

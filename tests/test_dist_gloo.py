@@ -47,6 +47,47 @@ def _worker(rank, world, port, fail_rank, out):
         dist.destroy_process_group()
 
 
+def _late_worker(rank, world, port, timeout_s, delay_s, out):
+    """Rank 1 reaches the collective `delay_s` seconds late; rank 0 waits at most `timeout_s`."""
+    import time
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    from datetime import timedelta
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=120))
+    try:
+        from tome_b200 import dist as tdist
+        packed = tdist.pack_triples(torch.ones(5), torch.ones(5), torch.zeros(5), rank, world)
+        dist.barrier()
+        if rank == 1:
+            time.sleep(delay_s)
+        t0 = time.monotonic()
+        try:
+            tdist.exchange_triples(packed, timeout_s=timeout_s)
+            out[rank] = ("completed", time.monotonic() - t0)
+        except Exception as exc:
+            out[rank] = (type(exc).__name__, time.monotonic() - t0)
+        if rank == 0 and out[rank][0] != "completed":
+            time.sleep(delay_s)  # stay until the late peer has had its partner
+    finally:
+        dist.destroy_process_group()
+
+
+def _run_late(timeout_s, delay_s):
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        out = mgr.dict()
+        port = _free_port()
+        procs = [ctx.Process(target=_late_worker, args=(r, 2, port, timeout_s, delay_s, out))
+                 for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(120)
+            assert not p.is_alive(), "a rank hung"
+        return dict(out)
+
+
 def _run(world, fail_rank=-1):
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
@@ -89,3 +130,14 @@ def test_pack_layout():
     assert p.shape == (7, 2)
     assert torch.equal(p[1], m) and torch.equal(p[4], s) and torch.equal(p[6], t)
     assert float(p[[0, 2, 3, 5]].abs().sum()) == 0.0
+
+
+@pytest.mark.timeout(300)
+def test_exchange_timeout_raises_instead_of_waiting_for_the_group_timeout():
+    # rank 1 comes 8 s late, rank 0 allows 2 s: it must raise long before the group's 120 s
+    out = _run_late(timeout_s=2.0, delay_s=8.0)
+    assert out[0][0] == "TomeRuntimeError", out
+    assert out[0][1] < 2.0 + 5.0, out
+    # a peer that is merely slow, within the limit, is waited for
+    out = _run_late(timeout_s=30.0, delay_s=1.0)
+    assert out[0][0] == "completed" and out[1][0] == "completed", out

@@ -104,6 +104,32 @@ def test_selective_mask_values_and_extreme_magnitudes(cuda_device, dtype):
     _check_selective(x[:5], ids[:5], 0.7, cuda_device)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_nan_logit_gives_nan_wherever_it_sits(cuda_device, dtype):
+    """mx.logsumexp (mlx-impl/node.py:401) and the Metal kernel's sum give NaN for a row that
+    holds a NaN.  The bf16 fast path computes some exponentials of every 8-logit vector with a
+    polynomial that clamps its argument, so the NaN's position within the vector matters: one
+    row per position, plus clean rows that must stay finite."""
+    import tome_b200
+    vocab = 8192 + 24
+    rows = 16
+    x, ids = _case(rows, vocab, dtype, seed=5150)
+    for r in range(8):
+        x[r, 4096 + 8 * r + r] = float("nan")      # position r of its vector (rows are aligned)
+    x[8, 3] = float("nan")
+    x[9, vocab - 1] = float("nan")                 # in the tail past the last 16-byte boundary
+    lp, lse = tome_b200.selective_log_softmax(x.to(cuda_device), ids.to(cuda_device), 0.7,
+                                              return_lse=True)
+    o_lp, o_lse, _ = oracle.selective_logprob(x, ids, 0.7)
+    assert torch.isnan(o_lse[:10]).all() and torch.isfinite(o_lse[10:]).all()
+    assert torch.isnan(lse[:10]).all() and torch.isnan(lp[:10]).all()
+    assert max_abs(lp[10:], o_lp[10:]) <= TOL[dtype]
+    full = tome_b200.fused_log_softmax(x.to(cuda_device), 0.7)
+    assert torch.isnan(full[:10].float()).all()
+    assert torch.isfinite(full[10:].float()).all()
+    tome_b200.check_device_status(cuda_device)
+
+
 @pytest.mark.parametrize("poly", ["1", "2"])
 def test_selective_polynomial_exp_variants(cuda_device, poly):
     """The FMA-pipe exp2 variants (TOME_K1_POLY, read once per process) in a child process."""
@@ -268,8 +294,7 @@ def test_full_log_softmax_matches_metal_order(cuda_device, dtype, shape):
             # outputs are bf16 values near -12: one bf16 ulp there is 0.0625; lse rounding may
             # differ by one ulp between two fp32 summation orders
             assert max_abs(out.float(), ref.float()) <= 0.0625 + 1e-6
-            exact = (out.cpu() == ref).float().mean()
-            assert float(exact) > 0.99 or max_abs(out.float(), ref.float()) <= 0.0625 + 1e-6
+            assert float((out.cpu() == ref).float().mean()) >= 0.99
 
 
 def test_full_log_softmax_into_a_given_buffer(cuda_device):
@@ -292,7 +317,10 @@ def test_full_log_softmax_reference_unit_test_shape(cuda_device):
     out = tome_b200.fused_log_softmax(x.to(cuda_device), temperature=1.0)
     lse = oracle.logsumexp_f32(x.float()).to(torch.bfloat16)
     expected = (x.float() - lse.float()[:, None]).to(torch.bfloat16)
-    assert max_abs(out.float(), expected.float()) < 5e-3 or float((out.cpu() == expected).float().mean()) > 0.99
+    # the reference asserts 5e-3 on its own bf16 outputs; here: at most one bf16 ulp (0.0625 near
+    # -12, from the rounding of the lse) and at least 99 % of the outputs bit-equal
+    assert max_abs(out.float(), expected.float()) <= 0.0625 + 1e-6
+    assert float((out.cpu() == expected).float().mean()) >= 0.99
     full32 = tome_b200.fused_log_softmax(x.float().to(cuda_device), 1.0)
     assert max_abs(torch.logsumexp(full32.double(), -1), torch.zeros(1)) < 1e-4
 
@@ -496,13 +524,14 @@ def test_full_every_cluster_size(cuda_device, monkeypatch, split, dtype):
 
 
 @pytest.mark.parametrize("small_batch_path", ["small_batches_split"], indirect=True)  # env set below
-@pytest.mark.parametrize("form", ["1", "s1", "s2", "s4", "s8"])
+@pytest.mark.parametrize("form", ["1", "r1", "r2", "r4", "r8", "s1", "s2", "s4", "s8"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("vocab", [8, 24, 7000, 7680 * 6, 7680 * 6 + 8, 151936, 151936 + 4, 300000])
+@pytest.mark.parametrize("vocab", [8, 24, 7000, 51200, 51200 + 8, 102400, 151936, 151936 + 4, 300000])
 def test_full_cluster_kernel_sizes(cuda_device, monkeypatch, small_batch_path, form, dtype, vocab):
-    """Row lengths around every cluster size of the resident form (1, 2, 4, 8 CTAs per row, and
-    beyond what 8 can hold) and the streamed form with every cluster size; more rows than
-    clusters so that ring slots are reused."""
+    """Row lengths around the ring capacity of the resident form (one part, two parts and a
+    part that leaves a single spare slot; 1, 2, 4, 8 CTAs per row, and rows beyond what the
+    requested cluster can hold, which fall back) and the streamed form with every cluster
+    size; more rows than clusters so that ring slots are reused."""
     import tome_b200
     monkeypatch.setenv("TOME_K1_SPLIT", "0")
     monkeypatch.setenv("TOME_K1_FULL_CLUSTER", form)

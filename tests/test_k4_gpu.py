@@ -131,7 +131,7 @@ def test_unaligned_rows_and_extreme_k(cuda_device, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("vocab", [24, 600, 4096 + 8, 40000])
+@pytest.mark.parametrize("vocab", [24, 600, 4096 + 8, 40000, 151936])
 def test_large_batches_take_the_streaming_path(cuda_device, monkeypatch, dtype, vocab):
     """Large bf16 batches go through the TMA-pipelined kernel (forced here for fp32 too); rows
     it cannot finish (sorted, constant or heavily tied ones overflow its small candidate ring)
@@ -139,7 +139,7 @@ def test_large_batches_take_the_streaming_path(cuda_device, monkeypatch, dtype, 
     oracle's top-k."""
     import tome_b200
     monkeypatch.setenv("TOME_K4_STREAM", "1")
-    rows = 1200
+    rows = 1200 if vocab < 100000 else 700
     x = _case(rows, vocab, dtype, 300 + vocab % 71)
     x[5] = torch.linspace(-8, 8, vocab).to(dtype)          # ascending: overflows the ring
     x[6, :] = 0.5                                           # constant
@@ -261,3 +261,42 @@ def test_three_kernel_path_when_every_row_overflows(cuda_device, monkeypatch, dt
     for r in range(4):
         idx, _ = oracle.topk_sampling_distribution(x[r], 0.9, 20)
         assert i1[r, : len(idx)].cpu().tolist() == idx.tolist()
+
+
+@pytest.mark.parametrize("stream", ["0", "1"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_rows_with_too_few_numbers(cuda_device, monkeypatch, stream, dtype):
+    """A NaN is never a candidate.  A row with fewer than top_k logits that are not NaN draws
+    from what it has and pads the top-k outputs; a row of NaNs gives token -1, log-prob NaN and
+    a status bit, never an index left over from another row."""
+    import tome_b200
+    monkeypatch.setenv("TOME_K4_STREAM", stream)
+    rows, vocab, k = 6, 32768, 20
+    nan = float("nan")
+    x = _case(rows, vocab, dtype, 77)
+    x[1] = nan
+    x[2] = nan
+    x[2, 5], x[2, 20000], x[2, vocab - 1] = 1.0, 3.0, 2.0
+    x[4, 100] = nan
+    xd = x.to(cuda_device)
+    for _ in range(2):  # twice: nothing may survive from the call before
+        tok, lp, tk_i, tk_v = tome_b200.sample_topk_logprob(xd, 0.7, k, seed=1, return_topk=True)
+        assert int(tok[1]) == -1 and bool(torch.isnan(lp[1])) and bool((tk_i[1] == -1).all())
+        assert bool(torch.isinf(tk_v[1]).all())
+        assert tk_i[2, :3].cpu().tolist() == [20000, vocab - 1, 5] and bool((tk_i[2, 3:] == -1).all())
+        assert tk_v[2, :3].cpu().tolist() == [3.0, 2.0, 1.0] and bool(torch.isinf(tk_v[2, 3:]).all())
+        assert int(tok[2]) in (5, 20000, vocab - 1) and bool(torch.isnan(lp[2]))
+        x4 = x[4].clone()
+        x4[100] = float("-inf")
+        idx4, _ = oracle.topk_sampling_distribution(x4, 0.7, k)
+        assert tk_i[4].cpu().tolist() == idx4.tolist() and int(tok[4]) in idx4.tolist()
+        assert bool(torch.isnan(lp[4]))
+        for r in (0, 3, 5):
+            idx, _ = oracle.topk_sampling_distribution(x[r], 0.7, k)
+            assert tk_i[r].cpu().tolist() == idx.tolist() and int(tok[r]) in idx.tolist()
+        clean = torch.tensor([0, 3, 5])
+        o_lp, _, _ = oracle.selective_logprob(x[clean], tok.cpu()[clean], 0.7)
+        assert max_abs(lp.cpu()[clean], o_lp) <= TOL[dtype]
+    with pytest.raises(tome_b200.TomeRuntimeError):
+        tome_b200.check_device_status(cuda_device)
+    tome_b200.check_device_status(cuda_device)  # the word was cleared

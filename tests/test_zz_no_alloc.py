@@ -53,6 +53,37 @@ def test_static_scratch_matches_workspace_variant_twice(cuda_device):
     assert err_lp <= TOL and err_lse <= TOL
 
 
+def test_static_scratch_large_problem_and_no_allocation(cuda_device):
+    """A problem whose scratch takes several MiB of the 8 MiB array (many rows against a wide
+    vocabulary, small K), so that the plane offsets inside the array are used, and a check of
+    the claim itself: once the first call on the device is over, further calls change neither
+    the driver's free-memory figure nor torch's own allocation count."""
+    from tome_b200 import _lib, synthetic
+    lib = _lib.lib
+    rows, k, vocab = 8192, 64, 120000
+    need = lib.tome_lmhead_workspace_bytes(rows, k, vocab)
+    assert (2 << 20) < need <= lib.tome_lmhead_static_scratch_bytes(), need
+    stream = torch.cuda.current_stream(cuda_device).cuda_stream
+    hidden, weight, ids = synthetic.cfg3_lm_head(rows, k, vocab, cuda_device, 44, 0.05)
+    err_lp, err_lse = _call_pair(lib, hidden, weight, ids, 0.9, stream)   # includes the first call
+    assert err_lp <= TOL and err_lse <= TOL, (err_lp, err_lse)
+    lp = torch.empty(rows, dtype=torch.float32, device=cuda_device)
+    lse = torch.empty_like(lp)
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info(cuda_device)[0]
+    allocated_before = torch.cuda.memory_allocated(cuda_device)
+    allocs_before = torch.cuda.memory_stats(cuda_device).get("allocation.all.allocated", 0)
+    for _ in range(3):
+        st = lib.tome_lmhead_logprob_static(hidden.data_ptr(), weight.data_ptr(), rows, k, vocab,
+                                            ids.data_ptr(), 0.9, lp.data_ptr(), lse.data_ptr(),
+                                            None, stream)
+        assert st == 0, lib.tome_last_error_string()
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info(cuda_device)[0] == free_before
+    assert torch.cuda.memory_allocated(cuda_device) == allocated_before
+    assert torch.cuda.memory_stats(cuda_device).get("allocation.all.allocated", 0) == allocs_before
+
+
 def test_static_scratch_python_wrapper_and_oracle(cuda_device):
     import tome_b200
     from oracle import oracle
@@ -66,6 +97,17 @@ def test_static_scratch_python_wrapper_and_oracle(cuda_device):
     o_lp, o_lse = oracle.lm_head_logprob(hidden, weight, ids, 0.7)
     assert (lp.cpu() - o_lp).abs().max().item() <= TOL
     assert (lse.cpu() - o_lse).abs().max().item() <= TOL
+    # shapes that would make the kernels run past a buffer are refused before the call
+    with pytest.raises(ValueError):
+        tome_b200.lm_head_logprob_static(hd, wd, idd[:-1], 0.7, lp, lse)
+    with pytest.raises(ValueError):
+        tome_b200.lm_head_logprob_static(hd, wd, idd, 0.7, lp[:-1], lse)
+    with pytest.raises(ValueError):
+        tome_b200.lm_head_logprob_static(hd, wd, idd, 0.7, lp, lse[:10])
+    with pytest.raises(ValueError):
+        tome_b200.lm_head_logprob_static(hd, wd[:, :32].contiguous(), idd, 0.7, lp, lse)
+    with pytest.raises(tome_b200.TomeRuntimeError):
+        tome_b200.lm_head_logprob_static(hd, wd, idd, 0.7, lp, lse.cpu())
 
 
 def test_static_scratch_rejects_oversized_problems(cuda_device):

@@ -9,10 +9,12 @@ The CUDA library is loaded on first use of any of these names, so that
 """
 import importlib
 
-_OPS = ["check_device_status", "combine_triples", "fused_log_softmax", "grpo_dual_logprob_kl",
+_OPS = ["BoundCall", "bind_log_softmax", "bind_sample", "bind_selective", "check_device_status",
+        "combine_triples", "fused_log_softmax", "gather_paged_kv", "grpo_dual_logprob_kl",
         "lm_head_logprob", "lm_head_logprob_static", "lm_head_partials",
-        "lm_head_workspace_bytes", "rms_norm", "ragged_logprobs", "sample_topk_logprob", "gather_paged_kv", "update_paged_kv", "local_compute_logprobs", "local_compute_logprobs_host",
-        "selective_log_softmax"]
+        "lm_head_workspace_bytes", "local_compute_logprobs", "local_compute_logprobs_host",
+        "ragged_logprobs", "rms_norm", "sample_topk_logprob", "sample_workspace_bytes",
+        "selective_log_softmax", "update_paged_kv"]
 _DIST = ["lm_head_logprob_vocab_parallel", "pack_triples", "exchange_triples"]
 _LIB = ["TomeArgumentError", "TomeRuntimeError"]
 

@@ -18,6 +18,7 @@ DEV_TARGET_OUT_OF_RANGE = 1
 DEV_TIMEOUT = 2
 DEV_RAGGED_OVERFLOW = 4
 DEV_BLOCK_OUT_OF_RANGE = 8
+DEV_NO_CANDIDATE = 16
 
 LMHEAD_ROUND_LOGITS_BF16 = 1
 

@@ -55,6 +55,32 @@ int32_t current_device_info(DeviceInfo* out) {
   return TOME_OK;
 }
 
+int32_t ensure_dynamic_smem(const void* kernel, int bytes) {
+  struct Entry {
+    int device;
+    const void* kernel;
+    int bytes;
+  };
+  static std::mutex mu;
+  static std::vector<Entry> cache;
+  int dev = 0;
+  int32_t st = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+  if (st != TOME_OK) return st;
+  std::lock_guard<std::mutex> lock(mu);
+  for (Entry& e : cache) {
+    if (e.device != dev || e.kernel != kernel) continue;
+    if (e.bytes >= bytes) return TOME_OK;
+    st = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes),
+                    "cudaFuncSetAttribute(dynamic shared memory)");
+    if (st == TOME_OK) e.bytes = bytes;
+    return st;
+  }
+  st = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes),
+                  "cudaFuncSetAttribute(dynamic shared memory)");
+  if (st == TOME_OK) cache.push_back({dev, kernel, bytes});
+  return st;
+}
+
 int max_active_clusters(const void* kernel, int threads, int dyn_smem, int cluster) {
   struct Entry {
     int device;

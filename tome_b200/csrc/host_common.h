@@ -30,6 +30,11 @@ int32_t current_device_info(DeviceInfo* out);
 // can hold at once; 0 if the query fails.  Cached per (device, kernel, cluster); thread-safe.
 int max_active_clusters(const void* kernel, int threads, int dyn_smem, int cluster);
 
+// Makes sure `kernel` may be launched with `bytes` of dynamic shared memory on the current
+// device.  The attribute is set once per (device, kernel) and remembered (thread-safe), which
+// keeps cudaFuncSetAttribute out of the per-call path.
+int32_t ensure_dynamic_smem(const void* kernel, int bytes);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline bool temperature_ok(float t) { return t > 0.0f && t <= 3.0e38f; }

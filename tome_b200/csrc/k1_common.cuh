@@ -77,11 +77,13 @@ struct K1Params {
   int32_t seq_len;         // DUAL
   int64_t packed_capacity; // RAGGED: entries the packed target/output arrays can hold
   int32_t* out_offsets;    // RAGGED: int32 [n_seq + 1], start of each sequence in the packed output
-  const float* row_thr;    // SAMPLE: per-row value threshold
-  int32_t* cand_count;     // SAMPLE: per-row number of vectors appended (cand_cap + 1: overflow)
-  uint4* cand_vec;         // SAMPLE: [rows, cand_cap] 16-byte vectors holding a candidate
-  int32_t* cand_idx;       // SAMPLE: [rows, cand_cap] their positions in the row, in 16-byte units
-  int32_t cand_cap;
+  float* row_thr;          // SAMPLE: out, per row the final threshold (>= top_k logits reach it)
+  int32_t* cand_count;     // SAMPLE: [rows, lists] vectors appended per list (cand_cap + 1: overflow)
+  uint4* cand_vec;         // SAMPLE: [rows, lists, cand_cap] 16-byte vectors holding a candidate
+  int32_t* cand_idx;       // SAMPLE: [rows, lists, cand_cap] their positions in the row, in 16-byte units
+  int32_t cand_cap;        // SAMPLE: entries per list (lists per row = consumer warps)
+  int32_t sample_q;        // SAMPLE: ceil(top_k / consumer warps), 1 .. 32
+  int32_t* zero_word;      // SAMPLE: nullable, a word the kernel sets to 0
   int32_t* status;         // nullable
   int32_t chunk_bytes;     // bulk-copy size (multiple of 16, <= K1_CHUNK_BYTES), set by launch
   int32_t n_chunks;        // bulk copies per row

@@ -40,15 +40,17 @@ namespace tome {
 constexpr int K1_FULL_STAGES = K1_CFG_FULL_STAGES;
 __host__ __device__ constexpr int k1_stages(int mode) { return mode == K1_FULL ? K1_FULL_STAGES : K1_STAGES; }
 
-// SAMPLE mode: the 16-byte vectors holding a logit that reaches the row's threshold are gathered
-// in shared memory, whole (one shared-memory atomic and two stores per vector; unpacking them
-// here cost ~600 warp-cycles per vector, and a global atomic per candidate a memory round
-// trip), and copied out once per row.
-constexpr int K1_SAMPLE_LIST = 256;
+// SAMPLE mode: the 16-byte vectors holding a logit that reaches the row's current threshold are
+// gathered in shared memory, whole, in one list per consumer warp: the warp's lanes place
+// their vectors with a ballot and a register counter (no atomic, no memory round trip), and
+// the warp copies its list out once per row.  (Earlier forms: unpacking the vectors here cost
+// ~600 warp-cycles each; one list per CTA filled through a shared-memory atomic stalled a warp
+// for the atomic's round trip at every second step of the loop.)
+constexpr int K1_SAMPLE_WARP_LIST = 64;
 struct K1SampleSmem {
-  uint4 vec[K1_SAMPLE_LIST];
-  int32_t idx[K1_SAMPLE_LIST];  // index of the vector within the row (16-byte units)
-  int32_t count[2];             // by row parity: the other one is reset while this one is read
+  uint4 vec[K1_CONSUMER_WARPS][K1_SAMPLE_WARP_LIST];
+  int32_t idx[K1_CONSUMER_WARPS][K1_SAMPLE_WARP_LIST];  // index of the vector within the row (16-byte units)
+  float pub[2][K1_CONSUMER_WARPS];  // threshold refinement: one certified value per warp
 };
 
 template <int STAGES>
@@ -89,11 +91,7 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       mbar_init(empty_bar + i * 8, K1_CONSUMER_WARPS);
     }
     fence_mbar_init();
-    if (MODE == K1_SAMPLE) {
-      K1SampleSmem* smp0 = reinterpret_cast<K1SampleSmem*>(smem + Smem::SAMPLE_OFF);
-      smp0->count[0] = 0;
-      smp0->count[1] = 0;
-    }
+    if (MODE == K1_SAMPLE && blockIdx.x == 0 && p.zero_word != nullptr) *p.zero_word = 0;
   }
   int64_t n_items = p.n_rows;
   if (WINDOWED) {
@@ -155,10 +153,15 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
   }
 
   // ---------------- consumers
+  // A consumer whose wait ran out (`dead`) stops touching the ring's data but stays in step
+  // with the others: it keeps arriving on the empty barriers and on the named barriers, so
+  // that nobody is left waiting for it; its rows are redone by exact_row() or come out NaN.
   const int ctid = threadIdx.x;  // 0 .. K1_CONSUMERS-1
   uint32_t it = 0;
   uint32_t red_it = 0;
   float carry = 0.0f;
+  bool dead = false;
+  uint32_t refinements = 0;  // SAMPLE: threshold updates so far (their parity picks the buffer)
   for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
     const int64_t row = WINDOWED ? dual_row_of_item(p, cum, item) : item;
     const int64_t oidx = (MODE == K1_RAGGED) ? item : row;  // where targets/outputs live
@@ -183,34 +186,72 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       T* dst = nullptr;
       if (MODE == K1_FULL) dst = reinterpret_cast<T*>(p.out_full) + row * p.out_stride;
 
-      // SAMPLE: vectors holding a logit that reaches the row's threshold (found by an earlier
-      // kernel) are appended to the row's list; a later kernel unpacks, ranks and draws.
+      // SAMPLE: the row's threshold is a value that at least top_k of its logits reach.  Every
+      // consumer keeps the maximum of the logits it has seen (128 disjoint groups); a warp
+      // certifies the q-th largest of its 32 lane maxima, q = ceil(top_k / warps), and the
+      // smallest of the warps' values is reached by at least top_k logits.  The first chunk is
+      // looked at twice (maxima first), later the threshold is raised after chunks 1, 3, 7, ...
+      // (each time the sample has doubled), which keeps the candidates near 100 per row.
+      // Vectors holding a logit that reaches the threshold of the moment go to the warp's list;
+      // a later kernel unpacks them, keeps what reaches the final threshold, ranks and draws.
       K1SampleSmem& smp = *reinterpret_cast<K1SampleSmem*>(smem + Smem::SAMPLE_OFF);
-      int32_t* smp_count = &smp.count[red_it & 1u];
       float thr_val = __int_as_float(0x7f800000);  // +inf: nothing qualifies
-      if (MODE == K1_SAMPLE) thr_val = p.row_thr[row];
-      auto collect = [&](uint4 q, int64_t vec_index) {
-        const int32_t slot = atomicAdd(smp_count, 1);
-        if (slot < K1_SAMPLE_LIST) {
-          smp.vec[slot] = q;
-          smp.idx[slot] = static_cast<int32_t>(vec_index);
+      float tmax = __int_as_float(0xff800000);     // largest logit this thread has seen
+      int32_t wcount = 0;                          // vectors in this warp's list (same in every lane)
+      auto append = [&](bool hit, uint4 q, int64_t vec_index) {
+        const uint32_t bal = __ballot_sync(0xffffffffu, hit);
+        if (hit) {
+          const int32_t slot = wcount + __popc(bal & ((1u << lane) - 1u));
+          if (slot < K1_SAMPLE_WARP_LIST) {
+            smp.vec[warp][slot] = q;
+            smp.idx[warp][slot] = static_cast<int32_t>(vec_index);
+          }
         }
+        wcount += __popc(bal);
+      };
+      auto refine = [&]() {
+        float x = tmax;  // bitonic sort of the lane maxima, largest in lane 0
+#pragma unroll
+        for (int kb = 2; kb <= 32; kb <<= 1) {
+#pragma unroll
+          for (int j = kb >> 1; j > 0; j >>= 1) {
+            const float o = __shfl_xor_sync(0xffffffffu, x, j);
+            const bool keep_max = ((lane & j) == 0) == ((lane & kb) == 0);
+            x = keep_max ? fmaxf(x, o) : fminf(x, o);
+          }
+        }
+        const float mine = __shfl_sync(0xffffffffu, x, p.sample_q - 1);
+        float* pub = smp.pub[refinements & 1u];
+        if (lane == 0) pub[warp] = mine;
+        named_bar_sync(2, K1_CONSUMERS);
+        float t = pub[0];
+#pragma unroll
+        for (int w = 1; w < K1_CONSUMER_WARPS; ++w) t = fminf(t, pub[w]);
+        ++refinements;
+        thr_val = t;  // never below the previous one: the lane maxima only grow
       };
 
       for (int64_t k = 0; k < n_chunks; ++k, ++it) {
         const uint32_t stage = it % STAGES;
         const uint32_t phase = (it / STAGES) & 1u;
-        if (!mbar_wait(full_bar + stage * 8, phase)) {
+        if (!dead && !mbar_wait(full_bar + stage * 8, phase)) {
           raise_status(p.status, TOME_DEV_TIMEOUT);
-          return;
+          dead = true;
         }
         const int64_t off = k * chunk_bytes;
         const uint32_t bytes = static_cast<uint32_t>(min(chunk_bytes, bulk_bytes - off));
-        const uint32_t nvec = bytes >> 4;
+        const uint32_t nvec = dead ? 0u : (bytes >> 4);
         const uint32_t sbase = smem_base + stage * K1_CHUNK_BYTES;
-        uint32_t v = ctid;
+        if (MODE == K1_SAMPLE && k == 0) {
+          for (uint32_t v = ctid; v < nvec; v += K1_CONSUMERS)
+            tmax = fmaxf(tmax, vec_max(lds128(sbase + v * 16), T()));
+          refine();
+        }
+        // the loops run on the warp's first vector so that every lane makes the same trips
+        uint32_t vb = warp * 32;
         if (reduce_pass) {
-          for (; v + 3 * K1_CONSUMERS < nvec; v += 4 * K1_CONSUMERS) {
+          for (; vb + 3 * K1_CONSUMERS + 32 <= nvec; vb += 4 * K1_CONSUMERS) {
+            const uint32_t v = vb + lane;
             const uint4 a = lds128(sbase + v * 16);
             const uint4 b = lds128(sbase + (v + K1_CONSUMERS) * 16);
             const uint4 cc = lds128(sbase + (v + 2 * K1_CONSUMERS) * 16);
@@ -220,21 +261,36 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
             const float mc = fast_update<POLY>(fs, cc, p.c, T());
             const float md = fast_update<POLY>(fs, d, p.c, T());
             if (MODE == K1_SAMPLE) {
-              const int64_t v0 = (off >> 4) + v;  // this thread's first vector within the row
-              if (ma >= thr_val) collect(a, v0);
-              if (mb >= thr_val) collect(b, v0 + K1_CONSUMERS);
-              if (mc >= thr_val) collect(cc, v0 + 2 * K1_CONSUMERS);
-              if (md >= thr_val) collect(d, v0 + 3 * K1_CONSUMERS);
+              // a NaN maximum (a vector holding a NaN) counts as a hit and is sorted out later
+              const bool ha = !(ma < thr_val), hb = !(mb < thr_val);
+              const bool hc = !(mc < thr_val), hd = !(md < thr_val);
+              tmax = fmaxf(fmaxf(tmax, fmaxf(ma, mb)), fmaxf(mc, md));
+              if (__any_sync(0xffffffffu, ha || hb || hc || hd)) {
+                const int64_t v0 = (off >> 4) + v;  // this thread's first vector within the row
+                append(ha, a, v0);
+                append(hb, b, v0 + K1_CONSUMERS);
+                append(hc, cc, v0 + 2 * K1_CONSUMERS);
+                append(hd, d, v0 + 3 * K1_CONSUMERS);
+              }
             }
           }
-          for (; v < nvec; v += K1_CONSUMERS) {
-            const uint4 a = lds128(sbase + v * 16);
-            const float ma = fast_update<POLY>(fs, a, p.c, T());
-            if (MODE == K1_SAMPLE && ma >= thr_val) collect(a, (off >> 4) + v);
+          for (; vb < nvec; vb += K1_CONSUMERS) {
+            const uint32_t v = vb + lane;
+            uint4 a = make_uint4(0u, 0u, 0u, 0u);
+            bool hit = false;
+            if (v < nvec) {
+              a = lds128(sbase + v * 16);
+              const float ma = fast_update<POLY>(fs, a, p.c, T());
+              if (MODE == K1_SAMPLE) {
+                hit = !(ma < thr_val);
+                tmax = fmaxf(tmax, ma);
+              }
+            }
+            if (MODE == K1_SAMPLE && __any_sync(0xffffffffu, hit)) append(hit, a, (off >> 4) + v);
           }
         } else {
           uint8_t* drow = reinterpret_cast<uint8_t*>(dst) + off;
-          for (; v < nvec; v += K1_CONSUMERS) {
+          for (uint32_t v = ctid; v < nvec; v += K1_CONSUMERS) {
             const uint4 a = lds128(sbase + v * 16);
             stg128_streaming(drow + static_cast<size_t>(v) * 16,
                              full_out_vec(a, p.inv_temp, lse_row, T()));
@@ -242,27 +298,30 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar + stage * 8);
+        // the sample has doubled: raise the threshold (not after the row's last chunk)
+        if (MODE == K1_SAMPLE && k >= 1 && ((k + 1) & k) == 0 && k + 1 < n_chunks) refine();
       }
 
       Online st = fast_finish(fs, p.c);
+      if (dead) st.s = __int_as_float(0x7fc00000);  // the row takes the exact path below
       // elements past the last 16-byte boundary of the row (at most PER_VEC - 1)
       if (ctid == 0) {
         for (int64_t j = tail_begin; j < p.vocab; ++j) {
           if (reduce_pass) online_update_scalar(st, to_float(src[j]), p.c);
           else dst[j] = full_out_scalar(src[j], p.inv_temp, lse_row);
         }
-        if (MODE == K1_SAMPLE && tail_begin < p.vocab) {
-          // the tail travels as one vector padded with -inf (tail_begin is a multiple of PER_VEC)
-          __align__(16) T pad[PER_VEC];
-          float tail_max = __int_as_float(0xff800000);
-          for (int j = 0; j < PER_VEC; ++j) {
-            const bool have = tail_begin + j < p.vocab;
-            const float x = have ? to_float(src[tail_begin + j]) : __int_as_float(0xff800000);
-            pad[j] = have ? src[tail_begin + j] : from_float_neg_inf(T());
-            tail_max = fmaxf(tail_max, x);
-          }
-          if (tail_max >= thr_val) collect(*reinterpret_cast<const uint4*>(pad), tail_begin / PER_VEC);
+      }
+      if (MODE == K1_SAMPLE && warp == 0 && tail_begin < p.vocab) {
+        // the tail travels as one vector padded with -inf (tail_begin is a multiple of PER_VEC)
+        __align__(16) T pad[PER_VEC];
+        float tail_max = __int_as_float(0xff800000);
+        for (int j = 0; j < PER_VEC; ++j) {
+          const bool have = tail_begin + j < p.vocab;
+          pad[j] = have ? src[tail_begin + j] : from_float_neg_inf(T());
+          tail_max = fmax_nan(tail_max, to_float(pad[j]));
         }
+        append(lane == 0 && !(tail_max < thr_val), *reinterpret_cast<const uint4*>(pad),
+               tail_begin / PER_VEC);
       }
 
       if (reduce_pass) {
@@ -286,19 +345,17 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
             emit_row<MODE>(p, oidx, sub, m, s, x_t, target_ok, carry);
         }
         if (MODE == K1_SAMPLE) {
-          // every consumer has passed the barrier above, so the list is complete: copy it out,
-          // reset the other counter for the next row, and let nobody start that row before
-          const int32_t n = *reinterpret_cast<volatile int32_t*>(smp_count);
-          const int32_t keep = min(n, min(K1_SAMPLE_LIST, p.cand_cap));
-          for (int32_t i = ctid; i < keep; i += K1_CONSUMERS) {
-            p.cand_vec[row * p.cand_cap + i] = smp.vec[i];
-            p.cand_idx[row * p.cand_cap + i] = smp.idx[i];
+          // each warp copies its own list out; nothing here waits for another warp
+          const int32_t keep = min(wcount, min(K1_SAMPLE_WARP_LIST, p.cand_cap));
+          const int64_t base = (row * K1_CONSUMER_WARPS + warp) * p.cand_cap;
+          for (int32_t i = lane; i < keep; i += 32) {
+            p.cand_vec[base + i] = smp.vec[warp][i];
+            p.cand_idx[base + i] = smp.idx[warp][i];
           }
-          if (ctid == 0) {
-            p.cand_count[row] = (n > keep) ? p.cand_cap + 1 : n;  // more than kept: overflow
-            smp.count[(red_it & 1u) ^ 1u] = 0;
-          }
-          named_bar_sync(2, K1_CONSUMERS);
+          if (lane == 0)  // more than kept: overflow
+            p.cand_count[row * K1_CONSUMER_WARPS + warp] = (wcount > keep) ? p.cand_cap + 1 : wcount;
+          if (ctid == 0) p.row_thr[row] = thr_val;
+          __syncwarp();  // the list is reused by the next row
         }
         ++red_it;
       }
@@ -459,9 +516,7 @@ static int32_t k1_launch_typed(const K1Params& p_in, bool bulk_ok, int64_t max_i
       return fail(TOME_ERR_UNSUPPORTED, "device offers %d bytes of shared memory, need %d",
                   info.max_smem_optin, smem);
     void (*kernel)(K1Params) = pick_stream_kernel<T, MODE>();
-    st = check_cuda(
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
-        "cudaFuncSetAttribute");
+    st = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     if (st != TOME_OK) return st;
     int64_t ctas_per_sm = K1_CTAS_PER_SM;
     if (MODE == K1_FULL) {
@@ -680,11 +735,12 @@ bool k1_sample_eligible(const void* logits, int32_t dtype, int64_t vocab, int64_
 }
 
 int32_t k1_launch_sample(const void* logits, int32_t dtype, int64_t rows, int64_t vocab,
-                         int64_t row_stride, float temperature, const float* row_thr,
+                         int64_t row_stride, float temperature, int32_t top_k, float* row_thr,
                          int32_t* cand_count, uint4* cand_vec, int32_t* cand_idx,
-                         int32_t cand_cap, float* out_lse, int32_t* dev_status,
-                         cudaStream_t stream) {
+                         int32_t cand_cap, float* out_lse, int32_t* zero_word,
+                         int32_t* dev_status, cudaStream_t stream) {
   K1Params p = {};
+  p.zero_word = zero_word;
   p.src[0] = logits;
   p.n_rows = rows;
   p.vocab = vocab;
@@ -698,8 +754,12 @@ int32_t k1_launch_sample(const void* logits, int32_t dtype, int64_t rows, int64_
   p.cand_vec = cand_vec;
   p.cand_idx = cand_idx;
   p.cand_cap = cand_cap;
+  const int64_t kk = std::max<int64_t>(1, std::min<int64_t>(top_k, vocab));
+  p.sample_q = static_cast<int32_t>((kk + K1_CONSUMER_WARPS - 1) / K1_CONSUMER_WARPS);
   p.status = dev_status;
   return k1_launch<K1_SAMPLE>(p, dtype, true, rows, stream);
 }
+
+int k1_sample_lists_per_row() { return K1_CONSUMER_WARPS; }
 
 }  // namespace tome

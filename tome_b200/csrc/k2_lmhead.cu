@@ -647,9 +647,7 @@ static int32_t k2_launch(const void* hidden, const void* weight, int64_t rows, i
   p.status = dev_status;
   if (pair) {
     constexpr int smem = K2Cfg<true>::SMEM_BYTES;
-    st = check_cuda(cudaFuncSetAttribute(k2_lmhead_kernel<true>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
-                    "cudaFuncSetAttribute(k2 pair)");
+    st = ensure_dynamic_smem(reinterpret_cast<const void*>(k2_lmhead_kernel<true>), smem);
     if (st != TOME_OK) return st;
     const int pairs = static_cast<int>(
         std::max<int64_t>(1, std::min<int64_t>(info.sm_count / 2, pl.n_items)));
@@ -669,9 +667,7 @@ static int32_t k2_launch(const void* hidden, const void* weight, int64_t rows, i
                       "k2 pair launch");
   }
   constexpr int smem = K2Cfg<false>::SMEM_BYTES;
-  st = check_cuda(cudaFuncSetAttribute(k2_lmhead_kernel<false>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
-                  "cudaFuncSetAttribute(k2)");
+  st = ensure_dynamic_smem(reinterpret_cast<const void*>(k2_lmhead_kernel<false>), smem);
   if (st != TOME_OK) return st;
   const int grid =
       static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(info.sm_count, pl.n_items)));

@@ -41,8 +41,10 @@ constexpr int K4_GROUPS = K4_THREADS / 4;  // sample maxima kept for the thresho
 constexpr int K4_RANK_MAX = 1024;  // above this many candidates, compact before ranking
 constexpr int K4_MAX_SWEEPS = 64;   // re-sweeps with a tightened threshold before giving up
 constexpr int64_t K4_STREAM_MIN_ROWS = 320;    // from here on a batch takes the three-kernel path
-constexpr int64_t K4_STREAM_MIN_VOCAB = 4096;  // its threshold kernel wants full groups
-constexpr int K4_LIST_CAP = 256;               // candidates kept per row on that path
+constexpr int64_t K4_STREAM_MIN_VOCAB = 4096;  // every consumer of the streaming kernel sees logits
+constexpr int K4_LIST_CAP = 64;                // vectors kept per list on that path
+constexpr int K4_MAX_LISTS = 8;                // lists per row (one per consumer warp of the streaming kernel)
+constexpr int K4_CODE_CAP = 256;               // logits of a row that may reach its final threshold
 constexpr int K4_LIST_THREADS = 128;
 constexpr int K4_SPLIT_MAX = 8;               // CTAs of a cluster that may share one row
 constexpr int64_t K4_SPLIT_MIN_VOCAB = 16384; // shorter rows stay with one CTA
@@ -57,8 +59,9 @@ struct K4Params {
   float* out_logprob;
   int32_t* out_topk_idx;  // nullable, [rows, top_k]
   float* out_topk_val;    // nullable, [rows, top_k]
-  int32_t only_flagged;   // redo only the rows whose token is -1 (left over by the streaming kernel)
-  int32_t* marked;        // with only_flagged: how many rows were marked (0: nothing to do)
+  int32_t only_flagged;   // redo only the rows listed in marked_rows (left over by the streaming path)
+  int32_t* marked;        // with only_flagged: how many rows are listed (0: nothing to do)
+  int32_t* marked_rows;   // with only_flagged: their indices
   int32_t* status;
 };
 
@@ -179,7 +182,7 @@ __device__ __forceinline__ void k4_sweep(const T* src, int64_t V, int64_t base, 
     for (int64_t v = threadIdx.x; v < nvec; v += K4_THREADS) {
       const uint4 q = __ldg(vp + v);
       const float vmax = SOFTMAX ? fast_update<0>(fs, q, c, T()) : vec_max(q, T());
-      if (vmax >= thr_val) {
+      if (!(vmax < thr_val)) {  // a NaN maximum (bf16 vector holding a NaN): look inside
         const uint32_t w[4] = {q.x, q.y, q.z, q.w};
         const int64_t i0 = v * PER;
 #pragma unroll
@@ -231,7 +234,8 @@ __device__ void k4_exact_row(const T* src, int64_t V, float c, K4Smem& sm, float
 
 // Works through `V` logits starting at `src` (a whole row, or one CTA's part of a split row;
 // `base` = index of src[0] within the row).  Afterwards sm.top[0 .. kk) holds the exact top-kk
-// of the part, best first (kk = min(k, V)), and every thread has the part's (max, sum-exp).
+// of the part, best first, and every thread has the part's (max, sum-exp).  kk = min(k, V),
+// or the number of logits that are not NaN if that is smaller (NaN is never a candidate).
 template <typename T>
 __device__ void k4_segment(const T* src, const int64_t V, const int64_t base, const int32_t k,
                            const float c, K4Smem& sm, int32_t* status, int32_t& kk_out,
@@ -239,7 +243,6 @@ __device__ void k4_segment(const T* src, const int64_t V, const int64_t base, co
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   const int32_t kk = static_cast<int32_t>(min(static_cast<int64_t>(k), V));
-  kk_out = kk;
 
   // ---- first threshold: the leading K4_SAMPLE logits are cut into 128 groups (4 adjacent
   //      threads each); the kk-th largest group maximum is a value that at least kk logits
@@ -349,7 +352,9 @@ __device__ void k4_segment(const T* src, const int64_t V, const int64_t base, co
     k4_compact(sm, n, kk);
     n = kk;
   }
-  k4_rank_top(sm, n, kk);
+  const int32_t have = min(kk, n);  // n < kk: the part holds fewer than kk logits that are not NaN
+  k4_rank_top(sm, n, have);
+  kk_out = have;
   __syncthreads();
 }
 
@@ -359,9 +364,15 @@ __device__ void k4_finish_row(const K4Params& p, K4Smem& sm, int64_t row, int32_
   const int tid = threadIdx.x;
   const int32_t k = p.top_k;
   if (tid == 0) {
-    const int32_t pick = greedy ? 0 : k4_draw(sm.top, kk, c, row, p.seed, p.offset);
-    p.out_tokens[row] = k4_index(sm.top[pick]);
-    p.out_logprob[row] = __fdiv_rn(k4_value(sm.top[pick]), temp) - lse;
+    if (kk > 0) {
+      const int32_t pick = greedy ? 0 : k4_draw(sm.top, kk, c, row, p.seed, p.offset);
+      p.out_tokens[row] = k4_index(sm.top[pick]);
+      p.out_logprob[row] = __fdiv_rn(k4_value(sm.top[pick]), temp) - lse;
+    } else {  // a row of NaNs: nothing to draw from
+      p.out_tokens[row] = -1;
+      p.out_logprob[row] = __int_as_float(0x7fc00000);
+      if (p.status != nullptr) atomicOr(p.status, TOME_DEV_NO_CANDIDATE);
+    }
   }
   if (p.out_topk_idx != nullptr || p.out_topk_val != nullptr) {
     for (int32_t j = tid; j < k; j += K4_THREADS) {
@@ -381,9 +392,9 @@ __global__ void __launch_bounds__(K4_THREADS) k4_sample_kernel(const K4Params p)
   const float temp = greedy ? 1.0f : p.temperature;  // temperature of the reported log-prob
   const float c = LOG2E / temp;
 
-  if (p.only_flagged && p.marked != nullptr && *p.marked == 0) return;
-  for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
-    if (p.only_flagged && p.out_tokens[row] != -1) continue;  // uniform across the CTA
+  const int64_t n_items = p.only_flagged ? static_cast<int64_t>(*p.marked) : p.rows;
+  for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int64_t row = p.only_flagged ? static_cast<int64_t>(p.marked_rows[item]) : item;
     const T* src = reinterpret_cast<const T*>(p.logits) + row * p.stride;
     int32_t kk;
     float row_m, row_s;
@@ -445,7 +456,9 @@ __global__ void __launch_bounds__(K4_THREADS, 2) k4_sample_split_kernel(const K4
   }
   __syncthreads();
   const int32_t n = sm.count;
-  const int32_t kk_row = static_cast<int32_t>(min(static_cast<int64_t>(p.top_k), p.vocab));
+  // fewer survivors than top_k: the row holds fewer logits that are not NaN
+  const int32_t kk_row =
+      min(n, static_cast<int32_t>(min(static_cast<int64_t>(p.top_k), p.vocab)));
   __syncthreads();
   k4_rank_top(sm, n, kk_row);
   __syncthreads();
@@ -454,48 +467,21 @@ __global__ void __launch_bounds__(K4_THREADS, 2) k4_sample_split_kernel(const K4
 }
 
 // ------------------------------------------------------------------ large batches
-// Three kernels, so that the pass over the logits is a plain streaming pass:
-//   1. k4_threshold_kernel: per row, the kk-th largest of 128 group maxima over the leading
-//      K4_SAMPLE logits (a value that at least kk logits reach); zeroes the row's counter;
-//   2. the streaming kernel's SAMPLE mode (k1_logprob.cu): one pass at HBM speed that keeps
-//      (max, sum-exp) and appends the logits reaching the threshold to the row's list;
-//   3. k4_finish_kernel: ranks the row's list (exact top-kk), draws, scores, writes.
-// A row whose list overflowed (sorted or heavily tied rows) is marked with token -1 and redone
-// by k4_sample_kernel (only_flagged).  Same tokens as the other kernels of this file.
+// Two kernels, so that the pass over the logits is a plain streaming pass:
+//   1. the streaming kernel's SAMPLE mode (k1_logprob.cu): one pass at HBM speed that keeps
+//      (max, sum-exp), derives the row's threshold (a value that at least kk logits reach)
+//      from the logits as they pass and gathers the 16-byte vectors holding a logit that
+//      reaches it into a few lists per row;
+//   2. k4_finish_kernel: unpacks the row's vectors, keeps the logits that reach the final
+//      threshold, ranks them (exact top-kk), draws, scores, writes.
+// A row whose lists ran over (sorted or heavily tied rows) or that holds fewer than kk logits
+// that are not NaN is put on a list and redone by k4_sample_kernel (only_flagged).  Same tokens
+// as the other kernels of this file.
 template <typename T>
 __global__ void __launch_bounds__(K4_LIST_THREADS)
-k4_threshold_kernel(const T* logits, int64_t rows, int64_t vocab, int64_t stride, int32_t kk,
-                    float* row_thr, int32_t* cand_count, int32_t* marked) {
-  __shared__ uint32_t keys[K4_LIST_THREADS];
-  if (blockIdx.x == 0 && threadIdx.x == 0) *marked = 0;
-  constexpr int PER = 16 / static_cast<int>(sizeof(T));
-  const int tid = threadIdx.x;
-  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-    const uint4* vp = reinterpret_cast<const uint4*>(logits + row * stride);
-    const int64_t nvec = min(static_cast<int64_t>(K4_SAMPLE), vocab) / PER;  // >= K4_LIST_THREADS
-    float lmax = __int_as_float(0xff800000);
-#pragma unroll 8
-    for (int64_t v = tid; v < nvec; v += K4_LIST_THREADS) lmax = fmaxf(lmax, vec_max(__ldg(vp + v), T()));
-    keys[tid] = k4_key(lmax);
-    if (tid == 0) cand_count[row] = 0;
-    __syncthreads();
-    const uint32_t mine = keys[tid];
-    int32_t rank = 0;
-#pragma unroll 8
-    for (int j = 0; j < K4_LIST_THREADS; ++j) {
-      const uint32_t o = keys[j];
-      rank += (o > mine || (o == mine && j < tid)) ? 1 : 0;
-    }
-    if (rank == kk - 1) row_thr[row] = lmax;
-    __syncthreads();
-  }
-}
-
-template <typename T>
-__global__ void __launch_bounds__(K4_LIST_THREADS)
-k4_finish_kernel(const K4Params p, const float* row_thr, const float* lse,
+k4_finish_kernel(const K4Params p, const int lists, const float* row_thr, const float* lse,
                  const int32_t* cand_count, const uint4* cand_vec, const int32_t* cand_idx) {
-  __shared__ unsigned long long list[K4_LIST_CAP];
+  __shared__ unsigned long long list[K4_CODE_CAP];
   __shared__ unsigned long long top[K4_MAX_K];
   __shared__ int32_t list_n;
   constexpr int PER = 16 / static_cast<int>(sizeof(T));
@@ -506,40 +492,41 @@ k4_finish_kernel(const K4Params p, const float* row_thr, const float* lse,
   const int32_t k = p.top_k;
   const int32_t kk = static_cast<int32_t>(min(static_cast<int64_t>(k), p.vocab));
   for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
-    const int32_t n_vec = cand_count[row];
     if (tid == 0) list_n = 0;
     __syncthreads();
-    // unpack the row's vectors: the logits that reach the threshold are the candidates
-    if (n_vec <= K4_LIST_CAP) {
-      const float thr = row_thr[row];
-      for (int32_t i = tid; i < n_vec; i += K4_LIST_THREADS) {
-        const uint4 q = cand_vec[row * K4_LIST_CAP + i];
-        const int64_t e0 = static_cast<int64_t>(cand_idx[row * K4_LIST_CAP + i]) * PER;
-        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    // unpack the row's vectors: the logits that reach the final threshold are the candidates
+    const float thr = row_thr[row];
+    bool overflow = false;
+    for (int32_t slot = tid; slot < lists * K4_LIST_CAP; slot += K4_LIST_THREADS) {
+      const int32_t l = slot / K4_LIST_CAP, i = slot - l * K4_LIST_CAP;
+      const int32_t n_vec = cand_count[row * lists + l];
+      overflow |= (n_vec > K4_LIST_CAP);
+      if (i >= n_vec) continue;
+      const int64_t at = (row * lists + l) * K4_LIST_CAP + i;
+      const uint4 q = cand_vec[at];
+      const int64_t e0 = static_cast<int64_t>(cand_idx[at]) * PER;
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-        for (int j = 0; j < PER; ++j) {
-          const float x = (sizeof(T) == 4)
-                              ? __uint_as_float(w[j])
-                              : __uint_as_float((j & 1) ? (w[j >> 1] & 0xffff0000u) : (w[j >> 1] << 16));
-          if (e0 + j < p.vocab && x >= thr) {
-            const int32_t slot = atomicAdd(&list_n, 1);
-            if (slot < K4_LIST_CAP) list[slot] = k4_pack(x, e0 + j);
-          }
+      for (int j = 0; j < PER; ++j) {
+        const float x = (sizeof(T) == 4)
+                            ? __uint_as_float(w[j])
+                            : __uint_as_float((j & 1) ? (w[j >> 1] & 0xffff0000u) : (w[j >> 1] << 16));
+        if (e0 + j < p.vocab && x >= thr) {
+          const int32_t at_list = atomicAdd(&list_n, 1);
+          if (at_list < K4_CODE_CAP) list[at_list] = k4_pack(x, e0 + j);
         }
       }
     }
-    __syncthreads();
+    const bool any_overflow = __syncthreads_or(overflow ? 1 : 0) != 0;
     const int32_t n = list_n;
-    if (n_vec > K4_LIST_CAP || n > K4_LIST_CAP || n < kk) {
-      // overflow (sorted or heavily tied rows) or a row of NaNs: left to the row kernel
-      if (tid == 0) {
-        p.out_tokens[row] = -1;
-        atomicAdd(p.marked, 1);
-      }
+    if (any_overflow || n > K4_CODE_CAP || n < kk) {
+      // lists that ran over (sorted or heavily tied rows) or a row with too few logits that
+      // are not NaN: left to the row kernel
+      if (tid == 0) p.marked_rows[atomicAdd(p.marked, 1)] = static_cast<int32_t>(row);
       __syncthreads();
       continue;
     }
-    constexpr int MINE = K4_LIST_CAP / K4_LIST_THREADS;
+    constexpr int MINE = K4_CODE_CAP / K4_LIST_THREADS;
     unsigned long long code[MINE];
     int32_t rank[MINE];
 #pragma unroll
@@ -575,36 +562,38 @@ k4_finish_kernel(const K4Params p, const float* row_thr, const float* lse,
   }
 }
 
-// Scratch layout of the three-kernel path: thresholds, logsumexps and counters per row, then
-// the candidate lists.
+// Scratch layout of the streaming path: per row the threshold, the logsumexp, a slot of the
+// list of rows to redo and the list counters; one counter for the batch; then the lists.
 struct K4Workspace {
   float* thr;
   float* lse;
-  int32_t* count;
+  int32_t* marked_rows;
+  int32_t* count;   // [rows, lists]
   int32_t* marked;  // one counter for the batch
-  uint4* cand_vec;  // [rows, K4_LIST_CAP] vectors holding a candidate
+  uint4* cand_vec;  // [rows, lists, K4_LIST_CAP] vectors holding a candidate
   int32_t* cand_idx;
 };
-static size_t k4_workspace_head(int64_t rows) {
-  return (static_cast<size_t>(rows) * 12 + 4 + 15) & ~static_cast<size_t>(15);
+static size_t k4_workspace_head(int64_t rows, int lists) {
+  return (static_cast<size_t>(rows) * (12 + 4 * lists) + 4 + 15) & ~static_cast<size_t>(15);
 }
-static size_t k4_workspace_bytes(int64_t rows) {
-  return k4_workspace_head(rows) +
-         static_cast<size_t>(rows) * K4_LIST_CAP * (sizeof(uint4) + sizeof(int32_t));
+static size_t k4_workspace_bytes(int64_t rows, int lists) {
+  return k4_workspace_head(rows, lists) +
+         static_cast<size_t>(rows) * lists * K4_LIST_CAP * (sizeof(uint4) + sizeof(int32_t));
 }
-static K4Workspace k4_workspace(void* base, int64_t rows) {
+static K4Workspace k4_workspace(void* base, int64_t rows, int lists) {
   K4Workspace w;
   uint8_t* b = static_cast<uint8_t*>(base);
   w.thr = reinterpret_cast<float*>(b);
   w.lse = w.thr + rows;
-  w.count = reinterpret_cast<int32_t*>(w.lse + rows);
-  w.marked = w.count + rows;
-  w.cand_vec = reinterpret_cast<uint4*>(b + k4_workspace_head(rows));
-  w.cand_idx = reinterpret_cast<int32_t*>(w.cand_vec + rows * K4_LIST_CAP);
+  w.marked_rows = reinterpret_cast<int32_t*>(w.lse + rows);
+  w.count = w.marked_rows + rows;
+  w.marked = w.count + rows * lists;
+  w.cand_vec = reinterpret_cast<uint4*>(b + k4_workspace_head(rows, lists));
+  w.cand_idx = reinterpret_cast<int32_t*>(w.cand_vec + rows * lists * K4_LIST_CAP);
   return w;
 }
 
-// Whether a batch takes the three-kernel path (given scratch): large batches of rows that the
+// Whether a batch takes the streaming path (given scratch): large batches of rows that the
 // streaming kernel can read.  TOME_K4_STREAM = 1 / 0 forces it on (where possible) / off.
 static bool k4_wants_stream(int64_t rows, int64_t vocab) {
   if (vocab < K4_STREAM_MIN_VOCAB) return false;
@@ -660,10 +649,12 @@ static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, i
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool streamed = workspace != nullptr && k4_wants_stream(rows, vocab) &&
                         k1_sample_eligible(logits, dtype, vocab, row_stride);
+  const int lists = k1_sample_lists_per_row();
   if (streamed) {
-    if (ws_bytes < k4_workspace_bytes(rows))
+    if (lists > K4_MAX_LISTS) return fail(TOME_ERR_UNSUPPORTED, "%d lists per row", lists);
+    if (ws_bytes < k4_workspace_bytes(rows, lists))
       return fail(TOME_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes, %zu needed", ws_bytes,
-                  k4_workspace_bytes(rows));
+                  k4_workspace_bytes(rows, lists));
     if (!aligned16(workspace)) return fail(TOME_ERR_MISALIGNED, "workspace is not 16-byte aligned");
   }
   K4Params p = {};
@@ -682,30 +673,21 @@ static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, i
   p.out_topk_val = out_topk_val;
   p.status = dev_status;
   if (streamed) {
-    const K4Workspace w = k4_workspace(workspace, rows);
+    const K4Workspace w = k4_workspace(workspace, rows, lists);
     p.marked = w.marked;
+    p.marked_rows = w.marked_rows;
     const float lse_temp = (temperature > 0.0f) ? temperature : 1.0f;
-    const int32_t kk = static_cast<int32_t>(std::min<int64_t>(top_k, vocab));
     const int grid_rows = static_cast<int>(
         std::min<int64_t>(rows, static_cast<int64_t>(info.sm_count) * 16));
-    if (dtype == TOME_F32)
-      k4_threshold_kernel<float><<<grid_rows, K4_LIST_THREADS, 0, s>>>(
-          static_cast<const float*>(logits), rows, vocab, row_stride, kk, w.thr, w.count, w.marked);
-    else
-      k4_threshold_kernel<__nv_bfloat16><<<grid_rows, K4_LIST_THREADS, 0, s>>>(
-          static_cast<const __nv_bfloat16*>(logits), rows, vocab, row_stride, kk, w.thr, w.count,
-          w.marked);
-    st = check_cuda(cudaGetLastError(), "k4 threshold launch");
-    if (st != TOME_OK) return st;
-    st = k1_launch_sample(logits, dtype, rows, vocab, row_stride, lse_temp, w.thr, w.count,
-                          w.cand_vec, w.cand_idx, K4_LIST_CAP, w.lse, dev_status, s);
+    st = k1_launch_sample(logits, dtype, rows, vocab, row_stride, lse_temp, top_k, w.thr, w.count,
+                          w.cand_vec, w.cand_idx, K4_LIST_CAP, w.lse, w.marked, dev_status, s);
     if (st != TOME_OK) return st;
     if (dtype == TOME_F32)
-      k4_finish_kernel<float><<<grid_rows, K4_LIST_THREADS, 0, s>>>(p, w.thr, w.lse, w.count,
+      k4_finish_kernel<float><<<grid_rows, K4_LIST_THREADS, 0, s>>>(p, lists, w.thr, w.lse, w.count,
                                                                     w.cand_vec, w.cand_idx);
     else
       k4_finish_kernel<__nv_bfloat16><<<grid_rows, K4_LIST_THREADS, 0, s>>>(
-          p, w.thr, w.lse, w.count, w.cand_vec, w.cand_idx);
+          p, lists, w.thr, w.lse, w.count, w.cand_vec, w.cand_idx);
     st = check_cuda(cudaGetLastError(), "k4 finish launch");
     if (st != TOME_OK) return st;
   }
@@ -713,9 +695,7 @@ static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, i
   void (*split_kernel)(K4Params, int) = (dtype == TOME_F32)
                                             ? k4_sample_split_kernel<float>
                                             : k4_sample_split_kernel<__nv_bfloat16>;
-  st = check_cuda(
-      cudaFuncSetAttribute(split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
-      "cudaFuncSetAttribute(k4 split)");
+  st = ensure_dynamic_smem(reinterpret_cast<const void*>(split_kernel), smem);
   if (st != TOME_OK) return st;
   const int split =
       streamed ? 0
@@ -737,19 +717,11 @@ static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, i
   }
   const int grid = static_cast<int>(
       std::max<int64_t>(1, std::min<int64_t>(static_cast<int64_t>(info.sm_count) * 3, rows)));
-  if (dtype == TOME_F32) {
-    st = check_cuda(cudaFuncSetAttribute(k4_sample_kernel<float>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
-                    "cudaFuncSetAttribute(k4)");
-    if (st != TOME_OK) return st;
-    k4_sample_kernel<float><<<grid, K4_THREADS, smem, s>>>(p);
-  } else {
-    st = check_cuda(cudaFuncSetAttribute(k4_sample_kernel<__nv_bfloat16>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
-                    "cudaFuncSetAttribute(k4)");
-    if (st != TOME_OK) return st;
-    k4_sample_kernel<__nv_bfloat16><<<grid, K4_THREADS, smem, s>>>(p);
-  }
+  void (*row_kernel)(K4Params) =
+      (dtype == TOME_F32) ? k4_sample_kernel<float> : k4_sample_kernel<__nv_bfloat16>;
+  st = ensure_dynamic_smem(reinterpret_cast<const void*>(row_kernel), smem);
+  if (st != TOME_OK) return st;
+  row_kernel<<<grid, K4_THREADS, smem, s>>>(p);
   return check_cuda(cudaGetLastError(), "k4 launch");
 }
 
@@ -766,7 +738,7 @@ extern "C" int32_t tome_sample_topk_logprob(const void* logits, int32_t dtype, i
 
 extern "C" size_t tome_sample_workspace_bytes(int64_t rows, int64_t vocab) {
   if (rows <= 0 || vocab <= 0 || !k4_wants_stream(rows, vocab)) return 0;
-  return k4_workspace_bytes(rows);
+  return k4_workspace_bytes(rows, k1_sample_lists_per_row());
 }
 
 extern "C" int32_t tome_sample_topk_logprob_ws(const void* logits, int32_t dtype, int64_t rows,

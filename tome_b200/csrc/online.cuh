@@ -60,8 +60,12 @@ __device__ __forceinline__ void fast_init(Fast& f, float c) {
   f.b = make_float2(0.0f, 0.0f);
 }
 
+// A NaN maximum (the bf16 overload of fast_update() propagates NaN into it) takes the branch
+// too and turns the whole state into NaN, which no later update can undo: a row that holds a
+// NaN gives NaN, as mx.logsumexp (mlx-impl/node.py:401) does, whichever exponential path
+// the NaN itself would have taken.
 __device__ __forceinline__ void fast_raise(Fast& f, float vmax, float c) {
-  if (vmax > f.m) {
+  if (!(vmax <= f.m)) {
     const float mc_new = vmax * c;
     const float r = ex2f(f.mc - mc_new);
     const float2 r2 = make_float2(r, r);
@@ -122,13 +126,15 @@ __device__ __forceinline__ float2 ex2_pair(float2 t, int slot) {
 }
 
 // 8 bf16 logits
-// (both overloads return the largest logit of the vector)
+// (both overloads return the largest logit of the vector; for bf16 it is NaN when the vector
+// holds one, because the polynomial exponentials would otherwise lose it; fp32 vectors take
+// ex2.approx for every logit, which keeps a NaN in the sum by itself)
 template <int POLY>
 __device__ __forceinline__ float fast_update(Fast& f, uint4 v, float c, __nv_bfloat16) {
-  const __nv_bfloat162 mx = __hmax2(__hmax2(as_bf162(v.x), as_bf162(v.y)),
-                                    __hmax2(as_bf162(v.z), as_bf162(v.w)));
+  const __nv_bfloat162 mx = __hmax2_nan(__hmax2_nan(as_bf162(v.x), as_bf162(v.y)),
+                                        __hmax2_nan(as_bf162(v.z), as_bf162(v.w)));
   const uint32_t mw = *reinterpret_cast<const uint32_t*>(&mx);
-  const float vmax = fmaxf(bf16_lo(mw), bf16_hi(mw));
+  const float vmax = fmax_nan(bf16_lo(mw), bf16_hi(mw));  // NaN if any of the 8 logits is
   fast_raise(f, vmax, c);
   const float2 c2 = make_float2(c, c);
   const float2 n2 = make_float2(-f.mc, -f.mc);

@@ -182,6 +182,13 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
+// Maximum that returns NaN if either operand is NaN (fmaxf drops it).
+__device__ __forceinline__ float fmax_nan(float a, float b) {
+  float d;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+  return d;
+}
+
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));

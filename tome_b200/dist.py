@@ -9,12 +9,14 @@ process, mlx-impl/node.py:966-970); parity is defined against the unsharded resu
 """
 from __future__ import annotations
 
+import time
 from typing import Optional
 
 import torch
 import torch.distributed as dist
 
 from . import ops
+from ._lib import TomeRuntimeError
 
 
 def pack_triples(m: torch.Tensor, s: torch.Tensor, t: torch.Tensor, rank: int, world: int,
@@ -36,26 +38,48 @@ def pack_triples(m: torch.Tensor, s: torch.Tensor, t: torch.Tensor, rank: int, w
     return out
 
 
-def exchange_triples(packed: torch.Tensor, group=None):
+def exchange_triples(packed: torch.Tensor, group=None, timeout_s: Optional[float] = None):
     """The single collective of the path: SUM all-reduce of the packed buffer, in place.
 
     Returns views ``(m_all [world, rows], s_all [world, rows], t_sum [1, rows])``.
+
+    With ``timeout_s`` the all-reduce is issued asynchronously and the host polls it: if it
+    has not completed after that many seconds (a peer that died or never made the call), a
+    ``TomeRuntimeError`` is raised instead of waiting for the process group's own timeout
+    (ten minutes by default).  The wait then holds the calling thread until the collective is
+    done, so use it where a stalled step must be noticed, not in a loop tuned for overlap.
+    After the error the group is in an undefined state: tear it down.
     """
     world = (packed.shape[0] - 1) // 2
     if world > 1:
-        dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
+        if timeout_s is None:
+            dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
+        else:
+            work = dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group, async_op=True)
+            deadline = time.monotonic() + float(timeout_s)
+            pause = 50e-6
+            while not work.is_completed():
+                if time.monotonic() > deadline:
+                    raise TomeRuntimeError(
+                        f"the all-reduce of the vocab-parallel head did not complete within "
+                        f"{timeout_s} s: a peer is gone or never made the call")
+                time.sleep(pause)
+                pause = min(2 * pause, 5e-3)
+            work.wait()  # completed: orders the current stream after the collective
     return packed[:world], packed[world:2 * world], packed[2 * world:]
 
 
 def lm_head_logprob_vocab_parallel(hidden: torch.Tensor, weight_shard: torch.Tensor,
                                    vocab_offset: int, ids: torch.Tensor, temp: float = 1.0,
                                    group=None, *, workspace: Optional[torch.Tensor] = None,
-                                   packed: Optional[torch.Tensor] = None):
+                                   packed: Optional[torch.Tensor] = None,
+                                   timeout_s: Optional[float] = None):
     """``(logprob, lse)`` of ``ids`` under the full-vocabulary softmax, head sharded by rows.
 
     ``weight_shard`` is this rank's ``[V_local, K]`` slice starting at global row
     ``vocab_offset``; ``ids`` are global indices.  All ranks of ``group`` must call this with
     the same ``hidden``/``ids``.  ``packed`` may be a reusable ``[2*world+1, rows]`` fp32 buffer.
+    ``timeout_s`` bounds the wait for the peers (see :func:`exchange_triples`).
     """
     if dist.is_available() and dist.is_initialized():
         world = dist.get_world_size(group)
@@ -73,7 +97,7 @@ def lm_head_logprob_vocab_parallel(hidden: torch.Tensor, weight_shard: torch.Ten
     # the kernel writes this rank's slots of the exchange buffer directly
     ops.lm_head_partials(hidden, weight_shard, vocab_offset, ids, temp, workspace=workspace,
                          out=(packed[rank], packed[world + rank], packed[2 * world]))
-    m_all, s_all, t_sum = exchange_triples(packed, group)
+    m_all, s_all, t_sum = exchange_triples(packed, group, timeout_s)
     lp, lse = ops.combine_triples(m_all, s_all, t_sum)
     lead = hidden.shape[:-1]
     return lp.reshape(lead), lse.reshape(lead)

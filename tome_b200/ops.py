@@ -13,6 +13,7 @@ Reference call sites mirrored here
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -53,6 +54,8 @@ def check_device_status(device=None) -> None:
         problems.append("the ragged windows cover more positions than the packed arrays hold")
     if bits & _lib.DEV_BLOCK_OUT_OF_RANGE:
         problems.append("a paged-KV block-table entry lies outside the pool")
+    if bits & _lib.DEV_NO_CANDIDATE:
+        problems.append("sampling met a row without a single logit that is not NaN")
     if bits & _lib.DEV_TIMEOUT:
         problems.append("a bounded device-side wait ran out (TOME_DEV_TIMEOUT)")
     raise TomeRuntimeError("; ".join(problems) or f"device status {bits}")
@@ -135,44 +138,83 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
+def _out_rows(name: str, t: Optional[torch.Tensor], rows: int, device: torch.device,
+              dtype: torch.dtype = torch.float32) -> None:
+    if t is None:
+        return
+    if not isinstance(t, torch.Tensor) or t.dtype != dtype or t.device != device or \
+            t.numel() != rows or not t.is_contiguous():
+        raise ValueError(f"{name} must be a contiguous {dtype} tensor of {rows} elements on {device}")
+
+
 def selective_log_softmax(logits: torch.Tensor, ids: torch.Tensor, temp: float = 1.0, *,
                           return_lse: bool = False, return_target_logit: bool = False,
-                          check: bool = False):
+                          check: bool = False, out: Optional[torch.Tensor] = None,
+                          out_lse: Optional[torch.Tensor] = None):
     """Log-probability of ``ids[i]`` under ``softmax(logits[i] / temp)``, fp32, one pass.
 
     Same arithmetic as ``local_compute_logprobs`` (mlx-impl/node.py:400-404): logits are
     up-cast to fp32, divided by ``temp``, reduced with a max-shifted logsumexp, and the target
     column is gathered.  ``logits`` is ``[..., V]`` in bf16 or fp32, ``ids`` has the leading
-    shape.  ``temp`` of 0 or None means 1.0, as at the reference call sites.
+    shape.  ``temp`` of 0 or None means 1.0, as at the reference call sites.  ``out`` (and
+    ``out_lse``, which implies ``return_lse``) name contiguous fp32 tensors with one element
+    per row to write into instead of fresh allocations; a decode loop that passes them and
+    int32 ids on the device pays for nothing but the launch.
     """
-    _require_cuda("logits", logits)
+    if not isinstance(logits, torch.Tensor) or not logits.is_cuda:
+        _require_cuda("logits", logits)
     temp = float(temp or 1.0)
-    flat, stride = _rows_view(logits)
+    device = logits.device
+    if logits.dim() == 2 and logits.stride(1) == 1 and logits.stride(0) >= logits.shape[1]:
+        flat, stride = logits, logits.stride(0)
+    else:
+        flat, stride = _rows_view(logits)
     rows, V = flat.shape
-    device = flat.device
-    ids32 = _ids32(ids, rows, device)
-    out = torch.empty(rows, dtype=torch.float32, device=device)
-    lse = torch.empty(rows, dtype=torch.float32, device=device) if return_lse else None
+    if isinstance(ids, torch.Tensor) and ids.dtype == torch.int32 and ids.device == device \
+            and ids.numel() == rows and ids.is_contiguous():
+        ids32 = ids
+    else:
+        ids32 = _ids32(ids, rows, device)
+    if out is None:
+        out = torch.empty(rows, dtype=torch.float32, device=device)
+    else:
+        _out_rows("out", out, rows, device)
+    if out_lse is not None:
+        _out_rows("out_lse", out_lse, rows, device)
+        lse, return_lse = out_lse, True
+    else:
+        lse = torch.empty(rows, dtype=torch.float32, device=device) if return_lse else None
     raw = torch.empty(rows, dtype=torch.float32, device=device) if return_target_logit else None
     with _on(device):
         status = lib.tome_selective_logprob(
-            flat.data_ptr(), _dtype_code(flat), rows, V, stride, ids32.data_ptr(), temp,
+            flat.data_ptr(), _DTYPES.get(flat.dtype, -1), rows, V, stride, ids32.data_ptr(), temp,
             out.data_ptr(), _ptr(lse), _ptr(raw), _status_word(device).data_ptr(), _stream(device))
-    _lib.check(status)
+    if status:
+        if flat.dtype not in _DTYPES:
+            _dtype_code(flat)
+        _lib.check(status)
     if check:
         check_device_status(device)
     lead = logits.shape[:-1]
-    result = [out.reshape(lead)]
+    if len(lead) != 1:
+        out = out.reshape(lead)
+        lse = None if lse is None else lse.reshape(lead)
+        raw = None if raw is None else raw.reshape(lead)
+    if not (return_lse or return_target_logit):
+        return out
+    result = [out]
     if return_lse:
-        result.append(lse.reshape(lead))
+        result.append(lse)
     if return_target_logit:
-        result.append(raw.reshape(lead))
-    return result[0] if len(result) == 1 else tuple(result)
+        result.append(raw)
+    return tuple(result)
 
 
-def local_compute_logprobs(logits: torch.Tensor, ids: torch.Tensor, temp: float) -> torch.Tensor:
-    """Drop-in for the closure of the same name in mlx-impl/node.py:400-404."""
-    return selective_log_softmax(logits, ids, temp)
+def local_compute_logprobs(logits: torch.Tensor, ids: torch.Tensor, temp: float, *,
+                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Drop-in for the closure of the same name in mlx-impl/node.py:400-404 (``out``: see
+    :func:`selective_log_softmax`)."""
+    return selective_log_softmax(logits, ids, temp, out=out)
 
 
 def local_compute_logprobs_host(logits_host: torch.Tensor, ids_host: torch.Tensor, temp: float,
@@ -213,11 +255,15 @@ def fused_log_softmax(logits: torch.Tensor, temperature: float = 1.0, *,
     """
     if targets is not None:
         return selective_log_softmax(logits, targets, temperature, check=check)
-    _require_cuda("logits", logits)
+    if not isinstance(logits, torch.Tensor) or not logits.is_cuda:
+        _require_cuda("logits", logits)
     temperature = float(temperature or 1.0)
-    flat, stride = _rows_view(logits)
+    device = logits.device
+    if logits.dim() == 2 and logits.stride(1) == 1 and logits.stride(0) >= logits.shape[1]:
+        flat, stride = logits, logits.stride(0)
+    else:
+        flat, stride = _rows_view(logits)
     rows, V = flat.shape
-    device = flat.device
     if out is None:
         out = torch.empty((rows, V), dtype=flat.dtype, device=device)
     elif (out.shape != logits.shape or out.dtype != flat.dtype or out.device != device
@@ -225,12 +271,15 @@ def fused_log_softmax(logits: torch.Tensor, temperature: float = 1.0, *,
         raise ValueError("out must be a contiguous tensor with the shape, dtype and device of logits")
     with _on(device):
         status = lib.tome_log_softmax_full(
-            flat.data_ptr(), _dtype_code(flat), rows, V, stride, temperature, out.data_ptr(), V,
-            None, _status_word(device).data_ptr(), _stream(device))
-    _lib.check(status)
+            flat.data_ptr(), _DTYPES.get(flat.dtype, -1), rows, V, stride, temperature,
+            out.data_ptr(), V, None, _status_word(device).data_ptr(), _stream(device))
+    if status:
+        if flat.dtype not in _DTYPES:
+            _dtype_code(flat)
+        _lib.check(status)
     if check:
         check_device_status(device)
-    return out.reshape(logits.shape)
+    return out if out.shape == logits.shape else out.reshape(logits.shape)
 
 
 def grpo_dual_logprob_kl(policy_logits: torch.Tensor, ref_logits: torch.Tensor,
@@ -314,9 +363,23 @@ def ragged_logprobs(logits: torch.Tensor, targets_packed: torch.Tensor, lengths:
     return (out, offsets, lse) if return_lse else (out, offsets)
 
 
+_sample_ws_bytes: dict = {}
+
+
+def sample_workspace_bytes(rows: int, vocab: int) -> int:
+    """Scratch bytes :func:`sample_topk_logprob` uses for a batch of this shape (0 for the
+    batches that need none)."""
+    key = (rows, vocab, os.environ.get("TOME_K4_STREAM"))
+    n = _sample_ws_bytes.get(key)
+    if n is None:
+        n = _sample_ws_bytes[key] = int(lib.tome_sample_workspace_bytes(rows, vocab))
+    return n
+
+
 def sample_topk_logprob(logits: torch.Tensor, temperature: float, top_k: int = 20, *,
                         seed: int = 0, offset: int = 0, return_topk: bool = False,
-                        check: bool = False):
+                        check: bool = False, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                        workspace: Optional[torch.Tensor] = None):
     """Sample one token per row and score it, on the device, in one pass over the logits.
 
     The batched replacement of the rollout's per-sequence loop (mlx-impl/node.py:593-610):
@@ -325,33 +388,147 @@ def sample_topk_logprob(logits: torch.Tensor, temperature: float, top_k: int = 2
     0 means greedy (argmax) scored at temperature 1, as in the reference.  Returns
     ``(tokens int32 [...], logprobs fp32 [...])`` and, with ``return_topk``, the top-k indices
     and raw logits.  Draws depend only on ``(seed, offset, row)``; advance ``offset`` per step.
-    ``check=True`` synchronises and raises if the kernels reported a device status.
+    ``out`` may name the ``(tokens, logprobs)`` tensors to write into (contiguous, one element
+    per row) and ``workspace`` a scratch tensor of :func:`sample_workspace_bytes` bytes, which a
+    decode loop reuses from step to step.  A row without a single logit that is not NaN gets
+    token -1 and log-prob NaN.  ``check=True`` synchronises and raises if the kernels reported
+    a device status.
     """
-    _require_cuda("logits", logits)
-    flat, stride = _rows_view(logits)
+    if not isinstance(logits, torch.Tensor) or not logits.is_cuda:
+        _require_cuda("logits", logits)
+    device = logits.device
+    if logits.dim() == 2 and logits.stride(1) == 1 and logits.stride(0) >= logits.shape[1]:
+        flat, stride = logits, logits.stride(0)
+    else:
+        flat, stride = _rows_view(logits)
     rows, V = flat.shape
-    device = flat.device
-    tokens = torch.empty(rows, dtype=torch.int32, device=device)
-    lp = torch.empty(rows, dtype=torch.float32, device=device)
+    if out is None:
+        tokens = torch.empty(rows, dtype=torch.int32, device=device)
+        lp = torch.empty(rows, dtype=torch.float32, device=device)
+    else:
+        tokens, lp = out
+        _out_rows("out[0] (tokens)", tokens, rows, device, torch.int32)
+        _out_rows("out[1] (logprobs)", lp, rows, device)
     tk_i = torch.empty((rows, top_k), dtype=torch.int32, device=device) if return_topk else None
     tk_v = torch.empty((rows, top_k), dtype=torch.float32, device=device) if return_topk else None
-    # large batches take a streaming three-kernel path that needs scratch (0: not this batch)
-    nbytes = int(lib.tome_sample_workspace_bytes(rows, V))
-    ws = torch.empty(nbytes, dtype=torch.uint8, device=device) if nbytes else None
+    # large batches take a streaming path that needs scratch (0: not this batch)
+    nbytes = sample_workspace_bytes(rows, V)
+    ws = None
+    if nbytes:
+        ws = _workspace(nbytes, device, workspace)
+        nbytes = ws.numel() * ws.element_size()
     with _on(device):
         status = lib.tome_sample_topk_logprob_ws(
-            flat.data_ptr(), _dtype_code(flat), rows, V, stride, float(temperature or 0.0),
+            flat.data_ptr(), _DTYPES.get(flat.dtype, -1), rows, V, stride, float(temperature or 0.0),
             int(top_k), int(seed) & (2 ** 64 - 1), int(offset) & (2 ** 64 - 1), tokens.data_ptr(),
             lp.data_ptr(), _ptr(tk_i), _ptr(tk_v), _ptr(ws), nbytes,
             _status_word(device).data_ptr(), _stream(device))
-    _lib.check(status)
+    if status:
+        if flat.dtype not in _DTYPES:
+            _dtype_code(flat)
+        _lib.check(status)
     if check:
         check_device_status(device)
     lead = logits.shape[:-1]
+    if len(lead) != 1:
+        tokens, lp = tokens.reshape(lead), lp.reshape(lead)
     if return_topk:
-        return (tokens.reshape(lead), lp.reshape(lead), tk_i.reshape(*lead, top_k),
-                tk_v.reshape(*lead, top_k))
-    return tokens.reshape(lead), lp.reshape(lead)
+        return tokens, lp, tk_i.reshape(*lead, top_k), tk_v.reshape(*lead, top_k)
+    return tokens, lp
+
+
+class BoundCall:
+    """One library call with everything but the stream resolved ahead of time.
+
+    The rollout makes the same call at every decode step (mlx-impl/node.py:590-605: same
+    shapes, same buffers); binding it once keeps the per-step host work down to fetching
+    torch's current stream and one foreign call.  ``outputs`` holds the tensors the call writes.
+    The bound tensors must keep their storage (write new logits INTO them); the object keeps
+    them alive.  Calls go to the stream that is current when they are made.
+    """
+    __slots__ = ("_fn", "_head", "_tail", "_device", "_index", "outputs", "_keep")
+
+    def __init__(self, fn, head, tail, device, outputs, keep):
+        self._fn, self._head, self._tail = fn, tuple(head), tuple(tail)
+        self._device = device
+        self._index = device.index if device.index is not None else torch.cuda.current_device()
+        self.outputs, self._keep = outputs, keep
+
+    def __call__(self, *step_args):
+        """Launch.  ``step_args`` are the per-step values of the call (sampling: the offset)."""
+        if self._index != torch.cuda.current_device():
+            with torch.cuda.device(self._index):
+                status = self._fn(*self._head, *step_args, *self._tail, _stream(self._device))
+        else:
+            status = self._fn(*self._head, *step_args, *self._tail, _stream(self._device))
+        if status:
+            _lib.check(status)
+        return self.outputs
+
+
+def _bind_rows(logits: torch.Tensor):
+    _require_cuda("logits", logits)
+    if logits.dim() != 2 or logits.stride(1) != 1 or logits.stride(0) < logits.shape[1]:
+        raise ValueError("a bound call needs 2-D logits [rows, V] with contiguous rows")
+    return logits.shape[0], logits.shape[1], logits.stride(0), _dtype_code(logits)
+
+
+def bind_selective(logits: torch.Tensor, ids: torch.Tensor, temp: float = 1.0, *,
+                   out: Optional[torch.Tensor] = None,
+                   out_lse: Optional[torch.Tensor] = None) -> BoundCall:
+    """:func:`local_compute_logprobs` as a :class:`BoundCall`: ``call()`` scores the current
+    contents of ``logits`` against the current contents of ``ids`` (int32, on the device) and
+    returns ``outputs = (logprobs,)`` or ``(logprobs, lse)``."""
+    rows, V, stride, code = _bind_rows(logits)
+    device = logits.device
+    _out_rows("ids", ids, rows, device, torch.int32)
+    if out is None:
+        out = torch.empty(rows, dtype=torch.float32, device=device)
+    _out_rows("out", out, rows, device)
+    _out_rows("out_lse", out_lse, rows, device)
+    head = (logits.data_ptr(), code, rows, V, stride, ids.data_ptr(), float(temp or 1.0),
+            out.data_ptr(), _ptr(out_lse), None, _status_word(device).data_ptr())
+    outputs = (out,) if out_lse is None else (out, out_lse)
+    return BoundCall(lib.tome_selective_logprob, head, (), device, outputs, (logits, ids))
+
+
+def bind_log_softmax(logits: torch.Tensor, temperature: float = 1.0, *,
+                     out: Optional[torch.Tensor] = None) -> BoundCall:
+    """:func:`fused_log_softmax` (the full matrix) as a :class:`BoundCall`; ``outputs = (out,)``."""
+    rows, V, stride, code = _bind_rows(logits)
+    device = logits.device
+    if out is None:
+        out = torch.empty((rows, V), dtype=logits.dtype, device=device)
+    elif out.shape != logits.shape or out.dtype != logits.dtype or out.device != device or \
+            not out.is_contiguous():
+        raise ValueError("out must be a contiguous tensor with the shape, dtype and device of logits")
+    head = (logits.data_ptr(), code, rows, V, stride, float(temperature or 1.0), out.data_ptr(), V,
+            None, _status_word(device).data_ptr())
+    return BoundCall(lib.tome_log_softmax_full, head, (), device, (out,), (logits,))
+
+
+def bind_sample(logits: torch.Tensor, temperature: float, top_k: int = 20, *, seed: int = 0,
+                out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                workspace: Optional[torch.Tensor] = None) -> BoundCall:
+    """:func:`sample_topk_logprob` as a :class:`BoundCall`: ``call(offset)`` draws one token per
+    row from the current contents of ``logits``; ``outputs = (tokens, logprobs)``.  The scratch
+    of large batches is allocated here once (or taken from ``workspace``) and reused by every
+    call, so calls of one bound object must not overlap on the device."""
+    rows, V, stride, code = _bind_rows(logits)
+    device = logits.device
+    if out is None:
+        out = (torch.empty(rows, dtype=torch.int32, device=device),
+               torch.empty(rows, dtype=torch.float32, device=device))
+    tokens, lp = out
+    _out_rows("out[0] (tokens)", tokens, rows, device, torch.int32)
+    _out_rows("out[1] (logprobs)", lp, rows, device)
+    nbytes = sample_workspace_bytes(rows, V)
+    ws = _workspace(nbytes, device, workspace) if nbytes else None
+    head = (logits.data_ptr(), code, rows, V, stride, float(temperature or 0.0), int(top_k),
+            int(seed) & (2 ** 64 - 1))
+    tail = (tokens.data_ptr(), lp.data_ptr(), None, None, _ptr(ws),
+            0 if ws is None else ws.numel() * ws.element_size(), _status_word(device).data_ptr())
+    return BoundCall(lib.tome_sample_topk_logprob_ws, head, tail, device, (tokens, lp), (logits, ws))
 
 
 def lm_head_workspace_bytes(rows: int, hidden_dim: int, vocab_local: int) -> int:
@@ -488,30 +665,47 @@ def lm_head_logprob(hidden: torch.Tensor, weight: torch.Tensor, ids: torch.Tenso
 
 def lm_head_logprob_static(hidden: torch.Tensor, weight: torch.Tensor, ids: torch.Tensor,
                            temp: float, out_logprob: torch.Tensor,
-                           out_lse: Optional[torch.Tensor] = None) -> None:
+                           out_lse: Optional[torch.Tensor] = None, *,
+                           dev_status: Optional[torch.Tensor] = None) -> None:
     """:func:`lm_head_logprob` for hosts that cannot allocate device memory around the call.
 
-    Nothing is allocated here or in the library: ``hidden`` ``[rows, K]`` and ``weight``
-    ``[V, K]`` must already be contiguous bf16, ``ids`` contiguous int32 ``[rows]``, and the
-    fp32 outputs ``[rows]`` are written in place.  The kernel's scratch is a fixed 8 MiB
-    array inside the library (see ``tome_lmhead_logprob_static`` in the header), so sizes
-    that need more raise ``TomeArgumentError``; calls on one GPU must not overlap in time.
-    The first call on a device resolves the array's address: make it before stream capture.
+    The library allocates nothing: ``hidden`` ``[rows, K]`` and ``weight`` ``[V, K]`` must
+    already be contiguous bf16, ``ids`` contiguous int32 ``[rows]``, and the fp32 outputs
+    ``[rows]`` are written in place.  The kernel's scratch is a fixed 8 MiB array inside the
+    library (see ``tome_lmhead_logprob_static`` in the header), so sizes that need more raise
+    ``TomeArgumentError``; calls on one GPU must not overlap in time.  The first call on a
+    device resolves the array's address: make it before stream capture.  The logits are reduced
+    un-rounded (there is no ``round_logits`` switch on this entry point).  ``dev_status`` is the
+    caller's int32 status word; without it this wrapper uses the module's own word, whose 4
+    bytes torch allocates on the first call per device: pass one to allocate nothing at all.
     """
     for name, t, dt in (("hidden", hidden, torch.bfloat16), ("weight", weight, torch.bfloat16),
-                        ("ids", ids, torch.int32), ("out_logprob", out_logprob, torch.float32)):
+                        ("ids", ids, torch.int32), ("out_logprob", out_logprob, torch.float32),
+                        ("out_lse", out_lse, torch.float32)):
+        if t is None and name == "out_lse":
+            continue
         _require_cuda(name, t)
         if t.dtype != dt or not t.is_contiguous():
             raise TypeError(f"{name} must be a contiguous {dt} tensor")
-    if out_lse is not None and (out_lse.dtype != torch.float32 or not out_lse.is_contiguous()):
-        raise TypeError("out_lse must be a contiguous float32 tensor")
+        if t.device != hidden.device:
+            raise ValueError(f"{name} lives on {t.device}, hidden on {hidden.device}")
+    if hidden.dim() != 2 or weight.dim() != 2 or hidden.shape[1] != weight.shape[1]:
+        raise ValueError(f"hidden [rows, K] and weight [V, K] disagree: {tuple(hidden.shape)} "
+                         f"vs {tuple(weight.shape)}")
     rows, K = hidden.shape
+    for name, t in (("ids", ids), ("out_logprob", out_logprob), ("out_lse", out_lse)):
+        if t is not None and t.numel() != rows:
+            raise ValueError(f"{name} holds {t.numel()} elements, expected one per row ({rows})")
     device = hidden.device
+    if dev_status is None:
+        dev_status = _status_word(device)  # 4 bytes, allocated on the first call per device
+    elif dev_status.dtype != torch.int32 or dev_status.device != device or dev_status.numel() < 1:
+        raise ValueError("dev_status must be an int32 tensor on the device of hidden")
     with _on(device):
         status = lib.tome_lmhead_logprob_static(
             hidden.data_ptr(), weight.data_ptr(), rows, K, weight.shape[0], ids.data_ptr(),
             float(temp or 1.0), out_logprob.data_ptr(), _ptr(out_lse),
-            _status_word(device).data_ptr(), _stream(device))
+            dev_status.data_ptr(), _stream(device))
     _lib.check(status)
 
 
