@@ -148,7 +148,7 @@ def test_large_batches_take_the_streaming_path(cuda_device, monkeypatch, dtype, 
                                                         return_topk=True)
     assert int(tok.min()) >= 0                              # no row left marked
     k = min(20, vocab)
-    for r in list(range(12)) + list(range(rows - 5, rows)) + [400, 777]:
+    for r in list(range(12)) + list(range(rows - 5, rows)) + [400, rows // 2 + 77]:
         idx, _ = oracle.topk_sampling_distribution(x[r], 0.7, 20)
         assert tk_i[r, :k].cpu().tolist() == idx.tolist(), r
         assert torch.equal(tk_v[r, :k].cpu(), x[r].float()[idx])
