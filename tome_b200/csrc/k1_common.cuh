@@ -78,10 +78,10 @@ struct K1Params {
   int64_t packed_capacity; // RAGGED: entries the packed target/output arrays can hold
   int32_t* out_offsets;    // RAGGED: int32 [n_seq + 1], start of each sequence in the packed output
   float* row_thr;          // SAMPLE: out, per row the final threshold (>= top_k logits reach it)
-  int32_t* cand_count;     // SAMPLE: [rows, lists] vectors appended per list (cand_cap + 1: overflow)
-  uint4* cand_vec;         // SAMPLE: [rows, lists, cand_cap] 16-byte vectors holding a candidate
-  int32_t* cand_idx;       // SAMPLE: [rows, lists, cand_cap] their positions in the row, in 16-byte units
+  int32_t* cand_count;     // SAMPLE: [rows, lists] entries per list (cand_cap + 1: overflow)
+  uint32_t* cand_entry;    // SAMPLE: [rows, lists, cand_cap] noted places, see K1SampleSmem
   int32_t cand_cap;        // SAMPLE: entries per list (lists per row = consumer warps)
+  int32_t sample_kk;       // SAMPLE: min(top_k, vocab)
   int32_t sample_q;        // SAMPLE: ceil(top_k / consumer warps), 1 .. 32
   int32_t* zero_word;      // SAMPLE: nullable, a word the kernel sets to 0
   int32_t* status;         // nullable
@@ -90,27 +90,46 @@ struct K1Params {
 };
 
 // ------------------------------------------------------------------ FULL mode output
-// out = T(float(x) * inv_temp) - T(lse), subtraction in T (mlx-impl/model.py:57-60)
-__device__ __forceinline__ uint32_t full_out_bf16x2(uint32_t w, float inv_temp,
-                                                    __nv_bfloat16 lse_t) {
-  const __nv_bfloat16 a = __float2bfloat16_rn(bf16_lo(w) * inv_temp);
-  const __nv_bfloat16 b = __float2bfloat16_rn(bf16_hi(w) * inv_temp);
-  const __nv_bfloat16 ra = __hsub(a, lse_t);
-  const __nv_bfloat16 rb = __hsub(b, lse_t);
-  return static_cast<uint32_t>(__bfloat16_as_ushort(ra)) |
-         (static_cast<uint32_t>(__bfloat16_as_ushort(rb)) << 16);
+// out = T(float(x) * inv_temp) - T(lse), subtraction in T (mlx-impl/model.py:57-60).
+// bf16 rows use packed forms, two logits per instruction (f32x2 multiply, bf16x2 convert and
+// subtract); the rounding steps are those of the scalar forms below, one by one.  Pass 2 of
+// the full-matrix kernels was bound by its instruction count: 48 -> 20 instructions per
+// 16-byte vector took 4096 x 151936 bf16 from 5.43 to 5.63 TB/s (5.92 at temperature 1, where
+// only the subtraction is left).
+__device__ __forceinline__ uint32_t full_out_bf16x2(uint32_t w, float2 inv2, uint32_t lse2) {
+  const float2 scaled = __fmul2_rn(make_float2(bf16_lo(w), bf16_hi(w)), inv2);
+  uint32_t t;  // round both to bf16 (nearest even), low half = first operand of the pair
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(t) : "f"(scaled.y), "f"(scaled.x));
+  const __nv_bfloat162 r = __hsub2(as_bf162(t), as_bf162(lse2));
+  return *reinterpret_cast<const uint32_t*>(&r);
 }
 
 __device__ __forceinline__ uint4 full_out_vec(uint4 v, float inv_temp, float lse, __nv_bfloat16) {
-  const __nv_bfloat16 lse_t = __float2bfloat16_rn(lse);
+  const uint32_t l16 = __bfloat16_as_ushort(__float2bfloat16_rn(lse));
+  const uint32_t lse2 = l16 | (l16 << 16);
   uint4 o;
-  o.x = full_out_bf16x2(v.x, inv_temp, lse_t);
-  o.y = full_out_bf16x2(v.y, inv_temp, lse_t);
-  o.z = full_out_bf16x2(v.z, inv_temp, lse_t);
-  o.w = full_out_bf16x2(v.w, inv_temp, lse_t);
+  if (inv_temp == 1.0f) {  // x * 1 rounds to x: only the subtraction is left
+    const __nv_bfloat162 l2 = as_bf162(lse2);
+    const __nv_bfloat162 a = __hsub2(as_bf162(v.x), l2), b = __hsub2(as_bf162(v.y), l2);
+    const __nv_bfloat162 c = __hsub2(as_bf162(v.z), l2), d = __hsub2(as_bf162(v.w), l2);
+    o.x = *reinterpret_cast<const uint32_t*>(&a);
+    o.y = *reinterpret_cast<const uint32_t*>(&b);
+    o.z = *reinterpret_cast<const uint32_t*>(&c);
+    o.w = *reinterpret_cast<const uint32_t*>(&d);
+    return o;
+  }
+  const float2 inv2 = make_float2(inv_temp, inv_temp);
+  o.x = full_out_bf16x2(v.x, inv2, lse2);
+  o.y = full_out_bf16x2(v.y, inv2, lse2);
+  o.z = full_out_bf16x2(v.z, inv2, lse2);
+  o.w = full_out_bf16x2(v.w, inv2, lse2);
   return o;
 }
 
+// fp32: scalar multiply and subtract with the rounding of each step spelt out.  (The packed
+// f32x2 multiply followed by a packed add came out fused into one multiply-add, which skips
+// the first rounding: an error of 1e22 on logits of -1e30.  fp32 rows are not bound by the
+// instruction count anyway.)
 __device__ __forceinline__ uint4 full_out_vec(uint4 v, float inv_temp, float lse, float) {
   uint4 o;
   o.x = __float_as_uint(__fsub_rn(__fmul_rn(__uint_as_float(v.x), inv_temp), lse));

@@ -40,17 +40,21 @@ namespace tome {
 constexpr int K1_FULL_STAGES = K1_CFG_FULL_STAGES;
 __host__ __device__ constexpr int k1_stages(int mode) { return mode == K1_FULL ? K1_FULL_STAGES : K1_STAGES; }
 
-// SAMPLE mode: the 16-byte vectors holding a logit that reaches the row's current threshold are
-// gathered in shared memory, whole, in one list per consumer warp: the warp's lanes place
-// their vectors with a ballot and a register counter (no atomic, no memory round trip), and
-// the warp copies its list out once per row.  (Earlier forms: unpacking the vectors here cost
-// ~600 warp-cycles each; one list per CTA filled through a shared-memory atomic stalled a warp
-// for the atomic's round trip at every second step of the loop.)
-constexpr int K1_SAMPLE_WARP_LIST = 64;
+// SAMPLE mode: where a logit reaches the row's current threshold, the place is noted: one
+// 32-bit entry per thread and loop step, (index of the step's first 16-byte vector << 4) | mask
+// of the step's four vectors (K1_CONSUMERS apart) that hold such a logit.  Each consumer warp
+// keeps a list of its own; its lanes take their slots with one ballot and a register counter
+// (no atomic, no memory round trip), and the warp copies the list out once per row.  The
+// kernel that follows fetches the vectors again (about 1 % of the row).  Earlier forms:
+// unpacking the vectors here cost ~600 warp-cycles each; one list per CTA filled through a
+// shared-memory atomic stalled a warp for the atomic's round trip at every second step;
+// copying the vectors themselves, with a ballot per vector, cost 45 instructions per hit step.
+constexpr int K1_SAMPLE_WARP_LIST = 128;
+constexpr int K1_SAMPLE_TOP = 32 / K1_CONSUMER_WARPS;  // lane maxima each warp puts forward
+static_assert(32 % K1_CONSUMER_WARPS == 0 && K1_CONSUMERS <= 128, "threshold keys: 7 id bits");
 struct K1SampleSmem {
-  uint4 vec[K1_CONSUMER_WARPS][K1_SAMPLE_WARP_LIST];
-  int32_t idx[K1_CONSUMER_WARPS][K1_SAMPLE_WARP_LIST];  // index of the vector within the row (16-byte units)
-  float pub[2][K1_CONSUMER_WARPS];  // threshold refinement: one certified value per warp
+  uint32_t entry[K1_CONSUMER_WARPS][K1_SAMPLE_WARP_LIST];
+  uint32_t pub[2][32];  // threshold refinement: what the warps put forward (by parity)
 };
 
 template <int STAGES>
@@ -187,48 +191,79 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       if (MODE == K1_FULL) dst = reinterpret_cast<T*>(p.out_full) + row * p.out_stride;
 
       // SAMPLE: the row's threshold is a value that at least top_k of its logits reach.  Every
-      // consumer keeps the maximum of the logits it has seen (128 disjoint groups); a warp
-      // certifies the q-th largest of its 32 lane maxima, q = ceil(top_k / warps), and the
-      // smallest of the warps' values is reached by at least top_k logits.  The first chunk is
-      // looked at twice (maxima first), later the threshold is raised after chunks 1, 3, 7, ...
-      // (each time the sample has doubled), which keeps the candidates near 100 per row.
-      // Vectors holding a logit that reaches the threshold of the moment go to the warp's list;
-      // a later kernel unpacks them, keeps what reaches the final threshold, ranks and draws.
+      // consumer keeps the maximum of the logits it has seen (128 disjoint groups).  Each warp
+      // puts its 8 largest lane maxima forward and the top_k-th largest of the 32 values put
+      // forward becomes the threshold: at least top_k groups, hence logits, reach it, and it is
+      // the exact top_k-th largest group maximum unless one warp holds more than 8 of the best.
+      // (top_k > 32: each warp certifies its ceil(top_k / warps)-th largest lane maximum and the
+      // smallest of those is taken.)  The first chunk is looked at twice (maxima first), later
+      // the threshold is raised after chunks 3, 15, 63, ... (each time the sample has grown
+      // fourfold), which keeps the noted places near 130 per row.  A later kernel fetches them,
+      // keeps what reaches the final threshold, ranks and draws.
       K1SampleSmem& smp = *reinterpret_cast<K1SampleSmem*>(smem + Smem::SAMPLE_OFF);
       float thr_val = __int_as_float(0x7f800000);  // +inf: nothing qualifies
       float tmax = __int_as_float(0xff800000);     // largest logit this thread has seen
-      int32_t wcount = 0;                          // vectors in this warp's list (same in every lane)
-      auto append = [&](bool hit, uint4 q, int64_t vec_index) {
-        const uint32_t bal = __ballot_sync(0xffffffffu, hit);
-        if (hit) {
+      int32_t wcount = 0;                          // entries in this warp's list (same in every lane)
+      auto note = [&](uint32_t mask, int64_t vec_index) {
+        const uint32_t bal = __ballot_sync(0xffffffffu, mask != 0u);
+        if (mask != 0u) {
           const int32_t slot = wcount + __popc(bal & ((1u << lane) - 1u));
-          if (slot < K1_SAMPLE_WARP_LIST) {
-            smp.vec[warp][slot] = q;
-            smp.idx[warp][slot] = static_cast<int32_t>(vec_index);
-          }
+          if (slot < K1_SAMPLE_WARP_LIST)
+            smp.entry[warp][slot] = (static_cast<uint32_t>(vec_index) << 4) | mask;
         }
         wcount += __popc(bal);
       };
       auto refine = [&]() {
-        float x = tmax;  // bitonic sort of the lane maxima, largest in lane 0
+        // order-preserving key of the lane maximum; its low 7 bits carry the thread's number,
+        // which makes the keys distinct and lowers the value by at most 127 ulps (still a
+        // value that the group reaches).  Selection is by warp-wide max / min reductions
+        // (redux.sync), one instruction each.
+        uint32_t key = (k4_key(tmax) & ~127u) | static_cast<uint32_t>(127 - ctid);
+        uint32_t* pub = smp.pub[refinements & 1u];
+        const bool union_form = p.sample_kk <= 32;
+        if (union_form) {
 #pragma unroll
-        for (int kb = 2; kb <= 32; kb <<= 1) {
-#pragma unroll
-          for (int j = kb >> 1; j > 0; j >>= 1) {
-            const float o = __shfl_xor_sync(0xffffffffu, x, j);
-            const bool keep_max = ((lane & j) == 0) == ((lane & kb) == 0);
-            x = keep_max ? fmaxf(x, o) : fminf(x, o);
+          for (int r = 0; r < K1_SAMPLE_TOP; ++r) {  // the warp's largest keys, one by one
+            const uint32_t best = __reduce_max_sync(0xffffffffu, key);
+            if (key == best) {
+              pub[warp * K1_SAMPLE_TOP + r] = best;
+              key = 0u;
+            }
           }
+        } else {
+          uint32_t best = 0u;
+          for (int r = 0; r < p.sample_q; ++r) {
+            best = __reduce_max_sync(0xffffffffu, key);
+            if (key == best) key = 0u;
+          }
+          if (lane == 0) pub[warp] = best;
         }
-        const float mine = __shfl_sync(0xffffffffu, x, p.sample_q - 1);
-        float* pub = smp.pub[refinements & 1u];
-        if (lane == 0) pub[warp] = mine;
         named_bar_sync(2, K1_CONSUMERS);
-        float t = pub[0];
+        uint32_t best = 0u;
+        if (union_form) {
+          // the kk-th largest of the 32 keys put forward is the (33 - kk)-th smallest: take it
+          // from the nearer end
+          uint32_t mine = pub[lane];
+          const int32_t kk = p.sample_kk;
+          if (2 * kk <= 33) {
+            for (int32_t r = 0; r < kk; ++r) {
+              best = __reduce_max_sync(0xffffffffu, mine);
+              if (mine == best) mine = 0u;
+            }
+          } else {
+            for (int32_t r = 0; r < 33 - kk; ++r) {
+              best = __reduce_min_sync(0xffffffffu, mine);
+              if (mine == best) mine = 0xffffffffu;
+            }
+          }
+        } else {
+          best = pub[0];
 #pragma unroll
-        for (int w = 1; w < K1_CONSUMER_WARPS; ++w) t = fminf(t, pub[w]);
+          for (int w = 1; w < K1_CONSUMER_WARPS; ++w) best = min(best, pub[w]);
+        }
         ++refinements;
-        thr_val = t;  // never below the previous one: the lane maxima only grow
+        const float t = k4_unkey(best & ~127u);
+        thr_val = (t != t) ? __int_as_float(0xff800000) : t;  // -inf with its low bits cleared
       };
 
       for (int64_t k = 0; k < n_chunks; ++k, ++it) {
@@ -261,32 +296,29 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
             const float mc = fast_update<POLY>(fs, cc, p.c, T());
             const float md = fast_update<POLY>(fs, d, p.c, T());
             if (MODE == K1_SAMPLE) {
-              // a NaN maximum (a vector holding a NaN) counts as a hit and is sorted out later
-              const bool ha = !(ma < thr_val), hb = !(mb < thr_val);
-              const bool hc = !(mc < thr_val), hd = !(md < thr_val);
-              tmax = fmaxf(fmaxf(tmax, fmaxf(ma, mb)), fmaxf(mc, md));
-              if (__any_sync(0xffffffffu, ha || hb || hc || hd)) {
-                const int64_t v0 = (off >> 4) + v;  // this thread's first vector within the row
-                append(ha, a, v0);
-                append(hb, b, v0 + K1_CONSUMERS);
-                append(hc, cc, v0 + 2 * K1_CONSUMERS);
-                append(hd, d, v0 + 3 * K1_CONSUMERS);
+              // a NaN maximum (a bf16 vector holding a NaN) counts as a hit: the vector's other
+              // logits are looked at later; the running maximum ignores it
+              const float m4 = fmax3_nan(fmax_nan(ma, mb), mc, md);
+              tmax = fmaxf(tmax, m4);
+              if (__any_sync(0xffffffffu, !(m4 < thr_val))) {
+                const uint32_t mask = (!(ma < thr_val) ? 1u : 0u) | (!(mb < thr_val) ? 2u : 0u) |
+                                      (!(mc < thr_val) ? 4u : 0u) | (!(md < thr_val) ? 8u : 0u);
+                note(mask, (off >> 4) + v);  // v: this thread's first vector of the step
               }
             }
           }
           for (; vb < nvec; vb += K1_CONSUMERS) {
             const uint32_t v = vb + lane;
-            uint4 a = make_uint4(0u, 0u, 0u, 0u);
             bool hit = false;
             if (v < nvec) {
-              a = lds128(sbase + v * 16);
-              const float ma = fast_update<POLY>(fs, a, p.c, T());
+              const float ma = fast_update<POLY>(fs, lds128(sbase + v * 16), p.c, T());
               if (MODE == K1_SAMPLE) {
                 hit = !(ma < thr_val);
                 tmax = fmaxf(tmax, ma);
               }
             }
-            if (MODE == K1_SAMPLE && __any_sync(0xffffffffu, hit)) append(hit, a, (off >> 4) + v);
+            if (MODE == K1_SAMPLE && __any_sync(0xffffffffu, hit))
+              note(hit ? 1u : 0u, (off >> 4) + v);
           }
         } else {
           uint8_t* drow = reinterpret_cast<uint8_t*>(dst) + off;
@@ -298,8 +330,10 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar + stage * 8);
-        // the sample has doubled: raise the threshold (not after the row's last chunk)
-        if (MODE == K1_SAMPLE && k >= 1 && ((k + 1) & k) == 0 && k + 1 < n_chunks) refine();
+        // the sample has grown fourfold: raise the threshold (not after the row's last chunk)
+        if (MODE == K1_SAMPLE && k >= 3 && ((k + 1) & k) == 0 && ((k + 1) & 0x55555555) != 0 &&
+            k + 1 < n_chunks)
+          refine();
       }
 
       Online st = fast_finish(fs, p.c);
@@ -312,16 +346,10 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
         }
       }
       if (MODE == K1_SAMPLE && warp == 0 && tail_begin < p.vocab) {
-        // the tail travels as one vector padded with -inf (tail_begin is a multiple of PER_VEC)
-        __align__(16) T pad[PER_VEC];
+        // the elements past the last 16-byte boundary count as one more (short) vector
         float tail_max = __int_as_float(0xff800000);
-        for (int j = 0; j < PER_VEC; ++j) {
-          const bool have = tail_begin + j < p.vocab;
-          pad[j] = have ? src[tail_begin + j] : from_float_neg_inf(T());
-          tail_max = fmax_nan(tail_max, to_float(pad[j]));
-        }
-        append(lane == 0 && !(tail_max < thr_val), *reinterpret_cast<const uint4*>(pad),
-               tail_begin / PER_VEC);
+        for (int64_t j = tail_begin; j < p.vocab; ++j) tail_max = fmax_nan(tail_max, to_float(src[j]));
+        note((lane == 0 && !(tail_max < thr_val)) ? 1u : 0u, tail_begin / PER_VEC);
       }
 
       if (reduce_pass) {
@@ -348,10 +376,7 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
           // each warp copies its own list out; nothing here waits for another warp
           const int32_t keep = min(wcount, min(K1_SAMPLE_WARP_LIST, p.cand_cap));
           const int64_t base = (row * K1_CONSUMER_WARPS + warp) * p.cand_cap;
-          for (int32_t i = lane; i < keep; i += 32) {
-            p.cand_vec[base + i] = smp.vec[warp][i];
-            p.cand_idx[base + i] = smp.idx[warp][i];
-          }
+          for (int32_t i = lane; i < keep; i += 32) p.cand_entry[base + i] = smp.entry[warp][i];
           if (lane == 0)  // more than kept: overflow
             p.cand_count[row * K1_CONSUMER_WARPS + warp] = (wcount > keep) ? p.cand_cap + 1 : wcount;
           if (ctid == 0) p.row_thr[row] = thr_val;
@@ -731,14 +756,16 @@ namespace tome {
 
 bool k1_sample_eligible(const void* logits, int32_t dtype, int64_t vocab, int64_t row_stride) {
   const int64_t es = (dtype == TOME_F32) ? 4 : 2;
-  return bulk_eligible(logits, row_stride, dtype) && vocab * es >= 16;
+  // a row holds at least one 16-byte vector and few enough for the entries' 28 index bits
+  return bulk_eligible(logits, row_stride, dtype) && vocab * es >= 16 &&
+         vocab * es / 16 < (int64_t{1} << 27);
 }
 
 int32_t k1_launch_sample(const void* logits, int32_t dtype, int64_t rows, int64_t vocab,
                          int64_t row_stride, float temperature, int32_t top_k, float* row_thr,
-                         int32_t* cand_count, uint4* cand_vec, int32_t* cand_idx,
-                         int32_t cand_cap, float* out_lse, int32_t* zero_word,
-                         int32_t* dev_status, cudaStream_t stream) {
+                         int32_t* cand_count, uint32_t* cand_entry, int32_t cand_cap,
+                         float* out_lse, int32_t* zero_word, int32_t* dev_status,
+                         cudaStream_t stream) {
   K1Params p = {};
   p.zero_word = zero_word;
   p.src[0] = logits;
@@ -751,15 +778,17 @@ int32_t k1_launch_sample(const void* logits, int32_t dtype, int64_t rows, int64_
   p.out1 = out_lse;
   p.row_thr = row_thr;
   p.cand_count = cand_count;
-  p.cand_vec = cand_vec;
-  p.cand_idx = cand_idx;
+  p.cand_entry = cand_entry;
   p.cand_cap = cand_cap;
   const int64_t kk = std::max<int64_t>(1, std::min<int64_t>(top_k, vocab));
+  p.sample_kk = static_cast<int32_t>(kk);
   p.sample_q = static_cast<int32_t>((kk + K1_CONSUMER_WARPS - 1) / K1_CONSUMER_WARPS);
   p.status = dev_status;
   return k1_launch<K1_SAMPLE>(p, dtype, true, rows, stream);
 }
 
 int k1_sample_lists_per_row() { return K1_CONSUMER_WARPS; }
+int k1_sample_list_capacity() { return K1_SAMPLE_WARP_LIST; }
+int k1_sample_vector_stride() { return K1_CONSUMERS; }
 
 }  // namespace tome

@@ -42,7 +42,6 @@ constexpr int K4_RANK_MAX = 1024;  // above this many candidates, compact before
 constexpr int K4_MAX_SWEEPS = 64;   // re-sweeps with a tightened threshold before giving up
 constexpr int64_t K4_STREAM_MIN_ROWS = 320;    // from here on a batch takes the three-kernel path
 constexpr int64_t K4_STREAM_MIN_VOCAB = 4096;  // every consumer of the streaming kernel sees logits
-constexpr int K4_LIST_CAP = 64;                // vectors kept per list on that path
 constexpr int K4_MAX_LISTS = 8;                // lists per row (one per consumer warp of the streaming kernel)
 constexpr int K4_CODE_CAP = 256;               // logits of a row that may reach its final threshold
 constexpr int K4_LIST_THREADS = 128;
@@ -470,95 +469,155 @@ __global__ void __launch_bounds__(K4_THREADS, 2) k4_sample_split_kernel(const K4
 // Two kernels, so that the pass over the logits is a plain streaming pass:
 //   1. the streaming kernel's SAMPLE mode (k1_logprob.cu): one pass at HBM speed that keeps
 //      (max, sum-exp), derives the row's threshold (a value that at least kk logits reach)
-//      from the logits as they pass and gathers the 16-byte vectors holding a logit that
-//      reaches it into a few lists per row;
-//   2. k4_finish_kernel: unpacks the row's vectors, keeps the logits that reach the final
-//      threshold, ranks them (exact top-kk), draws, scores, writes.
+//      from the logits as they pass and notes which 16-byte vectors hold a logit that reaches
+//      it, in a few lists per row;
+//   2. k4_finish_kernel: fetches the noted vectors again (about 1 % of the row), keeps the
+//      logits that reach the final threshold, ranks them (exact top-kk), draws, scores, writes.
 // A row whose lists ran over (sorted or heavily tied rows) or that holds fewer than kk logits
 // that are not NaN is put on a list and redone by k4_sample_kernel (only_flagged).  Same tokens
 // as the other kernels of this file.
+struct K4Lists {
+  int32_t lists;          // per row
+  int32_t cap;            // entries per list
+  int32_t vec_stride;     // 16-byte vectors between the four vectors of an entry
+  const float* row_thr;
+  const float* lse;
+  const int32_t* count;   // [rows, lists]
+  const uint32_t* entry;  // [rows, lists, cap]
+};
+
+// One warp per row (four rows per CTA at a time), nothing but warp-level synchronisation:
+// the row's entries are expanded into a list of vector numbers, the vectors are fetched and
+// their logits that reach the threshold become codes, the codes are ranked, the warp draws.
+constexpr int K4_VEC_CAP = 512;  // vectors a row's entries may name (beyond that: row kernel)
+
 template <typename T>
 __global__ void __launch_bounds__(K4_LIST_THREADS)
-k4_finish_kernel(const K4Params p, const int lists, const float* row_thr, const float* lse,
-                 const int32_t* cand_count, const uint4* cand_vec, const int32_t* cand_idx) {
-  __shared__ unsigned long long list[K4_CODE_CAP];
-  __shared__ unsigned long long top[K4_MAX_K];
-  __shared__ int32_t list_n;
+k4_finish_kernel(const K4Params p, const K4Lists w) {
+  constexpr int ROWS_PER_CTA = K4_LIST_THREADS / 32;
+  __shared__ unsigned long long codes[ROWS_PER_CTA][K4_CODE_CAP];
+  __shared__ unsigned long long tops[ROWS_PER_CTA][K4_MAX_K];
+  __shared__ int32_t vecs[ROWS_PER_CTA][K4_VEC_CAP];
+  __shared__ int32_t n_codes[ROWS_PER_CTA];
   constexpr int PER = 16 / static_cast<int>(sizeof(T));
-  const int tid = threadIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t lanes_below = (1u << lane) - 1u;
   const bool greedy = !(p.temperature > 0.0f);
   const float temp = greedy ? 1.0f : p.temperature;
   const float c = LOG2E / temp;
   const int32_t k = p.top_k;
   const int32_t kk = static_cast<int32_t>(min(static_cast<int64_t>(k), p.vocab));
-  for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
-    if (tid == 0) list_n = 0;
-    __syncthreads();
-    // unpack the row's vectors: the logits that reach the final threshold are the candidates
-    const float thr = row_thr[row];
-    bool overflow = false;
-    for (int32_t slot = tid; slot < lists * K4_LIST_CAP; slot += K4_LIST_THREADS) {
-      const int32_t l = slot / K4_LIST_CAP, i = slot - l * K4_LIST_CAP;
-      const int32_t n_vec = cand_count[row * lists + l];
-      overflow |= (n_vec > K4_LIST_CAP);
-      if (i >= n_vec) continue;
-      const int64_t at = (row * lists + l) * K4_LIST_CAP + i;
-      const uint4 q = cand_vec[at];
-      const int64_t e0 = static_cast<int64_t>(cand_idx[at]) * PER;
-      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  unsigned long long* list = codes[warp];
+  unsigned long long* top = tops[warp];
+  int32_t* vec = vecs[warp];
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * ROWS_PER_CTA + warp; row < p.rows;
+       row += static_cast<int64_t>(gridDim.x) * ROWS_PER_CTA) {
+    if (lane == 0) n_codes[warp] = 0;
+    const float thr = w.row_thr[row];
+    const T* src = reinterpret_cast<const T*>(p.logits) + row * p.stride;
+    // ---- the lists of the row, end to end: lane l knows where list l begins
+    int32_t my_count = (lane < w.lists) ? w.count[row * w.lists + lane] : 0;
+    const bool overflow = __any_sync(0xffffffffu, my_count > w.cap);
+    my_count = min(my_count, w.cap);
+    int32_t begin = my_count;  // inclusive prefix sum over the lanes, then made exclusive
 #pragma unroll
-      for (int j = 0; j < PER; ++j) {
-        const float x = (sizeof(T) == 4)
-                            ? __uint_as_float(w[j])
-                            : __uint_as_float((j & 1) ? (w[j >> 1] & 0xffff0000u) : (w[j >> 1] << 16));
-        if (e0 + j < p.vocab && x >= thr) {
-          const int32_t at_list = atomicAdd(&list_n, 1);
-          if (at_list < K4_CODE_CAP) list[at_list] = k4_pack(x, e0 + j);
+    for (int o = 1; o < K4_MAX_LISTS; o <<= 1) {
+      const int32_t up = __shfl_up_sync(0xffffffffu, begin, o);
+      if (lane >= o) begin += up;
+    }
+    const int32_t total = __shfl_sync(0xffffffffu, begin, K4_MAX_LISTS - 1);
+    begin -= my_count;
+    // ---- entries -> vector numbers (every logit that reaches the final threshold sits in a
+    //      vector some entry names)
+    int32_t n_vec = 0;
+    for (int32_t g0 = 0; g0 < total; g0 += 32) {
+      const int32_t g = g0 + lane;
+      int32_t l = 0, at = g;
+#pragma unroll
+      for (int q = 1; q < K4_MAX_LISTS; ++q) {  // the last list that begins at or before g
+        const int32_t b = __shfl_sync(0xffffffffu, begin, q);
+        if (q < w.lists && g >= b) {
+          l = q;
+          at = g - b;
+        }
+      }
+      const uint32_t e = (g < total) ? w.entry[(row * w.lists + l) * w.cap + at] : 0u;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const bool bit = (e >> j) & 1u;
+        const uint32_t bal = __ballot_sync(0xffffffffu, bit);
+        const int32_t at = n_vec + __popc(bal & lanes_below);
+        if (bit && at < K4_VEC_CAP) vec[at] = static_cast<int32_t>(e >> 4) + j * w.vec_stride;
+        n_vec += __popc(bal);
+      }
+    }
+    __syncwarp();
+    // ---- vectors -> codes of the logits that reach the threshold
+    for (int32_t i = lane; i < min(n_vec, K4_VEC_CAP); i += 32) {
+      const int64_t e0 = static_cast<int64_t>(vec[i]) * PER;
+      if (e0 + PER <= p.vocab) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(src + e0));
+        const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int t = 0; t < PER; ++t) {
+          const float x = (sizeof(T) == 4)
+                              ? __uint_as_float(u[t])
+                              : __uint_as_float((t & 1) ? (u[t >> 1] & 0xffff0000u) : (u[t >> 1] << 16));
+          if (x >= thr) {
+            const int32_t at = atomicAdd(&n_codes[warp], 1);
+            if (at < K4_CODE_CAP) list[at] = k4_pack(x, e0 + t);
+          }
+        }
+      } else {  // the short vector at the end of a row whose length is not a multiple of 16 bytes
+        for (int64_t t = e0; t < p.vocab; ++t) {
+          const float x = k4_load(src, t);
+          if (x >= thr) {
+            const int32_t at = atomicAdd(&n_codes[warp], 1);
+            if (at < K4_CODE_CAP) list[at] = k4_pack(x, t);
+          }
         }
       }
     }
-    const bool any_overflow = __syncthreads_or(overflow ? 1 : 0) != 0;
-    const int32_t n = list_n;
-    if (any_overflow || n > K4_CODE_CAP || n < kk) {
+    __syncwarp();
+    const int32_t n = n_codes[warp];
+    if (overflow || n_vec > K4_VEC_CAP || n > K4_CODE_CAP || n < kk) {
       // lists that ran over (sorted or heavily tied rows) or a row with too few logits that
       // are not NaN: left to the row kernel
-      if (tid == 0) p.marked_rows[atomicAdd(p.marked, 1)] = static_cast<int32_t>(row);
-      __syncthreads();
+      if (lane == 0) p.marked_rows[atomicAdd(p.marked, 1)] = static_cast<int32_t>(row);
+      __syncwarp();
       continue;
     }
-    constexpr int MINE = K4_CODE_CAP / K4_LIST_THREADS;
-    unsigned long long code[MINE];
-    int32_t rank[MINE];
-#pragma unroll
-    for (int q = 0; q < MINE; ++q) {
-      const int32_t i = tid + q * K4_LIST_THREADS;
-      code[q] = (i < n) ? list[i] : ~0ull;
-      rank[q] = 0;
-    }
+    // ---- exact top-kk by ranking every code against all (codes are distinct), two per lane
+    //      and trip
+    for (int32_t i0 = 0; i0 < n; i0 += 64) {
+      const int32_t ia = i0 + lane, ib = i0 + 32 + lane;
+      const unsigned long long a = (ia < n) ? list[ia] : ~0ull;
+      const unsigned long long b = (ib < n) ? list[ib] : ~0ull;
+      int32_t rank_a = 0, rank_b = 0;
 #pragma unroll 4
-    for (int32_t j = 0; j < n; ++j) {
-      const unsigned long long o = list[j];
-#pragma unroll
-      for (int q = 0; q < MINE; ++q) rank[q] += (o > code[q]) ? 1 : 0;
+      for (int32_t j = 0; j < n; ++j) {
+        const unsigned long long o = list[j];
+        rank_a += (o > a) ? 1 : 0;
+        rank_b += (o > b) ? 1 : 0;
+      }
+      if (ia < n && rank_a < kk) top[rank_a] = a;
+      if (ib < n && rank_b < kk) top[rank_b] = b;
     }
-#pragma unroll
-    for (int q = 0; q < MINE; ++q)
-      if (tid + q * K4_LIST_THREADS < n && rank[q] < kk) top[rank[q]] = code[q];
-    __syncthreads();
-    if (tid == 0) {
-      const int32_t pick = greedy ? 0 : k4_draw(top, kk, c, row, p.seed, p.offset);
+    __syncwarp();
+    const int32_t pick = greedy ? 0 : k4_draw_warp(top, kk, c, row, p.seed, p.offset);
+    if (lane == 0) {
       p.out_tokens[row] = k4_index(top[pick]);
-      p.out_logprob[row] = __fdiv_rn(k4_value(top[pick]), temp) - lse[row];
+      p.out_logprob[row] = __fdiv_rn(k4_value(top[pick]), temp) - w.lse[row];
     }
     if (p.out_topk_idx != nullptr || p.out_topk_val != nullptr) {
-      for (int32_t j = tid; j < k; j += K4_LIST_THREADS) {
+      for (int32_t j = lane; j < k; j += 32) {
         const bool have = j < kk;
         if (p.out_topk_idx != nullptr) p.out_topk_idx[row * k + j] = have ? k4_index(top[j]) : -1;
         if (p.out_topk_val != nullptr)
           p.out_topk_val[row * k + j] = have ? k4_value(top[j]) : -INFINITY;
       }
     }
-    __syncthreads();
+    __syncwarp();
   }
 }
 
@@ -568,17 +627,15 @@ struct K4Workspace {
   float* thr;
   float* lse;
   int32_t* marked_rows;
-  int32_t* count;   // [rows, lists]
-  int32_t* marked;  // one counter for the batch
-  uint4* cand_vec;  // [rows, lists, K4_LIST_CAP] vectors holding a candidate
-  int32_t* cand_idx;
+  int32_t* count;    // [rows, lists]
+  int32_t* marked;   // one counter for the batch
+  uint32_t* entry;   // [rows, lists, cap]
 };
 static size_t k4_workspace_head(int64_t rows, int lists) {
   return (static_cast<size_t>(rows) * (12 + 4 * lists) + 4 + 15) & ~static_cast<size_t>(15);
 }
-static size_t k4_workspace_bytes(int64_t rows, int lists) {
-  return k4_workspace_head(rows, lists) +
-         static_cast<size_t>(rows) * lists * K4_LIST_CAP * (sizeof(uint4) + sizeof(int32_t));
+static size_t k4_workspace_bytes(int64_t rows, int lists, int cap) {
+  return k4_workspace_head(rows, lists) + static_cast<size_t>(rows) * lists * cap * sizeof(uint32_t);
 }
 static K4Workspace k4_workspace(void* base, int64_t rows, int lists) {
   K4Workspace w;
@@ -588,8 +645,7 @@ static K4Workspace k4_workspace(void* base, int64_t rows, int lists) {
   w.marked_rows = reinterpret_cast<int32_t*>(w.lse + rows);
   w.count = w.marked_rows + rows;
   w.marked = w.count + rows * lists;
-  w.cand_vec = reinterpret_cast<uint4*>(b + k4_workspace_head(rows, lists));
-  w.cand_idx = reinterpret_cast<int32_t*>(w.cand_vec + rows * lists * K4_LIST_CAP);
+  w.entry = reinterpret_cast<uint32_t*>(b + k4_workspace_head(rows, lists));
   return w;
 }
 
@@ -650,11 +706,12 @@ static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, i
   const bool streamed = workspace != nullptr && k4_wants_stream(rows, vocab) &&
                         k1_sample_eligible(logits, dtype, vocab, row_stride);
   const int lists = k1_sample_lists_per_row();
+  const int list_cap = k1_sample_list_capacity();
   if (streamed) {
     if (lists > K4_MAX_LISTS) return fail(TOME_ERR_UNSUPPORTED, "%d lists per row", lists);
-    if (ws_bytes < k4_workspace_bytes(rows, lists))
+    if (ws_bytes < k4_workspace_bytes(rows, lists, list_cap))
       return fail(TOME_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes, %zu needed", ws_bytes,
-                  k4_workspace_bytes(rows, lists));
+                  k4_workspace_bytes(rows, lists, list_cap));
     if (!aligned16(workspace)) return fail(TOME_ERR_MISALIGNED, "workspace is not 16-byte aligned");
   }
   K4Params p = {};
@@ -677,17 +734,24 @@ static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, i
     p.marked = w.marked;
     p.marked_rows = w.marked_rows;
     const float lse_temp = (temperature > 0.0f) ? temperature : 1.0f;
-    const int grid_rows = static_cast<int>(
-        std::min<int64_t>(rows, static_cast<int64_t>(info.sm_count) * 16));
+    const int grid_rows = static_cast<int>(std::min<int64_t>(
+        (rows + K4_LIST_THREADS / 32 - 1) / (K4_LIST_THREADS / 32),
+        static_cast<int64_t>(info.sm_count) * 16));
     st = k1_launch_sample(logits, dtype, rows, vocab, row_stride, lse_temp, top_k, w.thr, w.count,
-                          w.cand_vec, w.cand_idx, K4_LIST_CAP, w.lse, w.marked, dev_status, s);
+                          w.entry, list_cap, w.lse, w.marked, dev_status, s);
     if (st != TOME_OK) return st;
+    K4Lists lw;
+    lw.lists = lists;
+    lw.cap = list_cap;
+    lw.vec_stride = k1_sample_vector_stride();
+    lw.row_thr = w.thr;
+    lw.lse = w.lse;
+    lw.count = w.count;
+    lw.entry = w.entry;
     if (dtype == TOME_F32)
-      k4_finish_kernel<float><<<grid_rows, K4_LIST_THREADS, 0, s>>>(p, lists, w.thr, w.lse, w.count,
-                                                                    w.cand_vec, w.cand_idx);
+      k4_finish_kernel<float><<<grid_rows, K4_LIST_THREADS, 0, s>>>(p, lw);
     else
-      k4_finish_kernel<__nv_bfloat16><<<grid_rows, K4_LIST_THREADS, 0, s>>>(
-          p, lists, w.thr, w.lse, w.count, w.cand_vec, w.cand_idx);
+      k4_finish_kernel<__nv_bfloat16><<<grid_rows, K4_LIST_THREADS, 0, s>>>(p, lw);
     st = check_cuda(cudaGetLastError(), "k4 finish launch");
     if (st != TOME_OK) return st;
   }
@@ -715,8 +779,9 @@ static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, i
     cfg.numAttrs = 1;
     return check_cuda(cudaLaunchKernelEx(&cfg, split_kernel, p, split), "k4 split launch");
   }
-  const int grid = static_cast<int>(
-      std::max<int64_t>(1, std::min<int64_t>(static_cast<int64_t>(info.sm_count) * 3, rows)));
+  // (redoing the rows a streamed batch left over: one CTA per SM; it usually finds none)
+  const int grid = static_cast<int>(std::max<int64_t>(
+      1, std::min<int64_t>(static_cast<int64_t>(info.sm_count) * (streamed ? 1 : 3), rows)));
   void (*row_kernel)(K4Params) =
       (dtype == TOME_F32) ? k4_sample_kernel<float> : k4_sample_kernel<__nv_bfloat16>;
   st = ensure_dynamic_smem(reinterpret_cast<const void*>(row_kernel), smem);
@@ -738,7 +803,7 @@ extern "C" int32_t tome_sample_topk_logprob(const void* logits, int32_t dtype, i
 
 extern "C" size_t tome_sample_workspace_bytes(int64_t rows, int64_t vocab) {
   if (rows <= 0 || vocab <= 0 || !k4_wants_stream(rows, vocab)) return 0;
-  return k4_workspace_bytes(rows, k1_sample_lists_per_row());
+  return k4_workspace_bytes(rows, k1_sample_lists_per_row(), k1_sample_list_capacity());
 }
 
 extern "C" int32_t tome_sample_topk_logprob_ws(const void* logits, int32_t dtype, int64_t rows,

@@ -72,4 +72,30 @@ __device__ __forceinline__ int32_t k4_draw(const unsigned long long* top, int32_
   return kk - 1;
 }
 
+// The same draw made by a whole warp (all 32 lanes call it, all get the index): the terms are
+// formed in parallel and summed in the same order as above, so the result is identical.
+__device__ __forceinline__ int32_t k4_draw_warp(const unsigned long long* top, int32_t kk, float c,
+                                                int64_t row, uint64_t seed, uint64_t offset) {
+  if (kk <= 1) return 0;
+  const int lane = static_cast<int>(lane_id());
+  const float best = k4_value(top[0]);
+  const float e_lo = (lane < kk) ? ex2f((k4_value(top[lane]) - best) * c) : 0.0f;
+  const float e_hi = (lane + 32 < kk) ? ex2f((k4_value(top[lane + 32]) - best) * c) : 0.0f;
+  // prefix sums in the serial order: every lane adds the terms one by one and keeps the
+  // partial sums that belong to its own two places
+  float acc = 0.0f, mine_lo = 0.0f, mine_hi = 0.0f;
+  for (int32_t j = 0; j < kk; ++j) {
+    acc += __shfl_sync(0xffffffffu, (j < 32) ? e_lo : e_hi, j & 31);
+    if (j == lane) mine_lo = acc;
+    if (j == lane + 32) mine_hi = acc;
+  }
+  const uint32_t r = k4_philox(static_cast<uint64_t>(row), offset, seed);
+  const float u = (static_cast<float>(r >> 8) + 0.5f) * (1.0f / 16777216.0f) * acc;
+  const uint32_t lo = __ballot_sync(0xffffffffu, lane < kk && u < mine_lo);
+  const uint32_t hi = __ballot_sync(0xffffffffu, lane + 32 < kk && u < mine_hi);
+  if (lo != 0u) return __ffs(lo) - 1;
+  if (hi != 0u) return 32 + __ffs(hi) - 1;
+  return kk - 1;
+}
+
 }  // namespace tome
