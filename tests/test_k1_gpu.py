@@ -60,6 +60,28 @@ def test_selective_row_counts(cuda_device, rows):
     _check_selective(x, ids, 0.7, cuda_device)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows", [75, 300, 591, 593, 1024, 2 * 592 - 1, 2 * 592 + 5])
+def test_selective_row_counts_around_a_round_of_ctas(cuda_device, monkeypatch, dtype, rows):
+    """The rows of a thin last round are shared by clusters of four CTAs (a quarter of the row
+    each, merged over distributed shared memory).  Forced here for every row count, up to four
+    shared rows per cluster; the same cases with the sharing switched off must agree."""
+    import tome_b200
+    vocab = 151936 if rows in (300, 1024) else 60000     # 24 / 12 chunks per row, or 10 / 5
+    x, ids = _case(rows, vocab, dtype, seed=40 + rows)
+    x[3, : vocab // 2] = float("-inf")       # a quarter without a finite logit
+    x[5] = -1.0e30                           # the exact fallback, on a shared row when rows < CTAs
+    x[rows - 1, vocab - 1] = 30.0            # the maximum in the last quarter of the last row
+    monkeypatch.setenv("TOME_K1_TAIL", "2")  # share whatever the last round holds
+    _check_selective(x, ids, 0.7, cuda_device)
+    xd, idd = x.to(cuda_device), ids.to(cuda_device)
+    shared = tome_b200.local_compute_logprobs(xd, idd, 0.7)
+    monkeypatch.setenv("TOME_K1_TAIL", "0")
+    plain = tome_b200.local_compute_logprobs(xd, idd, 0.7)
+    assert max_abs(shared, plain) <= 2e-6 * 20     # summation order only
+    tome_b200.check_device_status(cuda_device)
+
+
 def test_selective_targets_at_the_ends(cuda_device):
     x, ids = _case(4, 151936, torch.bfloat16, 5)
     ids[:] = torch.tensor([0, 151935, 151936 - 384, 4096], dtype=torch.int32)

@@ -57,6 +57,16 @@ struct K1SampleSmem {
   uint32_t pub[2][32];  // threshold refinement: what the warps put forward (by parity)
 };
 
+// SPLIT: with a few rows per CTA the last round leaves most CTAs idle (1024 rows on 592 CTAs:
+// 432 do two rows, 160 one).  The kernel is then launched in clusters of K1_SPLIT CTAs: the
+// rows that fill whole rounds are dealt one per CTA as usual, the remaining ones one per
+// cluster, each CTA taking a quarter of the row's chunks; the quarters' (m, s) pairs meet in
+// the first CTA's shared memory (st.shared::cluster + mbarrier), which merges them and writes
+// the row.  A cluster shares fewer than K1_SPLIT_ITEMS + 1 rows (the remainder is smaller
+// than the grid), so every pair slot and barrier is used once.
+constexpr int K1_SPLIT = 4;
+constexpr int K1_SPLIT_ITEMS = 4;
+
 template <int STAGES>
 struct K1SmemT {
   static constexpr int DATA = STAGES * K1_CHUNK_BYTES;
@@ -67,11 +77,48 @@ struct K1SmemT {
   static constexpr int TOTAL_DUAL = SCRATCH_OFF + K1_THREADS * 4;
   static constexpr int TOTAL_PLAIN = CUM_OFF;
   static constexpr int SAMPLE_OFF = (CUM_OFF + 15) & ~15;                // SAMPLE: K1SampleSmem
+  // SPLIT (selective mode, rows shared by a cluster): pairs [K1_SPLIT_ITEMS][K1_SPLIT] float2,
+  // then one mbarrier per shared row
+  static constexpr int SPLIT_OFF = (CUM_OFF + 15) & ~15;
+  static constexpr int SPLIT_BAR_OFF = SPLIT_OFF + K1_SPLIT_ITEMS * K1_SPLIT * 8;
+  static constexpr int TOTAL_SPLIT = SPLIT_BAR_OFF + K1_SPLIT_ITEMS * 8;
 };
 
 
-template <typename T, int MODE, int POLY>
+// One unit of work of a CTA: chunks [k_begin, k_end) of row / window position `item`.
+struct K1Item {
+  int64_t item;
+  int64_t k_begin, k_end;
+  bool shared;  // SPLIT: the row is shared by the cluster (this CTA has a quarter of it)
+};
+
+// The round-th unit of this CTA; false when there is none.  Without SPLIT: rows blockIdx.x,
+// blockIdx.x + gridDim.x, ...  With SPLIT: `whole_rounds` such rows, then the cluster's share
+// of the remaining rows, a quarter of the chunks each.
+template <bool SPLIT>
+__device__ __forceinline__ bool k1_next_item(int64_t round, int64_t n_items, int64_t whole_rounds,
+                                             int64_t split_rows, int64_t n_clusters,
+                                             int64_t cluster_id, uint32_t crank, int64_t n_chunks,
+                                             K1Item& w) {
+  w.k_begin = 0;
+  w.k_end = n_chunks;
+  w.shared = false;
+  if (!SPLIT || round < whole_rounds) {
+    w.item = static_cast<int64_t>(blockIdx.x) + round * gridDim.x;
+    return SPLIT || w.item < n_items;
+  }
+  const int64_t j = cluster_id + (round - whole_rounds) * n_clusters;
+  if (j >= split_rows) return false;
+  w.item = whole_rounds * gridDim.x + j;
+  w.k_begin = n_chunks * crank / K1_SPLIT;
+  w.k_end = n_chunks * (crank + 1) / K1_SPLIT;
+  w.shared = true;
+  return true;
+}
+
+template <typename T, int MODE, int POLY, bool SPLIT = false>
 __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(const K1Params p) {
+  static_assert(!SPLIT || MODE == K1_SELECTIVE, "rows are shared by clusters in selective mode only");
   constexpr int STAGES = k1_stages(MODE);
   using Smem = K1SmemT<STAGES>;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -94,9 +141,20 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       mbar_init(full_bar + i * 8, 1);
       mbar_init(empty_bar + i * 8, K1_CONSUMER_WARPS);
     }
+    if (SPLIT)
+      for (int i = 0; i < K1_SPLIT_ITEMS; ++i)
+        mbar_init(smem_base + Smem::SPLIT_BAR_OFF + i * 8, K1_SPLIT - 1);
     fence_mbar_init();
     if (MODE == K1_SAMPLE && blockIdx.x == 0 && p.zero_word != nullptr) *p.zero_word = 0;
   }
+  // SPLIT: every CTA does `whole_rounds` rows of its own, then a quarter of each row of its
+  // cluster's share of the remainder
+  const uint32_t crank = SPLIT ? cluster_ctarank() : 0u;
+  const int64_t whole_rounds = SPLIT ? p.n_rows / gridDim.x : 0;
+  const int64_t whole_rows = whole_rounds * gridDim.x;
+  const int64_t split_rows = SPLIT ? p.n_rows - whole_rows : 0;
+  const int64_t n_clusters = SPLIT ? gridDim.x / K1_SPLIT : 1;
+  const int64_t cluster_id = SPLIT ? blockIdx.x / K1_SPLIT : 0;
   int64_t n_items = p.n_rows;
   if (WINDOWED) {
     n_items = dual_build_prefix(p, cum, reinterpret_cast<int32_t*>(smem + Smem::SCRATCH_OFF));
@@ -110,6 +168,7 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
     }
   }
   __syncthreads();
+  if (SPLIT) cluster_sync_all();  // the peers' barriers exist before anything arrives on them
 
   const int64_t row_bytes = p.vocab * ES;
   const int64_t bulk_bytes = row_bytes & ~static_cast<int64_t>(15);
@@ -124,12 +183,16 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       const uint64_t keep = policy_evict_last();
       uint32_t it = 0;
       bool ok = true;
-      for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        const int64_t row = WINDOWED ? dual_row_of_item(p, cum, item) : item;
+      for (int64_t round = 0; ok; ++round) {
+        K1Item w;
+        if (!k1_next_item<SPLIT>(round, n_items, whole_rounds, split_rows, n_clusters, cluster_id,
+                                 crank, n_chunks, w))
+          break;
+        const int64_t row = WINDOWED ? dual_row_of_item(p, cum, w.item) : w.item;
         for (int sub = 0; sub < NSUB && ok; ++sub) {
           const uint8_t* src = reinterpret_cast<const uint8_t*>(
                                    p.src[(MODE == K1_DUAL) ? sub : 0]) + row * p.stride * ES;
-          for (int64_t k = 0; k < n_chunks; ++k, ++it) {
+          for (int64_t k = w.k_begin; k < w.k_end; ++k, ++it) {
             const uint32_t stage = it % STAGES;
             const uint32_t phase = (it / STAGES) & 1u;
             if (!mbar_wait(empty_bar + stage * 8, phase ^ 1u)) {
@@ -153,6 +216,10 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
         }
       }
     }
+    if (SPLIT) {  // nobody leaves while a peer may still address its shared memory
+      __syncwarp();
+      cluster_sync_all();
+    }
     return;
   }
 
@@ -166,7 +233,13 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
   float carry = 0.0f;
   bool dead = false;
   uint32_t refinements = 0;  // SAMPLE: threshold updates so far (their parity picks the buffer)
-  for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
+  uint32_t split_it = 0;     // SPLIT: shared rows this cluster has finished
+  for (int64_t round = 0;; ++round) {
+    K1Item w;
+    if (!k1_next_item<SPLIT>(round, n_items, whole_rounds, split_rows, n_clusters, cluster_id, crank,
+                             n_chunks, w))
+      break;
+    const int64_t item = w.item;
     const int64_t row = WINDOWED ? dual_row_of_item(p, cum, item) : item;
     const int64_t oidx = (MODE == K1_RAGGED) ? item : row;  // where targets/outputs live
     float lse_row = 0.0f;
@@ -178,7 +251,7 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       // the one thread that finishes the row fetches the target logit early
       float x_t = 0.0f;
       bool target_ok = true;
-      if (MODE != K1_FULL && MODE != K1_SAMPLE && ctid == 0) {
+      if (MODE != K1_FULL && MODE != K1_SAMPLE && ctid == 0 && !(w.shared && crank != 0)) {
         const int32_t t = p.targets[oidx];
         target_ok = (t >= 0) && (static_cast<int64_t>(t) < p.vocab);
         if (target_ok) x_t = to_float(src[t]);
@@ -198,8 +271,8 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       // (top_k > 32: each warp certifies its ceil(top_k / warps)-th largest lane maximum and the
       // smallest of those is taken.)  The first chunk is looked at twice (maxima first), later
       // the threshold is raised after chunks 3, 15, 63, ... (each time the sample has grown
-      // fourfold), which keeps the noted places near 130 per row.  A later kernel fetches them,
-      // keeps what reaches the final threshold, ranks and draws.
+      // fourfold), which keeps the noted places near 130 per row, and after the last chunk.  A
+      // later kernel fetches them, keeps what reaches the final threshold, ranks and draws.
       K1SampleSmem& smp = *reinterpret_cast<K1SampleSmem*>(smem + Smem::SAMPLE_OFF);
       float thr_val = __int_as_float(0x7f800000);  // +inf: nothing qualifies
       float tmax = __int_as_float(0xff800000);     // largest logit this thread has seen
@@ -266,7 +339,7 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
         thr_val = (t != t) ? __int_as_float(0xff800000) : t;  // -inf with its low bits cleared
       };
 
-      for (int64_t k = 0; k < n_chunks; ++k, ++it) {
+      for (int64_t k = w.k_begin; k < w.k_end; ++k, ++it) {
         const uint32_t stage = it % STAGES;
         const uint32_t phase = (it / STAGES) & 1u;
         if (!dead && !mbar_wait(full_bar + stage * 8, phase)) {
@@ -330,16 +403,18 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar + stage * 8);
-        // the sample has grown fourfold: raise the threshold (not after the row's last chunk)
-        if (MODE == K1_SAMPLE && k >= 3 && ((k + 1) & k) == 0 && ((k + 1) & 0x55555555) != 0 &&
-            k + 1 < n_chunks)
+        // the sample has grown fourfold: raise the threshold.  Once more after the row's last
+        // chunk: nothing is noted any more, but the kernel that follows has a third of the
+        // logits to rank.
+        if (MODE == K1_SAMPLE &&
+            ((k >= 3 && ((k + 1) & k) == 0 && ((k + 1) & 0x55555555) != 0) || k + 1 == n_chunks))
           refine();
       }
 
       Online st = fast_finish(fs, p.c);
       if (dead) st.s = __int_as_float(0x7fc00000);  // the row takes the exact path below
       // elements past the last 16-byte boundary of the row (at most PER_VEC - 1)
-      if (ctid == 0) {
+      if (ctid == 0 && w.k_end == n_chunks) {
         for (int64_t j = tail_begin; j < p.vocab; ++j) {
           if (reduce_pass) online_update_scalar(st, to_float(src[j]), p.c);
           else dst[j] = full_out_scalar(src[j], p.inv_temp, lse_row);
@@ -365,13 +440,40 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
           float s = ms.y * ex2f((ms.x - m) * p.c);
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+          bool writes_row = true;
+          if (SPLIT && w.shared) {
+            // the quarters meet in the cluster's first CTA; slot and barrier of this shared row
+            // are used this once
+            float2* pairs = reinterpret_cast<float2*>(smem + Smem::SPLIT_OFF) + split_it * K1_SPLIT;
+            const uint32_t bar = smem_base + Smem::SPLIT_BAR_OFF + split_it * 8;
+            if (crank != 0) {
+              if (lane == 0) {
+                st_cluster_f32x2(mapa_shared(smem_u32(&pairs[crank]), 0), m, s);
+                mbar_arrive_cluster(mapa_shared(bar, 0));
+              }
+              writes_row = false;
+            } else {
+              if (!mbar_wait_cluster(bar, 0)) {
+                raise_status(p.status, TOME_DEV_TIMEOUT);
+                s = __int_as_float(0x7fc00000);
+              }
+              const float2 o = (lane >= 1 && lane < K1_SPLIT) ? pairs[lane]
+                               : (lane == 0)                  ? make_float2(m, s)
+                                                              : make_float2(-FLT_MAX, 0.0f);
+              Online all = {o.x, o.y};
+              online_warp_reduce(all, p.c);
+              m = all.m;
+              s = all.s;
+            }
+          }
           // the true maximum contributes 2^0, so a healthy row has s >= ~1
-          if (!(s >= 0.5f && s <= FLT_MAX)) exact_row(src, p.vocab, p.c, lane, m, s);
+          if (writes_row && !(s >= 0.5f && s <= FLT_MAX)) exact_row(src, p.vocab, p.c, lane, m, s);
           if (MODE == K1_FULL) lse_row = finish_lse<MODE>(m, s, p);
           if (MODE == K1_SAMPLE && ctid == 0) p.out1[row] = finish_lse<MODE>(m, s, p);
-          if (MODE != K1_SAMPLE && ctid == 0)
+          if (MODE != K1_SAMPLE && ctid == 0 && writes_row)
             emit_row<MODE>(p, oidx, sub, m, s, x_t, target_ok, carry);
         }
+        if (SPLIT && w.shared) ++split_it;
         if (MODE == K1_SAMPLE) {
           // each warp copies its own list out; nothing here waits for another warp
           const int32_t keep = min(wcount, min(K1_SAMPLE_WARP_LIST, p.cand_cap));
@@ -387,6 +489,10 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
     }
   }
   (void)PER_VEC;
+  if (SPLIT) {  // nobody leaves while a peer may still address its shared memory
+    __syncwarp();
+    cluster_sync_all();
+  }
 }
 
 // ------------------------------------------------------------------ plain-load kernel
@@ -503,6 +609,56 @@ static void (*pick_stream_kernel())(K1Params) {
   return k1_stream_kernel<T, MODE, 0>;
 }
 
+// Selective mode with the rows of the last, partial round shared by clusters of K1_SPLIT CTAs.
+// Taken when that round is thin: at most one shared row per cluster after at least one whole
+// round, with fewer than 8 rows per CTA in all.  Then the few CTAs of the last round cannot
+// fill the memory system on their own (600 bf16 rows: 44.7 -> 38.3 us).  A fuller last round
+// keeps HBM busy as it is and sharing its rows gains nothing (1024 fp32 rows: 104.1 us plain,
+// 105.7 shared; 300 rows, all shared: 37.0 -> 41.1), so those stay with the plain launch.
+// Further conditions: a row has a chunk for every CTA of a cluster and the exponential variant
+// is the default one.  TOME_K1_TAIL=0 switches the sharing off, 2 takes it whenever the row
+// count allows (read at every call; tests).
+template <typename T>
+static int32_t k1_launch_split_tail(const K1Params& p, const DeviceInfo& info, cudaStream_t stream,
+                                    bool* taken) {
+  *taken = false;
+  constexpr bool bf16 = std::is_same<T, __nv_bfloat16>::value;
+  constexpr int POLY = bf16 ? K1_POLY_DEFAULT : 0;
+  if (bf16 && k1_poly_setting() != K1_POLY_DEFAULT) return TOME_OK;
+  if (p.n_chunks < K1_SPLIT) return TOME_OK;
+  const char* e = getenv("TOME_K1_TAIL");
+  const int knob = (e != nullptr) ? atoi(e) : 1;
+  if (knob == 0) return TOME_OK;
+  using Smem = K1SmemT<K1_STAGES>;
+  constexpr int smem = Smem::TOTAL_SPLIT;
+  void (*kernel)(K1Params) = k1_stream_kernel<T, K1_SELECTIVE, POLY, true>;
+  int32_t st = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
+  if (st != TOME_OK) return st;
+  const int fit = max_active_clusters(reinterpret_cast<const void*>(kernel), K1_THREADS, smem, K1_SPLIT);
+  if (fit <= 0) return TOME_OK;
+  const int64_t grid_full = static_cast<int64_t>(fit) * K1_SPLIT;
+  const int64_t last_round = p.n_rows % grid_full;
+  if (last_round == 0) return TOME_OK;
+  if (knob != 2 && (p.n_rows < grid_full || p.n_rows >= 8 * grid_full || last_round > fit))
+    return TOME_OK;
+  // fewer rows than CTAs: every row is shared, by as many clusters as there are rows at most
+  const int64_t n_clusters = (p.n_rows >= grid_full) ? fit : std::min<int64_t>(fit, p.n_rows);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(n_clusters * K1_SPLIT), 1, 1);
+  cfg.blockDim = dim3(K1_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = K1_SPLIT;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  *taken = true;
+  return check_cuda(cudaLaunchKernelEx(&cfg, kernel, p), "k1 split-tail launch");
+}
+
 template <typename T, int MODE>
 static int32_t k1_launch_typed(const K1Params& p_in, bool bulk_ok, int64_t max_items,
                                cudaStream_t stream) {
@@ -540,6 +696,12 @@ static int32_t k1_launch_typed(const K1Params& p_in, bool bulk_ok, int64_t max_i
     if (smem > info.max_smem_optin)
       return fail(TOME_ERR_UNSUPPORTED, "device offers %d bytes of shared memory, need %d",
                   info.max_smem_optin, smem);
+    if constexpr (MODE == K1_SELECTIVE) {
+      // few rows per CTA: the last round's rows are shared by clusters (see K1_SPLIT)
+      bool taken = false;
+      st = k1_launch_split_tail<T>(p, info, stream, &taken);
+      if (taken || st != TOME_OK) return st;
+    }
     void (*kernel)(K1Params) = pick_stream_kernel<T, MODE>();
     st = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     if (st != TOME_OK) return st;
