@@ -184,12 +184,15 @@ int32_t tome_sample_topk_logprob(const void* logits, int32_t dtype, int64_t rows
                                  int32_t* dev_status, void* stream);
 
 /*
- * The same call with caller-owned scratch, which lets large batches take a three-kernel path
- * whose pass over the logits is a plain streaming pass (per-row threshold, streaming pass
- * that collects the candidates, rank + draw).  Same results as tome_sample_topk_logprob: the
+ * The same call with caller-owned scratch, which lets large batches take a two-kernel path
+ * whose pass over the logits is a plain streaming pass (it keeps the row's sum, finds the
+ * row's top-k threshold on the way and notes where the logits that reach it sit; a second
+ * kernel fetches those, ranks and draws).  Same results as tome_sample_topk_logprob: the
  * draw depends on the row's top-k only.  tome_sample_workspace_bytes returns the bytes that
- * path needs for the batch, or 0 if the batch would not take it (then workspace may be NULL).
- * workspace must be 16-byte aligned; its contents need no initialisation.
+ * path needs for the batch, or 0 if a batch of that shape would not take it whatever its
+ * dtype (then workspace may be NULL).  workspace must be 16-byte aligned; its contents need
+ * no initialisation.  A row without a single logit that is not NaN gets token -1, log-prob
+ * NaN and TOME_DEV_NO_CANDIDATE (both entry points).
  */
 size_t tome_sample_workspace_bytes(int64_t rows, int64_t vocab);
 int32_t tome_sample_topk_logprob_ws(const void* logits, int32_t dtype, int64_t rows,

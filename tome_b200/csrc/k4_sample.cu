@@ -40,7 +40,12 @@ constexpr int K4_SAMPLE = 32768;   // leading logits used to derive the first th
 constexpr int K4_GROUPS = K4_THREADS / 4;  // sample maxima kept for the threshold
 constexpr int K4_RANK_MAX = 1024;  // above this many candidates, compact before ranking
 constexpr int K4_MAX_SWEEPS = 64;   // re-sweeps with a tightened threshold before giving up
-constexpr int64_t K4_STREAM_MIN_ROWS = 320;    // from here on a batch takes the three-kernel path
+// From these row counts on a batch takes the streaming path: one row more than a full wave of
+// the row kernel's CTAs (two per SM for bf16, one for fp32).  Measured, V = 151936, row kernel /
+// streaming path: bf16 256 rows 32 / 35 us, 320 rows 58 / 42 us; fp32 128 rows 29 / 40 us, 160
+// rows 45 / 45 us, 200 rows 53 / 46 us.
+constexpr int64_t K4_STREAM_MIN_ROWS_BF16 = 297;
+constexpr int64_t K4_STREAM_MIN_ROWS_F32 = 160;
 constexpr int64_t K4_STREAM_MIN_VOCAB = 4096;  // every consumer of the streaming kernel sees logits
 constexpr int K4_MAX_LISTS = 8;                // lists per row (one per consumer warp of the streaming kernel)
 constexpr int K4_CODE_CAP = 256;               // logits of a row that may reach its final threshold
@@ -651,10 +656,10 @@ static K4Workspace k4_workspace(void* base, int64_t rows, int lists) {
 
 // Whether a batch takes the streaming path (given scratch): large batches of rows that the
 // streaming kernel can read.  TOME_K4_STREAM = 1 / 0 forces it on (where possible) / off.
-static bool k4_wants_stream(int64_t rows, int64_t vocab) {
+static bool k4_wants_stream(int64_t rows, int64_t vocab, int32_t dtype) {
   if (vocab < K4_STREAM_MIN_VOCAB) return false;
   if (const char* e = getenv("TOME_K4_STREAM")) return atoi(e) != 0;
-  return rows >= K4_STREAM_MIN_ROWS;
+  return rows >= (dtype == TOME_F32 ? K4_STREAM_MIN_ROWS_F32 : K4_STREAM_MIN_ROWS_BF16);
 }
 
 // Cluster size for a batch too small to fill the GPU with one CTA per row: the largest of 8
@@ -703,7 +708,7 @@ static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, i
   int32_t st = current_device_info(&info);
   if (st != TOME_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool streamed = workspace != nullptr && k4_wants_stream(rows, vocab) &&
+  const bool streamed = workspace != nullptr && k4_wants_stream(rows, vocab, dtype) &&
                         k1_sample_eligible(logits, dtype, vocab, row_stride);
   const int lists = k1_sample_lists_per_row();
   const int list_cap = k1_sample_list_capacity();
@@ -802,7 +807,10 @@ extern "C" int32_t tome_sample_topk_logprob(const void* logits, int32_t dtype, i
 }
 
 extern "C" size_t tome_sample_workspace_bytes(int64_t rows, int64_t vocab) {
-  if (rows <= 0 || vocab <= 0 || !k4_wants_stream(rows, vocab)) return 0;
+  // the size does not know the dtype: whatever either dtype would use
+  if (rows <= 0 || vocab <= 0 ||
+      !(k4_wants_stream(rows, vocab, TOME_F32) || k4_wants_stream(rows, vocab, TOME_BF16)))
+    return 0;
   return k4_workspace_bytes(rows, k1_sample_lists_per_row(), k1_sample_list_capacity());
 }
 

@@ -411,7 +411,7 @@ def sample_topk_logprob(logits: torch.Tensor, temperature: float, top_k: int = 2
         _out_rows("out[1] (logprobs)", lp, rows, device)
     tk_i = torch.empty((rows, top_k), dtype=torch.int32, device=device) if return_topk else None
     tk_v = torch.empty((rows, top_k), dtype=torch.float32, device=device) if return_topk else None
-    # large batches take a streaming path that needs scratch (0: not this batch)
+    # large batches take a streaming path that needs scratch (0: not a batch of this shape)
     nbytes = sample_workspace_bytes(rows, V)
     ws = None
     if nbytes:
