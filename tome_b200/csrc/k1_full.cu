@@ -24,7 +24,13 @@ namespace tome {
 //     per SM hold too few of them;
 //   * one CTA per SM with separate rings, producers and warps for the two passes, pass 2
 //     trailing pass 1 by a row so that nothing waits for the exchange: 4850 - 5100 / 5060 - 5300.
-// What limited all of them was the instruction count of pass 2 (see full_out_vec).
+//   * this kernel with pass 1 of the cluster's next row run before pass 2 of the current one
+//     (the exchange's answer is then a pass old when it is needed): 4540 / 4780 against 5770 /
+//     5740; two rows per cluster between the passes no longer stay in L2.  It only wins with
+//     clusters larger than the default (half as many rows in flight), and then stays behind
+//     the default.
+// What helped was cutting the instruction count of pass 2 (see full_out_vec); with it the
+// kernel issues on 45 % of the cycles and keeps DRAM 67 % busy, the rest is the exchange.
 #ifndef KF_CFG_WARPS
 #define KF_CFG_WARPS 8
 #endif
