@@ -79,7 +79,7 @@ struct K1Params {
   int32_t* out_offsets;    // RAGGED: int32 [n_seq + 1], start of each sequence in the packed output
   float* row_thr;          // SAMPLE: out, per row the final threshold (>= top_k logits reach it)
   int32_t* cand_count;     // SAMPLE: [rows, lists] entries per list (cand_cap + 1: overflow)
-  uint32_t* cand_entry;    // SAMPLE: [rows, lists, cand_cap] noted places, see K1SampleSmem
+  uint2* cand_entry;       // SAMPLE: [rows, lists, cand_cap] noted places, see K1SampleSmem
   int32_t cand_cap;        // SAMPLE: entries per list (lists per row = consumer warps)
   int32_t sample_kk;       // SAMPLE: min(top_k, vocab)
   int32_t sample_q;        // SAMPLE: ceil(top_k / consumer warps), 1 .. 32

@@ -41,8 +41,10 @@ constexpr int K1_FULL_STAGES = K1_CFG_FULL_STAGES;
 __host__ __device__ constexpr int k1_stages(int mode) { return mode == K1_FULL ? K1_FULL_STAGES : K1_STAGES; }
 
 // SAMPLE mode: where a logit reaches the row's current threshold, the place is noted: one
-// 32-bit entry per thread and loop step, (index of the step's first 16-byte vector << 4) | mask
-// of the step's four vectors (K1_CONSUMERS apart) that hold such a logit.  Each consumer warp
+// entry per thread and loop step, two words: (index of the step's first 16-byte vector << 4) |
+// mask of the step's four vectors (K1_CONSUMERS apart) that hold such a logit, and the largest
+// logit of those four vectors (with which the next kernel drops, unread, the entries that the
+// row's final threshold has left behind).  Each consumer warp
 // keeps a list of its own; its lanes take their slots with one ballot and a register counter
 // (no atomic, no memory round trip), and the warp copies the list out once per row.  The
 // kernel that follows fetches the vectors again (about 1 % of the row).  Earlier forms:
@@ -53,7 +55,7 @@ constexpr int K1_SAMPLE_WARP_LIST = 128;
 constexpr int K1_SAMPLE_TOP = 32 / K1_CONSUMER_WARPS;  // lane maxima each warp puts forward
 static_assert(32 % K1_CONSUMER_WARPS == 0 && K1_CONSUMERS <= 128, "threshold keys: 7 id bits");
 struct K1SampleSmem {
-  uint32_t entry[K1_CONSUMER_WARPS][K1_SAMPLE_WARP_LIST];
+  uint2 entry[K1_CONSUMER_WARPS][K1_SAMPLE_WARP_LIST];
   uint32_t pub[2][32];  // threshold refinement: what the warps put forward (by parity)
 };
 
@@ -277,12 +279,13 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       float thr_val = __int_as_float(0x7f800000);  // +inf: nothing qualifies
       float tmax = __int_as_float(0xff800000);     // largest logit this thread has seen
       int32_t wcount = 0;                          // entries in this warp's list (same in every lane)
-      auto note = [&](uint32_t mask, int64_t vec_index) {
+      auto note = [&](uint32_t mask, int64_t vec_index, float largest) {
         const uint32_t bal = __ballot_sync(0xffffffffu, mask != 0u);
         if (mask != 0u) {
           const int32_t slot = wcount + __popc(bal & ((1u << lane) - 1u));
           if (slot < K1_SAMPLE_WARP_LIST)
-            smp.entry[warp][slot] = (static_cast<uint32_t>(vec_index) << 4) | mask;
+            smp.entry[warp][slot] =
+                make_uint2((static_cast<uint32_t>(vec_index) << 4) | mask, __float_as_uint(largest));
         }
         wcount += __popc(bal);
       };
@@ -376,22 +379,23 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
               if (__any_sync(0xffffffffu, !(m4 < thr_val))) {
                 const uint32_t mask = (!(ma < thr_val) ? 1u : 0u) | (!(mb < thr_val) ? 2u : 0u) |
                                       (!(mc < thr_val) ? 4u : 0u) | (!(md < thr_val) ? 8u : 0u);
-                note(mask, (off >> 4) + v);  // v: this thread's first vector of the step
+                note(mask, (off >> 4) + v, m4);  // v: this thread's first vector of the step
               }
             }
           }
           for (; vb < nvec; vb += K1_CONSUMERS) {
             const uint32_t v = vb + lane;
             bool hit = false;
+            float ma = 0.0f;
             if (v < nvec) {
-              const float ma = fast_update<POLY>(fs, lds128(sbase + v * 16), p.c, T());
+              ma = fast_update<POLY>(fs, lds128(sbase + v * 16), p.c, T());
               if (MODE == K1_SAMPLE) {
                 hit = !(ma < thr_val);
                 tmax = fmaxf(tmax, ma);
               }
             }
             if (MODE == K1_SAMPLE && __any_sync(0xffffffffu, hit))
-              note(hit ? 1u : 0u, (off >> 4) + v);
+              note(hit ? 1u : 0u, (off >> 4) + v, ma);
           }
         } else {
           uint8_t* drow = reinterpret_cast<uint8_t*>(dst) + off;
@@ -424,7 +428,7 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
         // the elements past the last 16-byte boundary count as one more (short) vector
         float tail_max = __int_as_float(0xff800000);
         for (int64_t j = tail_begin; j < p.vocab; ++j) tail_max = fmax_nan(tail_max, to_float(src[j]));
-        note((lane == 0 && !(tail_max < thr_val)) ? 1u : 0u, tail_begin / PER_VEC);
+        note((lane == 0 && !(tail_max < thr_val)) ? 1u : 0u, tail_begin / PER_VEC, tail_max);
       }
 
       if (reduce_pass) {
@@ -925,7 +929,7 @@ bool k1_sample_eligible(const void* logits, int32_t dtype, int64_t vocab, int64_
 
 int32_t k1_launch_sample(const void* logits, int32_t dtype, int64_t rows, int64_t vocab,
                          int64_t row_stride, float temperature, int32_t top_k, float* row_thr,
-                         int32_t* cand_count, uint32_t* cand_entry, int32_t cand_cap,
+                         int32_t* cand_count, uint2* cand_entry, int32_t cand_cap,
                          float* out_lse, int32_t* zero_word, int32_t* dev_status,
                          cudaStream_t stream) {
   K1Params p = {};

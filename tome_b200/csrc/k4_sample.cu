@@ -488,7 +488,7 @@ struct K4Lists {
   const float* row_thr;
   const float* lse;
   const int32_t* count;   // [rows, lists]
-  const uint32_t* entry;  // [rows, lists, cap]
+  const uint2* entry;     // [rows, lists, cap]
 };
 
 // One warp per row (four rows per CTA at a time), nothing but warp-level synchronisation:
@@ -532,9 +532,11 @@ k4_finish_kernel(const K4Params p, const K4Lists w) {
     }
     const int32_t total = __shfl_sync(0xffffffffu, begin, K4_MAX_LISTS - 1);
     begin -= my_count;
-    // ---- entries -> vector numbers (every logit that reaches the final threshold sits in a
-    //      vector some entry names)
-    int32_t n_vec = 0;
+    // ---- entries -> vector numbers.  Every logit that reaches the final threshold sits in a
+    //      vector some entry names; an entry whose largest logit stays below it is dropped
+    //      unread (a NaN there keeps it).  Two steps: the surviving entries are gathered (one
+    //      ballot per 32 entries), then expanded (four ballots per 32 survivors).
+    int32_t n_kept = 0;
     for (int32_t g0 = 0; g0 < total; g0 += 32) {
       const int32_t g = g0 + lane;
       int32_t l = 0, at = g;
@@ -546,13 +548,33 @@ k4_finish_kernel(const K4Params p, const K4Lists w) {
           at = g - b;
         }
       }
-      const uint32_t e = (g < total) ? w.entry[(row * w.lists + l) * w.cap + at] : 0u;
+      const uint2 e = (g < total) ? w.entry[(row * w.lists + l) * w.cap + at] : make_uint2(0u, 0u);
+      const bool keep = (g < total) && !(__uint_as_float(e.y) < thr);
+      const uint32_t bal = __ballot_sync(0xffffffffu, keep);
+      const int32_t to = n_kept + __popc(bal & lanes_below);
+      if (keep && to < K4_VEC_CAP) vec[to] = static_cast<int32_t>(e.x);
+      n_kept += __popc(bal);
+    }
+    __syncwarp();
+    // every surviving entry is taken into a register first; then the buffer is overwritten with
+    // the vector numbers
+    int32_t n_vec = 0;
+    const int32_t kept = min(n_kept, K4_VEC_CAP / 4);
+    uint32_t mine_e[(K4_VEC_CAP / 4 + 31) / 32];
+#pragma unroll
+    for (int t = 0; t < (K4_VEC_CAP / 4 + 31) / 32; ++t)
+      mine_e[t] = (t * 32 + lane < kept) ? static_cast<uint32_t>(vec[t * 32 + lane]) : 0u;
+    __syncwarp();
+#pragma unroll
+    for (int t = 0; t < (K4_VEC_CAP / 4 + 31) / 32; ++t) {
+      if (t * 32 >= kept) break;
+      const uint32_t e = mine_e[t];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const bool bit = (e >> j) & 1u;
         const uint32_t bal = __ballot_sync(0xffffffffu, bit);
-        const int32_t at = n_vec + __popc(bal & lanes_below);
-        if (bit && at < K4_VEC_CAP) vec[at] = static_cast<int32_t>(e >> 4) + j * w.vec_stride;
+        const int32_t to = n_vec + __popc(bal & lanes_below);
+        if (bit && to < K4_VEC_CAP) vec[to] = static_cast<int32_t>(e >> 4) + j * w.vec_stride;
         n_vec += __popc(bal);
       }
     }
@@ -585,7 +607,7 @@ k4_finish_kernel(const K4Params p, const K4Lists w) {
     }
     __syncwarp();
     const int32_t n = n_codes[warp];
-    if (overflow || n_vec > K4_VEC_CAP || n > K4_CODE_CAP || n < kk) {
+    if (overflow || n_kept > K4_VEC_CAP / 4 || n_vec > K4_VEC_CAP || n > K4_CODE_CAP || n < kk) {
       // lists that ran over (sorted or heavily tied rows) or a row with too few logits that
       // are not NaN: left to the row kernel
       if (lane == 0) p.marked_rows[atomicAdd(p.marked, 1)] = static_cast<int32_t>(row);
@@ -634,13 +656,13 @@ struct K4Workspace {
   int32_t* marked_rows;
   int32_t* count;    // [rows, lists]
   int32_t* marked;   // one counter for the batch
-  uint32_t* entry;   // [rows, lists, cap]
+  uint2* entry;      // [rows, lists, cap]
 };
 static size_t k4_workspace_head(int64_t rows, int lists) {
   return (static_cast<size_t>(rows) * (12 + 4 * lists) + 4 + 15) & ~static_cast<size_t>(15);
 }
 static size_t k4_workspace_bytes(int64_t rows, int lists, int cap) {
-  return k4_workspace_head(rows, lists) + static_cast<size_t>(rows) * lists * cap * sizeof(uint32_t);
+  return k4_workspace_head(rows, lists) + static_cast<size_t>(rows) * lists * cap * sizeof(uint2);
 }
 static K4Workspace k4_workspace(void* base, int64_t rows, int lists) {
   K4Workspace w;
@@ -650,7 +672,7 @@ static K4Workspace k4_workspace(void* base, int64_t rows, int lists) {
   w.marked_rows = reinterpret_cast<int32_t*>(w.lse + rows);
   w.count = w.marked_rows + rows;
   w.marked = w.count + rows * lists;
-  w.entry = reinterpret_cast<uint32_t*>(b + k4_workspace_head(rows, lists));
+  w.entry = reinterpret_cast<uint2*>(b + k4_workspace_head(rows, lists));
   return w;
 }
 
