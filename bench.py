@@ -511,10 +511,16 @@ def run_extra(args, device, rank, world, dist_on, barrier, peaks):
         xs = (torch.randn((rows_s, VOCAB), device=device, dtype=torch.float32) * 3.0).to(
             torch.bfloat16)
         step_no = [0]
+        # outputs and scratch are the caller's to reuse from step to step (a decode loop does)
+        s_out = (torch.empty(rows_s, dtype=torch.int32, device=device),
+                 torch.empty(rows_s, dtype=torch.float32, device=device))
+        s_ws = torch.empty(max(16, tome_b200.sample_workspace_bytes(rows_s, VOCAB)),
+                           dtype=torch.uint8, device=device)
 
         def sample_step():
             step_no[0] += 1
-            tome_b200.sample_topk_logprob(xs, 0.7, 20, seed=7, offset=step_no[0])
+            tome_b200.sample_topk_logprob(xs, 0.7, 20, seed=7, offset=step_no[0], out=s_out,
+                                          workspace=s_ws)
 
         ms_s, launch_s = timed(sample_step)
         extra[name] = {"rows": rows_s, "ms": ms_s, "rows_per_s": rows_s / (ms_s * 1e-3),
@@ -528,7 +534,7 @@ def run_extra(args, device, rank, world, dist_on, barrier, peaks):
         verdict(name, {"max_abs_logprob": (lp[sel] - torch_logprob(xs[sel], tok[sel], 0.7)).abs().max(),
                        "topk_values_max_abs": (tk_v[sel] - want_v).abs().max(),
                        "token_outside_topk": float((~in_topk).sum())})
-        del xs, tok, lp, tk_i, tk_v
+        del xs, tok, lp, tk_i, tk_v, s_out, s_ws
     torch.cuda.empty_cache()
 
     # paged KV gather / update: 64 sequences x 2048 tokens, 8 KV heads x 128, blocks of 16
