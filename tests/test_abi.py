@@ -91,7 +91,7 @@ def test_sampling_workspace_query_needs_no_gpu(built_lib, monkeypatch):
     monkeypatch.delenv("TOME_K4_STREAM", raising=False)
     q = _lib.lib.tome_sample_workspace_bytes
     assert q(8, 151936) == 0 and q(4096, 100) == 0 and q(0, 151936) == 0
-    per_row = 4 * 128 * 8          # four lists of 128 eight-byte entries per row
+    per_row = 4 * 112 * 8          # four lists of 112 eight-byte entries per row
     assert q(4096, 151936) >= 4096 * per_row
     assert q(4096, 151936) < 4096 * (per_row + 64)
     assert q(200, 151936) > 0      # fp32 batches of this size take the streaming path

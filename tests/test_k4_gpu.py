@@ -130,15 +130,18 @@ def test_unaligned_rows_and_extreme_k(cuda_device, dtype):
     assert tok.cpu().tolist() == torch.argmax(x[:, 1:1000].float(), dim=-1).tolist()
 
 
+@pytest.mark.parametrize("finish", ["kernel", "warp"])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("vocab", [24, 600, 4096 + 8, 40000, 151936])
-def test_large_batches_take_the_streaming_path(cuda_device, monkeypatch, dtype, vocab):
+def test_large_batches_take_the_streaming_path(cuda_device, monkeypatch, dtype, vocab, finish):
     """Large bf16 batches go through the TMA-pipelined kernel (forced here for fp32 too); rows
     it cannot finish (sorted, constant or heavily tied ones overflow its small candidate ring)
     come back marked and are redone by the one-CTA-per-row kernel.  Both must give the
     oracle's top-k."""
     import tome_b200
     monkeypatch.setenv("TOME_K4_STREAM", "1")
+    # the rows are finished by a kernel of their own or by the streaming kernel's producer warp
+    monkeypatch.setenv("TOME_K4_FINISH", finish)
     rows = 1200 if vocab < 100000 else 700
     x = _case(rows, vocab, dtype, 300 + vocab % 71)
     x[5] = torch.linspace(-8, 8, vocab).to(dtype)          # ascending: overflows the ring
@@ -263,14 +266,16 @@ def test_three_kernel_path_when_every_row_overflows(cuda_device, monkeypatch, dt
         assert i1[r, : len(idx)].cpu().tolist() == idx.tolist()
 
 
-@pytest.mark.parametrize("stream", ["0", "1"])
+@pytest.mark.parametrize("stream", ["0", "kernel", "warp"])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_rows_with_too_few_numbers(cuda_device, monkeypatch, stream, dtype):
     """A NaN is never a candidate.  A row with fewer than top_k logits that are not NaN draws
     from what it has and pads the top-k outputs; a row of NaNs gives token -1, log-prob NaN and
     a status bit, never an index left over from another row."""
     import tome_b200
-    monkeypatch.setenv("TOME_K4_STREAM", stream)
+    monkeypatch.setenv("TOME_K4_STREAM", "0" if stream == "0" else "1")
+    if stream != "0":
+        monkeypatch.setenv("TOME_K4_FINISH", stream)
     rows, vocab, k = 6, 32768, 20
     nan = float("nan")
     x = _case(rows, vocab, dtype, 77)

@@ -66,8 +66,8 @@ struct K1Params {
   float c;                 // log2(e) / temperature
   float temp;
   float inv_temp;
-  float* out0;             // SELECTIVE: logprob   DUAL: policy logprob   FULL: lse (nullable)
-  float* out1;             // SELECTIVE: lse (nullable)   DUAL: reference logprob
+  float* out0;             // SELECTIVE: logprob   DUAL: policy logprob   FULL: lse (nullable)   SAMPLE: logprob of the drawn token
+  float* out1;             // SELECTIVE: lse (nullable)   DUAL: reference logprob   SAMPLE: lse (scratch)
   float* out2;             // SELECTIVE: raw target logit (nullable)   DUAL: k3 KL
   void* out_full;          // FULL
   int64_t out_stride;      // FULL
@@ -83,7 +83,15 @@ struct K1Params {
   int32_t cand_cap;        // SAMPLE: entries per list (lists per row = consumer warps)
   int32_t sample_kk;       // SAMPLE: min(top_k, vocab)
   int32_t sample_q;        // SAMPLE: ceil(top_k / consumer warps), 1 .. 32
-  int32_t* zero_word;      // SAMPLE: nullable, a word the kernel sets to 0
+  int32_t finish_in_kernel;  // SAMPLE: the producer warp finishes the rows
+  int32_t sample_top_k;    // SAMPLE: top_k as asked for (width of the top-k outputs)
+  float sample_temperature;  // SAMPLE: as asked for; 0 = greedy (then temp is 1)
+  uint64_t sample_seed, sample_offset;
+  int32_t* out_tokens;     // SAMPLE: [rows]
+  int32_t* out_topk_idx;   // SAMPLE: nullable, [rows, top_k]
+  float* out_topk_val;     // SAMPLE: nullable, [rows, top_k]
+  int32_t* marked;         // SAMPLE: number of rows left to the row kernel (zero before the launch)
+  int32_t* marked_rows;    // SAMPLE: their indices
   int32_t* status;         // nullable
   int32_t chunk_bytes;     // bulk-copy size (multiple of 16, <= K1_CHUNK_BYTES), set by launch
   int32_t n_chunks;        // bulk copies per row

@@ -51,12 +51,22 @@ __host__ __device__ constexpr int k1_stages(int mode) { return mode == K1_FULL ?
 // unpacking the vectors here cost ~600 warp-cycles each; one list per CTA filled through a
 // shared-memory atomic stalled a warp for the atomic's round trip at every second step;
 // copying the vectors themselves, with a ballot per vector, cost 45 instructions per hit step.
-constexpr int K1_SAMPLE_WARP_LIST = 128;
+constexpr int K1_SAMPLE_WARP_LIST = 112;
+#ifndef K1_CFG_POLL_NS
+#define K1_CFG_POLL_NS 100
+#endif
+constexpr int K1_FINISH_CAP = 128;     // surviving entries, vectors and codes the finisher handles per row
+constexpr int K1_FINISH_TRIPS = 5;     // entries of a row it reads: at most 32 per trip
 constexpr int K1_SAMPLE_TOP = 32 / K1_CONSUMER_WARPS;  // lane maxima each warp puts forward
 static_assert(32 % K1_CONSUMER_WARPS == 0 && K1_CONSUMERS <= 128, "threshold keys: 7 id bits");
 struct K1SampleSmem {
   uint2 entry[K1_CONSUMER_WARPS][K1_SAMPLE_WARP_LIST];
   uint32_t pub[2][32];  // threshold refinement: what the warps put forward (by parity)
+  // the producer warp's scratch for finishing rows (see K1Finisher)
+  unsigned long long codes[K1_FINISH_CAP];  // first the surviving entries / vector numbers (32-bit)
+  unsigned long long top[K4_MAX_K];
+  int32_t lists_done;  // lists written out so far by the consumer warps, all rows together
+  int32_t n_codes;
 };
 
 // SPLIT: with a few rows per CTA the last round leaves most CTAs idle (1024 rows on 592 CTAs:
@@ -86,6 +96,233 @@ struct K1SmemT {
   static constexpr int TOTAL_SPLIT = SPLIT_BAR_OFF + K1_SPLIT_ITEMS * 8;
 };
 
+
+// SAMPLE mode: finishes a row once the consumers have streamed it, in the producer warp.  The
+// consumers leave, per row and in global memory, a threshold (a value that at least top_k
+// logits reach), the logsumexp and one list of entries per consumer warp.  The finisher drops
+// the entries whose largest logit stays below the threshold, fetches the vectors the others
+// name, keeps the logits that reach the threshold as (value, index) codes, ranks them (exact
+// top-k), draws a token and writes it with its log-prob.  A row it cannot hold (a list that ran
+// over, more than K1_FINISH_CAP survivors, fewer than top_k numbers) goes on the list of rows
+// for k4_sample_kernel.  The work is cut into steps of one global round trip or a few hundred
+// instructions, so that the copies the warp is there to issue are never kept waiting long;
+// what a step loads is used by the next one.
+template <typename T>
+struct K1Finisher {
+  static constexpr int PER = 16 / static_cast<int>(sizeof(T));
+  const K1Params& p;
+  K1SampleSmem& smp;
+  const int lane;
+  int32_t done = 0;   // rows finished
+  int phase = 0;
+  int64_t row = 0;
+  float thr = 0.0f;
+  bool spoilt = false;                 // the row goes to the row kernel
+  uint2 ent[K1_FINISH_TRIPS];          // phase 1: the entries this lane looks at
+  int32_t begin[K1_CONSUMER_WARPS];    // where each list begins when they are put end to end
+  int32_t trip0 = 0;                   // first of the trips held in ent[]
+  int32_t n_kept = 0;                  // entries that survived so far
+  int32_t total = 0;                   // entries of the row
+  uint4 vec[K1_FINISH_CAP / 32];       // phase 2: the vectors this lane unpacks
+  int32_t vec_at[K1_FINISH_CAP / 32];  // their numbers within the row (-1: none)
+  int32_t n_vec = 0;
+
+  __device__ K1Finisher(const K1Params& params, K1SampleSmem& s, int l) : p(params), smp(s), lane(l) {}
+  __device__ int64_t rows_finished() const { return done; }
+
+  __device__ __forceinline__ void give_up_row() {  // left to the row kernel
+    if (lane == 0) p.marked_rows[atomicAdd(p.marked, 1)] = static_cast<int32_t>(row);
+    ++done;
+    phase = 0;
+  }
+
+  // Asks for the entries of trips [trip0, trip0 + K1_FINISH_TRIPS).
+  __device__ __forceinline__ void load_entries() {
+#pragma unroll
+    for (int t = 0; t < K1_FINISH_TRIPS; ++t) {
+      const int32_t g = (trip0 + t) * 32 + lane;
+      int32_t l = 0, at = g;  // the last list that begins at or before g, and the place in it
+#pragma unroll
+      for (int q = 1; q < K1_CONSUMER_WARPS; ++q)
+        if (g >= begin[q]) {
+          l = q;
+          at = g - begin[q];
+        }
+      ent[t] = (g < total && !spoilt)
+                   ? p.cand_entry[(row * K1_CONSUMER_WARPS + l) * p.cand_cap + at]
+                   : make_uint2(0u, 0u);
+    }
+  }
+
+  // One step; false if there was nothing to do.
+  __device__ __forceinline__ bool step() {
+    const uint32_t below = (1u << lane) - 1u;
+    if (phase == 0) {
+      // a row is ready when every consumer warp has written its list out
+      const int32_t lists = *reinterpret_cast<volatile int32_t*>(&smp.lists_done);
+      if (lists < (done + 1) * K1_CONSUMER_WARPS) return false;
+      __threadfence_block();
+      row = static_cast<int64_t>(blockIdx.x) + static_cast<int64_t>(done) * gridDim.x;
+      thr = p.row_thr[row];
+      spoilt = false;
+      total = 0;
+#pragma unroll
+      for (int l = 0; l < K1_CONSUMER_WARPS; ++l) {
+        const int32_t n = p.cand_count[row * K1_CONSUMER_WARPS + l];
+        spoilt |= (n > p.cand_cap);
+        begin[l] = total;
+        total += min(n, p.cand_cap);
+      }
+      trip0 = 0;
+      n_kept = 0;
+      load_entries();
+      phase = 1;
+      return true;
+    }
+    if (phase == 1) {
+      if (spoilt) {
+        give_up_row();
+        return true;
+      }
+      // surviving entries, gathered (their first words) in shared memory ...
+      uint32_t* kept = reinterpret_cast<uint32_t*>(smp.codes);
+#pragma unroll
+      for (int t = 0; t < K1_FINISH_TRIPS; ++t) {
+        const bool keep =
+            ((trip0 + t) * 32 + lane < total) && !(__uint_as_float(ent[t].y) < thr);
+        const uint32_t bal = __ballot_sync(0xffffffffu, keep);
+        const int32_t to = n_kept + __popc(bal & below);
+        if (keep && to < K1_FINISH_CAP) kept[to] = ent[t].x;
+        n_kept += __popc(bal);
+      }
+      __syncwarp();
+      if (n_kept > K1_FINISH_CAP) {
+        give_up_row();
+        return true;
+      }
+      trip0 += K1_FINISH_TRIPS;
+      if (trip0 * 32 < total) {  // a long row: the next entries, same step again
+        load_entries();
+        return true;
+      }
+      // ... taken into registers, then expanded in place into vector numbers
+      uint32_t mine[K1_FINISH_CAP / 32];
+#pragma unroll
+      for (int t = 0; t < K1_FINISH_CAP / 32; ++t)
+        mine[t] = (t * 32 + lane < n_kept) ? kept[t * 32 + lane] : 0u;
+      __syncwarp();
+      n_vec = 0;
+#pragma unroll
+      for (int t = 0; t < K1_FINISH_CAP / 32; ++t) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const bool bit = (mine[t] >> j) & 1u;
+          const uint32_t bal = __ballot_sync(0xffffffffu, bit);
+          const int32_t to = n_vec + __popc(bal & below);
+          if (bit && to < K1_FINISH_CAP)
+            kept[to] = (mine[t] >> 4) + static_cast<uint32_t>(j * K1_CONSUMERS);
+          n_vec += __popc(bal);
+        }
+      }
+      __syncwarp();
+      if (n_vec > K1_FINISH_CAP) {
+        give_up_row();
+        return true;
+      }
+      // the vectors are asked for now and unpacked in the next step
+      const T* src = reinterpret_cast<const T*>(p.src[0]) + row * p.stride;
+#pragma unroll
+      for (int t = 0; t < K1_FINISH_CAP / 32; ++t) {
+        const int32_t i = t * 32 + lane;
+        vec_at[t] = (i < n_vec) ? static_cast<int32_t>(kept[i]) : -1;
+        vec[t] = make_uint4(0u, 0u, 0u, 0u);
+        if (vec_at[t] >= 0 && (static_cast<int64_t>(vec_at[t]) + 1) * PER <= p.vocab)
+          vec[t] = __ldg(reinterpret_cast<const uint4*>(src) + vec_at[t]);
+      }
+      if (lane == 0) smp.n_codes = 0;
+      __syncwarp();
+      phase = 2;
+      return true;
+    }
+    if (phase == 2) {
+      const T* src = reinterpret_cast<const T*>(p.src[0]) + row * p.stride;
+      const int32_t kk = p.sample_kk;
+#pragma unroll
+      for (int t = 0; t < K1_FINISH_CAP / 32; ++t) {
+        if (vec_at[t] < 0) continue;
+        const int64_t e0 = static_cast<int64_t>(vec_at[t]) * PER;
+        if (e0 + PER <= p.vocab) {
+          const uint32_t u[4] = {vec[t].x, vec[t].y, vec[t].z, vec[t].w};
+#pragma unroll
+          for (int q = 0; q < PER; ++q) {
+            const float x = (sizeof(T) == 4)
+                                ? __uint_as_float(u[q])
+                                : __uint_as_float((q & 1) ? (u[q >> 1] & 0xffff0000u) : (u[q >> 1] << 16));
+            if (x >= thr) {
+              const int32_t at = atomicAdd(&smp.n_codes, 1);
+              if (at < K1_FINISH_CAP) smp.codes[at] = k4_pack(x, e0 + q);
+            }
+          }
+        } else {  // the short vector at the end of a row whose length is not a multiple of 16 bytes
+          for (int64_t q = e0; q < p.vocab; ++q) {
+            const float x = to_float(src[q]);
+            if (x >= thr) {
+              const int32_t at = atomicAdd(&smp.n_codes, 1);
+              if (at < K1_FINISH_CAP) smp.codes[at] = k4_pack(x, q);
+            }
+          }
+        }
+      }
+      __syncwarp();
+      const int32_t n = smp.n_codes;
+      if (n > K1_FINISH_CAP || n < kk) {
+        give_up_row();
+        return true;
+      }
+      // exact top-kk by ranking every code against all (codes are distinct), two per lane and trip
+      for (int32_t i0 = 0; i0 < n; i0 += 64) {
+        const int32_t ia = i0 + lane, ib = i0 + 32 + lane;
+        const unsigned long long a = (ia < n) ? smp.codes[ia] : ~0ull;
+        const unsigned long long b = (ib < n) ? smp.codes[ib] : ~0ull;
+        int32_t rank_a = 0, rank_b = 0;
+#pragma unroll 4
+        for (int32_t j = 0; j < n; ++j) {
+          const unsigned long long o = smp.codes[j];
+          rank_a += (o > a) ? 1 : 0;
+          rank_b += (o > b) ? 1 : 0;
+        }
+        if (ia < n && rank_a < kk) smp.top[rank_a] = a;
+        if (ib < n && rank_b < kk) smp.top[rank_b] = b;
+      }
+      __syncwarp();
+      phase = 3;
+      return true;
+    }
+    // phase 3: draw, score, write
+    const int32_t kk = p.sample_kk;
+    const bool greedy = !(p.sample_temperature > 0.0f);
+    const int32_t pick =
+        greedy ? 0 : k4_draw_warp(smp.top, kk, p.c, row, p.sample_seed, p.sample_offset);
+    if (lane == 0) {
+      p.out_tokens[row] = k4_index(smp.top[pick]);
+      p.out0[row] = __fdiv_rn(k4_value(smp.top[pick]), p.temp) - p.out1[row];
+    }
+    const int32_t k = p.sample_top_k;
+    if (p.out_topk_idx != nullptr || p.out_topk_val != nullptr) {
+      for (int32_t j = lane; j < k; j += 32) {
+        const bool have = j < kk;
+        if (p.out_topk_idx != nullptr)
+          p.out_topk_idx[row * k + j] = have ? k4_index(smp.top[j]) : -1;
+        if (p.out_topk_val != nullptr)
+          p.out_topk_val[row * k + j] = have ? k4_value(smp.top[j]) : -INFINITY;
+      }
+    }
+    __syncwarp();
+    ++done;
+    phase = 0;
+    return true;
+  }
+};
 
 // One unit of work of a CTA: chunks [k_begin, k_end) of row / window position `item`.
 struct K1Item {
@@ -118,9 +355,10 @@ __device__ __forceinline__ bool k1_next_item(int64_t round, int64_t n_items, int
   return true;
 }
 
-template <typename T, int MODE, int POLY, bool SPLIT = false>
+template <typename T, int MODE, int POLY, bool SPLIT = false, bool FINISH = false>
 __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(const K1Params p) {
   static_assert(!SPLIT || MODE == K1_SELECTIVE, "rows are shared by clusters in selective mode only");
+  static_assert(!FINISH || MODE == K1_SAMPLE, "rows are finished in the kernel in sampling mode only");
   constexpr int STAGES = k1_stages(MODE);
   using Smem = K1SmemT<STAGES>;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -147,7 +385,8 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
       for (int i = 0; i < K1_SPLIT_ITEMS; ++i)
         mbar_init(smem_base + Smem::SPLIT_BAR_OFF + i * 8, K1_SPLIT - 1);
     fence_mbar_init();
-    if (MODE == K1_SAMPLE && blockIdx.x == 0 && p.zero_word != nullptr) *p.zero_word = 0;
+    if (MODE == K1_SAMPLE)
+      reinterpret_cast<K1SampleSmem*>(smem + Smem::SAMPLE_OFF)->lists_done = 0;
   }
   // SPLIT: every CTA does `whole_rounds` rows of its own, then a quarter of each row of its
   // cluster's share of the remainder
@@ -178,6 +417,57 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
   const int64_t chunk_bytes = p.chunk_bytes;
   const int64_t tail_begin = bulk_bytes / ES;  // first element not covered by bulk copies
 
+  if (FINISH && warp == K1_CONSUMER_WARPS) {
+    // ---------------- producer of the sampling mode: lane 0 issues the bulk copies, and while
+    // it waits for a stage to come free the whole warp finishes the rows the consumers have
+    // handed over (K1Finisher), one short step at a time
+    K1SampleSmem& smp = *reinterpret_cast<K1SampleSmem*>(smem + Smem::SAMPLE_OFF);
+    K1Finisher<T> fin(p, smp, lane);
+    const uint64_t policy = policy_evict_first();
+    uint32_t it = 0;
+    bool ok = true;
+    int64_t my_rows = 0;
+    for (int64_t row = blockIdx.x; row < n_items && ok; row += gridDim.x, ++my_rows) {
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(p.src[0]) + row * p.stride * ES;
+      for (int64_t k = 0; k < n_chunks && ok; ++k, ++it) {
+        const uint32_t stage = it % STAGES;
+        const uint32_t parity = ((it / STAGES) & 1u) ^ 1u;
+        const long long t0 = clock64();
+        for (;;) {
+          const bool ready = __shfl_sync(
+              0xffffffffu, (lane == 0) && mbar_try_wait(empty_bar + stage * 8, parity), 0);
+          if (ready) break;
+          if (!fin.step()) {
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+              if (lane == 0) raise_status(p.status, TOME_DEV_TIMEOUT);
+              ok = false;
+              break;
+            }
+            __nanosleep(K1_CFG_POLL_NS);  // nothing to do: leave the issue slots to the consumers
+          }
+        }
+        if (ok && lane == 0) {
+          const int64_t off = k * chunk_bytes;
+          const uint32_t bytes = static_cast<uint32_t>(min(chunk_bytes, bulk_bytes - off));
+          mbar_arrive_expect_tx(full_bar + stage * 8, bytes);
+          bulk_g2s_hint(smem_base + stage * K1_CHUNK_BYTES, src + off, bytes, full_bar + stage * 8,
+                        policy);
+        }
+      }
+    }
+    // the rows still to be finished once every copy is on its way
+    const long long t0 = clock64();
+    while (ok && fin.rows_finished() < my_rows) {
+      if (!fin.step()) {
+        if (clock64() - t0 > 4 * WAIT_LIMIT_CYCLES) {
+          if (lane == 0) raise_status(p.status, TOME_DEV_TIMEOUT);
+          break;
+        }
+        __nanosleep(K1_CFG_POLL_NS);
+      }
+    }
+    return;
+  }
   if (warp == K1_CONSUMER_WARPS) {
     // ---------------- producer: one thread issues every bulk copy of this CTA
     if (lane == 0) {
@@ -486,7 +776,11 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
           if (lane == 0)  // more than kept: overflow
             p.cand_count[row * K1_CONSUMER_WARPS + warp] = (wcount > keep) ? p.cand_cap + 1 : wcount;
           if (ctid == 0) p.row_thr[row] = thr_val;
-          __syncwarp();  // the list is reused by the next row
+          // FINISH: hand the row to the producer warp, which finishes it between its copies: the
+          // list (and, in warp 0, the threshold and the lse) is written before the count moves
+          if (FINISH) __threadfence_block();
+          __syncwarp();  // also: the list is reused by the next row
+          if (FINISH && lane == 0) atomicAdd(&smp.lists_done, 1);
         }
         ++red_it;
       }
@@ -707,6 +1001,11 @@ static int32_t k1_launch_typed(const K1Params& p_in, bool bulk_ok, int64_t max_i
       if (taken || st != TOME_OK) return st;
     }
     void (*kernel)(K1Params) = pick_stream_kernel<T, MODE>();
+    if constexpr (MODE == K1_SAMPLE) {
+      // the form whose producer warp also finishes the rows (default exponential variant only)
+      constexpr int POLY = std::is_same<T, __nv_bfloat16>::value ? K1_POLY_DEFAULT : 0;
+      if (p.finish_in_kernel) kernel = k1_stream_kernel<T, K1_SAMPLE, POLY, false, true>;
+    }
     st = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     if (st != TOME_OK) return st;
     int64_t ctas_per_sm = K1_CTAS_PER_SM;
@@ -928,27 +1227,36 @@ bool k1_sample_eligible(const void* logits, int32_t dtype, int64_t vocab, int64_
 }
 
 int32_t k1_launch_sample(const void* logits, int32_t dtype, int64_t rows, int64_t vocab,
-                         int64_t row_stride, float temperature, int32_t top_k, float* row_thr,
-                         int32_t* cand_count, uint2* cand_entry, int32_t cand_cap,
-                         float* out_lse, int32_t* zero_word, int32_t* dev_status,
+                         int64_t row_stride, const K1SampleArgs& a, int32_t* dev_status,
                          cudaStream_t stream) {
   K1Params p = {};
-  p.zero_word = zero_word;
   p.src[0] = logits;
   p.n_rows = rows;
   p.vocab = vocab;
   p.stride = row_stride;
-  p.c = LOG2E / temperature;
-  p.temp = temperature;
-  p.inv_temp = 1.0f / temperature;
-  p.out1 = out_lse;
-  p.row_thr = row_thr;
-  p.cand_count = cand_count;
-  p.cand_entry = cand_entry;
-  p.cand_cap = cand_cap;
-  const int64_t kk = std::max<int64_t>(1, std::min<int64_t>(top_k, vocab));
+  const float temp = (a.temperature > 0.0f) ? a.temperature : 1.0f;  // greedy: scored at 1
+  p.c = LOG2E / temp;
+  p.temp = temp;
+  p.inv_temp = 1.0f / temp;
+  p.finish_in_kernel = a.finish_in_kernel ? 1 : 0;
+  p.out0 = a.out_logprob;
+  p.out1 = a.lse;
+  p.row_thr = a.row_thr;
+  p.cand_count = a.cand_count;
+  p.cand_entry = a.cand_entry;
+  p.cand_cap = K1_SAMPLE_WARP_LIST;
+  const int64_t kk = std::max<int64_t>(1, std::min<int64_t>(a.top_k, vocab));
   p.sample_kk = static_cast<int32_t>(kk);
   p.sample_q = static_cast<int32_t>((kk + K1_CONSUMER_WARPS - 1) / K1_CONSUMER_WARPS);
+  p.sample_top_k = a.top_k;
+  p.sample_temperature = a.temperature;
+  p.sample_seed = a.seed;
+  p.sample_offset = a.offset;
+  p.out_tokens = a.out_tokens;
+  p.out_topk_idx = a.out_topk_idx;
+  p.out_topk_val = a.out_topk_val;
+  p.marked = a.marked;
+  p.marked_rows = a.marked_rows;
   p.status = dev_status;
   return k1_launch<K1_SAMPLE>(p, dtype, true, rows, stream);
 }

@@ -1,7 +1,8 @@
 // Internal interface of the streaming kernel's sampling mode (see k1_logprob.cu, MODE = SAMPLE),
-// the first stage of the large-batch sampling path of k4_sample.cu: it streams the logits once
-// at HBM speed, keeps the row's (max, sum-exp), derives the row's top-k threshold from the
-// logits as they pass and notes where the logits that reach it sit.
+// the large-batch sampling path of k4_sample.cu: it streams the logits once at HBM speed, keeps
+// the row's (max, sum-exp), derives the row's top-k threshold from the logits as they pass,
+// notes where the logits that reach it sit, and its producer warp turns those notes into the
+// exact top-k, a drawn token and its log-prob while the next rows stream.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -18,20 +19,38 @@ int k1_sample_lists_per_row();
 int k1_sample_list_capacity();
 int k1_sample_vector_stride();
 
-// Outputs, per row: row_thr [rows], a value that at least min(top_k, vocab) logits of the row
-// reach; L = k1_sample_lists_per_row() lists of entries {(v << 4) | mask, largest}: bit j of the
-// mask says that the 16-byte vector number v + j * k1_sample_vector_stride() of the row holds a
-// logit >= the threshold in force when it passed (never above row_thr, so every logit >=
-// row_thr sits in a vector some entry names; the elements past the row's last 16-byte boundary
-// count as one more, short, vector), and `largest` is the float bits of the largest logit of the
-// entry's four vectors (NaN if one of them holds a NaN): cand_count [rows, L] (cand_cap + 1 if a
-// list ran over) and cand_entry [rows, L, cand_cap].  out_lse [rows] receives
-// logsumexp(x / temperature).  *zero_word (nullable) is set to 0 by the kernel (the counter of
-// the stage that follows).
+struct K1SampleArgs {
+  bool finish_in_kernel;    // the producer warp finishes the rows (else only the notes are left)
+  float temperature;        // as asked for: 0 = greedy (argmax, scored at temperature 1)
+  int32_t top_k;
+  uint64_t seed, offset;
+  int32_t* out_tokens;      // [rows]
+  float* out_logprob;       // [rows]
+  int32_t* out_topk_idx;    // nullable, [rows, top_k]
+  float* out_topk_val;      // nullable, [rows, top_k]
+  // scratch, all device memory
+  float* row_thr;           // [rows]
+  float* lse;               // [rows]
+  int32_t* cand_count;      // [rows, lists]
+  uint2* cand_entry;        // [rows, lists, list capacity]
+  int32_t* marked;          // one word, ZERO before the launch: rows left to the row kernel
+  int32_t* marked_rows;     // [rows]: their indices
+};
+
+// Always left in the scratch, per row: row_thr, a value that at least min(top_k, vocab) logits
+// of the row reach; lse = logsumexp(x / temperature); L = k1_sample_lists_per_row() lists of
+// entries {(v << 4) | mask, largest}: bit j of the mask says that the 16-byte vector number
+// v + j * k1_sample_vector_stride() of the row holds a logit >= the threshold in force when it
+// passed (never above row_thr, so every logit >= row_thr sits in a vector some entry names; the
+// elements past the row's last 16-byte boundary count as one more, short, vector), and
+// `largest` is the float bits of the largest logit of the entry's four vectors (NaN if one of
+// them holds a NaN); cand_count (list capacity + 1 if a list ran over).
+// With finish_in_kernel the kernel also writes token and log-prob (and the optional top-k
+// lists) of every row it can finish; the others (a list that ran over, too many logits at the
+// threshold, fewer than top_k logits that are not NaN) are counted in *marked and listed in
+// marked_rows.
 int32_t k1_launch_sample(const void* logits, int32_t dtype, int64_t rows, int64_t vocab,
-                         int64_t row_stride, float temperature, int32_t top_k, float* row_thr,
-                         int32_t* cand_count, uint2* cand_entry, int32_t cand_cap,
-                         float* out_lse, int32_t* zero_word, int32_t* dev_status,
+                         int64_t row_stride, const K1SampleArgs& args, int32_t* dev_status,
                          cudaStream_t stream);
 
 }  // namespace tome

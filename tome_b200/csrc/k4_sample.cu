@@ -34,7 +34,6 @@ namespace tome {
 
 constexpr int K4_THREADS = 512;
 constexpr int K4_WARPS = K4_THREADS / 32;
-constexpr int K4_MAX_K = 64;
 constexpr int K4_CAP = 8192;       // candidate list capacity
 constexpr int K4_SAMPLE = 32768;   // leading logits used to derive the first threshold
 constexpr int K4_GROUPS = K4_THREADS / 4;  // sample maxima kept for the threshold
@@ -471,16 +470,21 @@ __global__ void __launch_bounds__(K4_THREADS, 2) k4_sample_split_kernel(const K4
 }
 
 // ------------------------------------------------------------------ large batches
-// Two kernels, so that the pass over the logits is a plain streaming pass:
-//   1. the streaming kernel's SAMPLE mode (k1_logprob.cu): one pass at HBM speed that keeps
-//      (max, sum-exp), derives the row's threshold (a value that at least kk logits reach)
-//      from the logits as they pass and notes which 16-byte vectors hold a logit that reaches
-//      it, in a few lists per row;
-//   2. k4_finish_kernel: fetches the noted vectors again (about 1 % of the row), keeps the
-//      logits that reach the final threshold, ranks them (exact top-kk), draws, scores, writes.
-// A row whose lists ran over (sorted or heavily tied rows) or that holds fewer than kk logits
-// that are not NaN is put on a list and redone by k4_sample_kernel (only_flagged).  Same tokens
-// as the other kernels of this file.
+// The streaming kernel's SAMPLE mode (k1_logprob.cu) makes one pass at HBM speed: its consumer
+// warps keep (max, sum-exp), derive the row's threshold (a value that at least kk logits reach)
+// from the logits as they pass and note which 16-byte vectors hold a logit that reaches it.
+// The noted vectors of a row are then fetched again, their logits ranked (exact top-kk), a token
+// drawn, scored and written.  A row whose lists ran
+// over (sorted or heavily tied rows) or that holds fewer than kk logits that are not NaN is put
+// on a list and redone by k4_sample_kernel (only_flagged).  Same tokens as the other kernels of
+// this file.
+//
+// The last step, from the noted places to token and log-prob, exists twice.  For fp32 logits
+// the streaming kernel's producer warp does it between two copies (nothing is added to the
+// call's time: 8192 x 151936 fp32 775 -> 727 us, the selective mode's own speed).  For bf16
+// logits that kernel is bound by its instruction count and the same work costs more there than
+// in a kernel of its own (4096 rows: 256 us against 238 us), so bf16 batches run
+// k4_finish_kernel afterwards.  TOME_K4_FINISH=kernel|warp forces one or the other (tests).
 struct K4Lists {
   int32_t lists;          // per row
   int32_t cap;            // entries per list
@@ -648,8 +652,8 @@ k4_finish_kernel(const K4Params p, const K4Lists w) {
   }
 }
 
-// Scratch layout of the streaming path: per row the threshold, the logsumexp, a slot of the
-// list of rows to redo and the list counters; one counter for the batch; then the lists.
+// Scratch layout: per row the threshold, the logsumexp, a slot of the list of rows to redo and
+// the list counters; one counter for the batch; then the lists.
 struct K4Workspace {
   float* thr;
   float* lse;
@@ -762,27 +766,47 @@ static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, i
     const K4Workspace w = k4_workspace(workspace, rows, lists);
     p.marked = w.marked;
     p.marked_rows = w.marked_rows;
-    const float lse_temp = (temperature > 0.0f) ? temperature : 1.0f;
-    const int grid_rows = static_cast<int>(std::min<int64_t>(
-        (rows + K4_LIST_THREADS / 32 - 1) / (K4_LIST_THREADS / 32),
-        static_cast<int64_t>(info.sm_count) * 16));
-    st = k1_launch_sample(logits, dtype, rows, vocab, row_stride, lse_temp, top_k, w.thr, w.count,
-                          w.entry, list_cap, w.lse, w.marked, dev_status, s);
+    st = check_cuda(cudaMemsetAsync(w.marked, 0, sizeof(int32_t), s), "cudaMemsetAsync(marked rows)");
     if (st != TOME_OK) return st;
-    K4Lists lw;
-    lw.lists = lists;
-    lw.cap = list_cap;
-    lw.vec_stride = k1_sample_vector_stride();
-    lw.row_thr = w.thr;
-    lw.lse = w.lse;
-    lw.count = w.count;
-    lw.entry = w.entry;
-    if (dtype == TOME_F32)
-      k4_finish_kernel<float><<<grid_rows, K4_LIST_THREADS, 0, s>>>(p, lw);
-    else
-      k4_finish_kernel<__nv_bfloat16><<<grid_rows, K4_LIST_THREADS, 0, s>>>(p, lw);
-    st = check_cuda(cudaGetLastError(), "k4 finish launch");
+    bool in_kernel = (dtype == TOME_F32);
+    if (const char* e = getenv("TOME_K4_FINISH")) in_kernel = (e[0] == 'w');  // "warp" / "kernel"
+    K1SampleArgs a;
+    a.finish_in_kernel = in_kernel;
+    a.temperature = temperature;
+    a.top_k = top_k;
+    a.seed = seed;
+    a.offset = offset;
+    a.out_tokens = out_tokens;
+    a.out_logprob = out_logprob;
+    a.out_topk_idx = out_topk_idx;
+    a.out_topk_val = out_topk_val;
+    a.row_thr = w.thr;
+    a.lse = w.lse;
+    a.cand_count = w.count;
+    a.cand_entry = w.entry;
+    a.marked = w.marked;
+    a.marked_rows = w.marked_rows;
+    st = k1_launch_sample(logits, dtype, rows, vocab, row_stride, a, dev_status, s);
     if (st != TOME_OK) return st;
+    if (!in_kernel) {
+      K4Lists lw;
+      lw.lists = lists;
+      lw.cap = list_cap;
+      lw.vec_stride = k1_sample_vector_stride();
+      lw.row_thr = w.thr;
+      lw.lse = w.lse;
+      lw.count = w.count;
+      lw.entry = w.entry;
+      const int grid_rows = static_cast<int>(std::min<int64_t>(
+          (rows + K4_LIST_THREADS / 32 - 1) / (K4_LIST_THREADS / 32),
+          static_cast<int64_t>(info.sm_count) * 16));
+      if (dtype == TOME_F32)
+        k4_finish_kernel<float><<<grid_rows, K4_LIST_THREADS, 0, s>>>(p, lw);
+      else
+        k4_finish_kernel<__nv_bfloat16><<<grid_rows, K4_LIST_THREADS, 0, s>>>(p, lw);
+      st = check_cuda(cudaGetLastError(), "k4 finish launch");
+      if (st != TOME_OK) return st;
+    }
   }
   const int smem = static_cast<int>(sizeof(K4Smem));
   void (*split_kernel)(K4Params, int) = (dtype == TOME_F32)

@@ -8,6 +8,8 @@
 
 namespace tome {
 
+constexpr int K4_MAX_K = 64;  // largest top_k
+
 // Order-preserving map float -> uint32 (larger float <=> larger key).  NaN maps to 0.
 __device__ __forceinline__ uint32_t k4_key(float x) {
   if (x != x) return 0u;
