@@ -184,10 +184,11 @@ int32_t tome_sample_topk_logprob(const void* logits, int32_t dtype, int64_t rows
                                  int32_t* dev_status, void* stream);
 
 /*
- * The same call with caller-owned scratch, which lets large batches take a two-kernel path
+ * The same call with caller-owned scratch, which lets batches of a few hundred rows and more
+ * (fp32: from 149, bf16: from 297) take a path
  * whose pass over the logits is a plain streaming pass (it keeps the row's sum, finds the
- * row's top-k threshold on the way and notes where the logits that reach it sit; a second
- * kernel fetches those, ranks and draws).  Same results as tome_sample_topk_logprob: the
+ * row's top-k threshold on the way and notes where the logits that reach it sit; those are
+ * fetched again, ranked and drawn from, by a second kernel or between the first one's copies).  Same results as tome_sample_topk_logprob: the
  * draw depends on the row's top-k only.  tome_sample_workspace_bytes returns the bytes that
  * path needs for the batch, or 0 if a batch of that shape would not take it whatever its
  * dtype (then workspace may be NULL).  workspace must be 16-byte aligned; its contents need

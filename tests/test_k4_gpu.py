@@ -165,6 +165,52 @@ def test_large_batches_take_the_streaming_path(cuda_device, monkeypatch, dtype, 
     assert max_abs(lp0, o_lp0) <= TOL[dtype]
 
 
+@pytest.mark.parametrize("parts", ["2", "4"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,vocab", [(100, 151936), (290, 40000 + 5), (700, 20000), (9, 4096 + 8)])
+def test_rows_cut_into_parts_give_the_same_tokens(cuda_device, monkeypatch, dtype, rows, vocab, parts):
+    """Batches smaller than the streaming kernel's grid have their rows cut into 2 or 4 work
+    items, each with a threshold, a (max, sum-exp) pair and lists of its own, which the finish
+    kernel puts together.  Same top-k lists and tokens as the one-CTA-per-row kernel, also when
+    there are more items than CTAs (700 rows), when a row is too short to be cut (4104 logits
+    in bf16: one copy per row) and when the rows end off the 16-byte grid."""
+    import tome_b200
+    wide = _case(rows, vocab + 3, dtype, 900 + rows)
+    wide[1] = torch.linspace(-8, 8, vocab + 3).to(dtype)       # ascending: overflows the lists
+    wide[2, :] = 0.5                                           # constant
+    wide[3, : vocab // 2] = float("-inf")                      # a part without a finite logit
+    wide[4, vocab // 3] = float("nan")
+    wide[5] = float("-inf")
+    wide[5, vocab - 1] = 2.0                                   # a single finite logit, in the last part
+    wide[6, vocab - 2:] = 50.0                                 # the winners sit past the last 16-byte boundary
+    pad = (-(vocab + 3)) % 8                                   # row pitch: a multiple of 16 bytes
+    xd = torch.nn.functional.pad(wide, (0, pad)).to(cuda_device)[:, :vocab]
+    x = wide[:, :vocab]
+    monkeypatch.setenv("TOME_K4_STREAM", "0")
+    t0, lp0, i0, v0 = tome_b200.sample_topk_logprob(xd, 0.7, 20, seed=3, offset=4, return_topk=True)
+    monkeypatch.setenv("TOME_K4_STREAM", "1")
+    monkeypatch.setenv("TOME_K4_PARTS", parts)
+    for _ in range(2):  # twice: the scratch keeps the call before
+        t1, lp1, i1, v1 = tome_b200.sample_topk_logprob(xd, 0.7, 20, seed=3, offset=4,
+                                                        return_topk=True)
+        assert torch.equal(t0, t1) and torch.equal(i0, i1)
+        assert torch.equal(v0.nan_to_num(), v1.nan_to_num())
+        ok = ~torch.isnan(lp0)
+        assert torch.equal(ok, ~torch.isnan(lp1))
+        assert max_abs(lp0[ok], lp1[ok]) <= (1e-5 if dtype == torch.float32 else 1e-4)
+    for r in [0, 3, 6, 7, rows - 1]:
+        idx, _ = oracle.topk_sampling_distribution(x[r], 0.7, 20)
+        assert i1[r, : len(idx)].cpu().tolist() == idx.tolist(), r
+    keep = [r for r in range(rows) if r != 4]
+    o_lp, _, _ = oracle.selective_logprob(x[keep], t1.cpu()[keep], 0.7)
+    assert max_abs(lp1.cpu()[keep], o_lp) <= TOL[dtype]
+    # a wide top-k with rows in parts: more logits reach the finish (or the row kernel)
+    t2, _, i2, _ = tome_b200.sample_topk_logprob(xd, 0.7, 64, seed=3, offset=4, return_topk=True)
+    for r in [0, 7]:
+        idx, _ = oracle.topk_sampling_distribution(x[r], 0.7, 64)
+        assert i2[r, : len(idx)].cpu().tolist() == idx.tolist(), r
+
+
 def test_streaming_path_draws_follow_the_topk_softmax(cuda_device, monkeypatch):
     import tome_b200
     g = torch.Generator().manual_seed(10)

@@ -77,13 +77,15 @@ struct K1Params {
   int32_t seq_len;         // DUAL
   int64_t packed_capacity; // RAGGED: entries the packed target/output arrays can hold
   int32_t* out_offsets;    // RAGGED: int32 [n_seq + 1], start of each sequence in the packed output
-  float* row_thr;          // SAMPLE: out, per row the final threshold (>= top_k logits reach it)
-  int32_t* cand_count;     // SAMPLE: [rows, lists] entries per list (cand_cap + 1: overflow)
-  uint2* cand_entry;       // SAMPLE: [rows, lists, cand_cap] noted places, see K1SampleSmem
+  float* row_thr;          // SAMPLE: out, per row (per part) the final threshold (>= top_k logits reach it)
+  int32_t* cand_count;     // SAMPLE: [rows, parts, lists] entries per list (cand_cap + 1: overflow)
+  uint2* cand_entry;       // SAMPLE: [rows, parts, lists, cand_cap] noted places, see K1SampleSmem
   int32_t cand_cap;        // SAMPLE: entries per list (lists per row = consumer warps)
   int32_t sample_kk;       // SAMPLE: min(top_k, vocab)
   int32_t sample_q;        // SAMPLE: ceil(top_k / consumer warps), 1 .. 32
   int32_t finish_in_kernel;  // SAMPLE: the producer warp finishes the rows
+  int32_t sample_parts_log2;  // SAMPLE: a row is cut into 1, 2 or 4 parts (work items of their own)
+  float2* part_ms;         // SAMPLE, rows in parts: [rows, parts] (max, sum-exp) of each part
   int32_t sample_top_k;    // SAMPLE: top_k as asked for (width of the top-k outputs)
   float sample_temperature;  // SAMPLE: as asked for; 0 = greedy (then temp is 1)
   uint64_t sample_seed, sample_offset;

@@ -355,6 +355,16 @@ __device__ __forceinline__ bool k1_next_item(int64_t round, int64_t n_items, int
   return true;
 }
 
+// SAMPLE mode with rows cut into parts: neighbouring items are the parts of one row, each with an
+// equal share of the row's chunks.  Returns the row and sets the item's chunk range.
+__device__ __forceinline__ int64_t k1_sample_part(const K1Params& p, int64_t n_chunks, K1Item& w) {
+  const int lg = p.sample_parts_log2;
+  const int64_t part = w.item & ((int64_t{1} << lg) - 1);
+  w.k_begin = (n_chunks * part) >> lg;
+  w.k_end = (n_chunks * (part + 1)) >> lg;
+  return w.item >> lg;
+}
+
 template <typename T, int MODE, int POLY, bool SPLIT = false, bool FINISH = false>
 __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(const K1Params p) {
   static_assert(!SPLIT || MODE == K1_SELECTIVE, "rows are shared by clusters in selective mode only");
@@ -397,6 +407,7 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
   const int64_t n_clusters = SPLIT ? gridDim.x / K1_SPLIT : 1;
   const int64_t cluster_id = SPLIT ? blockIdx.x / K1_SPLIT : 0;
   int64_t n_items = p.n_rows;
+  if (MODE == K1_SAMPLE) n_items <<= p.sample_parts_log2;
   if (WINDOWED) {
     n_items = dual_build_prefix(p, cum, reinterpret_cast<int32_t*>(smem + Smem::SCRATCH_OFF));
     if (MODE == K1_DUAL) dual_zero_masked(p);
@@ -410,6 +421,9 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
   }
   __syncthreads();
   if (SPLIT) cluster_sync_all();  // the peers' barriers exist before anything arrives on them
+  // SAMPLE: the kernels that follow (k4_sample.cu) may be set up while this one runs; they wait
+  // for its completion before they read anything
+  if (MODE == K1_SAMPLE) griddep_launch_dependents();
 
   const int64_t row_bytes = p.vocab * ES;
   const int64_t bulk_bytes = row_bytes & ~static_cast<int64_t>(15);
@@ -480,7 +494,9 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
         if (!k1_next_item<SPLIT>(round, n_items, whole_rounds, split_rows, n_clusters, cluster_id,
                                  crank, n_chunks, w))
           break;
-        const int64_t row = WINDOWED ? dual_row_of_item(p, cum, w.item) : w.item;
+        const int64_t row = WINDOWED               ? dual_row_of_item(p, cum, w.item)
+                            : (MODE == K1_SAMPLE) ? k1_sample_part(p, n_chunks, w)
+                                                  : w.item;
         for (int sub = 0; sub < NSUB && ok; ++sub) {
           const uint8_t* src = reinterpret_cast<const uint8_t*>(
                                    p.src[(MODE == K1_DUAL) ? sub : 0]) + row * p.stride * ES;
@@ -531,8 +547,10 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
     if (!k1_next_item<SPLIT>(round, n_items, whole_rounds, split_rows, n_clusters, cluster_id, crank,
                              n_chunks, w))
       break;
-    const int64_t item = w.item;
-    const int64_t row = WINDOWED ? dual_row_of_item(p, cum, item) : item;
+    const int64_t item = w.item;  // SAMPLE: also where the item's threshold and lists go
+    const int64_t row = WINDOWED               ? dual_row_of_item(p, cum, item)
+                        : (MODE == K1_SAMPLE) ? k1_sample_part(p, n_chunks, w)
+                                              : item;
     const int64_t oidx = (MODE == K1_RAGGED) ? item : row;  // where targets/outputs live
     float lse_row = 0.0f;
     for (int sub = 0; sub < NSUB; ++sub) {
@@ -643,7 +661,7 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
         const uint32_t bytes = static_cast<uint32_t>(min(chunk_bytes, bulk_bytes - off));
         const uint32_t nvec = dead ? 0u : (bytes >> 4);
         const uint32_t sbase = smem_base + stage * K1_CHUNK_BYTES;
-        if (MODE == K1_SAMPLE && k == 0) {
+        if (MODE == K1_SAMPLE && k == w.k_begin) {
           for (uint32_t v = ctid; v < nvec; v += K1_CONSUMERS)
             tmax = fmaxf(tmax, vec_max(lds128(sbase + v * 16), T()));
           refine();
@@ -700,8 +718,9 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
         // the sample has grown fourfold: raise the threshold.  Once more after the row's last
         // chunk: nothing is noted any more, but the kernel that follows has a third of the
         // logits to rank.
+        const int64_t kr = k - w.k_begin;  // chunks of this item so far, less one
         if (MODE == K1_SAMPLE &&
-            ((k >= 3 && ((k + 1) & k) == 0 && ((k + 1) & 0x55555555) != 0) || k + 1 == n_chunks))
+            ((kr >= 3 && ((kr + 1) & kr) == 0 && ((kr + 1) & 0x55555555) != 0) || k + 1 == w.k_end))
           refine();
       }
 
@@ -714,7 +733,7 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
           else dst[j] = full_out_scalar(src[j], p.inv_temp, lse_row);
         }
       }
-      if (MODE == K1_SAMPLE && warp == 0 && tail_begin < p.vocab) {
+      if (MODE == K1_SAMPLE && warp == 0 && tail_begin < p.vocab && w.k_end == n_chunks) {
         // the elements past the last 16-byte boundary count as one more (short) vector
         float tail_max = __int_as_float(0xff800000);
         for (int64_t j = tail_begin; j < p.vocab; ++j) tail_max = fmax_nan(tail_max, to_float(src[j]));
@@ -761,21 +780,38 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
             }
           }
           // the true maximum contributes 2^0, so a healthy row has s >= ~1
-          if (writes_row && !(s >= 0.5f && s <= FLT_MAX)) exact_row(src, p.vocab, p.c, lane, m, s);
+          // (a part of a row keeps its pair as it is: the kernel that merges the parts leaves a row
+          // with an unhealthy sum to the row kernel)
+          const bool in_parts = (MODE == K1_SAMPLE) && p.sample_parts_log2 != 0;
+          if (writes_row && !in_parts && !(s >= 0.5f && s <= FLT_MAX))
+            exact_row(src, p.vocab, p.c, lane, m, s);
           if (MODE == K1_FULL) lse_row = finish_lse<MODE>(m, s, p);
-          if (MODE == K1_SAMPLE && ctid == 0) p.out1[row] = finish_lse<MODE>(m, s, p);
+          if (MODE == K1_SAMPLE && ctid == 0) {
+            if (in_parts) p.part_ms[item] = make_float2(m, s);
+            else p.out1[row] = finish_lse<MODE>(m, s, p);
+          }
           if (MODE != K1_SAMPLE && ctid == 0 && writes_row)
             emit_row<MODE>(p, oidx, sub, m, s, x_t, target_ok, carry);
         }
         if (SPLIT && w.shared) ++split_it;
         if (MODE == K1_SAMPLE) {
-          // each warp copies its own list out; nothing here waits for another warp
+          // each warp copies its own list out; nothing here waits for another warp.  Entries
+          // that the final threshold has left behind (most: the threshold rose while the row
+          // passed) stay here, which shortens what the finishing step has to read.
           const int32_t keep = min(wcount, min(K1_SAMPLE_WARP_LIST, p.cand_cap));
-          const int64_t base = (row * K1_CONSUMER_WARPS + warp) * p.cand_cap;
-          for (int32_t i = lane; i < keep; i += 32) p.cand_entry[base + i] = smp.entry[warp][i];
+          const int64_t base = (item * K1_CONSUMER_WARPS + warp) * p.cand_cap;
+          int32_t alive = 0;
+          for (int32_t i0 = 0; i0 < keep; i0 += 32) {
+            const int32_t i = i0 + lane;
+            const uint2 e = (i < keep) ? smp.entry[warp][i] : make_uint2(0u, 0u);
+            const bool stays = (i < keep) && !(__uint_as_float(e.y) < thr_val);  // a NaN stays
+            const uint32_t bal = __ballot_sync(0xffffffffu, stays);
+            if (stays) p.cand_entry[base + alive + __popc(bal & ((1u << lane) - 1u))] = e;
+            alive += __popc(bal);
+          }
           if (lane == 0)  // more than kept: overflow
-            p.cand_count[row * K1_CONSUMER_WARPS + warp] = (wcount > keep) ? p.cand_cap + 1 : wcount;
-          if (ctid == 0) p.row_thr[row] = thr_val;
+            p.cand_count[item * K1_CONSUMER_WARPS + warp] = (wcount > keep) ? p.cand_cap + 1 : alive;
+          if (ctid == 0) p.row_thr[item] = thr_val;
           // FINISH: hand the row to the producer warp, which finishes it between its copies: the
           // list (and, in warp 0, the threshold and the lse) is written before the count moves
           if (FINISH) __threadfence_block();
@@ -1239,6 +1275,11 @@ int32_t k1_launch_sample(const void* logits, int32_t dtype, int64_t rows, int64_
   p.temp = temp;
   p.inv_temp = 1.0f / temp;
   p.finish_in_kernel = a.finish_in_kernel ? 1 : 0;
+  if ((a.parts != 1 && a.parts != 2 && a.parts != 4) || a.parts > k1_sample_max_parts(vocab, dtype) ||
+      (a.parts > 1 && (a.finish_in_kernel || a.part_ms == nullptr)))
+    return fail(TOME_ERR_UNSUPPORTED, "sampling pass: %d parts per row", a.parts);
+  p.sample_parts_log2 = (a.parts == 4) ? 2 : (a.parts == 2) ? 1 : 0;
+  p.part_ms = a.part_ms;
   p.out0 = a.out_logprob;
   p.out1 = a.lse;
   p.row_thr = a.row_thr;
@@ -1258,7 +1299,14 @@ int32_t k1_launch_sample(const void* logits, int32_t dtype, int64_t rows, int64_
   p.marked = a.marked;
   p.marked_rows = a.marked_rows;
   p.status = dev_status;
-  return k1_launch<K1_SAMPLE>(p, dtype, true, rows, stream);
+  return k1_launch<K1_SAMPLE>(p, dtype, true, rows * a.parts, stream);
+}
+
+int k1_sample_max_parts(int64_t vocab, int32_t dtype) {
+  const int64_t es = (dtype == TOME_F32) ? 4 : 2;
+  const int64_t bulk_bytes = (vocab * es) & ~static_cast<int64_t>(15);
+  const int64_t chunks = (bulk_bytes + K1_CHUNK_BYTES - 1) / K1_CHUNK_BYTES;  // as k1_launch_typed
+  return chunks >= 4 ? 4 : chunks >= 2 ? 2 : 1;
 }
 
 int k1_sample_lists_per_row() { return K1_CONSUMER_WARPS; }

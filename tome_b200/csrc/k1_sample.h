@@ -18,9 +18,12 @@ bool k1_sample_eligible(const void* logits, int32_t dtype, int64_t vocab, int64_
 int k1_sample_lists_per_row();
 int k1_sample_list_capacity();
 int k1_sample_vector_stride();
+// Most parts a row of this length may be cut into (1, 2 or 4): every part gets a bulk copy.
+int k1_sample_max_parts(int64_t vocab, int32_t dtype);
 
 struct K1SampleArgs {
   bool finish_in_kernel;    // the producer warp finishes the rows (else only the notes are left)
+  int32_t parts;            // 1, 2 or 4 work items per row (more than 1: not with finish_in_kernel)
   float temperature;        // as asked for: 0 = greedy (argmax, scored at temperature 1)
   int32_t top_k;
   uint64_t seed, offset;
@@ -29,10 +32,11 @@ struct K1SampleArgs {
   int32_t* out_topk_idx;    // nullable, [rows, top_k]
   float* out_topk_val;      // nullable, [rows, top_k]
   // scratch, all device memory
-  float* row_thr;           // [rows]
-  float* lse;               // [rows]
-  int32_t* cand_count;      // [rows, lists]
-  uint2* cand_entry;        // [rows, lists, list capacity]
+  float* row_thr;           // [rows, parts]
+  float* lse;               // [rows] (parts == 1)
+  float2* part_ms;          // [rows, parts] (parts > 1)
+  int32_t* cand_count;      // [rows, parts, lists]
+  uint2* cand_entry;        // [rows, parts, lists, list capacity]
   int32_t* marked;          // one word, ZERO before the launch: rows left to the row kernel
   int32_t* marked_rows;     // [rows]: their indices
 };
@@ -49,6 +53,11 @@ struct K1SampleArgs {
 // lists) of every row it can finish; the others (a list that ran over, too many logits at the
 // threshold, fewer than top_k logits that are not NaN) are counted in *marked and listed in
 // marked_rows.
+// With parts > 1 every part of a row is a work item of its own (small batches: more CTAs than
+// rows): it leaves its own threshold (a value that at least min(top_k, vocab) logits of the PART
+// reach, hence of the row: the largest of a row's part thresholds serves as row_thr), its own
+// lists (vector numbers count from the row's start) and, instead of lse, the pair (max,
+// sum of 2^((x - max) * log2(e) / temperature)) of the part in part_ms.
 int32_t k1_launch_sample(const void* logits, int32_t dtype, int64_t rows, int64_t vocab,
                          int64_t row_stride, const K1SampleArgs& args, int32_t* dev_status,
                          cudaStream_t stream);

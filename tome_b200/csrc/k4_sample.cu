@@ -39,14 +39,19 @@ constexpr int K4_SAMPLE = 32768;   // leading logits used to derive the first th
 constexpr int K4_GROUPS = K4_THREADS / 4;  // sample maxima kept for the threshold
 constexpr int K4_RANK_MAX = 1024;  // above this many candidates, compact before ranking
 constexpr int K4_MAX_SWEEPS = 64;   // re-sweeps with a tightened threshold before giving up
-// From these row counts on a batch takes the streaming path: one row more than a full wave of
-// the row kernel's CTAs (two per SM for bf16, one for fp32).  Measured, V = 151936, row kernel /
-// streaming path: bf16 256 rows 32 / 35 us, 320 rows 58 / 42 us; fp32 128 rows 29 / 40 us, 160
-// rows 45 / 45 us, 200 rows 53 / 46 us.
+// From these row counts on a batch takes the streaming path.  fp32: one row more than the
+// clusters of two CTAs per row can hold on 148 SMs; with the rows in two parts the streaming
+// path then wins clearly (V = 151936, one CTA per row / streaming path, CUDA-graph replay: 160
+// rows 47.0 / 32.8 us, 200 rows 52.6 / 34.9, 256 rows 54.7 / 39.1; 128 rows, cluster kernel, 26.1 /
+// 30.2).  bf16: one row more than a full wave of the row kernel's CTAs (two per SM); below that
+// the streaming path gains little on the GPU (160 rows 31.0 / 27.8 us, 200 rows 31.0 / 28.5, 256
+// rows 31.0 / 31.0, 320 rows 56.3 / 38.6) and costs a caller outside a CUDA graph three more
+// stream operations per call than the one kernel it replaces (256 rows, eager calls: 46 us).
 constexpr int64_t K4_STREAM_MIN_ROWS_BF16 = 297;
-constexpr int64_t K4_STREAM_MIN_ROWS_F32 = 160;
+constexpr int64_t K4_STREAM_MIN_ROWS_F32 = 149;
 constexpr int64_t K4_STREAM_MIN_VOCAB = 4096;  // every consumer of the streaming kernel sees logits
-constexpr int K4_MAX_LISTS = 8;                // lists per row (one per consumer warp of the streaming kernel)
+constexpr int K4_MAX_PARTS = 4;                // parts a row of a small streamed batch is cut into
+constexpr int K4_MAX_LISTS = 16;              // lists per row (one per consumer warp and part, streaming kernel)
 constexpr int K4_CODE_CAP = 256;               // logits of a row that may reach its final threshold
 constexpr int K4_LIST_THREADS = 128;
 constexpr int K4_SPLIT_MAX = 8;               // CTAs of a cluster that may share one row
@@ -395,6 +400,9 @@ __global__ void __launch_bounds__(K4_THREADS) k4_sample_kernel(const K4Params p)
   const float temp = greedy ? 1.0f : p.temperature;  // temperature of the reported log-prob
   const float c = LOG2E / temp;
 
+  // after a streamed batch: the list of rows left over is complete once the kernels before
+  // this one have finished (launched on its own the wait returns at once)
+  griddep_wait();
   const int64_t n_items = p.only_flagged ? static_cast<int64_t>(*p.marked) : p.rows;
   for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
     const int64_t row = p.only_flagged ? static_cast<int64_t>(p.marked_rows[item]) : item;
@@ -485,14 +493,21 @@ __global__ void __launch_bounds__(K4_THREADS, 2) k4_sample_split_kernel(const K4
 // logits that kernel is bound by its instruction count and the same work costs more there than
 // in a kernel of its own (4096 rows: 256 us against 238 us), so bf16 batches run
 // k4_finish_kernel afterwards.  TOME_K4_FINISH=kernel|warp forces one or the other (tests).
+//
+// Batches with fewer rows than the streaming kernel has CTAs (4 per SM) would leave it one slow
+// CTA per row, so their rows are cut into 2 or 4 parts, each a work item of that kernel with a
+// threshold, a (max, sum-exp) pair and lists of its own; k4_finish_kernel puts a row's parts
+// together (largest threshold, merged pair, all lists).  TOME_K4_PARTS=1|2|4 forces a count.
 struct K4Lists {
-  int32_t lists;          // per row
+  int32_t lists;          // per part (one per consumer warp of the streaming kernel)
+  int32_t parts;          // per row
   int32_t cap;            // entries per list
   int32_t vec_stride;     // 16-byte vectors between the four vectors of an entry
-  const float* row_thr;
-  const float* lse;
-  const int32_t* count;   // [rows, lists]
-  const uint2* entry;     // [rows, lists, cap]
+  const float* row_thr;   // [rows, parts]
+  const float* lse;       // [rows] (parts == 1)
+  const float2* part_ms;  // [rows, parts] (parts > 1)
+  const int32_t* count;   // [rows, parts, lists]
+  const uint2* entry;     // [rows, parts, lists, cap]
 };
 
 // One warp per row (four rows per CTA at a time), nothing but warp-level synchronisation:
@@ -500,7 +515,7 @@ struct K4Lists {
 // their logits that reach the threshold become codes, the codes are ranked, the warp draws.
 constexpr int K4_VEC_CAP = 512;  // vectors a row's entries may name (beyond that: row kernel)
 
-template <typename T>
+template <typename T, int MAXL>
 __global__ void __launch_bounds__(K4_LIST_THREADS)
 k4_finish_kernel(const K4Params p, const K4Lists w) {
   constexpr int ROWS_PER_CTA = K4_LIST_THREADS / 32;
@@ -519,45 +534,79 @@ k4_finish_kernel(const K4Params p, const K4Lists w) {
   unsigned long long* list = codes[warp];
   unsigned long long* top = tops[warp];
   int32_t* vec = vecs[warp];
+  griddep_wait();               // the streaming kernel's lists are complete and visible
+  griddep_launch_dependents();  // the row kernel after this one may be set up meanwhile
   for (int64_t row = static_cast<int64_t>(blockIdx.x) * ROWS_PER_CTA + warp; row < p.rows;
        row += static_cast<int64_t>(gridDim.x) * ROWS_PER_CTA) {
     if (lane == 0) n_codes[warp] = 0;
-    const float thr = w.row_thr[row];
+    // ---- what the streaming kernel left for the row, asked for in one go: lane l reads the
+    //      counter of list l, and the threshold and the (max, sum-exp) pair of part l
+    const int32_t n_lists = w.lists * w.parts;
+    int32_t my_count = (lane < n_lists) ? w.count[row * n_lists + lane] : 0;
+    float thr = (lane < w.parts) ? w.row_thr[row * w.parts + lane] : __int_as_float(0xff800000);
+    float lse;
+    bool sick = false;  // a sum that is no number: the row kernel takes the row
+    if (w.parts == 1) {
+      lse = w.lse[row];
+    } else {
+      // rows in parts: the largest of the parts' thresholds (each a value that top_k logits of
+      // the row reach) and the merged pair
+      const float2 ms = (lane < w.parts) ? w.part_ms[row * w.parts + lane] : make_float2(-FLT_MAX, 0.0f);
+      float m = ms.x;
+#pragma unroll
+      for (int o = 1; o < K4_MAX_PARTS; o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      float s = (lane < w.parts) ? ms.y * ex2f((ms.x - m) * c) : 0.0f;
+#pragma unroll
+      for (int o = 1; o < K4_MAX_PARTS; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      sick = !(s >= 0.5f && s <= FLT_MAX);  // a healthy row's maximum contributes 2^0
+      lse = __fdiv_rn(m, temp) + logf(s);
+    }
+#pragma unroll
+    for (int o = 1; o < K4_MAX_PARTS; o <<= 1) thr = fmaxf(thr, __shfl_xor_sync(0xffffffffu, thr, o));
+    thr = __shfl_sync(0xffffffffu, thr, 0);
+    lse = __shfl_sync(0xffffffffu, lse, 0);
+    sick = __shfl_sync(0xffffffffu, sick ? 1 : 0, 0) != 0;
     const T* src = reinterpret_cast<const T*>(p.logits) + row * p.stride;
     // ---- the lists of the row, end to end: lane l knows where list l begins
-    int32_t my_count = (lane < w.lists) ? w.count[row * w.lists + lane] : 0;
     const bool overflow = __any_sync(0xffffffffu, my_count > w.cap);
     my_count = min(my_count, w.cap);
     int32_t begin = my_count;  // inclusive prefix sum over the lanes, then made exclusive
 #pragma unroll
-    for (int o = 1; o < K4_MAX_LISTS; o <<= 1) {
+    for (int o = 1; o < MAXL; o <<= 1) {
       const int32_t up = __shfl_up_sync(0xffffffffu, begin, o);
       if (lane >= o) begin += up;
     }
-    const int32_t total = __shfl_sync(0xffffffffu, begin, K4_MAX_LISTS - 1);
+    const int32_t total = __shfl_sync(0xffffffffu, begin, MAXL - 1);
     begin -= my_count;
     // ---- entries -> vector numbers.  Every logit that reaches the final threshold sits in a
     //      vector some entry names; an entry whose largest logit stays below it is dropped
     //      unread (a NaN there keeps it).  Two steps: the surviving entries are gathered (one
     //      ballot per 32 entries), then expanded (four ballots per 32 survivors).
     int32_t n_kept = 0;
-    for (int32_t g0 = 0; g0 < total; g0 += 32) {
-      const int32_t g = g0 + lane;
-      int32_t l = 0, at = g;
+    for (int32_t g0 = 0; g0 < total; g0 += 128) {  // four entries per lane and trip, asked for together
+      uint2 e[4];
 #pragma unroll
-      for (int q = 1; q < K4_MAX_LISTS; ++q) {  // the last list that begins at or before g
-        const int32_t b = __shfl_sync(0xffffffffu, begin, q);
-        if (q < w.lists && g >= b) {
-          l = q;
-          at = g - b;
+      for (int t = 0; t < 4; ++t) {
+        const int32_t g = g0 + t * 32 + lane;
+        int32_t l = 0, at = g;
+#pragma unroll
+        for (int q = 1; q < MAXL; ++q) {  // the last list that begins at or before g
+          const int32_t b = __shfl_sync(0xffffffffu, begin, q);
+          if (q < n_lists && g >= b) {
+            l = q;
+            at = g - b;
+          }
         }
+        e[t] = (g < total) ? w.entry[(row * n_lists + l) * w.cap + at] : make_uint2(0u, 0u);
       }
-      const uint2 e = (g < total) ? w.entry[(row * w.lists + l) * w.cap + at] : make_uint2(0u, 0u);
-      const bool keep = (g < total) && !(__uint_as_float(e.y) < thr);
-      const uint32_t bal = __ballot_sync(0xffffffffu, keep);
-      const int32_t to = n_kept + __popc(bal & lanes_below);
-      if (keep && to < K4_VEC_CAP) vec[to] = static_cast<int32_t>(e.x);
-      n_kept += __popc(bal);
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const bool keep = (g0 + t * 32 + lane < total) && !(__uint_as_float(e[t].y) < thr);
+        const uint32_t bal = __ballot_sync(0xffffffffu, keep);
+        const int32_t to = n_kept + __popc(bal & lanes_below);
+        if (keep && to < K4_VEC_CAP) vec[to] = static_cast<int32_t>(e[t].x);
+        n_kept += __popc(bal);
+      }
     }
     __syncwarp();
     // every surviving entry is taken into a register first; then the buffer is overwritten with
@@ -611,7 +660,8 @@ k4_finish_kernel(const K4Params p, const K4Lists w) {
     }
     __syncwarp();
     const int32_t n = n_codes[warp];
-    if (overflow || n_kept > K4_VEC_CAP / 4 || n_vec > K4_VEC_CAP || n > K4_CODE_CAP || n < kk) {
+    if (overflow || sick || n_kept > K4_VEC_CAP / 4 || n_vec > K4_VEC_CAP || n > K4_CODE_CAP ||
+        n < kk) {
       // lists that ran over (sorted or heavily tied rows) or a row with too few logits that
       // are not NaN: left to the row kernel
       if (lane == 0) p.marked_rows[atomicAdd(p.marked, 1)] = static_cast<int32_t>(row);
@@ -638,7 +688,7 @@ k4_finish_kernel(const K4Params p, const K4Lists w) {
     const int32_t pick = greedy ? 0 : k4_draw_warp(top, kk, c, row, p.seed, p.offset);
     if (lane == 0) {
       p.out_tokens[row] = k4_index(top[pick]);
-      p.out_logprob[row] = __fdiv_rn(k4_value(top[pick]), temp) - w.lse[row];
+      p.out_logprob[row] = __fdiv_rn(k4_value(top[pick]), temp) - lse;
     }
     if (p.out_topk_idx != nullptr || p.out_topk_val != nullptr) {
       for (int32_t j = lane; j < k; j += 32) {
@@ -652,32 +702,60 @@ k4_finish_kernel(const K4Params p, const K4Lists w) {
   }
 }
 
-// Scratch layout: per row the threshold, the logsumexp, a slot of the list of rows to redo and
-// the list counters; one counter for the batch; then the lists.
+// Scratch layout: per part of a row its (max, sum-exp) pair and its threshold, per row the
+// logsumexp and a slot of the list of rows to redo, then the list counters; one counter for the
+// batch; then the lists.
 struct K4Workspace {
-  float* thr;
-  float* lse;
+  float2* part_ms;   // [rows, parts]
+  float* thr;        // [rows, parts]
+  float* lse;        // [rows]
   int32_t* marked_rows;
-  int32_t* count;    // [rows, lists]
+  int32_t* count;    // [rows, parts, lists]
   int32_t* marked;   // one counter for the batch
-  uint2* entry;      // [rows, lists, cap]
+  uint2* entry;      // [rows, parts, lists, cap]
 };
-static size_t k4_workspace_head(int64_t rows, int lists) {
-  return (static_cast<size_t>(rows) * (12 + 4 * lists) + 4 + 15) & ~static_cast<size_t>(15);
+static size_t k4_workspace_head(int64_t rows, int lists, int parts) {
+  return (static_cast<size_t>(rows) * (8 + parts * (12 + 4 * lists)) + 4 + 15) &
+         ~static_cast<size_t>(15);
 }
-static size_t k4_workspace_bytes(int64_t rows, int lists, int cap) {
-  return k4_workspace_head(rows, lists) + static_cast<size_t>(rows) * lists * cap * sizeof(uint2);
+static size_t k4_workspace_bytes(int64_t rows, int lists, int cap, int parts) {
+  return k4_workspace_head(rows, lists, parts) +
+         static_cast<size_t>(rows) * parts * lists * cap * sizeof(uint2);
 }
-static K4Workspace k4_workspace(void* base, int64_t rows, int lists) {
+static K4Workspace k4_workspace(void* base, int64_t rows, int lists, int parts) {
   K4Workspace w;
   uint8_t* b = static_cast<uint8_t*>(base);
-  w.thr = reinterpret_cast<float*>(b);
-  w.lse = w.thr + rows;
+  w.part_ms = reinterpret_cast<float2*>(b);
+  w.thr = reinterpret_cast<float*>(w.part_ms + rows * parts);
+  w.lse = w.thr + rows * parts;
   w.marked_rows = reinterpret_cast<int32_t*>(w.lse + rows);
   w.count = w.marked_rows + rows;
-  w.marked = w.count + rows * lists;
-  w.entry = reinterpret_cast<uint2*>(b + k4_workspace_head(rows, lists));
+  w.marked = w.count + rows * parts * lists;
+  w.entry = reinterpret_cast<uint2*>(b + k4_workspace_head(rows, lists, parts));
   return w;
+}
+
+// Parts a row of a streamed batch is cut into: two while every half row is a work item of a CTA
+// of its own on a GPU of 148 SMs, four CTAs each (one CTA streams a row at 15 - 20 B/ns
+// whatever runs beside it, so more and smaller items finish sooner: 256 bf16 rows leave the
+// streaming kernel after 25 us whole, after 21 us in halves); not for a wide top-k, whose
+// parts together would bring more logits to the finish than it holds.  Quarters (the kernels
+// take them, TOME_K4_PARTS=4) shorten the streaming kernel further (128 bf16 rows: 20 -> 12 us)
+// but the finish reads twice the lists and the call gains nothing.
+constexpr int64_t K4_PART_SLOTS = 148 * 4;
+static int k4_stream_parts(int64_t rows, int64_t vocab, int32_t dtype, int32_t top_k) {
+  const int most = k1_sample_max_parts(vocab, dtype);
+  if (const char* e = getenv("TOME_K4_PARTS")) {
+    const int v = atoi(e);
+    return (v == 1 || v == 2 || v == 4) ? std::min(v, most) : 1;
+  }
+  if (most >= 2 && rows * 2 <= K4_PART_SLOTS && top_k <= 48) return 2;
+  return 1;
+}
+// The most parts any call with this many rows may use (scratch is sized for it).
+static int k4_stream_parts_most(int64_t rows, int64_t vocab) {
+  return std::max(k4_stream_parts(rows, vocab, TOME_F32, 1),
+                  k4_stream_parts(rows, vocab, TOME_BF16, 1));
 }
 
 // Whether a batch takes the streaming path (given scratch): large batches of rows that the
@@ -703,6 +781,29 @@ static int k4_split_factor(const void* kernel, int smem, int64_t rows, int64_t v
   for (int split = K4_SPLIT_MAX; split >= 2; split >>= 1)
     if (rows <= max_active_clusters(kernel, K4_THREADS, smem, split)) return split;
   return 0;
+}
+
+// Launches a kernel of the streamed path behind the one before it in the stream with the
+// programmatic-serialization attribute: its CTAs are set up while that kernel drains and wait
+// in griddep_wait, which takes the launch latency (2 - 3 us each) out of a small batch's time.
+// TOME_K4_PDL=0 launches them the ordinary way (read at every call; measurements).
+template <typename... Args>
+static int32_t k4_launch_after(const void* kernel, int grid, int block, int smem, cudaStream_t s,
+                               Args... args) {
+  void* argv[] = {static_cast<void*>(&args)...};
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(static_cast<unsigned>(block), 1, 1);
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+  cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  const char* e = getenv("TOME_K4_PDL");
+  const bool pdl = (e == nullptr) || atoi(e) != 0;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return check_cuda(cudaLaunchKernelExC(&cfg, kernel, argv), "k4 dependent launch");
 }
 
 }  // namespace tome
@@ -740,11 +841,13 @@ static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, i
                         k1_sample_eligible(logits, dtype, vocab, row_stride);
   const int lists = k1_sample_lists_per_row();
   const int list_cap = k1_sample_list_capacity();
+  const int parts = streamed ? k4_stream_parts(rows, vocab, dtype, top_k) : 1;
   if (streamed) {
-    if (lists > K4_MAX_LISTS) return fail(TOME_ERR_UNSUPPORTED, "%d lists per row", lists);
-    if (ws_bytes < k4_workspace_bytes(rows, lists, list_cap))
+    if (lists * parts > K4_MAX_LISTS)
+      return fail(TOME_ERR_UNSUPPORTED, "%d lists per row", lists * parts);
+    if (ws_bytes < k4_workspace_bytes(rows, lists, list_cap, parts))
       return fail(TOME_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes, %zu needed", ws_bytes,
-                  k4_workspace_bytes(rows, lists, list_cap));
+                  k4_workspace_bytes(rows, lists, list_cap, parts));
     if (!aligned16(workspace)) return fail(TOME_ERR_MISALIGNED, "workspace is not 16-byte aligned");
   }
   K4Params p = {};
@@ -763,15 +866,18 @@ static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, i
   p.out_topk_val = out_topk_val;
   p.status = dev_status;
   if (streamed) {
-    const K4Workspace w = k4_workspace(workspace, rows, lists);
+    const K4Workspace w = k4_workspace(workspace, rows, lists, parts);
     p.marked = w.marked;
     p.marked_rows = w.marked_rows;
     st = check_cuda(cudaMemsetAsync(w.marked, 0, sizeof(int32_t), s), "cudaMemsetAsync(marked rows)");
     if (st != TOME_OK) return st;
     bool in_kernel = (dtype == TOME_F32);
     if (const char* e = getenv("TOME_K4_FINISH")) in_kernel = (e[0] == 'w');  // "warp" / "kernel"
+    if (parts > 1) in_kernel = false;  // a row's parts meet in k4_finish_kernel
     K1SampleArgs a;
     a.finish_in_kernel = in_kernel;
+    a.parts = parts;
+    a.part_ms = w.part_ms;
     a.temperature = temperature;
     a.top_k = top_k;
     a.seed = seed;
@@ -791,6 +897,8 @@ static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, i
     if (!in_kernel) {
       K4Lists lw;
       lw.lists = lists;
+      lw.parts = parts;
+      lw.part_ms = w.part_ms;
       lw.cap = list_cap;
       lw.vec_stride = k1_sample_vector_stride();
       lw.row_thr = w.thr;
@@ -800,11 +908,14 @@ static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, i
       const int grid_rows = static_cast<int>(std::min<int64_t>(
           (rows + K4_LIST_THREADS / 32 - 1) / (K4_LIST_THREADS / 32),
           static_cast<int64_t>(info.sm_count) * 16));
-      if (dtype == TOME_F32)
-        k4_finish_kernel<float><<<grid_rows, K4_LIST_THREADS, 0, s>>>(p, lw);
+      void (*finish)(K4Params, K4Lists);
+      if (lists * parts <= 8)
+        finish = (dtype == TOME_F32) ? k4_finish_kernel<float, 8> : k4_finish_kernel<__nv_bfloat16, 8>;
       else
-        k4_finish_kernel<__nv_bfloat16><<<grid_rows, K4_LIST_THREADS, 0, s>>>(p, lw);
-      st = check_cuda(cudaGetLastError(), "k4 finish launch");
+        finish = (dtype == TOME_F32) ? k4_finish_kernel<float, K4_MAX_LISTS>
+                                     : k4_finish_kernel<__nv_bfloat16, K4_MAX_LISTS>;
+      st = k4_launch_after(reinterpret_cast<const void*>(finish), grid_rows, K4_LIST_THREADS, 0, s,
+                           p, lw);
       if (st != TOME_OK) return st;
     }
   }
@@ -839,6 +950,8 @@ static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, i
       (dtype == TOME_F32) ? k4_sample_kernel<float> : k4_sample_kernel<__nv_bfloat16>;
   st = ensure_dynamic_smem(reinterpret_cast<const void*>(row_kernel), smem);
   if (st != TOME_OK) return st;
+  if (streamed)
+    return k4_launch_after(reinterpret_cast<const void*>(row_kernel), grid, K4_THREADS, smem, s, p);
   row_kernel<<<grid, K4_THREADS, smem, s>>>(p);
   return check_cuda(cudaGetLastError(), "k4 launch");
 }
@@ -859,7 +972,8 @@ extern "C" size_t tome_sample_workspace_bytes(int64_t rows, int64_t vocab) {
   if (rows <= 0 || vocab <= 0 ||
       !(k4_wants_stream(rows, vocab, TOME_F32) || k4_wants_stream(rows, vocab, TOME_BF16)))
     return 0;
-  return k4_workspace_bytes(rows, k1_sample_lists_per_row(), k1_sample_list_capacity());
+  return k4_workspace_bytes(rows, k1_sample_lists_per_row(), k1_sample_list_capacity(),
+                            k4_stream_parts_most(rows, vocab));
 }
 
 extern "C" int32_t tome_sample_topk_logprob_ws(const void* logits, int32_t dtype, int64_t rows,

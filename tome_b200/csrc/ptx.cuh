@@ -306,6 +306,18 @@ __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization
+// attribute may be set up on the SMs while the kernel before it in the stream still runs (once
+// every CTA of that one has called griddep_launch_dependents or left); it must not touch what
+// that kernel writes before griddep_wait, which returns when the earlier kernel has completed
+// and its writes are visible.  Without the attribute both are no-ops.
+__device__ __forceinline__ void griddep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");

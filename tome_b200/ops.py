@@ -369,7 +369,7 @@ _sample_ws_bytes: dict = {}
 def sample_workspace_bytes(rows: int, vocab: int) -> int:
     """Scratch bytes :func:`sample_topk_logprob` uses for a batch of this shape (0 for the
     batches that need none)."""
-    key = (rows, vocab, os.environ.get("TOME_K4_STREAM"))
+    key = (rows, vocab, os.environ.get("TOME_K4_STREAM"), os.environ.get("TOME_K4_PARTS"))
     n = _sample_ws_bytes.get(key)
     if n is None:
         n = _sample_ws_bytes[key] = int(lib.tome_sample_workspace_bytes(rows, vocab))
