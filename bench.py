@@ -447,6 +447,22 @@ def run_extra(args, device, rank, world, dist_on, barrier, peaks):
                                     "GBps": nbytes / ms / 1e6,
                                     "frac_of_measured_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"],
                                     "l2": "flushed by a 256 MB write + 256 MB read before each launch"}
+    # the same launch repeated without the flush (the 622 MB of logits are five times L2, so a
+    # launch finds nothing of them there): launch latency overlaps the launch before
+    lp_out = torch.empty(1024, dtype=torch.float32, device=device)
+    for _ in range(warm):
+        tome_b200.local_compute_logprobs(x, ids, 1.0, out=lp_out)
+    ev_a, ev_b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev_a.record()
+    for _ in range(steps):
+        tome_b200.local_compute_logprobs(x, ids, 1.0, out=lp_out)
+    ev_b.record()
+    torch.cuda.synchronize()
+    ms_b2b = max_over_ranks(ev_a.elapsed_time(ev_b) / steps, dist_on, device)
+    extra["cfg1_selective_fp32"]["back_to_back"] = {
+        "ms": ms_b2b, "GBps": nbytes / ms_b2b / 1e6,
+        "frac_of_measured_hbm": nbytes / ms_b2b / 1e6 / peaks["hbm_gbs"],
+        "l2": "no flush: inputs (622 MB) are larger than L2"}
     sel = torch.arange(0, 1024, 16, device=device)
     verdict("cfg1_selective_fp32",
             {"max_abs_logprob": (box["lp"][sel] - torch_logprob(x[sel], ids[sel], 1.0)).abs().max()},
@@ -526,6 +542,25 @@ def run_extra(args, device, rank, world, dist_on, barrier, peaks):
         extra[name] = {"rows": rows_s, "ms": ms_s, "rows_per_s": rows_s / (ms_s * 1e-3),
                        "GBps": rows_s * VOCAB * 2 / launch_s / 1e6,
                        "frac_of_measured_hbm": rows_s * VOCAB * 2 / launch_s / 1e6 / peaks["hbm_gbs"]}
+        if rows_s <= 256 and not dist_on:
+            # the kernels' own time, replayed from a CUDA graph (the eager figure above carries
+            # the host's launch cost and two event records per call); logits of this size stay
+            # in L2 between replays, as they do behind the GEMM that wrote them in a decode loop
+            bound = tome_b200.bind_sample(xs, 0.7, 20, seed=7, out=s_out, workspace=s_ws)
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    bound(1)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(20):
+                        bound(i)
+            torch.cuda.synchronize()
+            ms_g, _ = timed(graph.replay, k=20, w=3)
+            extra[name]["graph_us"] = ms_g / 20 * 1e3
+            extra[name]["graph_GBps"] = rows_s * VOCAB * 2 / (ms_g / 20) / 1e6
+            del graph, bound
         tok, lp, tk_i, tk_v = tome_b200.sample_topk_logprob(xs, 0.7, 20, seed=7, offset=1,
                                                             return_topk=True)
         sel = torch.arange(0, rows_s, max(1, rows_s // 32), device=device)

@@ -911,8 +911,22 @@ __global__ void __launch_bounds__(K1_PLAIN_THREADS) k1_plain_kernel(const K1Para
       if (MODE == K1_FULL) {
         const float lse = finish_lse<MODE>(result.x, result.y, p);
         T* dst = reinterpret_cast<T*>(p.out_full) + row * p.out_stride;
-        for (int64_t j = threadIdx.x; j < p.vocab; j += K1_PLAIN_THREADS)
-          dst[j] = full_out_scalar(src[j], p.inv_temp, lse);
+        // second pass (the row was just read: it comes from L2).  Where the output row sits
+        // on the 16-byte grid like the input row, the aligned body is written with 128-bit
+        // stores and only the ends element by element.
+        if ((reinterpret_cast<uintptr_t>(dst + head) & 15) == 0) {
+          uint4* out = reinterpret_cast<uint4*>(dst + head);
+#pragma unroll 4
+          for (int64_t v = threadIdx.x; v < nvec; v += K1_PLAIN_THREADS)
+            out[v] = full_out_vec(__ldg(body + v), p.inv_temp, lse, T());
+          for (int64_t j = threadIdx.x; j < head; j += K1_PLAIN_THREADS)
+            dst[j] = full_out_scalar(src[j], p.inv_temp, lse);
+          for (int64_t j = tail_begin + threadIdx.x; j < p.vocab; j += K1_PLAIN_THREADS)
+            dst[j] = full_out_scalar(src[j], p.inv_temp, lse);
+        } else {
+          for (int64_t j = threadIdx.x; j < p.vocab; j += K1_PLAIN_THREADS)
+            dst[j] = full_out_scalar(src[j], p.inv_temp, lse);
+        }
         __syncthreads();
       }
     }

@@ -163,10 +163,11 @@ __device__ __forceinline__ void k4_rank_top(K4Smem& sm, int32_t n, int32_t kk) {
 // whose code is >= thr go to the candidate ring (if more than the capacity arrive, later ones
 // overwrite earlier ones and the count tells).  With SOFTMAX the per-thread online softmax of
 // ALL logits is updated too: the packed fast path (`fs`) for whole vectors, the exact scalar
-// form (`tail`) for the elements outside them.  No barrier inside.
+// form (`tail`) for the elements outside them.  The vectors start `head` elements into the
+// row, at its first 16-byte boundary.  No barrier inside.
 template <typename T, bool VEC, bool SOFTMAX>
-__device__ __forceinline__ void k4_sweep(const T* src, int64_t V, int64_t base, float c,
-                                         unsigned long long thr, K4Smem& sm, Fast& fs,
+__device__ __forceinline__ void k4_sweep(const T* src, int64_t V, int64_t base, int64_t head,
+                                         float c, unsigned long long thr, K4Smem& sm, Fast& fs,
                                          Online& tail) {
   // thr == 0 means "no threshold": every logit is a candidate
   const float thr_val = (thr == 0ull) ? __int_as_float(0xff800000) : k4_value(thr);
@@ -184,15 +185,15 @@ __device__ __forceinline__ void k4_sweep(const T* src, int64_t V, int64_t base, 
   };
   if (VEC) {
     constexpr int PER = 16 / static_cast<int>(sizeof(T));
-    const int64_t nvec = V / PER;
-    const uint4* vp = reinterpret_cast<const uint4*>(src);
+    const int64_t nvec = (V - head) / PER;
+    const uint4* vp = reinterpret_cast<const uint4*>(src + head);
 #pragma unroll 4
     for (int64_t v = threadIdx.x; v < nvec; v += K4_THREADS) {
       const uint4 q = __ldg(vp + v);
       const float vmax = SOFTMAX ? fast_update<0>(fs, q, c, T()) : vec_max(q, T());
       if (!(vmax < thr_val)) {  // a NaN maximum (bf16 vector holding a NaN): look inside
         const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-        const int64_t i0 = v * PER;
+        const int64_t i0 = head + v * PER;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           if (sizeof(T) == 4) {
@@ -204,7 +205,8 @@ __device__ __forceinline__ void k4_sweep(const T* src, int64_t V, int64_t base, 
         }
       }
     }
-    for (int64_t i = nvec * PER + threadIdx.x; i < V; i += K4_THREADS) scalar(i);
+    for (int64_t i = threadIdx.x; i < head; i += K4_THREADS) scalar(i);
+    for (int64_t i = head + nvec * PER + threadIdx.x; i < V; i += K4_THREADS) scalar(i);
   } else {
 #pragma unroll 4
     for (int64_t i = threadIdx.x; i < V; i += K4_THREADS) scalar(i);
@@ -255,14 +257,18 @@ __device__ void k4_segment(const T* src, const int64_t V, const int64_t base, co
   // ---- first threshold: the leading K4_SAMPLE logits are cut into 128 groups (4 adjacent
   //      threads each); the kk-th largest group maximum is a value that at least kk logits
   //      reach, so it bounds the answer from below.  Values only: ties are kept.
-  const bool vec = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0);
-  const int64_t n_sample = min(static_cast<int64_t>(K4_SAMPLE), V);
+  // 128-bit loads from the part's first 16-byte boundary on (`head` elements in; the part
+  // begins on an element boundary, so there is one unless the part is shorter than that)
+  const int64_t head = static_cast<int64_t>(((16u - (reinterpret_cast<uintptr_t>(src) & 15u)) & 15u) /
+                                            sizeof(T));
+  const bool vec = head < V;
+  const int64_t n_sample = min(static_cast<int64_t>(K4_SAMPLE), V - (vec ? head : 0));
   float lmax = __int_as_float(0xff800000);
   int64_t filled_threads;  // threads that saw at least one logit
   if (vec) {
     constexpr int PER = 16 / static_cast<int>(sizeof(T));
     const int64_t nvec_s = n_sample / PER;
-    const uint4* vp = reinterpret_cast<const uint4*>(src);
+    const uint4* vp = reinterpret_cast<const uint4*>(src + head);
 #pragma unroll 4
     for (int64_t v = tid; v < nvec_s; v += K4_THREADS) lmax = fmaxf(lmax, vec_max(__ldg(vp + v), T()));
     filled_threads = min(nvec_s, static_cast<int64_t>(K4_THREADS));
@@ -302,11 +308,11 @@ __device__ void k4_segment(const T* src, const int64_t V, const int64_t base, co
   int32_t n = 0;
   for (int sweep = 0; sweep < K4_MAX_SWEEPS; ++sweep) {
     if (sweep == 0) {
-      if (vec) k4_sweep<T, true, true>(src, V, base, c, thr, sm, fs, tail);
-      else k4_sweep<T, false, true>(src, V, base, c, thr, sm, fs, tail);
+      if (vec) k4_sweep<T, true, true>(src, V, base, head, c, thr, sm, fs, tail);
+      else k4_sweep<T, false, true>(src, V, base, 0, c, thr, sm, fs, tail);
     } else {
-      if (vec) k4_sweep<T, true, false>(src, V, base, c, thr, sm, fs, tail);
-      else k4_sweep<T, false, false>(src, V, base, c, thr, sm, fs, tail);
+      if (vec) k4_sweep<T, true, false>(src, V, base, head, c, thr, sm, fs, tail);
+      else k4_sweep<T, false, false>(src, V, base, 0, c, thr, sm, fs, tail);
     }
     __syncthreads();
     const int32_t total = sm.count;
