@@ -173,17 +173,61 @@ def test_selective_polynomial_exp_variants(cuda_device, poly):
     assert out.returncode == 0, out.stdout + out.stderr
 
 
+@pytest.mark.parametrize("bulk", ["1", "0"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_selective_unaligned_views_take_the_plain_kernel(cuda_device, dtype):
+def test_selective_rows_off_the_16_byte_grid(cuda_device, monkeypatch, dtype, bulk):
+    """Odd base offsets and row pitches that are no multiple of 16 bytes: the bulk-copy pipeline
+    copies every row from its first 16-byte boundary and reads the few elements before and
+    after with ordinary loads (TOME_K1_BULK=0: the plain-load kernel).  Targets at both ends."""
     import tome_b200
+    monkeypatch.setenv("TOME_K1_BULK", bulk)
     x, ids = _case(6, 1003, dtype, 8)
     xd = x.to(cuda_device)
-    # odd base offset and a row pitch that is not a multiple of 16 bytes
     view = xd[:, 1:1000]
     ids = ids.clamp(max=998)
+    ids[0], ids[1], ids[2], ids[3] = 0, 998, 5, 993
     lp = tome_b200.local_compute_logprobs(view, ids.to(cuda_device), 0.7)
     o_lp, _, _ = oracle.selective_logprob(x[:, 1:1000], ids, 0.7)
     assert max_abs(lp, o_lp) <= TOL[dtype]
+    # long contiguous rows of an odd length (every row starts at another place of the grid),
+    # more rows than CTAs, the largest logit of some rows outside the 16-byte boundaries
+    for rows, vocab in ((700, 50257), (37, 151937), (300, 17), (300, 5)):
+        x, ids = _case(rows, vocab, dtype, 80 + rows)
+        x[1, 0] = 30.0
+        x[2, vocab - 1] = 30.0
+        x[3, : min(vocab - 1, 9)] = float("-inf")
+        ids[1], ids[2] = 0, vocab - 1
+        _check_selective(x, ids, 0.7, cuda_device)
+
+
+def test_dual_and_ragged_rows_off_the_16_byte_grid(cuda_device):
+    """The windowed modes on a vocabulary of odd size (policy and reference rows start at
+    different places of the 16-byte grid when their bases differ)."""
+    import tome_b200
+    from tome_b200 import synthetic
+    pol, ref, ids, lengths, temp = synthetic.cfg5_dual(5, 12, 8209, "cpu", 31, min_len=0)
+    _check_dual(pol, ref, ids, lengths, temp, cuda_device)
+    # the reference logits one element further along the grid than the policy's
+    wide_p = torch.zeros((5, 12, 8210), dtype=pol.dtype)
+    wide_r = torch.zeros((5, 12, 8210), dtype=ref.dtype)
+    wide_p[..., :8209] = pol
+    wide_r[..., 1:] = ref
+    p, r, kl = tome_b200.grpo_dual_logprob_kl(wide_p.to(cuda_device)[..., :8209],
+                                              wide_r.to(cuda_device)[..., 1:], ids.to(cuda_device),
+                                              lengths.to(cuda_device), temp, check=True)
+    o_p, o_r, o_kl = oracle.dual_logprob_kl(pol, ref, ids, lengths, temp, None)
+    assert max_abs(p, o_p) <= 2e-3 and max_abs(r, o_r) <= 2e-3 and max_abs(kl, o_kl) <= 4e-3
+    g = torch.Generator().manual_seed(61)
+    n_seq, seq_len, vocab = 4, 10, 6001
+    logits = (torch.randn((n_seq, seq_len, vocab), generator=g) * 3).to(torch.bfloat16)
+    lengths = torch.tensor([10, 3, 0, 7], dtype=torch.int32)
+    targets = [torch.randint(0, vocab, (int(l),), generator=g, dtype=torch.int32) for l in lengths]
+    packed, offsets = tome_b200.ragged_logprobs(logits.to(cuda_device), torch.cat(targets).to(cuda_device),
+                                                lengths.to(cuda_device), 0.7, check=True)
+    want = oracle.ragged_logprobs(logits, targets, lengths, 0.7, None)
+    off = offsets.cpu().tolist()
+    for i in range(n_seq):
+        assert max_abs(packed[off[i]:off[i + 1]], want[i]) <= 2e-3
 
 
 def test_selective_strided_rows_and_leading_dims(cuda_device):

@@ -211,6 +211,43 @@ def test_rows_cut_into_parts_give_the_same_tokens(cuda_device, monkeypatch, dtyp
         assert i2[r, : len(idx)].cpu().tolist() == idx.tolist(), r
 
 
+@pytest.mark.parametrize("form", ["kernel", "warp", "parts2"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,vocab", [(600, 50257), (150, 151937), (40, 4099)])
+def test_streaming_path_with_rows_off_the_16_byte_grid(cuda_device, monkeypatch, dtype, rows, vocab, form):
+    """Contiguous rows of an odd length: every row starts at another place of the 16-byte
+    grid.  The streaming kernel copies a row from its first boundary to its last, notes vector
+    numbers counted from there, and the elements outside count as one more short vector, which
+    is where some rows here hold their winners.  Same tokens and top-k as the row kernel."""
+    import tome_b200
+    x = _case(rows, vocab, dtype, 500 + rows)
+    x[1, 0] = 40.0                                  # before the first boundary (rows 1, 2, ...)
+    x[2, vocab - 1] = 40.0                          # after the last one
+    x[3, :7] = 45.0
+    x[4] = torch.linspace(-8, 8, vocab).to(dtype)   # overflows the lists: row kernel
+    x[5, vocab // 2] = float("nan")
+    xd = x.to(cuda_device)
+    monkeypatch.setenv("TOME_K4_STREAM", "0")
+    t0, lp0, i0, v0 = tome_b200.sample_topk_logprob(xd, 0.7, 20, seed=6, offset=2, return_topk=True)
+    monkeypatch.setenv("TOME_K4_STREAM", "1")
+    if form == "parts2":
+        monkeypatch.setenv("TOME_K4_PARTS", "2")
+    else:
+        monkeypatch.setenv("TOME_K4_PARTS", "1")
+        monkeypatch.setenv("TOME_K4_FINISH", form)
+    t1, lp1, i1, v1 = tome_b200.sample_topk_logprob(xd, 0.7, 20, seed=6, offset=2, return_topk=True)
+    assert torch.equal(t0, t1) and torch.equal(i0, i1) and torch.equal(v0, v1)
+    ok = ~torch.isnan(lp0)
+    assert torch.equal(ok, ~torch.isnan(lp1)) and not bool(ok[5])
+    assert max_abs(lp0[ok], lp1[ok]) <= (1e-5 if dtype == torch.float32 else 1e-4)
+    for r in [0, 1, 2, 3, 6, rows - 1]:
+        idx, _ = oracle.topk_sampling_distribution(x[r], 0.7, 20)
+        assert i1[r, : len(idx)].cpu().tolist() == idx.tolist(), r
+    keep = [r for r in range(rows) if r != 5]
+    o_lp, _, _ = oracle.selective_logprob(x[keep], t1.cpu()[keep], 0.7)
+    assert max_abs(lp1.cpu()[keep], o_lp) <= TOL[dtype]
+
+
 def test_streaming_path_draws_follow_the_topk_softmax(cuda_device, monkeypatch):
     import tome_b200
     g = torch.Generator().manual_seed(10)

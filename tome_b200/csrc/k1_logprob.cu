@@ -20,11 +20,15 @@
 //
 //   SAMPLE     top-k sampling + log-prob of the drawn token for large batches (see below)
 //
-// Inputs that do not meet the bulk-copy alignment rules (base or row pitch not a multiple
-// of 16 bytes) take a plain-load kernel with the same arithmetic.  Small batches and long
-// fp32 rows of the FULL mode have kernels of their own (k1_small.cu, k1_full.cu).
+// Rows may start anywhere on the element grid (odd vocabulary sizes, views): a row is copied
+// from its first 16-byte boundary to its last and one thread reads the few elements outside
+// with ordinary loads (row_geom.cuh).  Only the FULL mode, whose 128-bit stores need the output
+// rows on the grid as well, sends rows off it to a plain-load kernel with the same arithmetic.
+// Small batches and long rows of the FULL mode have kernels of their own (k1_small.cu,
+// k1_full.cu).
 #include "k1_common.cuh"
 #include "k1_sample.h"
+#include "row_geom.cuh"
 #include "sampling.cuh"
 
 namespace tome {
@@ -231,13 +235,15 @@ struct K1Finisher {
       }
       // the vectors are asked for now and unpacked in the next step
       const T* src = reinterpret_cast<const T*>(p.src[0]) + row * p.stride;
+      const K1RowGeom geom = k1_row_geom(src, p.vocab);
+      const uint4* body = reinterpret_cast<const uint4*>(src + geom.head);
 #pragma unroll
       for (int t = 0; t < K1_FINISH_CAP / 32; ++t) {
         const int32_t i = t * 32 + lane;
         vec_at[t] = (i < n_vec) ? static_cast<int32_t>(kept[i]) : -1;
         vec[t] = make_uint4(0u, 0u, 0u, 0u);
-        if (vec_at[t] >= 0 && (static_cast<int64_t>(vec_at[t]) + 1) * PER <= p.vocab)
-          vec[t] = __ldg(reinterpret_cast<const uint4*>(src) + vec_at[t]);
+        if (vec_at[t] >= 0 && static_cast<int64_t>(vec_at[t]) * 16 < geom.bulk_bytes)
+          vec[t] = __ldg(body + vec_at[t]);
       }
       if (lane == 0) smp.n_codes = 0;
       __syncwarp();
@@ -246,12 +252,13 @@ struct K1Finisher {
     }
     if (phase == 2) {
       const T* src = reinterpret_cast<const T*>(p.src[0]) + row * p.stride;
+      const K1RowGeom geom = k1_row_geom(src, p.vocab);
       const int32_t kk = p.sample_kk;
 #pragma unroll
       for (int t = 0; t < K1_FINISH_CAP / 32; ++t) {
         if (vec_at[t] < 0) continue;
-        const int64_t e0 = static_cast<int64_t>(vec_at[t]) * PER;
-        if (e0 + PER <= p.vocab) {
+        const int64_t e0 = geom.head + static_cast<int64_t>(vec_at[t]) * PER;
+        if (static_cast<int64_t>(vec_at[t]) * 16 < geom.bulk_bytes) {
           const uint32_t u[4] = {vec[t].x, vec[t].y, vec[t].z, vec[t].w};
 #pragma unroll
           for (int q = 0; q < PER; ++q) {
@@ -263,8 +270,10 @@ struct K1Finisher {
               if (at < K1_FINISH_CAP) smp.codes[at] = k4_pack(x, e0 + q);
             }
           }
-        } else {  // the short vector at the end of a row whose length is not a multiple of 16 bytes
-          for (int64_t q = e0; q < p.vocab; ++q) {
+        } else {  // the short vector: the elements outside the row's 16-byte boundaries
+          const int64_t n_ends = geom.head + (p.vocab - geom.tail_begin);
+          for (int64_t i = 0; i < n_ends; ++i) {
+            const int64_t q = (i < geom.head) ? i : geom.tail_begin + (i - geom.head);
             const float x = to_float(src[q]);
             if (x >= thr) {
               const int32_t at = atomicAdd(&smp.n_codes, 1);
@@ -355,6 +364,12 @@ __device__ __forceinline__ bool k1_next_item(int64_t round, int64_t n_items, int
   return true;
 }
 
+// Size of the k-th bulk copy of a row: chunk_bytes, less for the last one, which is empty for a
+// row that starts off the grid and so holds one vector fewer than the launch planned for.
+__device__ __forceinline__ uint32_t k1_chunk_size(int64_t k, int64_t chunk_bytes, int64_t bulk_bytes) {
+  return static_cast<uint32_t>(max(int64_t{0}, min(chunk_bytes, bulk_bytes - k * chunk_bytes)));
+}
+
 // SAMPLE mode with rows cut into parts: neighbouring items are the parts of one row, each with an
 // equal share of the row's chunks.  Returns the row and sets the item's chunk range.
 __device__ __forceinline__ int64_t k1_sample_part(const K1Params& p, int64_t n_chunks, K1Item& w) {
@@ -425,11 +440,8 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
   // for its completion before they read anything
   if (MODE == K1_SAMPLE) griddep_launch_dependents();
 
-  const int64_t row_bytes = p.vocab * ES;
-  const int64_t bulk_bytes = row_bytes & ~static_cast<int64_t>(15);
   const int64_t n_chunks = p.n_chunks;
   const int64_t chunk_bytes = p.chunk_bytes;
-  const int64_t tail_begin = bulk_bytes / ES;  // first element not covered by bulk copies
 
   if (FINISH && warp == K1_CONSUMER_WARPS) {
     // ---------------- producer of the sampling mode: lane 0 issues the bulk copies, and while
@@ -442,7 +454,9 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
     bool ok = true;
     int64_t my_rows = 0;
     for (int64_t row = blockIdx.x; row < n_items && ok; row += gridDim.x, ++my_rows) {
-      const uint8_t* src = reinterpret_cast<const uint8_t*>(p.src[0]) + row * p.stride * ES;
+      const K1RowGeom geom = k1_row_geom(reinterpret_cast<const T*>(p.src[0]) + row * p.stride, p.vocab);
+      const uint8_t* src =
+          reinterpret_cast<const uint8_t*>(p.src[0]) + (row * p.stride + geom.head) * ES;
       for (int64_t k = 0; k < n_chunks && ok; ++k, ++it) {
         const uint32_t stage = it % STAGES;
         const uint32_t parity = ((it / STAGES) & 1u) ^ 1u;
@@ -462,10 +476,11 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
         }
         if (ok && lane == 0) {
           const int64_t off = k * chunk_bytes;
-          const uint32_t bytes = static_cast<uint32_t>(min(chunk_bytes, bulk_bytes - off));
+          const uint32_t bytes = k1_chunk_size(k, chunk_bytes, geom.bulk_bytes);
           mbar_arrive_expect_tx(full_bar + stage * 8, bytes);
-          bulk_g2s_hint(smem_base + stage * K1_CHUNK_BYTES, src + off, bytes, full_bar + stage * 8,
-                        policy);
+          if (bytes != 0)
+            bulk_g2s_hint(smem_base + stage * K1_CHUNK_BYTES, src + off, bytes,
+                          full_bar + stage * 8, policy);
         }
       }
     }
@@ -498,8 +513,10 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
                             : (MODE == K1_SAMPLE) ? k1_sample_part(p, n_chunks, w)
                                                   : w.item;
         for (int sub = 0; sub < NSUB && ok; ++sub) {
-          const uint8_t* src = reinterpret_cast<const uint8_t*>(
-                                   p.src[(MODE == K1_DUAL) ? sub : 0]) + row * p.stride * ES;
+          const T* row_src =
+              reinterpret_cast<const T*>(p.src[(MODE == K1_DUAL) ? sub : 0]) + row * p.stride;
+          const K1RowGeom geom = k1_row_geom(row_src, p.vocab);
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(row_src + geom.head);
           for (int64_t k = w.k_begin; k < w.k_end; ++k, ++it) {
             const uint32_t stage = it % STAGES;
             const uint32_t phase = (it / STAGES) & 1u;
@@ -509,8 +526,9 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
               break;
             }
             const int64_t off = k * chunk_bytes;
-            const uint32_t bytes = static_cast<uint32_t>(min(chunk_bytes, bulk_bytes - off));
+            const uint32_t bytes = k1_chunk_size(k, chunk_bytes, geom.bulk_bytes);
             mbar_arrive_expect_tx(full_bar + stage * 8, bytes);
+            if (bytes == 0) continue;  // (a row off the 16-byte grid may lack the last copy)
             // FULL re-reads the row in its second pass: keep it in L2 after the first.
             if (K1_CFG_FULL_KEEP && MODE == K1_FULL && sub == 0)
               bulk_g2s_hint(smem_base + stage * K1_CHUNK_BYTES, src + off, bytes,
@@ -556,6 +574,7 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
     for (int sub = 0; sub < NSUB; ++sub) {
       const T* src = reinterpret_cast<const T*>(p.src[(MODE == K1_DUAL) ? sub : 0]) +
                      row * p.stride;
+      const K1RowGeom geom = k1_row_geom(src, p.vocab);
       const bool reduce_pass = (MODE != K1_FULL) || (sub == 0);
 
       // the one thread that finishes the row fetches the target logit early
@@ -658,7 +677,7 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
           dead = true;
         }
         const int64_t off = k * chunk_bytes;
-        const uint32_t bytes = static_cast<uint32_t>(min(chunk_bytes, bulk_bytes - off));
+        const uint32_t bytes = k1_chunk_size(k, chunk_bytes, geom.bulk_bytes);
         const uint32_t nvec = dead ? 0u : (bytes >> 4);
         const uint32_t sbase = smem_base + stage * K1_CHUNK_BYTES;
         if (MODE == K1_SAMPLE && k == w.k_begin) {
@@ -706,7 +725,7 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
               note(hit ? 1u : 0u, (off >> 4) + v, ma);
           }
         } else {
-          uint8_t* drow = reinterpret_cast<uint8_t*>(dst) + off;
+          uint8_t* drow = reinterpret_cast<uint8_t*>(dst + geom.head) + off;
           for (uint32_t v = ctid; v < nvec; v += K1_CONSUMERS) {
             const uint4 a = lds128(sbase + v * 16);
             stg128_streaming(drow + static_cast<size_t>(v) * 16,
@@ -726,18 +745,24 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
 
       Online st = fast_finish(fs, p.c);
       if (dead) st.s = __int_as_float(0x7fc00000);  // the row takes the exact path below
-      // elements past the last 16-byte boundary of the row (at most PER_VEC - 1)
+      // elements before the first and past the last 16-byte boundary of the row (at most
+      // PER_VEC - 1 each)
       if (ctid == 0 && w.k_end == n_chunks) {
-        for (int64_t j = tail_begin; j < p.vocab; ++j) {
+        auto end_element = [&](int64_t j) {
           if (reduce_pass) online_update_scalar(st, to_float(src[j]), p.c);
           else dst[j] = full_out_scalar(src[j], p.inv_temp, lse_row);
-        }
+        };
+        for (int64_t j = 0; j < geom.head; ++j) end_element(j);
+        for (int64_t j = geom.tail_begin; j < p.vocab; ++j) end_element(j);
       }
-      if (MODE == K1_SAMPLE && warp == 0 && tail_begin < p.vocab && w.k_end == n_chunks) {
-        // the elements past the last 16-byte boundary count as one more (short) vector
-        float tail_max = __int_as_float(0xff800000);
-        for (int64_t j = tail_begin; j < p.vocab; ++j) tail_max = fmax_nan(tail_max, to_float(src[j]));
-        note((lane == 0 && !(tail_max < thr_val)) ? 1u : 0u, tail_begin / PER_VEC, tail_max);
+      if (MODE == K1_SAMPLE && warp == 0 && w.k_end == n_chunks &&
+          (geom.head > 0 || geom.tail_begin < p.vocab)) {
+        // those elements count as one more (short) vector, numbered after the whole ones
+        float ends_max = __int_as_float(0xff800000);
+        for (int64_t j = 0; j < geom.head; ++j) ends_max = fmax_nan(ends_max, to_float(src[j]));
+        for (int64_t j = geom.tail_begin; j < p.vocab; ++j)
+          ends_max = fmax_nan(ends_max, to_float(src[j]));
+        note((lane == 0 && !(ends_max < thr_val)) ? 1u : 0u, geom.bulk_bytes >> 4, ends_max);
       }
 
       if (reduce_pass) {
@@ -1105,9 +1130,18 @@ static int32_t k1_check_common(const void* logits, int32_t dtype, int64_t rows, 
   return TOME_OK;
 }
 
+// Rows whose every start sits on the 16-byte grid (FULL mode: input and output rows alike,
+// for its 128-bit stores).
 static bool bulk_eligible(const void* base, int64_t stride, int32_t dtype) {
   const int64_t es = (dtype == TOME_F32) ? 4 : 2;
   return aligned16(base) && ((stride * es) % 16 == 0);
+}
+// The reading modes take the bulk-copy pipeline for any element-aligned rows (each row is copied
+// from its first 16-byte boundary, see row_geom.cuh).  TOME_K1_BULK=0 sends them to the
+// plain-load kernel instead (read at every call; tests).
+static bool bulk_wanted() {
+  const char* e = getenv("TOME_K1_BULK");
+  return e == nullptr || atoi(e) != 0;
 }
 
 }  // namespace tome
@@ -1138,7 +1172,7 @@ extern "C" int32_t tome_selective_logprob(const void* logits, int32_t dtype, int
   p.out1 = out_lse;
   p.out2 = out_target_raw;
   p.status = dev_status;
-  return k1_launch<K1_SELECTIVE>(p, dtype, bulk_eligible(logits, row_stride, dtype), rows,
+  return k1_launch<K1_SELECTIVE>(p, dtype, bulk_wanted(), rows,
                                  static_cast<cudaStream_t>(stream));
 }
 
@@ -1216,8 +1250,7 @@ extern "C" int32_t tome_dual_logprob_kl(const void* policy_logits, const void* r
   p.n_seq = static_cast<int32_t>(n_seq);
   p.seq_len = static_cast<int32_t>(seq_len);
   p.status = dev_status;
-  const bool bulk = bulk_eligible(policy_logits, row_stride, dtype) &&
-                    bulk_eligible(ref_logits, row_stride, dtype);
+  const bool bulk = bulk_wanted();
   return k1_launch<K1_DUAL>(p, dtype, bulk, rows, static_cast<cudaStream_t>(stream));
 }
 
@@ -1263,7 +1296,7 @@ extern "C" int32_t tome_ragged_logprob(const void* logits, int32_t dtype, int64_
   p.out_offsets = out_offsets;
   p.packed_capacity = packed_capacity;
   p.status = dev_status;
-  return k1_launch<K1_RAGGED>(p, dtype, bulk_eligible(logits, row_stride, dtype), rows,
+  return k1_launch<K1_RAGGED>(p, dtype, bulk_wanted(), rows,
                               static_cast<cudaStream_t>(stream));
 }
 
@@ -1271,9 +1304,11 @@ namespace tome {
 
 bool k1_sample_eligible(const void* logits, int32_t dtype, int64_t vocab, int64_t row_stride) {
   const int64_t es = (dtype == TOME_F32) ? 4 : 2;
-  // a row holds at least one 16-byte vector and few enough for the entries' 28 index bits
-  return bulk_eligible(logits, row_stride, dtype) && vocab * es >= 16 &&
-         vocab * es / 16 < (int64_t{1} << 27);
+  // (any element-aligned rows) a row holds 16-byte vectors, few enough for the entries' 28
+  // index bits
+  (void)logits;
+  (void)row_stride;
+  return vocab * es >= 32 && vocab * es / 16 < (int64_t{1} << 27);
 }
 
 int32_t k1_launch_sample(const void* logits, int32_t dtype, int64_t rows, int64_t vocab,

@@ -9,8 +9,9 @@
 
 namespace tome {
 
-// Base and row pitch are multiples of 16 bytes, a row holds at least one 16-byte vector and
-// fewer than 2^27 of them.
+// A row holds at least two 16-byte vectors and fewer than 2^27 of them (rows may start anywhere
+// on the element grid: vector numbers count from a row's first 16-byte boundary, and the
+// elements outside its boundaries count as one more, short, vector).
 bool k1_sample_eligible(const void* logits, int32_t dtype, int64_t vocab, int64_t row_stride);
 
 // Lists the kernel keeps per row (one per consumer warp), entries a list holds, and the
@@ -46,7 +47,7 @@ struct K1SampleArgs {
 // entries {(v << 4) | mask, largest}: bit j of the mask says that the 16-byte vector number
 // v + j * k1_sample_vector_stride() of the row holds a logit >= the threshold in force when it
 // passed (never above row_thr, so every logit >= row_thr sits in a vector some entry names; the
-// elements past the row's last 16-byte boundary count as one more, short, vector), and
+// elements outside the row's first and last 16-byte boundary count as one more, short, vector), and
 // `largest` is the float bits of the largest logit of the entry's four vectors (NaN if one of
 // them holds a NaN); cand_count (list capacity + 1 if a list ran over).
 // With finish_in_kernel the kernel also writes token and log-prob (and the optional top-k

@@ -28,6 +28,7 @@
 #include "k1_sample.h"
 #include "online.cuh"
 #include "ptx.cuh"
+#include "row_geom.cuh"
 #include "sampling.cuh"
 
 namespace tome {
@@ -573,6 +574,7 @@ k4_finish_kernel(const K4Params p, const K4Lists w) {
     lse = __shfl_sync(0xffffffffu, lse, 0);
     sick = __shfl_sync(0xffffffffu, sick ? 1 : 0, 0) != 0;
     const T* src = reinterpret_cast<const T*>(p.logits) + row * p.stride;
+    const K1RowGeom geom = k1_row_geom(src, p.vocab);  // vector numbers count from the row's first 16-byte boundary
     // ---- the lists of the row, end to end: lane l knows where list l begins
     const bool overflow = __any_sync(0xffffffffu, my_count > w.cap);
     my_count = min(my_count, w.cap);
@@ -640,8 +642,8 @@ k4_finish_kernel(const K4Params p, const K4Lists w) {
     __syncwarp();
     // ---- vectors -> codes of the logits that reach the threshold
     for (int32_t i = lane; i < min(n_vec, K4_VEC_CAP); i += 32) {
-      const int64_t e0 = static_cast<int64_t>(vec[i]) * PER;
-      if (e0 + PER <= p.vocab) {
+      const int64_t e0 = geom.head + static_cast<int64_t>(vec[i]) * PER;
+      if (static_cast<int64_t>(vec[i]) * 16 < geom.bulk_bytes) {
         const uint4 q = __ldg(reinterpret_cast<const uint4*>(src + e0));
         const uint32_t u[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
@@ -654,8 +656,10 @@ k4_finish_kernel(const K4Params p, const K4Lists w) {
             if (at < K4_CODE_CAP) list[at] = k4_pack(x, e0 + t);
           }
         }
-      } else {  // the short vector at the end of a row whose length is not a multiple of 16 bytes
-        for (int64_t t = e0; t < p.vocab; ++t) {
+      } else {  // the short vector: the elements outside the row's 16-byte boundaries
+        const int64_t n_ends = geom.head + (p.vocab - geom.tail_begin);
+        for (int64_t j = 0; j < n_ends; ++j) {
+          const int64_t t = (j < geom.head) ? j : geom.tail_begin + (j - geom.head);
           const float x = k4_load(src, t);
           if (x >= thr) {
             const int32_t at = atomicAdd(&n_codes[warp], 1);
