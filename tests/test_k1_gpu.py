@@ -592,11 +592,14 @@ def test_full_every_cluster_size(cuda_device, monkeypatch, split, dtype):
 @pytest.mark.parametrize("small_batch_path", ["small_batches_split"], indirect=True)  # env set below
 @pytest.mark.parametrize("form", ["1", "s1", "s2", "s4", "s8"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("vocab", [8, 24, 7000, 51200, 51200 + 8, 102400, 151936, 151936 + 4, 300000])
+@pytest.mark.parametrize("vocab", [8, 24, 25, 7000, 7001, 50257, 51200, 51200 + 8, 102400, 151936,
+                                   151936 + 4, 151937, 300000])
 def test_full_cluster_kernel_sizes(cuda_device, monkeypatch, small_batch_path, form, dtype, vocab):
     """The cluster kernel with every cluster size (1, 2, 4, 8 CTAs per row) on row lengths from
     less than one chunk per CTA (some CTAs of a cluster get nothing) to many chunks per CTA;
-    more rows than clusters so that ring slots, pair slots and lse entries are reused."""
+    more rows than clusters so that ring slots, pair slots and lse entries are reused.  Odd row
+    lengths put every row at another place of the 16-byte grid (input and output rows alike):
+    the copies then run from a row's first boundary to its last."""
     import tome_b200
     monkeypatch.setenv("TOME_K1_SPLIT", "0")
     monkeypatch.setenv("TOME_K1_FULL_CLUSTER", form)

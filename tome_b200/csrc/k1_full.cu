@@ -1,5 +1,6 @@
 // K1, full-matrix mode for rows of more than ~100 KB: a cluster of CTAs shares each row.
 #include "k1_common.cuh"
+#include "row_geom.cuh"
 
 namespace tome {
 
@@ -92,15 +93,21 @@ k1_full_cluster_kernel(const K1Params p, const int cluster, const int chunks_per
   if (cluster > 1) cluster_sync_all();  // nobody arrives on a barrier that is not there yet
 
   // this CTA's part of a row: chunks [rank * chunks_per_cta, (rank + 1) * chunks_per_cta) of
-  // chunk_bytes each (the last chunks of a row may be short or empty)
-  const int64_t bulk_bytes = (p.vocab * ES) & ~static_cast<int64_t>(15);
+  // chunk_bytes each, counted from the row's first 16-byte boundary (the last chunks of a row
+  // may be short or empty; a row that starts off the grid holds one vector fewer than the
+  // aligned row the chunks are planned for)
+  const int64_t bulk_most = (p.vocab * ES) & ~static_cast<int64_t>(15);
   const int64_t chunk_bytes = p.chunk_bytes;
   const int64_t part_begin = static_cast<int64_t>(rank) * chunks_per_cta * chunk_bytes;
   int my_chunks = 0;
   for (int k = 0; k < chunks_per_cta; ++k)
-    if (part_begin + k * chunk_bytes < bulk_bytes) ++my_chunks;
-  const int64_t tail_begin = bulk_bytes / ES;  // elements past the last 16-byte boundary
-  const bool owns_tail = (rank == static_cast<uint32_t>(cluster) - 1);
+    if (part_begin + k * chunk_bytes < bulk_most) ++my_chunks;
+  // the elements outside a row's 16-byte boundaries go with the last part
+  const bool owns_ends = (rank == static_cast<uint32_t>(cluster) - 1);
+  auto chunk_size = [&](int64_t bulk_bytes, int k) {
+    return static_cast<uint32_t>(
+        max(int64_t{0}, min(chunk_bytes, bulk_bytes - part_begin - k * chunk_bytes)));
+  };
 
   if (warp == KF_CONSUMER_WARPS) {
     // ---------------- producer
@@ -109,8 +116,9 @@ k1_full_cluster_kernel(const K1Params p, const int cluster, const int chunks_per
       uint32_t it = 0;
       bool ok = true;
       for (int64_t row = first_row; row < p.n_rows && ok; row += n_clusters) {
-        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.src[0]) + row * p.stride * ES +
-                             part_begin;
+        const T* row_src = reinterpret_cast<const T*>(p.src[0]) + row * p.stride;
+        const K1RowGeom geom = k1_row_geom(row_src, p.vocab);
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(row_src + geom.head) + part_begin;
         // every chunk is fetched once per pass, the second time (served by L2) marked as the
         // last use
         for (int pass = 0; pass < 2 && ok; ++pass) {
@@ -123,9 +131,9 @@ k1_full_cluster_kernel(const K1Params p, const int cluster, const int chunks_per
               break;
             }
             const int64_t off = k * chunk_bytes;
-            const uint32_t bytes =
-                static_cast<uint32_t>(min(chunk_bytes, bulk_bytes - part_begin - off));
+            const uint32_t bytes = chunk_size(geom.bulk_bytes, k);
             mbar_arrive_expect_tx(full_bar + slot * 8, bytes);
+            if (bytes == 0) continue;
             if (pass == 1)
               bulk_g2s_hint(smem_base + slot * KF_CHUNK_BYTES, src + off, bytes,
                             full_bar + slot * 8, policy);
@@ -147,6 +155,7 @@ k1_full_cluster_kernel(const K1Params p, const int cluster, const int chunks_per
   for (int64_t row = first_row; row < p.n_rows; row += n_clusters, ++row_it) {
     const T* src = reinterpret_cast<const T*>(p.src[0]) + row * p.stride;
     T* dst = reinterpret_cast<T*>(p.out_full) + row * p.out_stride;
+    const K1RowGeom geom = k1_row_geom(src, p.vocab);  // the output row sits on the grid alike
     const uint32_t par = row_it & 1u;
     // ---- pass 1: (m, s) of this CTA's part, chunks stay where they are
     Fast fs;
@@ -159,8 +168,7 @@ k1_full_cluster_kernel(const K1Params p, const int cluster, const int chunks_per
         dead = true;
       }
       if (dead) break;
-      const uint32_t bytes = static_cast<uint32_t>(
-          min(chunk_bytes, bulk_bytes - part_begin - k * chunk_bytes));
+      const uint32_t bytes = chunk_size(geom.bulk_bytes, k);
       const uint32_t nvec = bytes >> 4;
       const uint32_t sbase = smem_base + slot * KF_CHUNK_BYTES;
 #pragma unroll 4
@@ -171,8 +179,11 @@ k1_full_cluster_kernel(const K1Params p, const int cluster, const int chunks_per
     }
     it += static_cast<uint32_t>(my_chunks);  // the second pass has chunks of its own
     Online st = fast_finish(fs, p.c);
-    if (owns_tail && ctid == 0)
-      for (int64_t j = tail_begin; j < p.vocab; ++j) online_update_scalar(st, to_float(src[j]), p.c);
+    if (owns_ends && ctid == 0) {
+      for (int64_t j = 0; j < geom.head; ++j) online_update_scalar(st, to_float(src[j]), p.c);
+      for (int64_t j = geom.tail_begin; j < p.vocab; ++j)
+        online_update_scalar(st, to_float(src[j]), p.c);
+    }
     online_warp_reduce(st, p.c);
     if (lane == 0) part[par * KF_CONSUMER_WARPS + warp] = make_float2(st.m, st.s);
     named_bar_sync(1, KF_CONSUMERS);
@@ -220,10 +231,10 @@ k1_full_cluster_kernel(const K1Params p, const int cluster, const int chunks_per
         dead = true;
       }
       const int64_t off = part_begin + k * chunk_bytes;
-      const uint32_t bytes = static_cast<uint32_t>(min(chunk_bytes, bulk_bytes - off));
+      const uint32_t bytes = chunk_size(geom.bulk_bytes, k);
       const uint32_t nvec = dead ? 0u : (bytes >> 4);
       const uint32_t sbase = smem_base + slot * KF_CHUNK_BYTES;
-      uint8_t* drow = reinterpret_cast<uint8_t*>(dst) + off;
+      uint8_t* drow = reinterpret_cast<uint8_t*>(dst + geom.head) + off;
 #pragma unroll 4
       for (uint32_t v = ctid; v < nvec; v += KF_CONSUMERS)
         stg128_streaming(drow + static_cast<size_t>(v) * 16,
@@ -231,9 +242,11 @@ k1_full_cluster_kernel(const K1Params p, const int cluster, const int chunks_per
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar + slot * 8);
     }
-    if (owns_tail && ctid == 0)
-      for (int64_t j = tail_begin; j < p.vocab; ++j)
+    if (owns_ends && ctid == 0) {
+      for (int64_t j = 0; j < geom.head; ++j) dst[j] = full_out_scalar(src[j], p.inv_temp, lse);
+      for (int64_t j = geom.tail_begin; j < p.vocab; ++j)
         dst[j] = full_out_scalar(src[j], p.inv_temp, lse);
+    }
   }
   }
   // no CTA leaves while a peer may still store into its shared memory or arrive on its barriers

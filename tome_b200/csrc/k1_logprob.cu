@@ -22,8 +22,9 @@
 //
 // Rows may start anywhere on the element grid (odd vocabulary sizes, views): a row is copied
 // from its first 16-byte boundary to its last and one thread reads the few elements outside
-// with ordinary loads (row_geom.cuh).  Only the FULL mode, whose 128-bit stores need the output
-// rows on the grid as well, sends rows off it to a plain-load kernel with the same arithmetic.
+// with ordinary loads (row_geom.cuh).  The FULL mode's 128-bit stores need every output row to
+// sit on the grid like its input row; where they do not, a plain-load kernel with the same
+// arithmetic takes the call.
 // Small batches and long rows of the FULL mode have kernels of their own (k1_small.cu,
 // k1_full.cu).
 #include "k1_common.cuh"
@@ -1130,12 +1131,6 @@ static int32_t k1_check_common(const void* logits, int32_t dtype, int64_t rows, 
   return TOME_OK;
 }
 
-// Rows whose every start sits on the 16-byte grid (FULL mode: input and output rows alike,
-// for its 128-bit stores).
-static bool bulk_eligible(const void* base, int64_t stride, int32_t dtype) {
-  const int64_t es = (dtype == TOME_F32) ? 4 : 2;
-  return aligned16(base) && ((stride * es) % 16 == 0);
-}
 // The reading modes take the bulk-copy pipeline for any element-aligned rows (each row is copied
 // from its first 16-byte boundary, see row_geom.cuh).  TOME_K1_BULK=0 sends them to the
 // plain-load kernel instead (read at every call; tests).
@@ -1202,9 +1197,13 @@ extern "C" int32_t tome_log_softmax_full(const void* logits, int32_t dtype, int6
   p.out_full = out;
   p.out_stride = out_row_stride;
   p.status = dev_status;
-  const bool bulk = bulk_eligible(logits, row_stride, dtype) &&
-                    bulk_eligible(out, out_row_stride, dtype);
-  return k1_launch<K1_FULL>(p, dtype, bulk, rows, static_cast<cudaStream_t>(stream));
+  // the 128-bit stores of the bulk-copy kernels need every output row to sit on the 16-byte
+  // grid like its input row (e.g. two contiguous tensors of any row length)
+  const int64_t esz = static_cast<int64_t>(es);
+  const bool alike = ((reinterpret_cast<uintptr_t>(out) - reinterpret_cast<uintptr_t>(logits)) % 16 == 0) &&
+                     (((out_row_stride - row_stride) * esz) % 16 == 0);
+  return k1_launch<K1_FULL>(p, dtype, alike && bulk_wanted(), rows,
+                            static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int32_t tome_dual_logprob_kl(const void* policy_logits, const void* ref_logits,
