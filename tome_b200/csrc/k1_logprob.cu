@@ -367,7 +367,8 @@ __device__ __forceinline__ bool k1_next_item(int64_t round, int64_t n_items, int
 
 // Size of the k-th bulk copy of a row: chunk_bytes, less for the last one, which is empty for a
 // row that starts off the grid and so holds one vector fewer than the launch planned for.
-__device__ __forceinline__ uint32_t k1_chunk_size(int64_t k, int64_t chunk_bytes, int64_t bulk_bytes) {
+__device__ __forceinline__ uint32_t k1_chunk_size(int64_t k, int64_t chunk_bytes,
+                                                  int64_t bulk_bytes) {
   return static_cast<uint32_t>(max(int64_t{0}, min(chunk_bytes, bulk_bytes - k * chunk_bytes)));
 }
 
@@ -455,9 +456,9 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
     bool ok = true;
     int64_t my_rows = 0;
     for (int64_t row = blockIdx.x; row < n_items && ok; row += gridDim.x, ++my_rows) {
-      const K1RowGeom geom = k1_row_geom(reinterpret_cast<const T*>(p.src[0]) + row * p.stride, p.vocab);
-      const uint8_t* src =
-          reinterpret_cast<const uint8_t*>(p.src[0]) + (row * p.stride + geom.head) * ES;
+      const T* row_src = reinterpret_cast<const T*>(p.src[0]) + row * p.stride;
+      const K1RowGeom geom = k1_row_geom(row_src, p.vocab);
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(row_src + geom.head);
       for (int64_t k = 0; k < n_chunks && ok; ++k, ++it) {
         const uint32_t stage = it % STAGES;
         const uint32_t parity = ((it / STAGES) & 1u) ^ 1u;
@@ -1199,9 +1200,9 @@ extern "C" int32_t tome_log_softmax_full(const void* logits, int32_t dtype, int6
   p.status = dev_status;
   // the 128-bit stores of the bulk-copy kernels need every output row to sit on the 16-byte
   // grid like its input row (e.g. two contiguous tensors of any row length)
-  const int64_t esz = static_cast<int64_t>(es);
-  const bool alike = ((reinterpret_cast<uintptr_t>(out) - reinterpret_cast<uintptr_t>(logits)) % 16 == 0) &&
-                     (((out_row_stride - row_stride) * esz) % 16 == 0);
+  const uintptr_t apart = reinterpret_cast<uintptr_t>(out) - reinterpret_cast<uintptr_t>(logits);
+  const bool alike =
+      (apart % 16 == 0) && (((out_row_stride - row_stride) * static_cast<int64_t>(es)) % 16 == 0);
   return k1_launch<K1_FULL>(p, dtype, alike && bulk_wanted(), rows,
                             static_cast<cudaStream_t>(stream));
 }
@@ -1323,7 +1324,8 @@ int32_t k1_launch_sample(const void* logits, int32_t dtype, int64_t rows, int64_
   p.temp = temp;
   p.inv_temp = 1.0f / temp;
   p.finish_in_kernel = a.finish_in_kernel ? 1 : 0;
-  if ((a.parts != 1 && a.parts != 2 && a.parts != 4) || a.parts > k1_sample_max_parts(vocab, dtype) ||
+  if ((a.parts != 1 && a.parts != 2 && a.parts != 4) ||
+      a.parts > k1_sample_max_parts(vocab, dtype) ||
       (a.parts > 1 && (a.finish_in_kernel || a.part_ms == nullptr)))
     return fail(TOME_ERR_UNSUPPORTED, "sampling pass: %d parts per row", a.parts);
   p.sample_parts_log2 = (a.parts == 4) ? 2 : (a.parts == 2) ? 1 : 0;
