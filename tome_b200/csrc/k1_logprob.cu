@@ -671,15 +671,19 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
         thr_val = (t != t) ? __int_as_float(0xff800000) : t;  // -inf with its low bits cleared
       };
 
-      for (int64_t k = w.k_begin; k < w.k_end; ++k, ++it) {
+      // (running values instead of products per chunk: this loop's overhead is paid 12 - 24 times
+      // per row)
+      int64_t off = w.k_begin * chunk_bytes;        // of the chunk within the row's bulk range
+      int64_t left = geom.bulk_bytes - off;         // bytes of that range from this chunk on
+      int32_t kr = 0;                               // chunks of this item done
+      for (int64_t k = w.k_begin; k < w.k_end; ++k, ++it, off += chunk_bytes, left -= chunk_bytes) {
         const uint32_t stage = it % STAGES;
         const uint32_t phase = (it / STAGES) & 1u;
         if (!dead && !mbar_wait(full_bar + stage * 8, phase)) {
           raise_status(p.status, TOME_DEV_TIMEOUT);
           dead = true;
         }
-        const int64_t off = k * chunk_bytes;
-        const uint32_t bytes = k1_chunk_size(k, chunk_bytes, geom.bulk_bytes);
+        const uint32_t bytes = static_cast<uint32_t>(max(int64_t{0}, min(chunk_bytes, left)));
         const uint32_t nvec = dead ? 0u : (bytes >> 4);
         const uint32_t sbase = smem_base + stage * K1_CHUNK_BYTES;
         if (MODE == K1_SAMPLE && k == w.k_begin) {
@@ -739,9 +743,9 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
         // the sample has grown fourfold: raise the threshold.  Once more after the row's last
         // chunk: nothing is noted any more, but the kernel that follows has a third of the
         // logits to rank.
-        const int64_t kr = k - w.k_begin;  // chunks of this item so far, less one
+        ++kr;
         if (MODE == K1_SAMPLE &&
-            ((kr >= 3 && ((kr + 1) & kr) == 0 && ((kr + 1) & 0x55555555) != 0) || k + 1 == w.k_end))
+            ((kr >= 4 && (kr & (kr - 1)) == 0 && (kr & 0x55555555) != 0) || k + 1 == w.k_end))
           refine();
       }
 
