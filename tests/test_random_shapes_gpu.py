@@ -1,0 +1,122 @@
+"""Seeded random shapes: row counts, vocabulary sizes (odd ones included), element offsets of the
+first row and row pitches drawn at random, every mode against the oracle.  The fixed cases of
+the other files pin the known edges; this one looks for the ones nobody thought of."""
+import random
+
+import pytest
+import torch
+
+from helpers import TOL, max_abs
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _draw(rng, max_rows, max_vocab):
+    rows = rng.choice([1, 2, 3, rng.randint(4, 64), rng.randint(65, max_rows)])
+    vocab = rng.choice([rng.randint(1, 40), rng.randint(41, 5000), rng.randint(5001, max_vocab)])
+    offset = rng.choice([0, 0, rng.randint(1, 9)])
+    pitch = vocab + offset + rng.choice([0, 0, rng.randint(1, 17)])
+    dtype = rng.choice([torch.float32, torch.bfloat16])
+    temp = rng.choice([1.0, 0.7, 1.3])
+    return rows, vocab, offset, pitch, dtype, temp
+
+
+def _view(rows, vocab, offset, pitch, dtype, seed, dev):
+    g = torch.Generator().manual_seed(seed)
+    wide = (torch.randn((rows, pitch), generator=g) * 3.0).to(dtype)
+    return wide[:, offset:offset + vocab], wide.to(dev)[:, offset:offset + vocab]
+
+
+@pytest.mark.parametrize("seed", range(120))
+def test_selective_random_shapes(cuda_device, seed):
+    import tome_b200
+    rng = random.Random(1000 + seed)
+    rows, vocab, offset, pitch, dtype, temp = _draw(rng, 900, 70000)
+    x, xd = _view(rows, vocab, offset, pitch, dtype, seed, cuda_device)
+    ids = torch.randint(0, vocab, (rows,), generator=torch.Generator().manual_seed(seed), dtype=torch.int32)
+    lp, lse, raw = tome_b200.selective_log_softmax(xd, ids.to(cuda_device), temp, return_lse=True,
+                                                   return_target_logit=True, check=True)
+    o_lp, o_lse, o_raw = oracle.selective_logprob(x, ids, temp)
+    assert max_abs(lp, o_lp) <= TOL[dtype], (rows, vocab, offset, pitch, dtype)
+    assert max_abs(lse, o_lse) <= TOL[dtype]
+    assert torch.equal(raw.cpu(), o_raw)
+
+
+@pytest.mark.parametrize("seed", range(80))
+def test_full_matrix_random_shapes(cuda_device, seed):
+    import tome_b200
+    rng = random.Random(2000 + seed)
+    rows, vocab, offset, pitch, dtype, temp = _draw(rng, 500, 60000)
+    x, xd = _view(rows, vocab, offset, pitch, dtype, seed, cuda_device)
+    out = tome_b200.fused_log_softmax(xd, temp)
+    ref = oracle.log_softmax_metal_order(x.contiguous(), temp)
+    tol = 1e-4 if dtype == torch.float32 else 0.0625 + 1e-6   # one bf16 ulp near -12
+    assert out.shape == ref.shape and out.dtype == dtype
+    assert max_abs(out.float(), ref.float()) <= tol, (rows, vocab, offset, pitch, dtype)
+    # a contiguous input of the same values: output and input rows now sit alike on the 16-byte
+    # grid, which sends rows of an odd length through the bulk-copy kernels
+    out2 = tome_b200.fused_log_softmax(xd.contiguous(), temp)
+    assert torch.equal(out2, out) or max_abs(out2.float(), ref.float()) <= tol
+
+
+@pytest.mark.parametrize("seed", range(100))
+def test_sampling_random_shapes(cuda_device, monkeypatch, seed):
+    import tome_b200
+    rng = random.Random(3000 + seed)
+    rows, vocab, offset, pitch, dtype, temp = _draw(rng, 700, 60000)
+    k = rng.choice([1, 5, 20, 33, 64])
+    form = rng.choice(["default", "rows", "stream", "stream_warp", "stream_parts"])
+    if form == "rows":
+        monkeypatch.setenv("TOME_K4_STREAM", "0")
+    elif form != "default":
+        monkeypatch.setenv("TOME_K4_STREAM", "1")
+        if form == "stream_warp":
+            monkeypatch.setenv("TOME_K4_FINISH", "warp")
+        if form == "stream_parts":
+            monkeypatch.setenv("TOME_K4_PARTS", rng.choice(["2", "4"]))
+    x, xd = _view(rows, vocab, offset, pitch, dtype, seed, cuda_device)
+    tok, lp, tk_i, tk_v = tome_b200.sample_topk_logprob(xd, temp, k, seed=seed, offset=3,
+                                                        return_topk=True, check=True)
+    kk = min(k, vocab)
+    for r in sorted({0, rows // 2, rows - 1}):
+        idx, _ = oracle.topk_sampling_distribution(x[r], temp, k)
+        assert tk_i[r, :kk].cpu().tolist() == idx.tolist(), (r, rows, vocab, offset, pitch, dtype, form)
+        assert int(tok[r]) in idx.tolist()
+    o_lp, _, _ = oracle.selective_logprob(x, tok.cpu(), temp)
+    assert max_abs(lp, o_lp) <= TOL[dtype], (rows, vocab, offset, pitch, dtype, form)
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_dual_and_ragged_random_shapes(cuda_device, seed):
+    """Policy / reference scoring with the k3 KL estimate over ragged windows, and the packed
+    single-model form, on random sequence counts, lengths, windows and vocabulary sizes."""
+    import tome_b200
+    rng = random.Random(4000 + seed)
+    n_seq = rng.choice([1, 2, rng.randint(3, 12)])
+    seq_len = rng.choice([1, 2, rng.randint(3, 24)])
+    vocab = rng.choice([rng.randint(1, 40), rng.randint(41, 5000), rng.randint(5001, 30000)])
+    dtype = rng.choice([torch.float32, torch.bfloat16])
+    temp = rng.choice([1.0, 0.7])
+    g = torch.Generator().manual_seed(seed)
+    pol = (torch.randn((n_seq, seq_len, vocab), generator=g) * 3.0).to(dtype)
+    ref = (pol.float() + torch.randn((n_seq, seq_len, vocab), generator=g) * 0.3).to(dtype)
+    ids = torch.randint(0, vocab, (n_seq, seq_len), generator=g, dtype=torch.int32)
+    starts = torch.tensor([rng.randint(0, seq_len) for _ in range(n_seq)], dtype=torch.int32)
+    lengths = torch.tensor([rng.randint(0, seq_len + 2) for _ in range(n_seq)], dtype=torch.int32)
+    dev = cuda_device
+    p, r, kl = tome_b200.grpo_dual_logprob_kl(pol.to(dev), ref.to(dev), ids.to(dev), lengths.to(dev),
+                                              temp, starts=starts.to(dev), check=True)
+    o_p, o_r, o_kl = oracle.dual_logprob_kl(pol, ref, ids, lengths, temp, starts)
+    tol = TOL[dtype]
+    assert max_abs(p, o_p) <= tol and max_abs(r, o_r) <= tol and max_abs(kl, o_kl) <= 2 * tol
+    clamped = [max(0, min(int(l), seq_len - int(s))) for s, l in zip(starts, lengths)]
+    targets = [torch.randint(0, vocab, (c,), generator=g, dtype=torch.int32) for c in clamped]
+    packed, offsets = tome_b200.ragged_logprobs(pol.to(dev), torch.cat(targets).to(dev), lengths.to(dev),
+                                                temp, starts=starts.to(dev), check=True)
+    want = oracle.ragged_logprobs(pol, targets, lengths, temp, starts)
+    off = offsets.cpu().tolist()
+    assert off == [0] + torch.tensor(clamped).cumsum(0).tolist()
+    for i in range(n_seq):
+        if clamped[i]:
+            assert max_abs(packed[off[i]:off[i + 1]], want[i]) <= tol
