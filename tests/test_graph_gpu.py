@@ -51,7 +51,8 @@ def test_selective_sampling_and_head_replay_from_a_cuda_graph(cuda_device):
 
 
 def test_large_batch_sampling_and_full_matrix_replay_from_a_cuda_graph(cuda_device):
-    """The three-kernel sampling path (scratch allocated by the wrapper inside the capture) and
+    """The streaming sampling path (scratch allocated by the wrapper inside the capture; its
+    kernels are chained by programmatic launches) and
     the cluster full-matrix kernel, captured and replayed on new inputs."""
     import tome_b200
     g = torch.Generator().manual_seed(72)
