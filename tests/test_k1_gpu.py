@@ -433,8 +433,39 @@ def test_dual_windows_with_starts_and_poisoned_padding(cuda_device):
     assert not torch.isnan(p).any() and not torch.isnan(kl).any()
 
 
+def test_dual_and_ragged_beyond_the_sequence_limit_of_one_call(cuda_device):
+    """More sequences than one library call takes (1024): the wrappers go in slices, the packed
+    form writing each slice behind the one before."""
+    import tome_b200
+    g = torch.Generator().manual_seed(24)
+    n_seq, seq_len, vocab = 2500, 3, 300
+    pol = (torch.randn((n_seq, seq_len, vocab), generator=g) * 2).to(torch.bfloat16)
+    ref = (pol.float() + torch.randn((n_seq, seq_len, vocab), generator=g) * 0.2).to(torch.bfloat16)
+    ids = torch.randint(0, vocab, (n_seq, seq_len), generator=g, dtype=torch.int32)
+    lengths = torch.randint(0, seq_len + 2, (n_seq,), generator=g, dtype=torch.int32)
+    starts = torch.randint(0, seq_len + 1, (n_seq,), generator=g, dtype=torch.int32)
+    dev = cuda_device
+    p, r, kl = tome_b200.grpo_dual_logprob_kl(pol.to(dev), ref.to(dev), ids.to(dev), lengths.to(dev),
+                                              0.7, starts=starts.to(dev), check=True)
+    o_p, o_r, o_kl = oracle.dual_logprob_kl(pol, ref, ids, lengths, 0.7, starts)
+    assert max_abs(p, o_p) <= 2e-3 and max_abs(r, o_r) <= 2e-3 and max_abs(kl, o_kl) <= 4e-3
+    clamped = [max(0, min(int(l), seq_len - int(s))) for s, l in zip(starts, lengths)]
+    targets = [torch.randint(0, vocab, (c,), generator=g, dtype=torch.int32) for c in clamped]
+    packed, offsets, lse = tome_b200.ragged_logprobs(pol.to(dev), torch.cat(targets).to(dev),
+                                                     lengths.to(dev), 0.7, starts=starts.to(dev),
+                                                     return_lse=True, check=True)
+    assert offsets.cpu().tolist() == [0] + torch.tensor(clamped).cumsum(0).tolist()
+    want = oracle.ragged_logprobs(pol, targets, lengths, 0.7, starts)
+    got = packed.cpu()
+    off = offsets.cpu().tolist()
+    for i in list(range(0, n_seq, 97)) + [1023, 1024, 1025, 2047, 2048, n_seq - 1]:
+        if clamped[i]:
+            assert max_abs(got[off[i]:off[i + 1]], want[i]) <= 2e-3, i
+    assert not torch.isnan(lse).any()
+
+
 def test_dual_at_the_sequence_limit(cuda_device):
-    """1024 sequences per call is the limit (the prefix sums live in shared memory)."""
+    """1024 sequences per library call is the limit (the prefix sums live in shared memory)."""
     import tome_b200
     g = torch.Generator().manual_seed(23)
     n_seq, seq_len, vocab = 1024, 3, 520
@@ -443,10 +474,12 @@ def test_dual_at_the_sequence_limit(cuda_device):
     ids = torch.randint(0, vocab, (n_seq, seq_len), generator=g, dtype=torch.int32)
     lengths = torch.randint(0, seq_len + 1, (n_seq,), generator=g, dtype=torch.int32)
     _check_dual(pol, ref, ids, lengths, 0.7, cuda_device)
-    big = torch.zeros((1025, 1, 16), dtype=torch.bfloat16, device=cuda_device)
-    with pytest.raises(tome_b200.TomeArgumentError):
-        tome_b200.grpo_dual_logprob_kl(big, big, torch.zeros((1025, 1), dtype=torch.int32),
-                                       torch.ones(1025, dtype=torch.int32), 1.0)
+    # one sequence more is refused by the library before any pointer is used (the Python
+    # wrappers slice such batches, see the test above)
+    from tome_b200 import _lib
+    fake = 0x1000
+    assert _lib.lib.tome_dual_logprob_kl(fake, fake, _lib.TOME_BF16, 1025, 1, 16, 16, fake, fake, None,
+                                         1.0, fake, fake, fake, None, None) == -9
 
 
 def test_dual_fp32_and_cfg5_shape(cuda_device):

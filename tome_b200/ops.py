@@ -22,6 +22,8 @@ from . import _lib
 from ._lib import TOME_BF16, TOME_F32, TomeRuntimeError, check, lib
 
 _DTYPES = {torch.float32: TOME_F32, torch.bfloat16: TOME_BF16}
+# sequences tome_dual_logprob_kl / tome_ragged_logprob take per call (the wrappers slice larger batches)
+MAX_SEQ_PER_CALL = 1024
 _status_words: dict = {}
 
 
@@ -292,7 +294,8 @@ def grpo_dual_logprob_kl(policy_logits: torch.Tensor, ref_logits: torch.Tensor,
     ``[start, start + length)`` of each sequence, the completion slice of
     mlx-impl/node.py:446-451.  Returns ``(lp_policy, lp_ref, kl)``, fp32 ``[n_seq, seq_len]``,
     zero outside the windows, with ``kl = exp(r - p) - (r - p) - 1``.  Rows outside the
-    windows are never read.
+    windows are never read.  Any number of sequences (the library takes 1024 per call; larger
+    batches go in slices).
     """
     _require_cuda("policy_logits", policy_logits)
     _require_cuda("ref_logits", ref_logits)
@@ -309,13 +312,18 @@ def grpo_dual_logprob_kl(policy_logits: torch.Tensor, ref_logits: torch.Tensor,
     len32 = _ids32(lengths, n_seq, device)
     st32 = None if starts is None else _ids32(starts, n_seq, device)
     outs = [torch.empty((n_seq, seq_len), dtype=torch.float32, device=device) for _ in range(3)]
+    ids2 = ids32.view(n_seq, seq_len)
     with _on(device):
-        status = lib.tome_dual_logprob_kl(
-            pol.data_ptr(), ref.data_ptr(), _dtype_code(pol), n_seq, seq_len, V, V,
-            ids32.data_ptr(), len32.data_ptr(), _ptr(st32), temp, outs[0].data_ptr(),
-            outs[1].data_ptr(), outs[2].data_ptr(), _status_word(device).data_ptr(),
-            _stream(device))
-    _lib.check(status)
+        # the library takes MAX_SEQ_PER_CALL sequences per call: larger batches go in slices
+        for i0 in range(0, max(n_seq, 1), MAX_SEQ_PER_CALL):
+            n = min(MAX_SEQ_PER_CALL, n_seq - i0)
+            status = lib.tome_dual_logprob_kl(
+                pol[i0:].data_ptr(), ref[i0:].data_ptr(), _dtype_code(pol), n, seq_len, V, V,
+                ids2[i0:].data_ptr(), len32[i0:].data_ptr(),
+                None if st32 is None else st32[i0:].data_ptr(), temp, outs[0][i0:].data_ptr(),
+                outs[1][i0:].data_ptr(), outs[2][i0:].data_ptr(), _status_word(device).data_ptr(),
+                _stream(device))
+            _lib.check(status)
     if check:
         check_device_status(device)
     return tuple(outs)
@@ -333,7 +341,9 @@ def ragged_logprobs(logits: torch.Tensor, targets_packed: torch.Tensor, lengths:
     ``Completion.ref_log_probs`` on the wire (scheduler/proto/inference.proto:108-112).
     ``logits`` is ``[n_seq, seq_len, V]``.  Returns ``(packed, offsets)`` (plus the packed
     logsumexp with ``return_lse``); ``packed[offsets[i]:offsets[i+1]]`` belongs to sequence
-    ``i``.  Rows outside the windows are never read.
+    ``i``.  Rows outside the windows are never read.  Any number of sequences; beyond the 1024
+    the library takes per call the batch goes in slices, which costs one synchronising read of
+    the slices' starting offsets.
     """
     _require_cuda("logits", logits)
     if logits.dim() != 3:
@@ -349,12 +359,35 @@ def ragged_logprobs(logits: torch.Tensor, targets_packed: torch.Tensor, lengths:
     out = torch.empty(total, dtype=torch.float32, device=device)
     lse = torch.empty(total, dtype=torch.float32, device=device) if return_lse else None
     offsets = torch.empty(n_seq + 1, dtype=torch.int32, device=device)
-    with _on(device):
-        status = lib.tome_ragged_logprob(
-            lg.data_ptr(), _dtype_code(lg), n_seq, seq_len, V, V, tg.data_ptr(), total, len32.data_ptr(),
-            _ptr(st32), temp, out.data_ptr(), _ptr(lse), offsets.data_ptr(),
-            _status_word(device).data_ptr(), _stream(device))
-    _lib.check(status)
+    if n_seq <= MAX_SEQ_PER_CALL:
+        with _on(device):
+            status = lib.tome_ragged_logprob(
+                lg.data_ptr(), _dtype_code(lg), n_seq, seq_len, V, V, tg.data_ptr(), total,
+                len32.data_ptr(), _ptr(st32), temp, out.data_ptr(), _ptr(lse), offsets.data_ptr(),
+                _status_word(device).data_ptr(), _stream(device))
+        _lib.check(status)
+    else:
+        # more sequences than one call takes: slices of MAX_SEQ_PER_CALL, each writing behind
+        # the one before.  Where a slice begins in the packed arrays is needed on the host
+        # (one synchronising read of a few integers); the windows are clamped as the kernel
+        # clamps them.
+        begin = torch.zeros_like(len32) if st32 is None else st32.clamp(0, seq_len)
+        window = torch.minimum(len32.clamp(min=0), seq_len - begin)
+        firsts = list(range(0, n_seq, MAX_SEQ_PER_CALL))
+        ends = torch.cumsum(window, 0, dtype=torch.int64)
+        bases = [0] + ends[[f - 1 for f in firsts[1:]]].tolist()
+        with _on(device):
+            for i0, base in zip(firsts, bases):
+                n = min(MAX_SEQ_PER_CALL, n_seq - i0)
+                base = min(int(base), total)
+                status = lib.tome_ragged_logprob(
+                    lg[i0:].data_ptr(), _dtype_code(lg), n, seq_len, V, V,
+                    tg.data_ptr() + 4 * base, total - base, len32[i0:].data_ptr(),
+                    None if st32 is None else st32[i0:].data_ptr(), temp,
+                    out.data_ptr() + 4 * base, None if lse is None else lse.data_ptr() + 4 * base,
+                    offsets[i0:].data_ptr(), _status_word(device).data_ptr(), _stream(device))
+                _lib.check(status)
+                offsets[i0:i0 + n + 1] += base
     if check:
         check_device_status(device)  # raises if the windows needed more than `total` entries
         if int(offsets[-1].item()) != total:
