@@ -188,11 +188,14 @@ __device__ __forceinline__ void k4_sweep(const T* src, int64_t V, int64_t base, 
     constexpr int PER = 16 / static_cast<int>(sizeof(T));
     const int64_t nvec = (V - head) / PER;
     const uint4* vp = reinterpret_cast<const uint4*>(src + head);
-#pragma unroll 4
-    for (int64_t v = threadIdx.x; v < nvec; v += K4_THREADS) {
-      const uint4 q = __ldg(vp + v);
-      const float vmax = SOFTMAX ? fast_update<0>(fs, q, c, T()) : vec_max(q, T());
+    auto reduce = [&](const uint4& q) {  // folds a vector into the sums, returns its largest logit
+      return SOFTMAX ? fast_update<0>(fs, q, c, T()) : vec_max(q, T());
+    };
+    // (the vector is fetched again for the look, from L1: holding four of them across the
+    // updates would not fit the 64 registers two CTAs per SM leave a thread)
+    auto look = [&](float vmax, int64_t v) {
       if (!(vmax < thr_val)) {  // a NaN maximum (bf16 vector holding a NaN): look inside
+        const uint4 q = __ldg(vp + v);
         const uint32_t w[4] = {q.x, q.y, q.z, q.w};
         const int64_t i0 = head + v * PER;
 #pragma unroll
@@ -205,6 +208,31 @@ __device__ __forceinline__ void k4_sweep(const T* src, int64_t V, int64_t base, 
           }
         }
       }
+    };
+    // Four vectors per step: the loads are asked for together, the four updates of the sums run
+    // as one straight piece of code, and one test tells whether any of the vectors needs a
+    // look.  (Left to `#pragma unroll` the loop kept program order, load - update - candidates
+    // - load, because the candidate branch stores to shared memory: four memory round trips per
+    // step instead of one, and no update overlapping another.)
+    int64_t v = threadIdx.x;
+    for (; v + 3 * K4_THREADS < nvec; v += 4 * K4_THREADS) {
+      const uint4 q0 = __ldg(vp + v);
+      const uint4 q1 = __ldg(vp + v + K4_THREADS);
+      const uint4 q2 = __ldg(vp + v + 2 * K4_THREADS);
+      const uint4 q3 = __ldg(vp + v + 3 * K4_THREADS);
+      const float m0 = reduce(q0);
+      const float m1 = reduce(q1);
+      const float m2 = reduce(q2);
+      const float m3 = reduce(q3);
+      if (!(fmax3_nan(fmax_nan(m0, m1), m2, m3) < thr_val)) {
+        look(m0, v);
+        look(m1, v + K4_THREADS);
+        look(m2, v + 2 * K4_THREADS);
+        look(m3, v + 3 * K4_THREADS);
+      }
+    }
+    for (; v < nvec; v += K4_THREADS) {
+      look(reduce(__ldg(vp + v)), v);
     }
     for (int64_t i = threadIdx.x; i < head; i += K4_THREADS) scalar(i);
     for (int64_t i = head + nvec * PER + threadIdx.x; i < V; i += K4_THREADS) scalar(i);
@@ -400,7 +428,7 @@ __device__ void k4_finish_row(const K4Params& p, K4Smem& sm, int64_t row, int32_
 }
 
 template <typename T>
-__global__ void __launch_bounds__(K4_THREADS) k4_sample_kernel(const K4Params p) {
+__global__ void __launch_bounds__(K4_THREADS, 2) k4_sample_kernel(const K4Params p) {
   extern __shared__ __align__(16) uint8_t k4_smem_raw[];
   K4Smem& sm = *reinterpret_cast<K4Smem*>(k4_smem_raw);
   const bool greedy = !(p.temperature > 0.0f);
