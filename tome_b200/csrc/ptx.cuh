@@ -306,22 +306,6 @@ __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 
-// Asynchronous 16-byte copies global -> shared (one per thread, completion by groups): the data
-// never passes through registers, so a thread can keep several loads in flight at no register
-// cost.  Both addresses 16-byte aligned.
-__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gmem_src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() {
-  asm volatile("cp.async.commit_group;" ::: "memory");
-}
-// Returns when at most N of this thread's committed groups are still pending.
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
 // Programmatic dependent launch.  A kernel launched with the programmatic-serialization
 // attribute may be set up on the SMs while the kernel before it in the stream still runs (once
 // every CTA of that one has called griddep_launch_dependents or left); it must not touch what
