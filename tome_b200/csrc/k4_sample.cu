@@ -136,27 +136,30 @@ __device__ unsigned long long k4_compact(K4Smem& sm, int32_t n, int32_t k) {
 }
 
 // Exact top-kk of cand[0..n), best first, into top[] (n <= K4_RANK_MAX, codes distinct): each
-// thread ranks its (at most two) candidates in one pipelined pass over the list.
+// thread ranks its (at most two) candidates in one pipelined pass over the list.  Warps none of
+// whose threads holds a candidate skip the pass (a few hundred candidates are the rule, so
+// half the warps do), and the second candidate is only looked at by the warps that have one.
 __device__ __forceinline__ void k4_rank_top(K4Smem& sm, int32_t n, int32_t kk) {
   const int tid = threadIdx.x;
-  constexpr int MINE = K4_RANK_MAX / K4_THREADS;
-  unsigned long long code[MINE];
-  int32_t rank[MINE];
-#pragma unroll
-  for (int q = 0; q < MINE; ++q) {
-    const int32_t i = tid + q * K4_THREADS;
-    code[q] = (i < n) ? sm.cand[i] : ~0ull;  // ~0 outranks everything: never placed
-    rank[q] = 0;
-  }
+  const int warp_first = tid & ~31;  // index of the candidate of this warp's first lane
+  if (warp_first >= n) return;
+  const unsigned long long mine0 = (tid < n) ? sm.cand[tid] : ~0ull;  // ~0 outranks everything: never placed
+  int32_t rank0 = 0;
+  if (warp_first + K4_THREADS < n) {
+    const unsigned long long mine1 = (tid + K4_THREADS < n) ? sm.cand[tid + K4_THREADS] : ~0ull;
+    int32_t rank1 = 0;
 #pragma unroll 4
-  for (int32_t j = 0; j < n; ++j) {
-    const unsigned long long o = sm.cand[j];
-#pragma unroll
-    for (int q = 0; q < MINE; ++q) rank[q] += (o > code[q]) ? 1 : 0;
+    for (int32_t j = 0; j < n; ++j) {
+      const unsigned long long o = sm.cand[j];
+      rank0 += (o > mine0) ? 1 : 0;
+      rank1 += (o > mine1) ? 1 : 0;
+    }
+    if (tid + K4_THREADS < n && rank1 < kk) sm.top[rank1] = mine1;
+  } else {
+#pragma unroll 4
+    for (int32_t j = 0; j < n; ++j) rank0 += (sm.cand[j] > mine0) ? 1 : 0;
   }
-#pragma unroll
-  for (int q = 0; q < MINE; ++q)
-    if (tid + q * K4_THREADS < n && rank[q] < kk) sm.top[rank[q]] = code[q];
+  if (tid < n && rank0 < kk) sm.top[rank0] = mine0;
 }
 
 // One pass over a row.  Candidate collection: a 16-byte vector is looked at element by element
@@ -401,17 +404,19 @@ __device__ void k4_segment(const T* src, const int64_t V, const int64_t base, co
   __syncthreads();
 }
 
-// One thread draws the token and scores it; all write the optional top-k outputs.
+// The first warp draws the token and scores it; all write the optional top-k outputs.
 __device__ void k4_finish_row(const K4Params& p, K4Smem& sm, int64_t row, int32_t kk, float c,
                               float temp, bool greedy, float lse) {
   const int tid = threadIdx.x;
   const int32_t k = p.top_k;
-  if (tid == 0) {
+  if (tid < 32) {  // the first warp draws (its lanes form the terms of the sum side by side)
     if (kk > 0) {
-      const int32_t pick = greedy ? 0 : k4_draw(sm.top, kk, c, row, p.seed, p.offset);
-      p.out_tokens[row] = k4_index(sm.top[pick]);
-      p.out_logprob[row] = __fdiv_rn(k4_value(sm.top[pick]), temp) - lse;
-    } else {  // a row of NaNs: nothing to draw from
+      const int32_t pick = greedy ? 0 : k4_draw_warp(sm.top, kk, c, row, p.seed, p.offset);
+      if (tid == 0) {
+        p.out_tokens[row] = k4_index(sm.top[pick]);
+        p.out_logprob[row] = __fdiv_rn(k4_value(sm.top[pick]), temp) - lse;
+      }
+    } else if (tid == 0) {  // a row of NaNs: nothing to draw from
       p.out_tokens[row] = -1;
       p.out_logprob[row] = __int_as_float(0x7fc00000);
       if (p.status != nullptr) atomicOr(p.status, TOME_DEV_NO_CANDIDATE);

@@ -56,26 +56,11 @@ __device__ __forceinline__ uint32_t k4_philox(uint64_t ctr_lo, uint64_t ctr_hi, 
 }
 
 // Index (0 = best) drawn from softmax(top / temperature) over the kk best codes of a row,
-// `top` sorted best first, c = log2(e) / temperature.  The draw depends only on
-// (seed, offset, row).
-__device__ __forceinline__ int32_t k4_draw(const unsigned long long* top, int32_t kk, float c,
-                                           int64_t row, uint64_t seed, uint64_t offset) {
-  if (kk <= 1) return 0;
-  const float best = k4_value(top[0]);
-  float total = 0.0f;
-  for (int32_t j = 0; j < kk; ++j) total += ex2f((k4_value(top[j]) - best) * c);
-  const uint32_t r = k4_philox(static_cast<uint64_t>(row), offset, seed);
-  const float u = (static_cast<float>(r >> 8) + 0.5f) * (1.0f / 16777216.0f) * total;
-  float acc = 0.0f;
-  for (int32_t j = 0; j < kk; ++j) {
-    acc += ex2f((k4_value(top[j]) - best) * c);
-    if (u < acc) return j;
-  }
-  return kk - 1;
-}
-
-// The same draw made by a whole warp (all 32 lanes call it, all get the index): the terms are
-// formed in parallel and summed in the same order as above, so the result is identical.
+// `top` sorted best first (at most 64), c = log2(e) / temperature.  The draw depends only on
+// (seed, offset, row): u = uniform(row, offset, seed) * sum_j e_j with e_j = 2^((top_j - top_0) c)
+// summed in the order j = 0, 1, ..., and the index is the first j whose partial sum exceeds u.
+// Made by a whole warp (all 32 lanes call it, all get the index): the terms are formed side by
+// side, the sums are taken one term at a time so that every caller gets the same bits.
 __device__ __forceinline__ int32_t k4_draw_warp(const unsigned long long* top, int32_t kk, float c,
                                                 int64_t row, uint64_t seed, uint64_t offset) {
   if (kk <= 1) return 0;
