@@ -40,14 +40,16 @@ constexpr int K4_SAMPLE = 32768;   // leading logits used to derive the first th
 constexpr int K4_GROUPS = K4_THREADS / 4;  // sample maxima kept for the threshold
 constexpr int K4_RANK_MAX = 1024;  // above this many candidates, compact before ranking
 constexpr int K4_MAX_SWEEPS = 64;   // re-sweeps with a tightened threshold before giving up
-// From these row counts on a batch takes the streaming path.  fp32: one row more than the
-// clusters of two CTAs per row can hold on 148 SMs; with the rows in two parts the streaming
-// path then wins clearly (V = 151936, one CTA per row / streaming path, CUDA-graph replay: 160
-// rows 47.0 / 32.8 us, 200 rows 52.6 / 34.9, 256 rows 54.7 / 39.1; 128 rows, cluster kernel, 26.1 /
-// 30.2).  bf16: one row more than a full wave of the row kernel's CTAs (two per SM); below that
-// the streaming path gains little on the GPU (160 rows 31.0 / 27.8 us, 200 rows 31.0 / 28.5, 256
-// rows 31.0 / 31.0, 320 rows 56.3 / 38.6) and costs a caller outside a CUDA graph three more
-// stream operations per call than the one kernel it replaces (256 rows, eager calls: 46 us).
+// From these row counts on a batch takes the streaming path.  bf16: one row more than a full
+// wave of the row kernel's CTAs (two per SM); below that the row kernel is as fast or faster
+// (V = 151936, row kernel / streaming path, CUDA-graph replay: 200 rows 27.7 / 30.8 us, 296 rows
+// 28.7 / 34.7; 320 rows 45.5 / 39.1) and is one launch instead of four stream operations.
+// fp32: one row more than the clusters of two CTAs per row can hold on 148 SMs.  Rows of that
+// length (608 KB) do not stay in L2 between the GEMM that writes them and this call, and from
+// DRAM the streaming path with the rows in two parts is ahead (160 / 200 / 256 rows, L2 flushed:
+// 43.1 / 45.9 / 49.8 us row kernel, 38.3 / 41.8 / 47.4 streaming); replayed from a graph over
+// logits that fit L2 it is the other way round by as much (29.1 / 34.7 / 37.5 against 34.3 /
+// 36.2 / 39.5).  From 297 rows on the streaming path wins either way (400 rows 63 against 51 us).
 constexpr int64_t K4_STREAM_MIN_ROWS_BF16 = 297;
 constexpr int64_t K4_STREAM_MIN_ROWS_F32 = 149;
 constexpr int64_t K4_STREAM_MIN_VOCAB = 4096;  // every consumer of the streaming kernel sees logits
