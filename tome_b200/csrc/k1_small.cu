@@ -32,9 +32,20 @@ __global__ void __launch_bounds__(K1_SPLIT_THREADS) k1_split_kernel(const K1Para
   const int64_t v_end = nvec * (rank + 1) / split;
   Fast fs;
   fast_init(fs, p.c);
-#pragma unroll 4
-  for (int64_t v = v_begin + threadIdx.x; v < v_end; v += K1_SPLIT_THREADS)
-    fast_update<0>(fs, __ldg(body + v), p.c, T());
+  // four loads asked for before the first is used (the update's branch on a new maximum keeps
+  // a `#pragma unroll`ed loop from hoisting them by itself)
+  int64_t v = v_begin + threadIdx.x;
+  for (; v + 3 * K1_SPLIT_THREADS < v_end; v += 4 * K1_SPLIT_THREADS) {
+    const uint4 q0 = __ldg(body + v);
+    const uint4 q1 = __ldg(body + v + K1_SPLIT_THREADS);
+    const uint4 q2 = __ldg(body + v + 2 * K1_SPLIT_THREADS);
+    const uint4 q3 = __ldg(body + v + 3 * K1_SPLIT_THREADS);
+    fast_update<0>(fs, q0, p.c, T());
+    fast_update<0>(fs, q1, p.c, T());
+    fast_update<0>(fs, q2, p.c, T());
+    fast_update<0>(fs, q3, p.c, T());
+  }
+  for (; v < v_end; v += K1_SPLIT_THREADS) fast_update<0>(fs, __ldg(body + v), p.c, T());
   Online st = fast_finish(fs, p.c);
   if (rank == 0) {  // the unaligned ends of the row
     for (int64_t j = threadIdx.x; j < head; j += K1_SPLIT_THREADS)
