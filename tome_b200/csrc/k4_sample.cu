@@ -492,12 +492,26 @@ __global__ void __launch_bounds__(K4_THREADS, 2) k4_sample_split_kernel(const K4
   }
   cluster_sync_all();  // release/acquire: the first CTA sees what the others stored
   if (rank != 0) return;
-  // gather the survivors of every part into the candidate list (at most split * k codes)
-  if (tid == 0) sm.count = 0;
-  __syncthreads();
-  if (tid < kk) sm.cand[atomicAdd(&sm.count, 1)] = sm.top[tid];
-  for (int r = 1; r < split; ++r)
-    if (tid < sm.inbox_n[r]) sm.cand[atomicAdd(&sm.count, 1)] = sm.inbox[r * K4_MAX_K + tid];
+  // gather the survivors of every part into the candidate list (at most split * k codes), part
+  // after part: thread r * K4_MAX_K + j moves survivor j of part r (K4_SPLIT_MAX * K4_MAX_K =
+  // K4_THREADS).  (Taking the places with an atomic counter cost the first CTA 2 - 3 us per row:
+  // up to 160 shared-memory atomics in a row.)
+  static_assert(K4_SPLIT_MAX * K4_MAX_K <= K4_THREADS, "one thread per survivor of any part");
+  {
+    const int r = tid / K4_MAX_K, j = tid % K4_MAX_K;
+    int32_t before = 0, total = kk;
+    for (int q = 1; q < split; ++q) {
+      const int32_t n_q = sm.inbox_n[q];
+      if (q <= r) before = total;
+      total += n_q;
+    }
+    if (r == 0) {
+      if (j < kk) sm.cand[j] = sm.top[j];
+    } else if (r < split && j < sm.inbox_n[r]) {
+      sm.cand[before + j] = sm.inbox[r * K4_MAX_K + j];
+    }
+    if (tid == 0) sm.count = total;
+  }
   // a part without a finite logit (maximum -inf, sum NaN) adds nothing to the row's sum
   const float ninf = __int_as_float(0xff800000);
   float row_m = part_m;
