@@ -120,3 +120,51 @@ def test_dual_and_ragged_random_shapes(cuda_device, seed):
     for i in range(n_seq):
         if clamped[i]:
             assert max_abs(packed[off[i]:off[i + 1]], want[i]) <= tol
+
+
+@pytest.mark.parametrize("seed", range(60))
+def test_fused_lm_head_random_shapes(cuda_device, seed):
+    """The fused LM head + log-prob on random row counts, hidden sizes (multiples of 8) and
+    vocabulary sizes, alone and with the final RMSNorm and the bf16-rounded logits, sharded or
+    not, against the oracle (2e-3, the fused head's tolerance)."""
+    import tome_b200
+    from tome_b200 import synthetic
+    rng = random.Random(5000 + seed)
+    rows = rng.choice([1, rng.randint(2, 127), 128, rng.randint(129, 700)])
+    k = 8 * rng.choice([1, rng.randint(2, 16), rng.randint(17, 96)])
+    vocab = rng.choice([rng.randint(1, 255), 256, rng.randint(257, 6000)])
+    temp = rng.choice([1.0, 0.7, 1.5])
+    hidden, weight, ids = synthetic.cfg3_lm_head(rows, k, vocab, "cpu", 6000 + seed, 0.05)
+    dev = cuda_device
+    form = rng.choice(["plain", "norm", "rounded", "sharded"])
+    if form == "plain":
+        lp, lse = tome_b200.lm_head_logprob(hidden.to(dev), weight.to(dev), ids.to(dev), temp, check=True)
+        o_lp, o_lse = oracle.lm_head_logprob(hidden, weight, ids, temp)
+    elif form == "norm":
+        g = torch.Generator().manual_seed(seed)
+        nw = (1.0 + 0.1 * torch.randn(k, generator=g)).to(torch.bfloat16)
+        lp, lse = tome_b200.lm_head_logprob(hidden.to(dev), weight.to(dev), ids.to(dev), temp,
+                                            norm_weight=nw.to(dev), eps=1e-6, check=True)
+        o_lp, o_lse = oracle.lm_head_logprob(oracle.rms_norm(hidden, nw, 1e-6), weight, ids, temp)
+    elif form == "rounded":
+        lp, lse = tome_b200.lm_head_logprob(hidden.to(dev), weight.to(dev), ids.to(dev), temp,
+                                            round_logits=True, check=True)
+        o_lp, o_lse = oracle.lm_head_logprob(hidden, weight, ids, temp, round_to_bf16=True)
+    else:  # vocabulary shards of one process, combined as the ranks of a vocab-parallel head do
+        world = rng.choice([2, 3, 5])
+        hd, wd, idd = hidden.to(dev), weight.to(dev), ids.to(dev)
+        ms, ss, ts = [], [], []
+        for r in range(world):
+            b, e = synthetic.shard_bounds(vocab, r, world)
+            if e <= b:
+                continue
+            m, s_, t = tome_b200.lm_head_partials(hd, wd[b:e].contiguous(), b, idd, temp)
+            ms.append(m), ss.append(s_), ts.append(t)
+        lp, lse = tome_b200.combine_triples(torch.stack(ms), torch.stack(ss), torch.stack(ts))
+        o_lp, o_lse = oracle.lm_head_logprob(hidden, weight, ids, temp)
+    # rounded logits: one that sits on a bf16 rounding boundary may round the other way on the
+    # GPU (different fp32 summation order), one bf16 ulp of the target logit; the norm may differ
+    # from the oracle's by an ulp of the hidden state
+    tol = {"plain": 2e-3, "sharded": 2e-3, "norm": 5e-3, "rounded": 2e-3 + 2 ** -6}[form]
+    assert max_abs(lse, o_lse) <= tol, (form, rows, k, vocab, max_abs(lse, o_lse))
+    assert max_abs(lp, o_lp) <= tol, (form, rows, k, vocab, max_abs(lp, o_lp))
