@@ -168,3 +168,43 @@ def test_fused_lm_head_random_shapes(cuda_device, seed):
     tol = {"plain": 2e-3, "sharded": 2e-3, "norm": 5e-3, "rounded": 2e-3 + 2 ** -6}[form]
     assert max_abs(lse, o_lse) <= tol, (form, rows, k, vocab, max_abs(lse, o_lse))
     assert max_abs(lp, o_lp) <= tol, (form, rows, k, vocab, max_abs(lp, o_lp))
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_paged_kv_random_shapes(cuda_device, seed):
+    """Paged KV gather and update (mlx-impl/paged_kv.py) on random pool sizes, head counts,
+    block sizes, head dimensions, tables, offsets and lengths; byte-exact against the oracle's
+    loops."""
+    import tome_b200
+    rng = random.Random(7000 + seed)
+    dtype = rng.choice([torch.bfloat16, torch.float32])
+    H = rng.randint(1, 4)
+    bs = rng.choice([1, 4, 16, 32])
+    D = rng.choice([8, 64, 128]) if dtype == torch.bfloat16 else rng.choice([4, 64, 128])
+    B = rng.randint(1, 6)
+    per_seq = rng.randint(1, 6)
+    num_blocks = B * per_seq + rng.randint(0, 5)
+    g = torch.Generator().manual_seed(seed)
+    k_pool = torch.randn((num_blocks, H, bs, D), generator=g).to(dtype)
+    v_pool = torch.randn((num_blocks, H, bs, D), generator=g).to(dtype)
+    tables = torch.randperm(num_blocks, generator=g)[: B * per_seq].reshape(B, per_seq).to(torch.int32)
+    cap = per_seq * bs
+    dev = cuda_device
+    # gather
+    offsets = torch.tensor([rng.randint(0, cap) for _ in range(B)], dtype=torch.int32)
+    max_len = rng.randint(1, cap + 3)
+    k_out, v_out = tome_b200.gather_paged_kv(tables.to(dev), offsets.to(dev), k_pool.to(dev),
+                                             v_pool.to(dev), max_len)
+    o_k, o_v = oracle.gather_paged_kv(tables, offsets, k_pool, v_pool, max_len)
+    assert torch.equal(k_out.cpu(), o_k) and torch.equal(v_out.cpu(), o_v), (H, bs, D, B, per_seq, max_len)
+    # update (disjoint blocks per sequence, writes may run off the table's end)
+    s_new = rng.randint(1, cap + 2)
+    k_new = torch.randn((B, H, s_new, D), generator=g).to(dtype)
+    v_new = torch.randn((B, H, s_new, D), generator=g).to(dtype)
+    start = torch.tensor([rng.randint(0, cap) for _ in range(B)], dtype=torch.int32)
+    lengths = torch.tensor([rng.randint(0, s_new) for _ in range(B)], dtype=torch.int32)
+    kp, vp = k_pool.to(dev), v_pool.to(dev)
+    tome_b200.update_paged_kv(k_new.to(dev), v_new.to(dev), tables.to(dev), start.to(dev), kp, vp,
+                              lengths=lengths.to(dev))
+    o_k, o_v = oracle.update_paged_kv(k_new, v_new, tables, start, k_pool, v_pool, bs, lengths)
+    assert torch.equal(kp.cpu(), o_k) and torch.equal(vp.cpu(), o_v), (H, bs, D, B, per_seq, s_new)
