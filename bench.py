@@ -584,6 +584,40 @@ def run_extra(args, device, rank, world, dist_on, barrier, peaks):
         del xs, tok, lp, tk_i, tk_v, s_out, s_ws
     torch.cuda.empty_cache()
 
+    # a vocabulary off the 16-byte grid (50257 bf16 logits per row, contiguous: every row starts
+    # at another place of the grid): the same kernels, each row copied from its first 16-byte
+    # boundary to its last
+    rows_o, vocab_o = 8192, 50257
+    xo = (torch.randn((rows_o, vocab_o), device=device, dtype=torch.float32) * 3.0).to(torch.bfloat16)
+    ido = torch.randint(0, vocab_o, (rows_o,), device=device, dtype=torch.int32)
+    lp_o = torch.empty(rows_o, dtype=torch.float32, device=device)
+    full_o = torch.empty_like(xo)
+    tok_o = (torch.empty(rows_o, dtype=torch.int32, device=device),
+             torch.empty(rows_o, dtype=torch.float32, device=device))
+    ws_o = torch.empty(max(16, tome_b200.sample_workspace_bytes(rows_o, vocab_o)),
+                       dtype=torch.uint8, device=device)
+    nb_o = rows_o * vocab_o * 2
+    _, t_sel = timed(lambda: tome_b200.local_compute_logprobs(xo, ido, 1.0, out=lp_o))
+    _, t_full = timed(lambda: tome_b200.fused_log_softmax(xo, 1.0, out=full_o))
+    _, t_smp = timed(lambda: tome_b200.sample_topk_logprob(xo, 0.7, 20, seed=7, offset=1, out=tok_o,
+                                                           workspace=ws_o))
+    extra["odd_vocab_50257_bf16"] = {
+        "rows": rows_o, "vocab": vocab_o, "selective_ms": t_sel, "selective_GBps": nb_o / t_sel / 1e6,
+        "full_ms": t_full, "full_GBps": 2 * nb_o / t_full / 1e6,
+        "sample_ms": t_smp, "sample_GBps": nb_o / t_smp / 1e6,
+        "l2": "inputs (823 MB) are larger than L2"}
+    sel = torch.arange(0, rows_o, rows_o // 32, device=device)
+    want_full = xo[sel] - torch.logsumexp(xo[sel].float(), dim=-1, keepdim=True).to(torch.bfloat16)
+    verdict("odd_vocab_50257_bf16",
+            {"max_abs_logprob": (lp_o[sel] - torch_logprob(xo[sel], ido[sel], 1.0)).abs().max(),
+             "max_abs_sampled_logprob": (tok_o[1][sel] - torch_logprob(xo[sel], tok_o[0][sel], 0.7)).abs().max()})
+    full_err = float((full_o[sel].float() - want_full.float()).abs().max())
+    extra["odd_vocab_50257_bf16"]["check"]["max_abs_full_bf16_ulp_0.0625"] = full_err
+    if not full_err <= 0.0625 + 1e-3:
+        failures.append(f"odd_vocab_50257_bf16 full: {full_err:.3g}")
+    del xo, ido, lp_o, full_o, tok_o, ws_o, want_full
+    torch.cuda.empty_cache()
+
     # paged KV gather / update: 64 sequences x 2048 tokens, 8 KV heads x 128, blocks of 16
     n_blk, Hkv, bs_kv, Dh, Bkv, Lkv = 64 * 128, 8, 16, 128, 64, 2048
     k_pool = torch.randn((n_blk, Hkv, bs_kv, Dh), device=device, dtype=torch.bfloat16)
