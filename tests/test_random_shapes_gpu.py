@@ -1,6 +1,7 @@
 """Seeded random shapes: row counts, vocabulary sizes (odd ones included), element offsets of the
 first row and row pitches drawn at random, every mode against the oracle.  The fixed cases of
 the other files pin the known edges; this one looks for the ones nobody thought of."""
+import os
 import random
 
 import pytest
@@ -10,6 +11,9 @@ from helpers import TOL, max_abs
 from oracle import oracle
 
 pytestmark = pytest.mark.gpu
+
+# TOME_TEST_SEED_OFFSET=n shifts every seed of this file: the same tests over other shapes
+SEED_OFFSET = int(os.environ.get("TOME_TEST_SEED_OFFSET", "0")) * 100000
 
 
 def _draw(rng, max_rows, max_vocab):
@@ -31,7 +35,7 @@ def _view(rows, vocab, offset, pitch, dtype, seed, dev):
 @pytest.mark.parametrize("seed", range(120))
 def test_selective_random_shapes(cuda_device, seed):
     import tome_b200
-    rng = random.Random(1000 + seed)
+    rng = random.Random(1000 + seed + SEED_OFFSET)
     rows, vocab, offset, pitch, dtype, temp = _draw(rng, 900, 70000)
     x, xd = _view(rows, vocab, offset, pitch, dtype, seed, cuda_device)
     ids = torch.randint(0, vocab, (rows,), generator=torch.Generator().manual_seed(seed), dtype=torch.int32)
@@ -46,7 +50,7 @@ def test_selective_random_shapes(cuda_device, seed):
 @pytest.mark.parametrize("seed", range(80))
 def test_full_matrix_random_shapes(cuda_device, seed):
     import tome_b200
-    rng = random.Random(2000 + seed)
+    rng = random.Random(2000 + seed + SEED_OFFSET)
     rows, vocab, offset, pitch, dtype, temp = _draw(rng, 500, 60000)
     x, xd = _view(rows, vocab, offset, pitch, dtype, seed, cuda_device)
     out = tome_b200.fused_log_softmax(xd, temp)
@@ -63,7 +67,7 @@ def test_full_matrix_random_shapes(cuda_device, seed):
 @pytest.mark.parametrize("seed", range(100))
 def test_sampling_random_shapes(cuda_device, monkeypatch, seed):
     import tome_b200
-    rng = random.Random(3000 + seed)
+    rng = random.Random(3000 + seed + SEED_OFFSET)
     rows, vocab, offset, pitch, dtype, temp = _draw(rng, 700, 60000)
     k = rng.choice([1, 5, 20, 33, 64])
     form = rng.choice(["default", "rows", "stream", "stream_warp", "stream_parts"])
@@ -92,7 +96,7 @@ def test_dual_and_ragged_random_shapes(cuda_device, seed):
     """Policy / reference scoring with the k3 KL estimate over ragged windows, and the packed
     single-model form, on random sequence counts, lengths, windows and vocabulary sizes."""
     import tome_b200
-    rng = random.Random(4000 + seed)
+    rng = random.Random(4000 + seed + SEED_OFFSET)
     n_seq = rng.choice([1, 2, rng.randint(3, 12)])
     seq_len = rng.choice([1, 2, rng.randint(3, 24)])
     vocab = rng.choice([rng.randint(1, 40), rng.randint(41, 5000), rng.randint(5001, 30000)])
@@ -129,7 +133,7 @@ def test_fused_lm_head_random_shapes(cuda_device, seed):
     not, against the oracle (2e-3, the fused head's tolerance)."""
     import tome_b200
     from tome_b200 import synthetic
-    rng = random.Random(5000 + seed)
+    rng = random.Random(5000 + seed + SEED_OFFSET)
     rows = rng.choice([1, rng.randint(2, 127), 128, rng.randint(129, 700)])
     k = 8 * rng.choice([1, rng.randint(2, 16), rng.randint(17, 96)])
     vocab = rng.choice([rng.randint(1, 255), 256, rng.randint(257, 6000)])
@@ -176,7 +180,7 @@ def test_paged_kv_random_shapes(cuda_device, seed):
     block sizes, head dimensions, tables, offsets and lengths; byte-exact against the oracle's
     loops."""
     import tome_b200
-    rng = random.Random(7000 + seed)
+    rng = random.Random(7000 + seed + SEED_OFFSET)
     dtype = rng.choice([torch.bfloat16, torch.float32])
     H = rng.randint(1, 4)
     bs = rng.choice([1, 4, 16, 32])
