@@ -388,3 +388,28 @@ def test_rows_with_too_few_numbers(cuda_device, monkeypatch, stream, dtype):
     with pytest.raises(tome_b200.TomeRuntimeError):
         tome_b200.check_device_status(cuda_device)
     tome_b200.check_device_status(cuda_device)  # the word was cleared
+
+
+@pytest.mark.parametrize("rows", [64, 400])
+def test_sampling_on_concurrent_streams(cuda_device, rows):
+    """Four streams sample different batches at once, each with outputs and scratch of its own
+    (the kernels of a call are chained by programmatic launches within their stream); every
+    stream gets what it gets alone."""
+    import tome_b200
+    xs = [_case(rows, 32768 + 8 * i, torch.bfloat16, 900 + i).to(cuda_device) for i in range(4)]
+    alone = [tome_b200.sample_topk_logprob(x, 0.7, 20, seed=5, offset=i) for i, x in enumerate(xs)]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(device=cuda_device) for _ in xs]
+    outs = [(torch.empty(rows, dtype=torch.int32, device=cuda_device),
+             torch.empty(rows, dtype=torch.float32, device=cuda_device)) for _ in xs]
+    scratch = [torch.empty(max(16, tome_b200.sample_workspace_bytes(rows, x.shape[1])), dtype=torch.uint8,
+                           device=cuda_device) for x in xs]
+    for _ in range(5):
+        for i, (x, st) in enumerate(zip(xs, streams)):
+            with torch.cuda.stream(st):
+                tome_b200.sample_topk_logprob(x, 0.7, 20, seed=5, offset=i, out=outs[i],
+                                              workspace=scratch[i])
+    torch.cuda.synchronize()
+    for (tok, lp), (tok1, lp1) in zip(outs, alone):
+        assert torch.equal(tok, tok1) and torch.equal(lp, lp1)
+    tome_b200.check_device_status(cuda_device)
