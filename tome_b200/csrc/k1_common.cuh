@@ -92,7 +92,7 @@ struct K1Params {
   int32_t* out_tokens;     // SAMPLE: [rows]
   int32_t* out_topk_idx;   // SAMPLE: nullable, [rows, top_k]
   float* out_topk_val;     // SAMPLE: nullable, [rows, top_k]
-  int32_t* marked;         // SAMPLE: number of rows left to the row kernel (zero before the launch)
+  int32_t* marked;         // SAMPLE: number of rows left to the row kernel (see K1SampleArgs)
   int32_t* marked_rows;    // SAMPLE: their indices
   int32_t* status;         // nullable
   int32_t chunk_bytes;     // bulk-copy size (multiple of 16, <= K1_CHUNK_BYTES), set by launch

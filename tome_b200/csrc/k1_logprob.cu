@@ -414,6 +414,9 @@ __global__ void __launch_bounds__(K1_THREADS, K1_CTAS_PER_SM) k1_stream_kernel(c
     fence_mbar_init();
     if (MODE == K1_SAMPLE)
       reinterpret_cast<K1SampleSmem*>(smem + Smem::SAMPLE_OFF)->lists_done = 0;
+    // SAMPLE without the finisher: this kernel never touches the count of rows left to the row
+    // kernel (the kernels after it do, once it has completed), so it can clear it for them
+    if (MODE == K1_SAMPLE && !FINISH && blockIdx.x == 0 && p.marked != nullptr) *p.marked = 0;
   }
   // SPLIT: every CTA does `whole_rounds` rows of its own, then a quarter of each row of its
   // cluster's share of the remainder

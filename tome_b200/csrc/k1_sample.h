@@ -38,7 +38,8 @@ struct K1SampleArgs {
   float2* part_ms;          // [rows, parts] (parts > 1)
   int32_t* cand_count;      // [rows, parts, lists]
   uint2* cand_entry;        // [rows, parts, lists, list capacity]
-  int32_t* marked;          // one word, ZERO before the launch: rows left to the row kernel
+  int32_t* marked;          // one word: rows left to the row kernel (with finish_in_kernel it
+                            // must be ZERO before the launch; without, the kernel clears it)
   int32_t* marked_rows;     // [rows]: their indices
 };
 

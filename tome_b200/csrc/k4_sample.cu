@@ -52,6 +52,7 @@ constexpr int K4_MAX_SWEEPS = 64;   // re-sweeps with a tightened threshold befo
 // 36.2 / 39.5).  From 297 rows on the streaming path wins either way (400 rows 63 against 51 us).
 constexpr int64_t K4_STREAM_MIN_ROWS_BF16 = 297;
 constexpr int64_t K4_STREAM_MIN_ROWS_F32 = 149;
+constexpr int64_t K4_FINISH_IN_KERNEL_MIN_ROWS = 4096;  // fp32: rows finished inside the streaming kernel
 constexpr int64_t K4_STREAM_MIN_VOCAB = 4096;  // every consumer of the streaming kernel sees logits
 constexpr int K4_MAX_PARTS = 4;                // parts a row of a small streamed batch is cut into
 constexpr int K4_MAX_LISTS = 16;              // lists per row (one per consumer warp and part, streaming kernel)
@@ -543,12 +544,17 @@ __global__ void __launch_bounds__(K4_THREADS, 2) k4_sample_split_kernel(const K4
 // on a list and redone by k4_sample_kernel (only_flagged).  Same tokens as the other kernels of
 // this file.
 //
-// The last step, from the noted places to token and log-prob, exists twice.  For fp32 logits
-// the streaming kernel's producer warp does it between two copies (nothing is added to the
-// call's time: 8192 x 151936 fp32 775 -> 727 us, the selective mode's own speed).  For bf16
-// logits that kernel is bound by its instruction count and the same work costs more there than
-// in a kernel of its own (4096 rows: 256 us against 238 us), so bf16 batches run
-// k4_finish_kernel afterwards.  TOME_K4_FINISH=kernel|warp forces one or the other (tests).
+// The last step, from the noted places to token and log-prob, exists twice: k4_finish_kernel
+// after the streaming kernel, or the streaming kernel's own producer warp between two copies.
+// For bf16 logits the streaming kernel is bound by its instruction count and the work costs
+// more there than in a kernel of its own (4096 rows: 256 us against 238 us).  For fp32 logits
+// the producer warp's version adds nothing to the streaming kernel's time (8192 x 151936: 775 ->
+// 727 us when the finish kernel still read every noted entry); since the lists are compacted
+// and the streaming kernel clears the counter of left-over rows itself (no memset node), the
+// finish kernel is as cheap up to a few thousand rows or cheaper (297 / 800 / 2048 rows: 42.6 /
+// 91.3 / 195.5 us against 46.3 / 96.5 / 200.7, CUDA-graph replay; 4096 rows 379 / 378), so the
+// producer warp finishes fp32 batches from 4096 rows on only.  TOME_K4_FINISH=kernel|warp
+// forces one or the other (tests).
 //
 // Batches with fewer rows than the streaming kernel has CTAs (4 per SM) would leave it one slow
 // CTA per row, so their rows are cut into 2 or 4 parts, each a work item of that kernel with a
@@ -928,11 +934,16 @@ static int32_t k4_sample_impl(const void* logits, int32_t dtype, int64_t rows, i
     const K4Workspace w = k4_workspace(workspace, rows, lists, parts);
     p.marked = w.marked;
     p.marked_rows = w.marked_rows;
-    st = check_cuda(cudaMemsetAsync(w.marked, 0, sizeof(int32_t), s), "cudaMemsetAsync(marked rows)");
-    if (st != TOME_OK) return st;
-    bool in_kernel = (dtype == TOME_F32);
+    bool in_kernel = (dtype == TOME_F32) && rows >= K4_FINISH_IN_KERNEL_MIN_ROWS;
     if (const char* e = getenv("TOME_K4_FINISH")) in_kernel = (e[0] == 'w');  // "warp" / "kernel"
     if (parts > 1) in_kernel = false;  // a row's parts meet in k4_finish_kernel
+    // the count of rows left to the row kernel starts at zero: with the finisher inside the
+    // streaming kernel (whose CTAs add to it at any time) by a memset before the launch,
+    // otherwise the streaming kernel clears it itself (one stream operation fewer per call)
+    if (in_kernel) {
+      st = check_cuda(cudaMemsetAsync(w.marked, 0, sizeof(int32_t), s), "cudaMemsetAsync(marked rows)");
+      if (st != TOME_OK) return st;
+    }
     K1SampleArgs a;
     a.finish_in_kernel = in_kernel;
     a.parts = parts;
